@@ -1,0 +1,134 @@
+"""Seeded synthetic tensors in the GGUF block formats of the decode path.
+
+No model file or dataset is involved anywhere in this repository: every weight
+matrix used by the tests and by the benchmark is drawn here from
+``numpy.random.default_rng(seed)`` with the value distributions the benchmark
+configurations state (block scale ``|N(0,1)|*0.01`` as f16, uniform quants,
+``x ~ N(0,1)``).  Block layouts follow ALICE-LLM ``src/gguf.rs`` (Q4_K :903-939,
+Q5_K :949-988, Q6_K :1205-1246, Q8_0 :990-1004, Q1_0/Q2_0 :1248-1300, ternary
+bit planes :5190-5195, sparse-ternary masks :5425-5445).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+QK_K = 256
+
+# GGML type ids (src/gguf.rs:101-122)
+Q8_0, Q4_K, Q5_K, Q6_K, Q1_0, Q2_0 = 8, 12, 13, 14, 41, 42
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q1_0: 18, Q2_0: 34}
+BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, Q1_0: 128, Q2_0: 128}
+TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", Q1_0: "Q1_0", Q2_0: "Q2_0"}
+
+
+def row_bytes(qtype: int, cols: int) -> int:
+    return cols // BLOCK_ELEMS[qtype] * BLOCK_BYTES[qtype]
+
+
+def _f16_scale(rng, shape, sigma):
+    """|N(0,1)|*sigma rounded to f16, returned as little-endian byte pairs."""
+    v = (np.abs(rng.standard_normal(shape, dtype=np.float32)) * np.float32(sigma)).astype(np.float16)
+    return v.view(np.uint8).reshape(*shape, 2)
+
+
+def pack_scales_k4(sc, mn):
+    """Inverse of get_scale_min_k4 (src/gguf.rs:794-802): eight 6-bit scales and
+    eight 6-bit mins -> the 12-byte header. ``sc``/``mn`` have shape (..., 8)."""
+    sc = np.asarray(sc, dtype=np.uint8)
+    mn = np.asarray(mn, dtype=np.uint8)
+    out = np.zeros(sc.shape[:-1] + (12,), dtype=np.uint8)
+    out[..., 0:4] = (sc[..., 0:4] & 63) | ((sc[..., 4:8] >> 4) << 6)
+    out[..., 4:8] = (mn[..., 0:4] & 63) | ((mn[..., 4:8] >> 4) << 6)
+    out[..., 8:12] = (sc[..., 4:8] & 0xF) | ((mn[..., 4:8] & 0xF) << 4)
+    return out
+
+
+def make_q4k(rng, rows: int, cols: int) -> np.ndarray:
+    """Q4_K matrix, [rows * cols/256 * 144] bytes: f16 d ~ |N|*0.01, f16 dmin ~ |N|*0.005,
+    6-bit scales/mins uniform 0..63, nibbles uniform 0..15."""
+    nb = cols // QK_K
+    blk = rng.integers(0, 256, size=(rows, nb, 144), dtype=np.uint8)  # uniform bytes = uniform fields
+    blk[:, :, 0:2] = _f16_scale(rng, (rows, nb), 0.01)
+    blk[:, :, 2:4] = _f16_scale(rng, (rows, nb), 0.005)
+    return blk.reshape(-1)
+
+
+def make_q5k(rng, rows: int, cols: int) -> np.ndarray:
+    nb = cols // QK_K
+    blk = rng.integers(0, 256, size=(rows, nb, 176), dtype=np.uint8)
+    blk[:, :, 0:2] = _f16_scale(rng, (rows, nb), 0.01)
+    blk[:, :, 2:4] = _f16_scale(rng, (rows, nb), 0.005)
+    return blk.reshape(-1)
+
+
+def make_q6k(rng, rows: int, cols: int) -> np.ndarray:
+    """Q6_K: ql/qh uniform bytes, 16 int8 scales uniform -32..31, f16 d ~ |N|*0.01."""
+    nb = cols // QK_K
+    blk = rng.integers(0, 256, size=(rows, nb, 210), dtype=np.uint8)
+    blk[:, :, 192:208] = rng.integers(-32, 32, size=(rows, nb, 16), dtype=np.int8).view(np.uint8)
+    blk[:, :, 208:210] = _f16_scale(rng, (rows, nb), 0.01)
+    return blk.reshape(-1)
+
+
+def make_q8_0(rng, rows: int, cols: int) -> np.ndarray:
+    """Q8_0: f16 d ~ |N|*0.01, int8 uniform -127..127."""
+    nb = cols // 32
+    blk = np.empty((rows, nb, 34), dtype=np.uint8)
+    blk[:, :, 0:2] = _f16_scale(rng, (rows, nb), 0.01)
+    blk[:, :, 2:] = rng.integers(-127, 128, size=(rows, nb, 32), dtype=np.int8).view(np.uint8)
+    return blk.reshape(-1)
+
+
+def make_q1_0(rng, rows: int, cols: int) -> np.ndarray:
+    """Q1_0: f16 d ~ |N|*0.02, 16 bytes of uniform sign bits per 128 weights."""
+    nb = cols // 128
+    blk = rng.integers(0, 256, size=(rows, nb, 18), dtype=np.uint8)
+    blk[:, :, 0:2] = _f16_scale(rng, (rows, nb), 0.02)
+    return blk.reshape(-1)
+
+
+def make_q2_0(rng, rows: int, cols: int) -> np.ndarray:
+    """Q2_0: f16 d ~ |N|*0.02, 2-bit slots uniform over the three codes the encoder emits."""
+    nb = cols // 128
+    slots = rng.integers(0, 3, size=(rows, nb, 32, 4), dtype=np.uint8)
+    by = slots[..., 0] | (slots[..., 1] << 2) | (slots[..., 2] << 4) | (slots[..., 3] << 6)
+    blk = np.empty((rows, nb, 34), dtype=np.uint8)
+    blk[:, :, 0:2] = _f16_scale(rng, (rows, nb), 0.02)
+    blk[:, :, 2:] = by
+    return blk.reshape(-1)
+
+
+MAKERS = {Q4_K: make_q4k, Q5_K: make_q5k, Q6_K: make_q6k, Q8_0: make_q8_0, Q1_0: make_q1_0, Q2_0: make_q2_0}
+
+
+def make_weights(qtype: int, rng, rows: int, cols: int) -> np.ndarray:
+    return MAKERS[qtype](rng, rows, cols)
+
+
+def make_ternary(rng, rows: int, cols: int):
+    """Ternary bit planes: P(0)=0.5, P(+1)=P(-1)=0.25, per-row f32 scale ~ |N|*0.01.
+    Returns (pos[rows, ceil(cols/8)], neg[...], scales[rows]); bit i%8 of byte i/8, LSB first."""
+    code = rng.integers(0, 4, size=(rows, cols), dtype=np.uint8)  # 0,1 -> 0 ; 2 -> +1 ; 3 -> -1
+    pos = np.packbits(code == 2, axis=1, bitorder="little")
+    neg = np.packbits(code == 3, axis=1, bitorder="little")
+    scales = (np.abs(rng.standard_normal(rows, dtype=np.float32)) * np.float32(0.01)).astype(np.float32)
+    return np.ascontiguousarray(pos), np.ascontiguousarray(neg), scales
+
+
+def ternary_to_sparse(pos: np.ndarray, neg: np.ndarray, cols: int):
+    """Re-express bit planes as SparseTernaryMatrix masks (active u16, sign u16 per 16 columns;
+    sign bit 1 = negative) without dropping any weight."""
+    rows = pos.shape[0]
+    bpr = (cols + 15) // 16
+    padded = np.zeros((rows, bpr * 2), dtype=np.uint8)
+    padded[:, : pos.shape[1]] = pos | neg
+    active = padded.view("<u2").copy()
+    padded[:] = 0
+    padded[:, : neg.shape[1]] = neg
+    sign = padded.view("<u2").copy()
+    return active, sign
+
+
+def make_x(rng, n: int, batch: int = 1) -> np.ndarray:
+    """Activations ~ N(0,1), f32, layout x[k*n + c]."""
+    return rng.standard_normal(batch * n, dtype=np.float32)
