@@ -1,0 +1,558 @@
+// extern "C" surface of the library (include/alice_cuda.h): handles, uploads, dispatch.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/alice_cuda.h"
+#include "gemv_launch.cuh"
+#include "q8k.cuh"
+
+using namespace alice;
+
+struct alice_engine {
+    int device = 0;
+    int num_sms = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    bool pdl = true;
+    int force_rps = 0, force_stages = 0;
+    int* status = nullptr;        // device status word
+    void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
+    size_t scratch_bytes = 0;
+};
+
+struct alice_weights {
+    alice_engine* e;
+    WeightDesc d;
+    void* owned_data = nullptr;
+    void* owned_scales = nullptr;
+};
+
+struct alice_buf {
+    alice_engine* e;
+    float* p;
+    size_t len;
+    bool owned;
+};
+
+struct alice_q8k {
+    alice_engine* e;
+    void* base;
+    uint32_t cols, batch, nb;
+    Q8KLayout lay;
+};
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t err, const char* what) {
+    return fail(err == cudaErrorMemoryAllocation ? ALICE_E_NOMEM : ALICE_E_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+#define CU(call)                                               \
+    do {                                                       \
+        cudaError_t err__ = (call);                            \
+        if (err__ != cudaSuccess) return cuda_fail(err__, #call); \
+    } while (0)
+
+bool known_ggml(uint32_t t) { return ggml_block_bytes((WeightFormat)t) != 0; }
+
+LaunchCfg cfg_of(const alice_engine* e) {
+    LaunchCfg c;
+    c.stream = e->stream; c.num_sms = e->num_sms; c.status = e->status; c.pdl = e->pdl;
+    c.force_rps = e->force_rps; c.force_stages = e->force_stages;
+    return c;
+}
+
+Q8KView view_of(const alice_q8k* q, uint32_t k) {
+    auto* p = static_cast<uint8_t*>(q->base);
+    Q8KView v;
+    v.qs = reinterpret_cast<const int8_t*>(p + q->lay.qs_off) + (size_t)k * q->nb * 256;
+    v.d = reinterpret_cast<const float*>(p + q->lay.d_off) + (size_t)k * q->nb;
+    v.bsums = reinterpret_cast<const int16_t*>(p + q->lay.bsums_off) + (size_t)k * q->nb * 16;
+    v.nb = q->nb;
+    return v;
+}
+
+// Engine scratch grows on demand and is reused by later calls on the same stream.
+int ensure_scratch(alice_engine* e, size_t bytes) {
+    if (bytes <= e->scratch_bytes) return ALICE_OK;
+    CU(cudaStreamSynchronize(e->stream));
+    if (e->scratch) CU(cudaFree(e->scratch));
+    e->scratch = nullptr; e->scratch_bytes = 0;
+    CU(cudaMalloc(&e->scratch, bytes));
+    e->scratch_bytes = bytes;
+    return ALICE_OK;
+}
+
+int launch_rc(int rc, const char* what) {
+    if (rc == ALICE_OK) return rc;
+    if (rc == ALICE_E_CUDA) return fail(rc, "%s: launch failed: %s", what, cudaGetErrorString(cudaGetLastError()));
+    if (rc == ALICE_E_SHAPE) return fail(rc, "%s: shape not supported by the streaming kernel", what);
+    return fail(rc, "%s: error %d", what, rc);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* alice_last_error(void) { return g_err.c_str(); }
+
+uint32_t alice_type_block_bytes(uint32_t t) { return ggml_block_bytes((WeightFormat)t); }
+uint32_t alice_type_block_elems(uint32_t t) { return ggml_block_elems((WeightFormat)t); }
+
+int32_t alice_engine_create(int32_t device, alice_engine** out) {
+    if (!out) return fail(ALICE_E_INVALID, "alice_engine_create: out is null");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t err = cudaGetDeviceCount(&n);
+    if (err != cudaSuccess || n == 0)
+        return fail(ALICE_E_CUDA, "alice_engine_create: no CUDA device (%s); this library has no CPU path",
+                    cudaGetErrorString(err));
+    if (device < 0 || device >= n) return fail(ALICE_E_INVALID, "alice_engine_create: device %d of %d", device, n);
+    CU(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(ALICE_E_UNSUPPORTED, "alice_engine_create: device is sm_%d%d; kernels are built for sm_100a",
+                    prop.major, prop.minor);
+    auto* e = new (std::nothrow) alice_engine();
+    if (!e) return fail(ALICE_E_NOMEM, "alice_engine_create: host allocation failed");
+    e->device = device;
+    e->num_sms = prop.multiProcessorCount;
+    err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    if (err != cudaSuccess) { delete e; return cuda_fail(err, "cudaStreamCreate"); }
+    e->own_stream = true;
+    err = cudaMalloc(&e->status, sizeof(int));
+    if (err == cudaSuccess) err = cudaMemset(e->status, 0, sizeof(int));
+    if (err != cudaSuccess) { cudaStreamDestroy(e->stream); delete e; return cuda_fail(err, "status word"); }
+    *out = e;
+    return ALICE_OK;
+}
+
+int32_t alice_engine_destroy(alice_engine* e) {
+    if (!e) return ALICE_OK;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    if (e->scratch) cudaFree(e->scratch);
+    if (e->status) cudaFree(e->status);
+    if (e->own_stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return ALICE_OK;
+}
+
+int32_t alice_engine_set_stream(alice_engine* e, void* s) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_engine_set_stream: null engine");
+    CU(cudaStreamSynchronize(e->stream));
+    if (e->own_stream) { cudaStreamDestroy(e->stream); e->own_stream = false; }
+    e->stream = static_cast<cudaStream_t>(s);
+    return ALICE_OK;
+}
+
+int32_t alice_engine_set_pdl(alice_engine* e, int32_t on) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_engine_set_pdl: null engine");
+    e->pdl = on != 0;
+    return ALICE_OK;
+}
+
+int32_t alice_engine_set_tuning(alice_engine* e, int32_t rps, int32_t stages) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_engine_set_tuning: null engine");
+    e->force_rps = rps; e->force_stages = stages;
+    return ALICE_OK;
+}
+
+int32_t alice_sync(alice_engine* e) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_sync: null engine");
+    CU(cudaStreamSynchronize(e->stream));
+    int st = 0;
+    CU(cudaMemcpy(&st, e->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(e->status, 0, sizeof(int));
+        return fail(ALICE_E_KERNEL, "alice_sync: a kernel reported status %d (1 = barrier wait timed out)", st);
+    }
+    return ALICE_OK;
+}
+
+// ---- weights -------------------------------------------------------------------------------
+
+static int make_ggml_desc(const char* who, size_t nbytes, uint32_t type, uint32_t rows, uint32_t cols, WeightDesc& d) {
+    if (!known_ggml(type)) return fail(ALICE_E_UNSUPPORTED, "%s: unsupported quantization type %u", who, type);
+    const uint32_t rb = ggml_row_bytes((WeightFormat)type, cols);
+    if (rows == 0 || rb == 0)
+        return fail(ALICE_E_SHAPE, "%s: cols %u is not a whole number of %u-element blocks (rows %u)", who, cols,
+                    ggml_block_elems((WeightFormat)type), rows);
+    if ((size_t)rows * rb != nbytes)
+        return fail(ALICE_E_SHAPE, "%s: %zu bytes given, %u x %u needs %zu", who, nbytes, rows, cols, (size_t)rows * rb);
+    d = WeightDesc{};
+    d.fmt = (WeightFormat)type; d.rows = rows; d.cols = cols; d.row_bytes = rb;
+    return ALICE_OK;
+}
+
+int32_t alice_upload_weights(alice_engine* e, const uint8_t* data, size_t nbytes, uint32_t type, uint32_t rows,
+                             uint32_t cols, alice_weights** out) {
+    if (!e || !data || !out) return fail(ALICE_E_INVALID, "alice_upload_weights: null argument");
+    WeightDesc d;
+    int rc = make_ggml_desc("alice_upload_weights", nbytes, type, rows, cols, d);
+    if (rc) return rc;
+    CU(cudaSetDevice(e->device));
+    void* p = nullptr;
+    CU(cudaMalloc(&p, nbytes + 64));  // tail slack: bulk copies round their end up to 16 bytes
+    cudaError_t err = cudaMemcpyAsync(p, data, nbytes, cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaMemsetAsync(static_cast<uint8_t*>(p) + nbytes, 0, 64, e->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);  // the host slice is only borrowed
+    if (err != cudaSuccess) { cudaFree(p); return cuda_fail(err, "alice_upload_weights copy"); }
+    d.data = static_cast<const uint8_t*>(p);
+    *out = new alice_weights{e, d, p, nullptr};
+    return ALICE_OK;
+}
+
+int32_t alice_weights_from_device(alice_engine* e, const void* dptr, size_t nbytes, uint32_t type, uint32_t rows,
+                                  uint32_t cols, alice_weights** out) {
+    if (!e || !dptr || !out) return fail(ALICE_E_INVALID, "alice_weights_from_device: null argument");
+    if ((uintptr_t)dptr & 15) return fail(ALICE_E_INVALID, "alice_weights_from_device: pointer not 16-byte aligned");
+    WeightDesc d;
+    int rc = make_ggml_desc("alice_weights_from_device", nbytes, type, rows, cols, d);
+    if (rc) return rc;
+    if (nbytes & 15)
+        return fail(ALICE_E_SHAPE, "alice_weights_from_device: byte size %zu must be a multiple of 16", nbytes);
+    d.data = static_cast<const uint8_t*>(dptr);
+    *out = new alice_weights{e, d, nullptr, nullptr};
+    return ALICE_OK;
+}
+
+static int upload_rows_and_scales(alice_engine* e, const std::vector<uint8_t>& host, const float* scales,
+                                  WeightDesc d, alice_weights** out) {
+    CU(cudaSetDevice(e->device));
+    void* p = nullptr;
+    void* s = nullptr;
+    CU(cudaMalloc(&p, host.size() + 64));
+    cudaError_t err = cudaMalloc(&s, (size_t)d.rows * sizeof(float));
+    if (err == cudaSuccess) err = cudaMemcpyAsync(p, host.data(), host.size(), cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaMemsetAsync(static_cast<uint8_t*>(p) + host.size(), 0, 64, e->stream);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(s, scales, (size_t)d.rows * sizeof(float), cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
+    if (err != cudaSuccess) { cudaFree(p); if (s) cudaFree(s); return cuda_fail(err, "ternary upload"); }
+    d.data = static_cast<const uint8_t*>(p);
+    d.scales = static_cast<const float*>(s);
+    *out = new alice_weights{e, d, p, s};
+    return ALICE_OK;
+}
+
+int32_t alice_upload_ternary(alice_engine* e, const uint8_t* pos, const uint8_t* neg, const float* scales,
+                             uint32_t rows, uint32_t cols, alice_weights** out) {
+    if (!e || !pos || !neg || !scales || !out) return fail(ALICE_E_INVALID, "alice_upload_ternary: null argument");
+    if (rows == 0 || cols == 0) return fail(ALICE_E_SHAPE, "alice_upload_ternary: empty matrix");
+    // device row = [pos plane | neg plane]; planes padded with zero bits to a whole number of 32-bit words
+    const uint32_t src_pb = (cols + 7) / 8, pb = ((cols + 31) / 32) * 4;
+    std::vector<uint8_t> host((size_t)rows * 2 * pb, 0);
+    const uint8_t tail_mask = (cols % 8) ? (uint8_t)((1u << (cols % 8)) - 1) : 0xFF;
+    for (uint32_t r = 0; r < rows; r++) {
+        uint8_t* dp = host.data() + (size_t)r * 2 * pb;
+        memcpy(dp, pos + (size_t)r * src_pb, src_pb);
+        memcpy(dp + pb, neg + (size_t)r * src_pb, src_pb);
+        dp[src_pb - 1] &= tail_mask;       // bits past num_cols are never read by the reference
+        dp[pb + src_pb - 1] &= tail_mask;
+    }
+    WeightDesc d = {};
+    d.fmt = WF_TERNARY; d.rows = rows; d.cols = cols; d.row_bytes = 2 * pb;
+    return upload_rows_and_scales(e, host, scales, d, out);
+}
+
+int32_t alice_upload_sparse_ternary(alice_engine* e, const uint8_t* packed, const float* scales, uint32_t rows,
+                                    uint32_t cols, alice_weights** out) {
+    if (!e || !packed || !scales || !out) return fail(ALICE_E_INVALID, "alice_upload_sparse_ternary: null argument");
+    if (rows == 0 || cols == 0) return fail(ALICE_E_SHAPE, "alice_upload_sparse_ternary: empty matrix");
+    const uint32_t rb = ((cols + 15) / 16) * 4;
+    std::vector<uint8_t> host(packed, packed + (size_t)rows * rb);
+    WeightDesc d = {};
+    d.fmt = WF_SPARSE_TERNARY; d.rows = rows; d.cols = cols; d.row_bytes = rb;
+    return upload_rows_and_scales(e, host, scales, d, out);
+}
+
+int32_t alice_weights_free(alice_weights* w) {
+    if (!w) return ALICE_OK;
+    cudaSetDevice(w->e->device);
+    cudaStreamSynchronize(w->e->stream);
+    if (w->owned_data) cudaFree(w->owned_data);
+    if (w->owned_scales) cudaFree(w->owned_scales);
+    delete w;
+    return ALICE_OK;
+}
+
+// ---- f32 buffers ---------------------------------------------------------------------------
+
+int32_t alice_buf_alloc_f32(alice_engine* e, size_t len, alice_buf** out) {
+    if (!e || !out) return fail(ALICE_E_INVALID, "alice_buf_alloc_f32: null argument");
+    CU(cudaSetDevice(e->device));
+    void* p = nullptr;
+    CU(cudaMalloc(&p, std::max<size_t>(len, 1) * sizeof(float)));
+    cudaError_t err = cudaMemsetAsync(p, 0, std::max<size_t>(len, 1) * sizeof(float), e->stream);
+    if (err != cudaSuccess) { cudaFree(p); return cuda_fail(err, "alice_buf_alloc_f32 memset"); }
+    *out = new alice_buf{e, static_cast<float*>(p), len, true};
+    return ALICE_OK;
+}
+
+int32_t alice_buf_write_f32(alice_engine* e, alice_buf* b, const float* data, size_t len) {
+    if (!e || !b || (!data && len)) return fail(ALICE_E_INVALID, "alice_buf_write_f32: null argument");
+    if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_write_f32: %zu floats into a buffer of %zu", len, b->len);
+    CU(cudaMemcpyAsync(b->p, data, len * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));  // the host slice is only borrowed for the call
+    return ALICE_OK;
+}
+
+int32_t alice_buf_upload_f32(alice_engine* e, const float* data, size_t len, alice_buf** out) {
+    int rc = alice_buf_alloc_f32(e, len, out);
+    if (rc) return rc;
+    rc = alice_buf_write_f32(e, *out, data, len);
+    if (rc) { alice_buf_free(*out); *out = nullptr; }
+    return rc;
+}
+
+int32_t alice_buf_read_f32(alice_engine* e, const alice_buf* b, float* out, size_t len) {
+    if (!e || !b || (!out && len)) return fail(ALICE_E_INVALID, "alice_buf_read_f32: null argument");
+    if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_read_f32: %zu floats from a buffer of %zu", len, b->len);
+    CU(cudaMemcpyAsync(out, b->p, len * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return ALICE_OK;
+}
+
+int32_t alice_buf_from_device(alice_engine* e, void* dptr, size_t len, alice_buf** out) {
+    if (!e || !dptr || !out) return fail(ALICE_E_INVALID, "alice_buf_from_device: null argument");
+    if ((uintptr_t)dptr & 15) return fail(ALICE_E_INVALID, "alice_buf_from_device: pointer not 16-byte aligned");
+    *out = new alice_buf{e, static_cast<float*>(dptr), len, false};
+    return ALICE_OK;
+}
+
+int32_t alice_buf_free(alice_buf* b) {
+    if (!b) return ALICE_OK;
+    if (b->owned) {
+        cudaSetDevice(b->e->device);
+        cudaStreamSynchronize(b->e->stream);
+        cudaFree(b->p);
+    }
+    delete b;
+    return ALICE_OK;
+}
+
+// ---- Q8_K activations ----------------------------------------------------------------------
+
+int32_t alice_q8k_alloc(alice_engine* e, uint32_t cols, uint32_t batch, alice_q8k** out) {
+    if (!e || !out) return fail(ALICE_E_INVALID, "alice_q8k_alloc: null argument");
+    if (cols == 0 || cols % 256 != 0) return fail(ALICE_E_SHAPE, "alice_q8k_alloc: cols %u is not a multiple of 256", cols);
+    if (batch == 0) return fail(ALICE_E_SHAPE, "alice_q8k_alloc: batch 0");
+    CU(cudaSetDevice(e->device));
+    auto* q = new alice_q8k{e, nullptr, cols, batch, cols / 256, Q8KLayout::make(cols / 256, batch)};
+    cudaError_t err = cudaMalloc(&q->base, q->lay.total);
+    if (err != cudaSuccess) { delete q; return cuda_fail(err, "alice_q8k_alloc"); }
+    *out = q;
+    return ALICE_OK;
+}
+
+int32_t alice_quantize_q8k(alice_engine* e, const alice_buf* x, alice_q8k* q) {
+    if (!e || !x || !q) return fail(ALICE_E_INVALID, "alice_quantize_q8k: null argument");
+    if (x->len < (size_t)q->cols * q->batch)
+        return fail(ALICE_E_SHAPE, "alice_quantize_q8k: input has %zu floats, need %zu", x->len, (size_t)q->cols * q->batch);
+    launch_quantize_q8k(x->p, q->cols, q->batch, q->base, e->stream);
+    CU(cudaGetLastError());
+    return ALICE_OK;
+}
+
+int32_t alice_q8k_read(alice_engine* e, const alice_q8k* q, float* d, int8_t* qs, int16_t* bsums) {
+    if (!e || !q || !d || !qs || !bsums) return fail(ALICE_E_INVALID, "alice_q8k_read: null argument");
+    const size_t n = (size_t)q->batch * q->nb;
+    auto* p = static_cast<const uint8_t*>(q->base);
+    CU(cudaMemcpyAsync(qs, p + q->lay.qs_off, n * 256, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaMemcpyAsync(d, p + q->lay.d_off, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaMemcpyAsync(bsums, p + q->lay.bsums_off, n * 32, cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    return ALICE_OK;
+}
+
+int32_t alice_q8k_upload(alice_engine* e, const float* d, const int8_t* qs, const int16_t* bsums, uint32_t cols,
+                         uint32_t batch, alice_q8k** out) {
+    if (!d || !qs || !bsums) return fail(ALICE_E_INVALID, "alice_q8k_upload: null argument");
+    int rc = alice_q8k_alloc(e, cols, batch, out);
+    if (rc) return rc;
+    alice_q8k* q = *out;
+    const size_t n = (size_t)batch * q->nb;
+    auto* p = static_cast<uint8_t*>(q->base);
+    cudaError_t err = cudaMemcpyAsync(p + q->lay.qs_off, qs, n * 256, cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(p + q->lay.d_off, d, n * 4, cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(p + q->lay.bsums_off, bsums, n * 32, cudaMemcpyHostToDevice, e->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
+    if (err != cudaSuccess) { alice_q8k_free(q); *out = nullptr; return cuda_fail(err, "alice_q8k_upload"); }
+    return ALICE_OK;
+}
+
+int32_t alice_q8k_free(alice_q8k* q) {
+    if (!q) return ALICE_OK;
+    cudaSetDevice(q->e->device);
+    cudaStreamSynchronize(q->e->stream);
+    cudaFree(q->base);
+    delete q;
+    return ALICE_OK;
+}
+
+// ---- the hot path --------------------------------------------------------------------------
+
+// Shared body of matvec / swiglu on already prepared activations: one launch per batch vector.
+static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_q8k* q,
+                    const float* xf, float* y, uint32_t batch, const char* who) {
+    const LaunchCfg cfg = cfg_of(e);
+    for (uint32_t k = 0; k < batch; k++) {
+        Q8KView v;
+        if (q) v = view_of(q, k);
+        int rc = launch_stream_gemv(w0->d, w1 ? &w1->d : nullptr, q ? &v : nullptr,
+                                    xf ? xf + (size_t)k * w0->d.cols : nullptr, y + (size_t)k * w0->d.rows, cfg);
+        if (rc) return launch_rc(rc, who);
+    }
+    return ALICE_OK;
+}
+
+static int check_pair(const alice_weights* g, const alice_weights* u, const char* who) {
+    if (g->d.fmt != u->d.fmt || g->d.rows != u->d.rows || g->d.cols != u->d.cols)
+        return fail(ALICE_E_SHAPE, "%s: gate and up differ in format or shape", who);
+    return ALICE_OK;
+}
+
+static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_buf* x,
+                         alice_buf* y, uint32_t batch, const char* who) {
+    if (!e || !w0 || !x || !y) return fail(ALICE_E_INVALID, "%s: null argument", who);
+    if (batch == 0 || batch > 8) return fail(ALICE_E_SHAPE, "%s: batch %u outside 1..8", who, batch);
+    if (w1) { int rc = check_pair(w0, w1, who); if (rc) return rc; }
+    const WeightDesc& d = w0->d;
+    if (x->len < (size_t)batch * d.cols) return fail(ALICE_E_SHAPE, "%s: input has %zu floats, need %zu", who, x->len, (size_t)batch * d.cols);
+    if (y->len < (size_t)batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output has %zu floats, need %zu", who, y->len, (size_t)batch * d.rows);
+    CU(cudaSetDevice(e->device));
+    if (format_uses_q8k(d.fmt)) {
+        // q4k_matvec = quantize_row_q8_k + q4k_matvec_preq (src/gguf.rs:3600-3603)
+        alice_q8k tmp{e, nullptr, d.cols, batch, d.cols / 256, Q8KLayout::make(d.cols / 256, batch)};
+        int rc = ensure_scratch(e, tmp.lay.total);
+        if (rc) return rc;
+        tmp.base = e->scratch;
+        launch_quantize_q8k(x->p, d.cols, batch, tmp.base, e->stream);
+        return run_gemv(e, w0, w1, &tmp, nullptr, y->p, batch, who);
+    }
+    return run_gemv(e, w0, w1, nullptr, x->p, y->p, batch, who);
+}
+
+static int preq_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_q8k* q,
+                       alice_buf* y, const char* who) {
+    if (!e || !w0 || !q || !y) return fail(ALICE_E_INVALID, "%s: null argument", who);
+    if (w1) { int rc = check_pair(w0, w1, who); if (rc) return rc; }
+    const WeightDesc& d = w0->d;
+    if (q->cols != d.cols) return fail(ALICE_E_SHAPE, "%s: Q8_K input has %u columns, weights %u", who, q->cols, d.cols);
+    if (q->batch > 8) return fail(ALICE_E_SHAPE, "%s: batch %u outside 1..8", who, q->batch);
+    if (y->len < (size_t)q->batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output too small", who);
+    CU(cudaSetDevice(e->device));
+    if (format_uses_q8k(d.fmt)) return run_gemv(e, w0, w1, q, nullptr, y->p, q->batch, who);
+    if (d.fmt == WF_Q1_0 || d.fmt == WF_Q2_0) {
+        const size_t total = (size_t)q->batch * d.cols;
+        int rc = ensure_scratch(e, total * sizeof(float));
+        if (rc) return rc;
+        launch_q8k_to_f32(view_of(q, 0), total, static_cast<float*>(e->scratch), e->stream);
+        return run_gemv(e, w0, w1, nullptr, static_cast<float*>(e->scratch), y->p, q->batch, who);
+    }
+    // quantized_matvec_preq panics for every other type (src/gguf.rs:4606)
+    return fail(ALICE_E_UNSUPPORTED, "%s: pre-quantized input only for Q4_K/Q5_K/Q6_K/Q1_0/Q2_0", who);
+}
+
+int32_t alice_matvec(alice_engine* e, const alice_weights* w, const alice_buf* x, alice_buf* y, uint32_t batch) {
+    return matvec_common(e, w, nullptr, x, y, batch, "alice_matvec");
+}
+
+int32_t alice_matvec_preq(alice_engine* e, const alice_weights* w, const alice_q8k* q, alice_buf* y) {
+    return preq_common(e, w, nullptr, q, y, "alice_matvec_preq");
+}
+
+int32_t alice_swiglu(alice_engine* e, const alice_weights* gate, const alice_weights* up, const alice_buf* x,
+                     alice_buf* y, uint32_t batch) {
+    if (!up) return fail(ALICE_E_INVALID, "alice_swiglu: null argument");
+    return matvec_common(e, gate, up, x, y, batch, "alice_swiglu");
+}
+
+int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alice_weights* up, const alice_q8k* q,
+                          alice_buf* y) {
+    if (!up) return fail(ALICE_E_INVALID, "alice_swiglu_preq: null argument");
+    return preq_common(e, gate, up, q, y, "alice_swiglu_preq");
+}
+
+int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out) {
+    if (!e || !w || !out) return fail(ALICE_E_INVALID, "alice_dequantize: null argument");
+    if (out->len < (size_t)w->d.rows * w->d.cols) return fail(ALICE_E_SHAPE, "alice_dequantize: output too small");
+    CU(cudaSetDevice(e->device));
+    return launch_rc(launch_dequantize(w->d, out->p, e->stream), "alice_dequantize");
+}
+
+// ---- host-pointer convenience --------------------------------------------------------------
+
+static alice_engine* g_host_engine = nullptr;
+static std::mutex g_host_mu;
+
+static int host_engine(alice_engine** out) {
+    if (!g_host_engine) {
+        int rc = alice_engine_create(0, &g_host_engine);
+        if (rc) return rc;
+    }
+    *out = g_host_engine;
+    return ALICE_OK;
+}
+
+int32_t alice_matvec_host(uint32_t type, const uint8_t* data, size_t nbytes, uint32_t rows, uint32_t cols,
+                          const float* x, float* y) {
+    if (!data || !x || !y) return fail(ALICE_E_INVALID, "alice_matvec_host: null argument");
+    std::lock_guard<std::mutex> lk(g_host_mu);
+    alice_engine* e;
+    int rc = host_engine(&e);
+    if (rc) return rc;
+    alice_weights* w = nullptr;
+    alice_buf *bx = nullptr, *by = nullptr;
+    rc = alice_upload_weights(e, data, nbytes, type, rows, cols, &w);
+    if (!rc) rc = alice_buf_upload_f32(e, x, cols, &bx);
+    if (!rc) rc = alice_buf_alloc_f32(e, rows, &by);
+    if (!rc) rc = alice_matvec(e, w, bx, by, 1);
+    if (!rc) rc = alice_buf_read_f32(e, by, y, rows);
+    if (!rc) rc = alice_sync(e);
+    alice_buf_free(by); alice_buf_free(bx); alice_weights_free(w);
+    return rc;
+}
+
+int32_t alice_dequantize_host(uint32_t type, const uint8_t* data, size_t nbytes, float* out, size_t n_out) {
+    if (!data || !out) return fail(ALICE_E_INVALID, "alice_dequantize_host: null argument");
+    const uint32_t be = ggml_block_elems((WeightFormat)type);
+    if (be == 0) return fail(ALICE_E_UNSUPPORTED, "alice_dequantize_host: unsupported quantization type %u", type);
+    if (n_out == 0 || n_out % be != 0 || n_out > 0xFFFFFFFFu)
+        return fail(ALICE_E_SHAPE, "alice_dequantize_host: %zu outputs is not a whole number of blocks", n_out);
+    std::lock_guard<std::mutex> lk(g_host_mu);
+    alice_engine* e;
+    int rc = host_engine(&e);
+    if (rc) return rc;
+    alice_weights* w = nullptr;
+    alice_buf* bo = nullptr;
+    rc = alice_upload_weights(e, data, nbytes, type, 1, (uint32_t)n_out, &w);
+    if (!rc) rc = alice_buf_alloc_f32(e, n_out, &bo);
+    if (!rc) rc = alice_dequantize(e, w, bo);
+    if (!rc) rc = alice_buf_read_f32(e, bo, out, n_out);
+    alice_buf_free(bo); alice_weights_free(w);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,153 @@
+// Planning and launch of the streaming matvec kernels (one template instance per format,
+// activation positions per lane KL in {1,2,4}, plain / fused SwiGLU).
+#include <algorithm>
+
+#include "../../include/alice_cuda.h"
+#include "formats.cuh"
+#include "gemv_launch.cuh"
+
+namespace alice {
+
+bool format_uses_q8k(WeightFormat f) { return f == WF_Q4_K || f == WF_Q5_K || f == WF_Q6_K; }
+
+uint32_t ggml_block_bytes(WeightFormat f) {
+    switch (f) {
+        case WF_Q8_0: return 34; case WF_Q4_K: return 144; case WF_Q5_K: return 176;
+        case WF_Q6_K: return 210; case WF_Q1_0: return 18; case WF_Q2_0: return 34;
+        default: return 0;
+    }
+}
+uint32_t ggml_block_elems(WeightFormat f) {
+    switch (f) {
+        case WF_Q8_0: return 32;
+        case WF_Q4_K: case WF_Q5_K: case WF_Q6_K: return 256;
+        case WF_Q1_0: case WF_Q2_0: return 128;
+        default: return 0;
+    }
+}
+uint32_t ggml_row_bytes(WeightFormat f, uint32_t cols) {
+    const uint32_t e = ggml_block_elems(f);
+    if (e == 0 || cols == 0 || cols % e != 0) return 0;
+    return cols / e * ggml_block_bytes(f);
+}
+
+namespace {
+
+constexpr uint32_t SMEM_BUDGET = 200 * 1024;   // of the 227 KB a CTA may opt in to
+constexpr uint32_t STAGE_TARGET = 16 * 1024;   // preferred bytes per matrix per stage
+constexpr uint32_t HDR_BYTES = (sizeof(StreamSmem) + 127) & ~127u;
+
+uint32_t units_per_row(WeightFormat f, uint32_t cols) {
+    switch (f) {
+        case WF_Q4_K: case WF_Q5_K: return cols / 64;
+        case WF_Q6_K: return cols / 32;
+        case WF_Q8_0: return cols / 16;
+        case WF_Q1_0: return cols / 32;
+        case WF_Q2_0: return cols / 16;
+        case WF_TERNARY: case WF_SPARSE_TERNARY: return (cols + 31) / 32;
+        default: return 0;
+    }
+}
+
+template <class F, int KL, bool SW>
+int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+    static bool attr_set = false;  // per template instance
+    auto kern = stream_gemv_kernel<F, KL, SW>;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET) != cudaSuccess)
+            return ALICE_E_CUDA;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(STREAM_THREADS);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = cfg.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = cfg.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
+}
+
+template <class F>
+int launch_fmt(const StreamArgs& a, uint32_t kl, bool sw, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+    if (sw) {
+        if (kl == 1) return launch_one<F, 1, true>(a, grid, smem, cfg);
+        if (kl == 2) return launch_one<F, 2, true>(a, grid, smem, cfg);
+        return launch_one<F, 4, true>(a, grid, smem, cfg);
+    }
+    if (kl == 1) return launch_one<F, 1, false>(a, grid, smem, cfg);
+    if (kl == 2) return launch_one<F, 2, false>(a, grid, smem, cfg);
+    return launch_one<F, 4, false>(a, grid, smem, cfg);
+}
+
+}  // namespace
+
+int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
+                       const LaunchCfg& cfg) {
+    const bool sw = w1 != nullptr;
+    if (w0.rows == 0 || w0.cols == 0 || !w0.data || !y) return ALICE_E_INVALID;
+    if (sw && (w1->fmt != w0.fmt || w1->rows != w0.rows || w1->cols != w0.cols || w1->row_bytes != w0.row_bytes))
+        return ALICE_E_SHAPE;
+    if (((uintptr_t)w0.data & 15) || (sw && ((uintptr_t)w1->data & 15))) return ALICE_E_INVALID;
+    if (format_uses_q8k(w0.fmt)) {
+        if (!q8 || q8->nb * 256u != w0.cols) return ALICE_E_SHAPE;
+    } else if (!x) {
+        return ALICE_E_INVALID;
+    }
+    const uint32_t units = units_per_row(w0.fmt, w0.cols);
+    if (units == 0) return ALICE_E_UNSUPPORTED;
+
+    StreamArgs a = {};
+    a.w0 = w0.data; a.w1 = sw ? w1->data : nullptr;
+    if (q8) a.q8 = *q8;
+    a.x = x; a.aux0 = w0.scales; a.aux1 = sw ? w1->scales : nullptr;
+    a.y = y; a.status = cfg.status;
+    a.rows = w0.rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
+
+    // warps per row: just enough lanes for one unit each, at most all eight
+    uint32_t P = 1;
+    while (P < (uint32_t)NCW && P * 32 < units) P *= 2;
+    uint32_t kl = (units + P * 32 - 1) / (P * 32);
+    if (kl > 4) return ALICE_E_SHAPE;  // row too wide for the register-resident activation scheme
+    if (kl == 3) kl = 4;
+    a.P = P; a.slots = NCW / P;
+
+    const uint32_t nmat = sw ? 2 : 1;
+    const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1);
+    // rows per warp set per stage: fill ~STAGE_TARGET bytes but keep >= 8 stages of work per CTA
+    uint32_t rps_bytes = std::max<uint32_t>(1, STAGE_TARGET / std::max<uint32_t>(1, a.slots * a.row_bytes));
+    uint32_t rps_bal = std::max<uint32_t>(1, a.rows / (a.slots * ctas * 8));
+    uint32_t rps = std::min<uint32_t>(std::min(rps_bytes, rps_bal), MAX_RPS);
+    if (cfg.force_rps > 0) rps = std::min<uint32_t>(cfg.force_rps, MAX_RPS);
+    uint32_t cap, stage, nst;
+    for (;;) {
+        cap = (a.slots * rps * a.row_bytes + 48 + 127) & ~127u;
+        stage = cap * nmat;
+        nst = std::min<uint32_t>(MAX_STAGES, (SMEM_BUDGET - HDR_BYTES) / stage);
+        if (nst >= 2 || rps == 1) break;
+        rps = rps / 2;
+    }
+    if (nst < 2) return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
+    if (cfg.force_stages >= 2) nst = std::min<uint32_t>(nst, cfg.force_stages);
+    a.rps = rps; a.cap = cap; a.nstages = nst;
+    a.groups = (a.rows + a.slots * rps - 1) / (a.slots * rps);
+    const uint32_t grid = std::min(ctas, a.groups);
+    const size_t smem = HDR_BYTES + (size_t)nst * stage;
+
+    switch (w0.fmt) {
+        case WF_Q4_K: return launch_fmt<FmtQ4K>(a, kl, sw, grid, smem, cfg);
+        case WF_Q5_K: return launch_fmt<FmtQ5K>(a, kl, sw, grid, smem, cfg);
+        case WF_Q6_K: return launch_fmt<FmtQ6K>(a, kl, sw, grid, smem, cfg);
+        case WF_Q8_0: return launch_fmt<FmtQ8_0>(a, kl, sw, grid, smem, cfg);
+        case WF_Q1_0: return launch_fmt<FmtQ1_0>(a, kl, sw, grid, smem, cfg);
+        case WF_Q2_0: return launch_fmt<FmtQ2_0>(a, kl, sw, grid, smem, cfg);
+        case WF_TERNARY: return launch_fmt<FmtTernary>(a, kl, sw, grid, smem, cfg);
+        case WF_SPARSE_TERNARY: return launch_fmt<FmtSparseTernary>(a, kl, sw, grid, smem, cfg);
+        default: return ALICE_E_UNSUPPORTED;
+    }
+}
+
+}  // namespace alice

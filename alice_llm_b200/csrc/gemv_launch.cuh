@@ -1,0 +1,52 @@
+// Host-side description and launch of the streaming matvec.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "q8k.cuh"
+
+namespace alice {
+
+// Storage formats of a device-resident weight matrix.
+enum WeightFormat : uint32_t {
+    WF_Q8_0 = 8, WF_Q4_K = 12, WF_Q5_K = 13, WF_Q6_K = 14, WF_Q1_0 = 41, WF_Q2_0 = 42,  // GGML ids (src/gguf.rs:101-122)
+    WF_TERNARY = 1000,         // interleaved bit planes, see FmtTernary
+    WF_SPARSE_TERNARY = 1001,  // packed 2-bit codes, see FmtSparseTernary
+};
+
+struct WeightDesc {
+    WeightFormat fmt;
+    const uint8_t* data;   // device, 16-byte aligned
+    const float* scales;   // device per-row scales (ternary formats) or null
+    uint32_t rows, cols;
+    uint32_t row_bytes;
+};
+
+bool format_uses_q8k(WeightFormat f);
+// Bytes of one device row for a GGML block format; 0 if cols is not a whole number of blocks.
+uint32_t ggml_row_bytes(WeightFormat f, uint32_t cols);
+uint32_t ggml_block_bytes(WeightFormat f);
+uint32_t ggml_block_elems(WeightFormat f);
+
+struct LaunchCfg {
+    cudaStream_t stream;
+    int num_sms;
+    int* status;      // device status word
+    bool pdl;         // launch with programmatic stream serialization
+    int force_rps;    // 0 = automatic
+    int force_stages; // 0 = automatic
+};
+
+// y[r] = W[r,:] . x  (or silu(W0 x) * (W1 x) when w1 != null). K-quant formats read `q8`,
+// the others read the f32 vector `x`. Returns 0 or a negative ALICE_E_* code.
+int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
+                       const LaunchCfg& cfg);
+
+// out[r*cols + c] = dequantized weight, bit-exact with the reference dequantizers.
+int launch_dequantize(const WeightDesc& w, float* out, cudaStream_t stream);
+
+// out[i] = d[i/256] * q[i] for i < total (the Q8_K -> f32 step of quantized_matvec_preq for
+// Q1_0/Q2_0, src/gguf.rs:4593-4605); total = batch * cols.
+void launch_q8k_to_f32(const Q8KView& q8, size_t total, float* out, cudaStream_t stream);
+
+}  // namespace alice

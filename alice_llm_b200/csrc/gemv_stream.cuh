@@ -1,0 +1,196 @@
+// Streaming fused dequantize + matvec for GGUF block formats on sm_100a.
+//
+// One persistent CTA per SM streams the raw weight rows it owns, in order, through a ring of
+// shared-memory stages filled by untiled TMA bulk copies (cp.async.bulk + mbarrier complete_tx),
+// so the number of bytes in flight does not depend on registers. A stage holds slots*rps whole
+// consecutive rows (and, for the fused SwiGLU variant, the same rows of the second matrix).
+// Eight consumer warps decode from shared memory: P = 8/slots warps share a row, each warp set
+// walks rps rows per stage, and every lane owns the same KL "unit" positions (column ranges) of
+// every row it ever sees, so the activations of those columns are loaded ONCE into registers
+// and no activation traffic touches shared memory inside the loop. A ninth warp is the copy
+// producer.
+//
+// Row result = fixed-order sum of the P warp partials (deterministic run to run).
+#pragma once
+#include "common.cuh"
+#include "q8k.cuh"
+
+namespace alice {
+
+constexpr int NCW = 8;                        // consumer warps per CTA
+constexpr int STREAM_THREADS = (NCW + 1) * 32;  // + one producer warp
+constexpr int MAX_STAGES = 16;
+constexpr int MAX_RPS = 16;                   // rows per warp set per stage (must stay <= 32)
+
+struct StreamArgs {
+    const uint8_t* w0;   // weight rows (gate matrix for SwiGLU)
+    const uint8_t* w1;   // up matrix for SwiGLU, else null
+    const void* act;     // Q8KView base (K-quants) or const float* x (f32-activation formats)
+    Q8KView q8;          // valid for K-quants
+    const float* x;      // valid for f32-activation formats
+    const float* aux0;   // per-row scales (ternary formats) for w0
+    const float* aux1;   // per-row scales for w1
+    float* y;            // y[k*rows + r]
+    int* status;         // device status word (0 = ok)
+    uint32_t rows, cols;
+    uint32_t row_bytes;  // bytes of one weight row
+    uint32_t units;      // units per row (format specific)
+    uint32_t P;          // consumer warps per row: 1, 2, 4 or 8
+    uint32_t slots;      // warp sets per CTA = NCW / P
+    uint32_t rps;        // rows each warp set handles per stage (<= MAX_RPS)
+    uint32_t groups;     // ceil(rows / (slots * rps)) = number of stage-sized row groups
+    uint32_t nstages;
+    uint32_t cap;        // bytes reserved per matrix per stage (multiple of 128)
+};
+
+// Shared-memory header in front of the ring.
+struct StreamSmem {
+    unsigned long long full[MAX_STAGES];
+    unsigned long long empty[MAX_STAGES];
+    unsigned long long red[MAX_STAGES][NCW];  // per (stage, slot): partials of the P-1 helper warps posted
+    float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
+    int abort_flag;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+            *abort_flag = 1;
+            atomicExch(status, KERR_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+
+// F supplies:
+//   struct Act;                                            per-position activation registers
+//   static void load_act(Act&, const StreamArgs&, uint32_t u, bool valid)
+//   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
+//   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
+template <class F, int KL, bool SWIGLU>
+__global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const StreamArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
+    constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
+    const uint32_t ring = smem_u32(smem_raw) + HDR;
+    const uint32_t stage_bytes = a.cap * (SWIGLU ? 2u : 1u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t P = a.P, slots = a.slots, rps = a.rps;
+    const uint32_t rows_per_group = slots * rps;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < a.nstages; s++) {
+            mbar_init(smem_u32(&sm->full[s]), 1);
+            mbar_init(smem_u32(&sm->empty[s]), NCW);
+            for (uint32_t q = 0; q < slots; q++) mbar_init(smem_u32(&sm->red[s][q]), P > 1 ? P - 1 : 1);
+        }
+        sm->abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
+    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
+    const uint32_t nchunks = g1 - g0;
+    volatile int* abort_flag = &sm->abort_flag;
+
+    if (warp == NCW) {
+        // ── producer: weights do not depend on the previous kernel, so copies start at once ──
+        if (lane == 0) {
+            uint32_t issued = 0;
+            for (uint32_t c = 0; c < nchunks; c++) {
+                const uint32_t s = c % a.nstages, use = c / a.nstages;
+                if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status)) break;
+                const uint32_t r0 = (g0 + c) * rows_per_group;
+                const uint32_t nrow = min(rows_per_group, a.rows - r0);
+                const uint64_t off = (uint64_t)r0 * a.row_bytes;
+                const uint64_t a0 = off & ~uint64_t(15);
+                const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
+                const uint32_t fb = smem_u32(&sm->full[s]);
+                mbar_arrive_expect_tx(fb, SWIGLU ? 2 * cb : cb);
+                bulk_g2s(ring + s * stage_bytes, a.w0 + a0, cb, fb);
+                if (SWIGLU) bulk_g2s(ring + s * stage_bytes + a.cap, a.w1 + a0, cb, fb);
+                issued = c + 1;
+            }
+            if (*abort_flag) {
+                // Drain: let copies already issued land before the CTA gives its shared memory back.
+                const uint32_t first = issued > a.nstages ? issued - a.nstages : 0;
+                for (uint32_t c = first; c < issued; c++)
+                    mbar_wait(smem_u32(&sm->full[c % a.nstages]), (c / a.nstages) & 1);
+            }
+        }
+        return;
+    }
+
+    // ── consumers ──
+    const uint32_t slot = warp / P, part = warp % P;
+    pdl_wait();  // activations come from the previous kernel
+    typename F::Act act[KL];
+#pragma unroll
+    for (int k = 0; k < KL; k++) {
+        const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
+        F::load_act(act[k], a, u, u < a.units);
+    }
+
+    for (uint32_t c = 0; c < nchunks; c++) {
+        const uint32_t s = c % a.nstages, ph = (c / a.nstages) & 1;
+        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status)) break;
+        const uint32_t r0 = (g0 + c) * rows_per_group;
+        const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
+        const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
+        const uint32_t nrow = r0 + set0 < a.rows ? min(rps, a.rows - r0 - set0) : 0;
+        const uint32_t sb = ring + s * stage_bytes + pad + set0 * a.row_bytes;
+        float keep0 = 0.0f, keep1 = 0.0f;                 // finalizer warp: lane rr keeps row rr's own partial
+        for (uint32_t rr = 0; rr < nrow; rr++) {
+            const uint32_t rb = sb + rr * a.row_bytes;
+            float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+            for (int k = 0; k < KL; k++) {
+                const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
+                if (u < a.units) {
+                    v0 += F::unit(rb, u, act[k], a);
+                    if (SWIGLU) v1 += F::unit(rb + a.cap, u, act[k], a);
+                }
+            }
+            v0 = warp_sum(v0);
+            if (SWIGLU) v1 = warp_sum(v1);
+            if (part != 0) {
+                if (lane == 0) {
+                    sm->partial[s][warp][rr][0] = v0;
+                    if (SWIGLU) sm->partial[s][warp][rr][1] = v1;
+                }
+            } else if (lane == (rr & 31)) {
+                keep0 = v0;
+                keep1 = v1;
+            }
+        }
+        if (nrow > 0) {
+            if (part != 0) {
+                if (lane == 0) mbar_arrive(smem_u32(&sm->red[s][slot]));
+            } else {
+                if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status)) break;
+                if (lane < nrow) {
+                    float v0 = keep0, v1 = keep1;
+                    for (uint32_t p = 1; p < P; p++) {
+                        v0 += sm->partial[s][warp + p][lane][0];
+                        if (SWIGLU) v1 += sm->partial[s][warp + p][lane][1];
+                    }
+                    const uint32_t row = r0 + set0 + lane;
+                    float r = F::finish(v0, a, a.aux0, row);
+                    if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
+                    a.y[row] = r;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
+    }
+}
+
+}  // namespace alice

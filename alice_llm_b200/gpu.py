@@ -1,0 +1,317 @@
+"""Host-side mirror of ALICE-LLM's device API (src/gpu.rs) over the CUDA C ABI.
+
+Names, argument meaning and error behaviour follow the reference so that tests read like its
+own: ``GpuEngine`` (src/gpu.rs:320, methods :434-964), ``GpuWeightBuffer`` (:302), ``GpuBuffer``
+(:277), ``GpuPass`` (:418, :1016-2105).  Shape or format violations raise (the reference panics).
+Nothing here computes on the CPU; every method is a call into libalice_cuda.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from enum import Enum
+
+import numpy as np
+
+from . import _lib
+from ._lib import AliceError, check  # noqa: F401
+
+
+class GpuQuantType(Enum):
+    """src/gpu.rs:285 plus the two in-memory ternary packings of src/gguf.rs."""
+    Q4K = 12
+    Q5K = 13
+    Q6K = 14
+    Q8_0 = 8
+    Q1_0 = 41
+    Q2_0 = 42
+    Ternary = 1000
+    SparseTernary = 1001
+
+
+def _np(a, dtype):
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _ptr(a):
+    return C.c_void_p(a.ctypes.data)
+
+
+class GpuBuffer:
+    """f32 storage on the device (src/gpu.rs:277)."""
+
+    def __init__(self, engine, handle, length):
+        self.engine, self._h, self.len = engine, handle, length
+
+    def free(self):
+        if self._h:
+            _lib.load().alice_buf_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class GpuWeightBuffer:
+    """Raw quantized blocks on the device (src/gpu.rs:302)."""
+
+    def __init__(self, engine, handle, rows, cols, quant):
+        self.engine, self._h, self.rows, self.cols, self.quant = engine, handle, rows, cols, quant
+
+    def free(self):
+        if self._h:
+            _lib.load().alice_weights_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Q8KBuffer:
+    """Vec<BlockQ8K> on the device (src/gguf.rs:1306)."""
+
+    def __init__(self, engine, handle, cols, batch):
+        self.engine, self._h, self.cols, self.batch = engine, handle, cols, batch
+
+    def read(self):
+        """-> (d[batch, nb], qs[batch, nb, 256], bsums[batch, nb, 16])"""
+        nb = self.cols // 256
+        d = np.empty((self.batch, nb), np.float32)
+        qs = np.empty((self.batch, nb, 256), np.int8)
+        bs = np.empty((self.batch, nb, 16), np.int16)
+        check(_lib.load().alice_q8k_read(self.engine._h, self._h, _ptr(d), _ptr(qs), _ptr(bs)))
+        return d, qs, bs
+
+    def free(self):
+        if self._h:
+            _lib.load().alice_q8k_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class GpuEngine:
+    """GpuEngine (src/gpu.rs:320). ``GpuEngine()`` = ``GpuEngine::new`` (:434)."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        h = C.c_void_p()
+        check(self._lib.alice_engine_create(device, C.byref(h)))
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.alice_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- configuration (no reference counterpart) --
+    def set_stream(self, cuda_stream: int):
+        check(self._lib.alice_engine_set_stream(self._h, C.c_void_p(cuda_stream)))
+
+    def set_pdl(self, enabled: bool):
+        check(self._lib.alice_engine_set_pdl(self._h, int(enabled)))
+
+    def set_tuning(self, rows_per_set: int = 0, stages: int = 0):
+        check(self._lib.alice_engine_set_tuning(self._h, rows_per_set, stages))
+
+    # -- weights: upload_weights* (src/gpu.rs:698-798) --
+    def upload_weights_typed(self, data, rows: int, cols: int, quant: GpuQuantType) -> GpuWeightBuffer:
+        d = _np(data, np.uint8)
+        h = C.c_void_p()
+        check(self._lib.alice_upload_weights(self._h, _ptr(d), d.size, quant.value, rows, cols, C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, quant)
+
+    def upload_weights(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q4K)
+
+    def upload_weights_q5k(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q5K)
+
+    def upload_weights_q6k(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q6K)
+
+    def upload_weights_q8_0(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q8_0)
+
+    def upload_weights_q1_0(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q1_0)
+
+    def upload_weights_q2_0(self, data, rows, cols):
+        return self.upload_weights_typed(data, rows, cols, GpuQuantType.Q2_0)
+
+    def weights_from_device(self, device_ptr: int, nbytes: int, rows, cols, quant: GpuQuantType) -> GpuWeightBuffer:
+        h = C.c_void_p()
+        check(self._lib.alice_weights_from_device(self._h, C.c_void_p(device_ptr), nbytes, quant.value, rows, cols,
+                                                  C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, quant)
+
+    def upload_ternary(self, pos, neg, scales, rows, cols) -> GpuWeightBuffer:
+        """TernaryMatrix (src/gguf.rs:5198): bit planes [rows][ceil(cols/8)] + per-row scale."""
+        p, n, s = _np(pos, np.uint8), _np(neg, np.uint8), _np(scales, np.float32)
+        if p.size != rows * ((cols + 7) // 8) or n.size != p.size or s.size != rows:
+            raise AliceError(_lib.E_SHAPE, "upload_ternary: plane or scale size does not match rows x cols")
+        h = C.c_void_p()
+        check(self._lib.alice_upload_ternary(self._h, _ptr(p), _ptr(n), _ptr(s), rows, cols, C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.Ternary)
+
+    def upload_sparse_ternary(self, packed_2bit, scales, rows, cols) -> GpuWeightBuffer:
+        """SparseTernaryMatrix.packed_2bit (src/gguf.rs:5432) + per-row scale."""
+        p, s = _np(packed_2bit, np.uint8), _np(scales, np.float32)
+        if p.size < rows * ((cols + 15) // 16) * 4 or s.size != rows:
+            raise AliceError(_lib.E_SHAPE, "upload_sparse_ternary: packed or scale size does not match rows x cols")
+        h = C.c_void_p()
+        check(self._lib.alice_upload_sparse_ternary(self._h, _ptr(p), _ptr(s), rows, cols, C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.SparseTernary)
+
+    # -- f32 buffers (src/gpu.rs:667-695, 801-824) --
+    def alloc_f32(self, length: int) -> GpuBuffer:
+        h = C.c_void_p()
+        check(self._lib.alice_buf_alloc_f32(self._h, length, C.byref(h)))
+        return GpuBuffer(self, h, length)
+
+    def upload_f32(self, data) -> GpuBuffer:
+        d = _np(data, np.float32).reshape(-1)
+        h = C.c_void_p()
+        check(self._lib.alice_buf_upload_f32(self._h, _ptr(d), d.size, C.byref(h)))
+        return GpuBuffer(self, h, d.size)
+
+    def write_f32(self, buf: GpuBuffer, data):
+        d = _np(data, np.float32).reshape(-1)
+        check(self._lib.alice_buf_write_f32(self._h, buf._h, _ptr(d), d.size))
+
+    def read_f32(self, buf: GpuBuffer, length: int | None = None) -> np.ndarray:
+        n = buf.len if length is None else length
+        out = np.empty(n, np.float32)
+        check(self._lib.alice_buf_read_f32(self._h, buf._h, _ptr(out), n))
+        return out
+
+    def buf_from_device(self, device_ptr: int, length: int) -> GpuBuffer:
+        h = C.c_void_p()
+        check(self._lib.alice_buf_from_device(self._h, C.c_void_p(device_ptr), length, C.byref(h)))
+        return GpuBuffer(self, h, length)
+
+    # -- Q8_K (src/gguf.rs:1323) --
+    def alloc_q8k(self, cols: int, batch: int = 1) -> Q8KBuffer:
+        h = C.c_void_p()
+        check(self._lib.alice_q8k_alloc(self._h, cols, batch, C.byref(h)))
+        return Q8KBuffer(self, h, cols, batch)
+
+    def quantize_q8k(self, x: GpuBuffer, q: Q8KBuffer):
+        check(self._lib.alice_quantize_q8k(self._h, x._h, q._h))
+
+    def upload_q8k(self, d, qs, bsums, cols: int, batch: int = 1) -> Q8KBuffer:
+        d, qs, bs = _np(d, np.float32), _np(qs, np.int8), _np(bsums, np.int16)
+        nb = cols // 256
+        if d.size != batch * nb or qs.size != batch * nb * 256 or bs.size != batch * nb * 16:
+            raise AliceError(_lib.E_SHAPE, "upload_q8k: array sizes do not match cols x batch")
+        h = C.c_void_p()
+        check(self._lib.alice_q8k_upload(self._h, _ptr(d), _ptr(qs), _ptr(bs), cols, batch, C.byref(h)))
+        return Q8KBuffer(self, h, cols, batch)
+
+    # -- device-side ops --
+    def matvec_dev(self, w: GpuWeightBuffer, x: GpuBuffer, y: GpuBuffer, batch: int = 1):
+        check(self._lib.alice_matvec(self._h, w._h, x._h, y._h, batch))
+
+    def matvec_preq_dev(self, w: GpuWeightBuffer, q: Q8KBuffer, y: GpuBuffer):
+        check(self._lib.alice_matvec_preq(self._h, w._h, q._h, y._h))
+
+    def swiglu_dev(self, gate: GpuWeightBuffer, up: GpuWeightBuffer, x: GpuBuffer, y: GpuBuffer, batch: int = 1):
+        check(self._lib.alice_swiglu(self._h, gate._h, up._h, x._h, y._h, batch))
+
+    def swiglu_preq_dev(self, gate, up, q: Q8KBuffer, y: GpuBuffer):
+        check(self._lib.alice_swiglu_preq(self._h, gate._h, up._h, q._h, y._h))
+
+    def dequantize_dev(self, w: GpuWeightBuffer, out: GpuBuffer):
+        check(self._lib.alice_dequantize(self._h, w._h, out._h))
+
+    # -- one-shot helpers (src/gpu.rs:838, 962) --
+    def matvec(self, weights: GpuWeightBuffer, input_) -> np.ndarray:
+        """GpuEngine::matvec (src/gpu.rs:838): upload input, run, read back."""
+        x = self.upload_f32(input_)
+        y = self.alloc_f32(weights.rows)
+        self.matvec_dev(weights, x, y, 1)
+        out = self.read_f32(y)
+        self.sync()
+        return out
+
+    def dequantize(self, weights: GpuWeightBuffer) -> np.ndarray:
+        out = self.alloc_f32(weights.rows * weights.cols)
+        self.dequantize_dev(weights, out)
+        r = self.read_f32(out)
+        self.sync()
+        return r
+
+    def begin_pass(self) -> "GpuPass":
+        return GpuPass(self)
+
+    def sync(self):
+        check(self._lib.alice_sync(self._h))
+
+
+class GpuPass:
+    """GpuPass (src/gpu.rs:418): ops are queued in order and run by ``execute``. On CUDA the
+    engine's stream is already an in-order queue, so encoding an op launches it and ``execute``
+    is the blocking wait (src/gpu.rs:2087)."""
+
+    def __init__(self, engine: GpuEngine):
+        self.engine = engine
+
+    def _mv(self, weights, input_, output, quant, batch=1):
+        if quant is not None and weights.quant != quant:
+            raise AliceError(_lib.E_INVALID, f"weights are {weights.quant.name}, op wants {quant.name}")
+        self.engine.matvec_dev(weights, input_, output, batch)
+
+    def matvec_q4k(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q4K)
+
+    def matvec_q5k(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q5K)
+
+    def matvec_q6k(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q6K)
+
+    def matvec_q8_0(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q8_0)
+
+    def matvec_q1_0(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q1_0)
+
+    # the row4 / row8 shader variants differ only in tiling (src/gpu.rs:1161-1344); one kernel serves all
+    matvec_q1_0_row4 = matvec_q1_0
+
+    def matvec_q1_0_batch4(self, weights, input_, output):
+        self._mv(weights, input_, output, GpuQuantType.Q1_0, 4)
+
+    matvec_q1_0_row4_batch4 = matvec_q1_0_batch4
+    matvec_q1_0_row8_batch4 = matvec_q1_0_batch4
+
+    def matvec_auto(self, weights, input_, output, batch: int = 1):
+        """src/gpu.rs:1947: dispatch on the weight buffer's own type."""
+        self._mv(weights, input_, output, None, batch)
+
+    def swiglu(self, gate, up, input_, output, batch: int = 1):
+        self.engine.swiglu_dev(gate, up, input_, output, batch)
+
+    def execute(self):
+        self.engine.sync()
+
+    def execute_and_read(self, buf: GpuBuffer) -> np.ndarray:
+        out = self.engine.read_f32(buf)
+        self.engine.sync()
+        return out

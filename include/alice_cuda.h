@@ -1,0 +1,143 @@
+/* alice_cuda.h -- C ABI of the B200 (sm_100a) quantized-matvec decode path for ALICE-LLM.
+ *
+ * This library replaces, for the decode hot path only, the wgpu backend of ALICE-LLM
+ * (src/gpu.rs) and the CPU quantized matvec of src/gguf.rs. Weights are uploaded as the raw
+ * GGUF blocks and stay on the device; every entry point below names the reference interface
+ * it stands in for (file:line in ext-sakamoro/ALICE-LLM v1.6.0).
+ *
+ * Conventions
+ *   - Every function returns an int32_t status: ALICE_OK (0) or a negative ALICE_E_* code.
+ *     The reference panics on shape / format violations (src/gguf.rs:4243, src/gpu.rs:721-734);
+ *     a binding turns a non-zero status into its language's panic. alice_last_error() gives
+ *     the message of the calling thread's last failure.
+ *   - No CPU fallback exists: without a CUDA device alice_engine_create fails.
+ *   - All device work of an engine is queued on one CUDA stream, in call order (the reference
+ *     has a single in-order wgpu queue). Calls on one engine are not thread-safe, like the
+ *     reference's Mutex<ModelBackend> usage (src/bin/server.rs:359).
+ *   - Batch layout: inputs x[k*cols + c], outputs y[k*rows + r] (src/gpu.rs:1141-1143).
+ *   - Kernels that wait on a barrier give up after about one second, record an error in the
+ *     engine's device status word and return; alice_sync reports it as ALICE_E_KERNEL.
+ */
+#ifndef ALICE_CUDA_H
+#define ALICE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ALICE_OK 0
+#define ALICE_E_INVALID (-1)     /* null pointer, misaligned device pointer, bad handle */
+#define ALICE_E_UNSUPPORTED (-2) /* quantization type outside the path */
+#define ALICE_E_SHAPE (-3)       /* rows/cols/bytes do not fit the format or each other */
+#define ALICE_E_CUDA (-4)        /* a CUDA runtime call failed */
+#define ALICE_E_KERNEL (-5)      /* a kernel recorded an error in the status word */
+#define ALICE_E_NOMEM (-6)       /* device allocation failed */
+
+/* GGML type ids of the block formats on the path (GgmlType::from_u32, src/gguf.rs:101-122). */
+#define ALICE_TYPE_Q8_0 8u
+#define ALICE_TYPE_Q4_K 12u
+#define ALICE_TYPE_Q5_K 13u
+#define ALICE_TYPE_Q6_K 14u
+#define ALICE_TYPE_Q1_0 41u
+#define ALICE_TYPE_Q2_0 42u
+
+typedef struct alice_engine alice_engine;   /* GpuEngine, src/gpu.rs:320 */
+typedef struct alice_weights alice_weights; /* GpuWeightBuffer, src/gpu.rs:302 */
+typedef struct alice_buf alice_buf;         /* GpuBuffer (f32 storage), src/gpu.rs:277 */
+typedef struct alice_q8k alice_q8k;         /* Vec<BlockQ8K> on the device, src/gguf.rs:1306 */
+
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* alice_last_error(void);
+
+/* Block geometry, GgmlType::block_bytes / elements_per_block (src/gguf.rs:126, :161). 0 = unknown type. */
+uint32_t alice_type_block_bytes(uint32_t ggml_type);
+uint32_t alice_type_block_elems(uint32_t ggml_type);
+
+/* ---- engine ------------------------------------------------------------------------------ */
+/* GpuEngine::new (src/gpu.rs:434). Selects `device`, creates the engine's stream. */
+int32_t alice_engine_create(int32_t device, alice_engine** out);
+int32_t alice_engine_destroy(alice_engine* e);
+/* Queue the engine's work on a caller-owned CUDA stream (cudaStream_t passed as void*), e.g. the
+ * current stream of a framework that owns the device buffers. No reference counterpart. */
+int32_t alice_engine_set_stream(alice_engine* e, void* cuda_stream);
+/* GpuEngine::sync (src/gpu.rs:962): block until queued work is done; ALICE_E_KERNEL if a kernel
+ * recorded an error (the status word is cleared). */
+int32_t alice_sync(alice_engine* e);
+/* Launch dependent kernels with programmatic stream serialization (on by default). */
+int32_t alice_engine_set_pdl(alice_engine* e, int32_t enabled);
+/* Tuning overrides for the streaming matvec: rows per warp set per stage and ring depth; 0 = automatic. */
+int32_t alice_engine_set_tuning(alice_engine* e, int32_t rows_per_set, int32_t stages);
+
+/* ---- weights ----------------------------------------------------------------------------- */
+/* GpuEngine::upload_weights / _q5k / _q6k / _q8_0 / _q1_0 (src/gpu.rs:698-798): raw GGUF blocks,
+ * row-major, rows * (cols / block_elems) * block_bytes bytes, copied verbatim (Q8_0 is NOT
+ * re-padded to 36 bytes as the wgpu backend does). cols must be a whole number of blocks. */
+int32_t alice_upload_weights(alice_engine* e, const uint8_t* data, size_t nbytes, uint32_t ggml_type,
+                             uint32_t rows, uint32_t cols, alice_weights** out);
+/* Same, for blocks already resident on the device (16-byte aligned, not copied, not owned). */
+int32_t alice_weights_from_device(alice_engine* e, const void* device_ptr, size_t nbytes, uint32_t ggml_type,
+                                  uint32_t rows, uint32_t cols, alice_weights** out);
+/* TernaryMatrix (src/gguf.rs:5190-5202): pos/neg bit planes flattened to [rows][ceil(cols/8)]
+ * (bit i%8 of byte i/8), one f32 scale per row. */
+int32_t alice_upload_ternary(alice_engine* e, const uint8_t* pos, const uint8_t* neg, const float* scales,
+                             uint32_t rows, uint32_t cols, alice_weights** out);
+/* SparseTernaryMatrix (src/gguf.rs:5425-5445): packed_2bit rows, 4 bytes per 16 columns
+ * (00 = 0, 01 = +1, 11 = -1), [rows][ceil(cols/16)*4] bytes, one f32 scale per row. */
+int32_t alice_upload_sparse_ternary(alice_engine* e, const uint8_t* packed_2bit, const float* scales,
+                                    uint32_t rows, uint32_t cols, alice_weights** out);
+int32_t alice_weights_free(alice_weights* w);
+
+/* ---- f32 buffers ------------------------------------------------------------------------- */
+/* GpuEngine::alloc_f32 / upload_f32 / write_f32 / read_f32 (src/gpu.rs:667-695, 801-824). */
+int32_t alice_buf_alloc_f32(alice_engine* e, size_t len, alice_buf** out);
+int32_t alice_buf_upload_f32(alice_engine* e, const float* data, size_t len, alice_buf** out);
+int32_t alice_buf_write_f32(alice_engine* e, alice_buf* b, const float* data, size_t len);
+int32_t alice_buf_read_f32(alice_engine* e, const alice_buf* b, float* out, size_t len); /* blocks */
+/* Wrap `len` floats of caller-owned device memory (not copied, not owned). */
+int32_t alice_buf_from_device(alice_engine* e, void* device_ptr, size_t len, alice_buf** out);
+int32_t alice_buf_free(alice_buf* b);
+
+/* ---- Q8_K activations -------------------------------------------------------------------- */
+/* quantize_row_q8_k (src/gguf.rs:1323): `batch` vectors of `cols` floats (cols % 256 == 0). */
+int32_t alice_q8k_alloc(alice_engine* e, uint32_t cols, uint32_t batch, alice_q8k** out);
+int32_t alice_quantize_q8k(alice_engine* e, const alice_buf* x, alice_q8k* q);
+/* Copy to host as structure-of-arrays: d[batch*nb], qs[batch*nb*256], bsums[batch*nb*16]. Blocks. */
+int32_t alice_q8k_read(alice_engine* e, const alice_q8k* q, float* d, int8_t* qs, int16_t* bsums);
+/* Upload host BlockQ8K data given as the same three arrays (for the *_matvec_preq signatures). */
+int32_t alice_q8k_upload(alice_engine* e, const float* d, const int8_t* qs, const int16_t* bsums,
+                         uint32_t cols, uint32_t batch, alice_q8k** out);
+int32_t alice_q8k_free(alice_q8k* q);
+
+/* ---- the hot path ------------------------------------------------------------------------ */
+/* quantized_matvec / q4k_matvec / q5k_matvec / q6k_matvec / q8_0_matvec / ternary_matvec /
+ * sparse_ternary_matvec (src/gguf.rs:4214, 3600, 3502, 4077, 3811, 5303, 5808) and
+ * GpuPass::matvec_* / matvec_auto (src/gpu.rs:1022-1392, 1795-1960): y = W x for `batch`
+ * input vectors (1..8). K-quant weights quantize x to Q8_K first, as the CPU path does. */
+int32_t alice_matvec(alice_engine* e, const alice_weights* w, const alice_buf* x, alice_buf* y, uint32_t batch);
+/* quantized_matvec_preq / q4k_matvec_preq / ... (src/gguf.rs:4574, 3607, 3509, 4084). For Q1_0 /
+ * Q2_0 weights the Q8_K blocks are turned back into f32 first (src/gguf.rs:4593-4605). */
+int32_t alice_matvec_preq(alice_engine* e, const alice_weights* w, const alice_q8k* q, alice_buf* y);
+/* Fused SwiGLU gate/up, swiglu_fused_q4k / _q1_0 dispatch (src/gpu.rs:4711-4721, 5995) and the
+ * CPU model's gate/up/silu sequence (src/llama3.rs:14519-14534): y = silu(gate x) * (up x). */
+int32_t alice_swiglu(alice_engine* e, const alice_weights* gate, const alice_weights* up, const alice_buf* x,
+                     alice_buf* y, uint32_t batch);
+int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alice_weights* up, const alice_q8k* q,
+                          alice_buf* y);
+/* dequantize_weight_row / GgufFile::tensor_to_f32 (src/gguf.rs:6168, 574): out[r*cols + c], bit-exact. */
+int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out);
+
+/* ---- host-pointer convenience (the gguf.rs-level signatures) ------------------------------- */
+/* quantized_matvec(input, data, qtype, rows, cols, output) (src/gguf.rs:4214): uploads, runs on
+ * device 0 through a process-wide engine, reads back. */
+int32_t alice_matvec_host(uint32_t ggml_type, const uint8_t* data, size_t nbytes, uint32_t rows, uint32_t cols,
+                          const float* x, float* y);
+/* dequantize_weight_row(data, qtype, out) (src/gguf.rs:6168) for n_out = whole blocks of one row. */
+int32_t alice_dequantize_host(uint32_t ggml_type, const uint8_t* data, size_t nbytes, float* out, size_t n_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALICE_CUDA_H */

@@ -222,3 +222,38 @@ def sparsify_row(pos, neg, dense_scale: float, w, n_keep: int):
 
 def silu(x: float) -> np.float32:
     return np.float32(lib().orc_silu(C.c_float(x)))
+
+
+# ── threaded CPU baseline (oracle/cpu_baseline.cpp) ─────────────────────────
+_base = None
+
+
+def baseline():
+    global _base
+    if _base is None:
+        build()
+        _base = C.CDLL(_BASE_LIB)
+    return _base
+
+
+def hw_threads() -> int:
+    return int(baseline().base_hw_threads())
+
+
+def base_matvec(qtype: int, x, data, rows: int, cols: int, nthreads: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    d = _u8(data)
+    y = np.empty(rows, dtype=np.float32)
+    baseline().base_matvec(C.c_uint32(qtype), _p(x, _f32p), _p(d, _u8p), C.c_size_t(d.size), C.c_size_t(rows),
+                           C.c_size_t(cols), _p(y, _f32p), C.c_int(nthreads))
+    return y
+
+
+def base_ffn(gu_type: int, gate, up, down_type: int, down, hidden: int, ffn: int, x, nthreads: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    g, u, dn = _u8(gate), _u8(up), _u8(down)
+    y = np.empty(hidden, dtype=np.float32)
+    baseline().base_ffn(C.c_uint32(gu_type), _p(g, _u8p), _p(u, _u8p), C.c_size_t(g.size), C.c_uint32(down_type),
+                        _p(dn, _u8p), C.c_size_t(dn.size), C.c_size_t(hidden), C.c_size_t(ffn), _p(x, _f32p),
+                        _p(y, _f32p), C.c_int(nthreads))
+    return y

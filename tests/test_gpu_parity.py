@@ -1,0 +1,204 @@
+"""GPU parity: every CUDA entry point against the CPU oracle on the same seeded inputs.
+
+Gates (the reference's own convention, src/gpu.rs:7133, src/gguf.rs:8038):
+  dequantized weights  bit-exact
+  Q8_K activations     bit-exact
+  matvec / SwiGLU      max_i |y_i - ref_i| / max(|ref_i|, 1) <= 1e-3  and  rel-L2 <= 1e-3
+"""
+import numpy as np
+import pytest
+
+from alice_llm_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+Q8_0, Q4_K, Q5_K, Q6_K, Q1_0, Q2_0 = synth.Q8_0, synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.Q1_0, synth.Q2_0
+TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from alice_llm_b200.gpu import GpuEngine
+    e = GpuEngine(0)
+    yield e
+    e.close()
+
+
+def bits(a):
+    return np.asarray(a, np.float32).view(np.uint32)
+
+
+def assert_close(got, ref, what=""):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    err = np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)
+    l2 = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)
+    assert np.isfinite(got).all(), what
+    assert err.max() <= TOL and l2 <= TOL, f"{what}: max err {err.max():.3e} at {err.argmax()}, rel-L2 {l2:.3e}"
+
+
+def quant(qtype):
+    from alice_llm_b200.gpu import GpuQuantType
+    return GpuQuantType(qtype)
+
+
+SHAPES = {
+    Q4_K: [(1, 256), (3, 512), (70, 4096), (129, 1024), (33, 14336), (64, 16384)],
+    Q5_K: [(1, 256), (5, 768), (70, 4096), (16, 14336)],
+    Q6_K: [(1, 256), (3, 512), (7, 768), (70, 4096), (40, 14336)],
+    Q8_0: [(2, 32), (3, 96), (70, 4096), (50, 5120), (9, 14336)],
+    Q1_0: [(4, 256), (3, 128), (70, 5120), (20, 25600)],
+    Q2_0: [(4, 256), (70, 5120), (10, 16384)],
+}
+
+
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K, Q8_0, Q1_0, Q2_0])
+def test_dequantize_bit_exact(eng, oracle, qtype):
+    rng = np.random.default_rng(100 + qtype)
+    for rows, cols in SHAPES[qtype][:4]:
+        data = synth.make_weights(qtype, rng, rows, cols)
+        w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
+        got = eng.dequantize(w)
+        ref = oracle.dequantize(qtype, data)
+        assert np.array_equal(bits(got), bits(ref)), (synth.TYPE_NAMES[qtype], rows, cols)
+
+
+def test_q8k_quantizer_bit_exact(eng, oracle):
+    rng = np.random.default_rng(7)
+    for cols, batch in [(256, 1), (4096, 1), (14336, 1), (4096, 4), (5120, 8)]:
+        x = synth.make_x(rng, cols, batch)
+        x[:256] = 0.0
+        if cols > 512:
+            x[300], x[301] = 5.5, -5.5
+            x[700] = -9.25
+        q = eng.alloc_q8k(cols, batch)
+        eng.quantize_q8k(eng.upload_f32(x), q)
+        d, qs, bs = q.read()
+        eng.sync()
+        for k in range(batch):
+            rd, rqs, rbs = oracle.quantize_row_q8_k(x[k * cols:(k + 1) * cols])
+            assert np.array_equal(bits(d[k]), bits(rd))
+            assert np.array_equal(qs[k], rqs) and np.array_equal(bs[k], rbs)
+
+
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K, Q8_0, Q1_0, Q2_0])
+def test_matvec_matches_oracle(eng, oracle, qtype):
+    rng = np.random.default_rng(200 + qtype)
+    for rows, cols in SHAPES[qtype]:
+        data = synth.make_weights(qtype, rng, rows, cols)
+        x = synth.make_x(rng, cols)
+        w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
+        got = eng.matvec(w, x)
+        ref = oracle.matvec(qtype, x, data, rows, cols)
+        assert_close(got, ref, f"{synth.TYPE_NAMES[qtype]} {rows}x{cols}")
+
+
+@pytest.mark.parametrize("qtype", [Q4_K, Q6_K, Q1_0])
+def test_matvec_preq_matches_oracle(eng, oracle, qtype):
+    rng = np.random.default_rng(300 + qtype)
+    rows, cols = 37, 5120 if qtype == Q1_0 else 4096
+    cols = cols // 256 * 256
+    data = synth.make_weights(qtype, rng, rows, cols)
+    x = synth.make_x(rng, cols)
+    q8 = oracle.quantize_row_q8_k(x)
+    w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
+    q = eng.upload_q8k(*q8, cols, 1)
+    y = eng.alloc_f32(rows)
+    eng.matvec_preq_dev(w, q, y)
+    got = eng.read_f32(y)
+    eng.sync()
+    assert_close(got, oracle.matvec_preq(qtype, data, rows, cols, q8), synth.TYPE_NAMES[qtype])
+
+
+@pytest.mark.parametrize("qtype,rows,cols", [(Q4_K, 300, 4096), (Q4_K, 17, 512), (Q1_0, 200, 5120), (Q6_K, 33, 1024),
+                                             (Q8_0, 40, 1024)])
+def test_swiglu_matches_oracle(eng, oracle, qtype, rows, cols):
+    rng = np.random.default_rng(400 + qtype)
+    gate = synth.make_weights(qtype, rng, rows, cols)
+    up = synth.make_weights(qtype, rng, rows, cols)
+    x = synth.make_x(rng, cols)
+    g = eng.upload_weights_typed(gate, rows, cols, quant(qtype))
+    u = eng.upload_weights_typed(up, rows, cols, quant(qtype))
+    y = eng.alloc_f32(rows)
+    eng.swiglu_dev(g, u, eng.upload_f32(x), y, 1)
+    got = eng.read_f32(y)
+    eng.sync()
+    assert_close(got, oracle.swiglu(qtype, x, gate, up, rows, cols), synth.TYPE_NAMES[qtype])
+
+
+@pytest.mark.parametrize("qtype,batch", [(Q4_K, 4), (Q6_K, 4), (Q1_0, 8), (Q8_0, 2)])
+def test_batched_matvec_matches_oracle(eng, oracle, qtype, batch):
+    rng = np.random.default_rng(500 + qtype)
+    rows, cols = 130, 5120 if qtype in (Q1_0, Q8_0) else 4096
+    data = synth.make_weights(qtype, rng, rows, cols)
+    x = synth.make_x(rng, cols, batch)
+    w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
+    y = eng.alloc_f32(rows * batch)
+    eng.matvec_dev(w, eng.upload_f32(x), y, batch)
+    got = eng.read_f32(y).reshape(batch, rows)
+    eng.sync()
+    for k in range(batch):   # layout x[k*cols + c] -> y[k*rows + r] (src/gpu.rs:1141-1143)
+        assert_close(got[k], oracle.matvec(qtype, x[k * cols:(k + 1) * cols], data, rows, cols), f"batch {k}")
+
+
+@pytest.mark.parametrize("rows,cols", [(5, 128), (3, 100), (70, 8192), (12, 28672), (9, 1000)])
+def test_ternary_matvec_matches_oracle(eng, oracle, rows, cols):
+    rng = np.random.default_rng(600 + cols)
+    pos, neg, sc = synth.make_ternary(rng, rows, cols)
+    x = synth.make_x(rng, cols)
+    w = eng.upload_ternary(pos, neg, sc, rows, cols)
+    assert_close(eng.matvec(w, x), oracle.ternary_matvec(pos, neg, sc, rows, cols, x), f"ternary {rows}x{cols}")
+    # bit-exact dequantization: scale * {-1, 0, +1}
+    p = np.unpackbits(pos, axis=1, bitorder="little")[:, :cols].astype(np.float32)
+    n = np.unpackbits(neg, axis=1, bitorder="little")[:, :cols].astype(np.float32)
+    assert np.array_equal(bits(eng.dequantize(w)), bits((sc[:, None] * (p - n)).reshape(-1)))
+
+
+@pytest.mark.parametrize("rows,cols", [(5, 128), (4, 48), (70, 8192), (12, 28672)])
+def test_sparse_ternary_matvec_matches_oracle(eng, oracle, rows, cols):
+    rng = np.random.default_rng(700 + cols)
+    pos, neg, sc = synth.make_ternary(rng, rows, cols)
+    active, sign = synth.ternary_to_sparse(pos, neg, cols)
+    packed = oracle.sparse_pack_2bit(active, sign, rows, cols)
+    x = synth.make_x(rng, cols)
+    w = eng.upload_sparse_ternary(packed, sc, rows, cols)
+    assert_close(eng.matvec(w, x), oracle.sparse_ternary_matvec(active, sign, sc, rows, cols, x), f"sparse {rows}x{cols}")
+
+
+def test_ternary_swiglu_matches_oracle(eng, oracle):
+    rng = np.random.default_rng(8)
+    rows, cols = 150, 8192
+    g = synth.make_ternary(rng, rows, cols)
+    u = synth.make_ternary(rng, rows, cols)
+    x = synth.make_x(rng, cols)
+    y = eng.alloc_f32(rows)
+    eng.swiglu_dev(eng.upload_ternary(*g, rows, cols), eng.upload_ternary(*u, rows, cols), eng.upload_f32(x), y, 1)
+    got = eng.read_f32(y)
+    eng.sync()
+    assert_close(got, oracle.ternary_swiglu(g, u, rows, cols, x), "ternary swiglu")
+
+
+def test_reference_known_answers_on_gpu(eng):
+    """The reference's own known-answer cases (src/gguf.rs:7257-7283, 7419-7445) through the C ABI."""
+    from alice_llm_b200 import gguf
+    data = np.zeros(68, dtype=np.uint8)
+    data[0:2] = [0x00, 0x3C]; data[2] = 1
+    data[34:36] = [0x00, 0x3C]; data[37] = 1
+    x = np.zeros(32, np.float32); x[0], x[1] = 3.0, 7.0
+    y = gguf.q8_0_matvec(x, data, 2, 32)
+    assert abs(y[0] - 3.0) < 1e-4 and abs(y[1] - 7.0) < 1e-4
+    d2 = np.zeros(34, dtype=np.uint8); d2[0:2] = [0x00, 0x3C]; d2[2:] = 0x46
+    y = gguf.quantized_matvec(np.arange(1, 129, dtype=np.float32), d2, gguf.GgmlType.Q2_0, 1, 128)
+    assert abs(y[0] + 64.0) < 1e-3
+
+
+def test_errors_instead_of_panics(eng):
+    from alice_llm_b200.gpu import AliceError, GpuQuantType
+    with pytest.raises(AliceError):   # cols not a whole number of blocks
+        eng.upload_weights_typed(np.zeros(144, np.uint8), 1, 200, GpuQuantType.Q4K)
+    with pytest.raises(AliceError):   # byte count does not match
+        eng.upload_weights_typed(np.zeros(100, np.uint8), 1, 256, GpuQuantType.Q4K)
+    w = eng.upload_weights_typed(np.zeros(144, np.uint8), 1, 256, GpuQuantType.Q4K)
+    with pytest.raises(AliceError):   # input too short
+        eng.matvec_dev(w, eng.alloc_f32(100), eng.alloc_f32(1), 1)
+    with pytest.raises(AliceError):   # batch outside 1..8
+        eng.matvec_dev(w, eng.alloc_f32(256 * 9), eng.alloc_f32(9), 9)
