@@ -442,15 +442,8 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
     if (x->len < (size_t)batch * d.cols) return fail(ALICE_E_SHAPE, "%s: input has %zu floats, need %zu", who, x->len, (size_t)batch * d.cols);
     if (y->len < (size_t)batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output has %zu floats, need %zu", who, y->len, (size_t)batch * d.rows);
     CU(cudaSetDevice(e->device));
-    if (format_uses_q8k(d.fmt)) {
-        // q4k_matvec = quantize_row_q8_k + q4k_matvec_preq (src/gguf.rs:3600-3603)
-        alice_q8k tmp{e, nullptr, d.cols, batch, d.cols / 256, Q8KLayout::make(d.cols / 256, batch)};
-        int rc = ensure_scratch(e, tmp.lay.total);
-        if (rc) return rc;
-        tmp.base = e->scratch;
-        launch_quantize_q8k(x->p, d.cols, batch, tmp.base, e->stream);
-        return run_gemv(e, w0, w1, &tmp, nullptr, y->p, batch, who);
-    }
+    // K-quant kernels quantize x to Q8_K in their prologue: q4k_matvec = quantize_row_q8_k +
+    // q4k_matvec_preq (src/gguf.rs:3600-3603) in one launch.
     return run_gemv(e, w0, w1, nullptr, x->p, y->p, batch, who);
 }
 

@@ -29,14 +29,16 @@ struct ActGroup64 {
     float d8;              // Q8_K block scale
 };
 
-__device__ __forceinline__ void load_act_group64(ActGroup64& r, const StreamArgs& a, uint32_t u, bool valid) {
+// Loads from a Q8KView that may live in global memory (pre-quantized input) or in shared memory
+// (input quantized by the kernel's own prologue): plain generic loads serve both.
+__device__ __forceinline__ void load_act_group64(ActGroup64& r, const Q8KView& v, uint32_t u, bool valid) {
     if (!valid) { r = ActGroup64{}; return; }
-    const int8_t* q = a.q8.qs + (size_t)u * 64;
-    r.p0 = ldg128(q); r.p1 = ldg128(q + 16); r.p2 = ldg128(q + 32); r.p3 = ldg128(q + 48);
-    const uint2 b = ldg64(a.q8.bsums + (size_t)u * 4);
+    const uint4* q = reinterpret_cast<const uint4*>(v.qs + (size_t)u * 64);
+    r.p0 = q[0]; r.p1 = q[1]; r.p2 = q[2]; r.p3 = q[3];
+    const uint2 b = *reinterpret_cast<const uint2*>(v.bsums + (size_t)u * 4);
     r.bs0 = (int)(short)(b.x & 0xffff) + (int)(short)(b.x >> 16);
     r.bs1 = (int)(short)(b.y & 0xffff) + (int)(short)(b.y >> 16);
-    r.d8 = __ldg(a.q8.d + (u >> 2));
+    r.d8 = v.d[u >> 2];
 }
 
 // ── Q4_K: 144-byte block = d f16, dmin f16, 12 B scales, 128 B nibbles (src/gguf.rs:903-939).
@@ -45,7 +47,8 @@ __device__ __forceinline__ void load_act_group64(ActGroup64& r, const StreamArgs
 struct FmtQ4K {
     static constexpr uint32_t BLOCK_BYTES = 144, UNITS_PER_BLOCK = 4;
     using Act = ActGroup64;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act_group64(r, a, u, valid); }
+    static constexpr bool USES_Q8K = true;
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& v, uint32_t u, bool valid) { load_act_group64(r, v, u, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t g = u & 3u;
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
@@ -77,7 +80,8 @@ struct FmtQ4K {
 struct FmtQ5K {
     static constexpr uint32_t BLOCK_BYTES = 176, UNITS_PER_BLOCK = 4;
     using Act = ActGroup64;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act_group64(r, a, u, valid); }
+    static constexpr bool USES_Q8K = true;
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& v, uint32_t u, bool valid) { load_act_group64(r, v, u, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t g = u & 3u;
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
@@ -117,16 +121,17 @@ struct FmtQ6K {
         int s[4];    // their sums
         float d8;
     };
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    static constexpr bool USES_Q8K = true;
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& v, uint32_t u, bool valid) {
         if (!valid) { r = Act{}; return; }
         const uint32_t b = u >> 3, n = (u >> 2) & 1u, l0 = (u & 3u) * 8u;
-        const int8_t* q = a.q8.qs + (size_t)b * 256 + n * 128 + l0;
+        const int8_t* q = v.qs + (size_t)b * 256 + n * 128 + l0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            r.p[j] = ldg64(q + 32 * j);
+            r.p[j] = *reinterpret_cast<const uint2*>(q + 32 * j);
             r.s[j] = dp4a_ss(0x01010101u, r.p[j].x, dp4a_ss(0x01010101u, r.p[j].y, 0));
         }
-        r.d8 = __ldg(a.q8.d + b);
+        r.d8 = v.d[b];
     }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t n = (u >> 2) & 1u, l0 = (u & 3u) * 8u;
@@ -172,7 +177,8 @@ struct FmtQ6K {
 struct FmtQ8_0 {
     static constexpr uint32_t BLOCK_BYTES = 34, UNITS_PER_BLOCK = 2;
     struct Act { float x[16]; };
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    static constexpr bool USES_Q8K = false;
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, uint32_t u, bool valid) {
 #pragma unroll
         for (int i = 0; i < 16; i++) r.x[i] = 0.0f;
         if (!valid) return;
@@ -232,7 +238,8 @@ __device__ __forceinline__ void load_act32(Act32& r, const float* x, uint32_t u,
 struct FmtQ1_0 {
     static constexpr uint32_t BLOCK_BYTES = 18, UNITS_PER_BLOCK = 4;
     using Act = Act32;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    static constexpr bool USES_Q8K = false;
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
         const uint32_t bits = lds32_u2(blk + 2 + (u & 3u) * 4);
@@ -246,7 +253,8 @@ struct FmtQ1_0 {
 struct FmtQ2_0 {
     static constexpr uint32_t BLOCK_BYTES = 34, UNITS_PER_BLOCK = 8;
     struct Act { float x[16]; float sum; };
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    static constexpr bool USES_Q8K = false;
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, uint32_t u, bool valid) {
         r.sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
@@ -271,7 +279,8 @@ struct FmtQ2_0 {
 struct FmtTernary {
     static constexpr uint32_t UNIT_COLS = 32;
     using Act = Act32;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    static constexpr bool USES_Q8K = false;
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t pm = lds32(rb + 4 * u), nm = lds32(rb + (a.row_bytes >> 1) + 4 * u);
         return masked_sum32(pm, x.x) - masked_sum32(nm, x.x);
@@ -285,7 +294,8 @@ struct FmtTernary {
 struct FmtSparseTernary {
     static constexpr uint32_t UNIT_COLS = 32;
     using Act = Act32;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    static constexpr bool USES_Q8K = false;
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
     __device__ static float half(uint32_t w, const float* x) {
         const uint32_t act = w & 0x55555555u, neg = (w >> 1) & act;
         float s = 0.0f;

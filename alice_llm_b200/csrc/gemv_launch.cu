@@ -1,6 +1,7 @@
 // Planning and launch of the streaming matvec kernels (one template instance per format,
 // activation positions per lane KL in {1,2,4}, plain / fused SwiGLU).
 #include <algorithm>
+#include <cstdlib>
 
 #include "../../include/alice_cuda.h"
 #include "formats.cuh"
@@ -33,8 +34,10 @@ uint32_t ggml_row_bytes(WeightFormat f, uint32_t cols) {
 
 namespace {
 
-constexpr uint32_t SMEM_BUDGET = 200 * 1024;   // of the 227 KB a CTA may opt in to
-constexpr uint32_t STAGE_TARGET = 16 * 1024;   // preferred bytes per matrix per stage
+// Shared memory per CTA: two CTAs share an SM when a lane holds at most two activation positions
+// (KL <= 2), else one CTA has the SM to itself (of the 227 KB a CTA may opt in to).
+constexpr uint32_t SMEM_BUDGET_2 = 100 * 1024, SMEM_BUDGET_1 = 200 * 1024;
+constexpr uint32_t DEFAULT_STAGES = 2;         // measured: a deeper ring buys nothing, larger stages do
 constexpr uint32_t HDR_BYTES = (sizeof(StreamSmem) + 127) & ~127u;
 
 uint32_t units_per_row(WeightFormat f, uint32_t cols) {
@@ -54,7 +57,8 @@ int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg&
     static bool attr_set = false;  // per template instance
     auto kern = stream_gemv_kernel<F, KL, SW>;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
             return ALICE_E_CUDA;
         attr_set = true;
     }
@@ -93,7 +97,8 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
         return ALICE_E_SHAPE;
     if (((uintptr_t)w0.data & 15) || (sw && ((uintptr_t)w1->data & 15))) return ALICE_E_INVALID;
     if (format_uses_q8k(w0.fmt)) {
-        if (!q8 || q8->nb * 256u != w0.cols) return ALICE_E_SHAPE;
+        // K-quants take either pre-quantized Q8_K blocks or the f32 vector (quantized in the prologue)
+        if (q8 ? q8->nb * 256u != w0.cols : x == nullptr) return q8 ? ALICE_E_SHAPE : ALICE_E_INVALID;
     } else if (!x) {
         return ALICE_E_INVALID;
     }
@@ -116,26 +121,33 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
     a.P = P; a.slots = NCW / P;
 
     const uint32_t nmat = sw ? 2 : 1;
-    const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1);
-    // rows per warp set per stage: fill ~STAGE_TARGET bytes but keep >= 8 stages of work per CTA
-    uint32_t rps_bytes = std::max<uint32_t>(1, STAGE_TARGET / std::max<uint32_t>(1, a.slots * a.row_bytes));
-    uint32_t rps_bal = std::max<uint32_t>(1, a.rows / (a.slots * ctas * 8));
+    static const char* env_cps = getenv("ALICE_CTAS_PER_SM");  // experiment knob
+    const uint32_t per_sm = env_cps ? (uint32_t)atoi(env_cps) : (kl <= 2 ? 2 : 1);
+    // in-kernel Q8_K area: qs[cols] + d[nb] f32 + bsums[nb][16] i16
+    const uint32_t q8_bytes = (format_uses_q8k(w0.fmt) && !q8) ? ((w0.cols / 256u) * 292u + 127u) & ~127u : 0u;
+    const uint32_t budget = (kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1) - HDR_BYTES - q8_bytes;
+    const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
+    uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
+    // rows per warp set per stage: as many as the ring allows (per-stage costs are amortised over
+    // them) while every CTA still gets at least ~4 stages of work
+    uint32_t rps_bytes = std::max<uint32_t>(1, (budget / nst - 256) / std::max<uint32_t>(1, a.slots * a.row_bytes * nmat));
+    uint32_t rps_bal = std::max<uint32_t>(1, a.rows / (a.slots * ctas * 4));
     uint32_t rps = std::min<uint32_t>(std::min(rps_bytes, rps_bal), MAX_RPS);
     if (cfg.force_rps > 0) rps = std::min<uint32_t>(cfg.force_rps, MAX_RPS);
-    uint32_t cap, stage, nst;
+    uint32_t cap, stage;
     for (;;) {
         cap = (a.slots * rps * a.row_bytes + 48 + 127) & ~127u;
         stage = cap * nmat;
-        nst = std::min<uint32_t>(MAX_STAGES, (SMEM_BUDGET - HDR_BYTES) / stage);
-        if (nst >= 2 || rps == 1) break;
-        rps = rps / 2;
+        if (stage * nst <= budget) break;
+        if (rps > 1) { rps--; continue; }
+        if (nst > 2) { nst--; continue; }
+        return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
     }
-    if (nst < 2) return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
-    if (cfg.force_stages >= 2) nst = std::min<uint32_t>(nst, cfg.force_stages);
     a.rps = rps; a.cap = cap; a.nstages = nst;
     a.groups = (a.rows + a.slots * rps - 1) / (a.slots * rps);
     const uint32_t grid = std::min(ctas, a.groups);
-    const size_t smem = HDR_BYTES + (size_t)nst * stage;
+    a.q8_off = HDR_BYTES + nst * stage;
+    const size_t smem = HDR_BYTES + (size_t)nst * stage + q8_bytes;
 
     switch (w0.fmt) {
         case WF_Q4_K: return launch_fmt<FmtQ4K>(a, kl, sw, grid, smem, cfg);

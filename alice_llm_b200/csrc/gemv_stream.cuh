@@ -19,7 +19,7 @@ namespace alice {
 
 constexpr int NCW = 8;                        // consumer warps per CTA
 constexpr int STREAM_THREADS = (NCW + 1) * 32;  // + one producer warp
-constexpr int MAX_STAGES = 16;
+constexpr int MAX_STAGES = 4;
 constexpr int MAX_RPS = 16;                   // rows per warp set per stage (must stay <= 32)
 
 struct StreamArgs {
@@ -41,6 +41,7 @@ struct StreamArgs {
     uint32_t groups;     // ceil(rows / (slots * rps)) = number of stage-sized row groups
     uint32_t nstages;
     uint32_t cap;        // bytes reserved per matrix per stage (multiple of 128)
+    uint32_t q8_off;     // shared-memory offset of the in-kernel Q8_K area (K-quants with f32 input)
 };
 
 // Shared-memory header in front of the ring.
@@ -66,13 +67,37 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return true;
 }
 
+// Sums NV per-lane values across the warp with one butterfly: each halving step trades half of
+// the values with the partner lane, so NV-1 shuffles replace 5*NV. On return the lanes
+// [i*32/NV, (i+1)*32/NV) all hold the warp total of value i.
+template <int NV>
+__device__ __forceinline__ float reduce_values(float (&v)[NV], uint32_t lane) {
+    static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8, "NV must be a power of two <= 8");
+    int off = 16;
+#pragma unroll
+    for (int n = NV; n > 1; n >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; i++) {
+            const float keep = upper ? v[i + n / 2] : v[i];
+            const float send = upper ? v[i] : v[i + n / 2];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+        off >>= 1;
+    }
+    float r = v[0];
+    for (; off > 0; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+    return r;
+}
+
 // F supplies:
 //   struct Act;                                            per-position activation registers
-//   static void load_act(Act&, const StreamArgs&, uint32_t u, bool valid)
+//   static constexpr bool USES_Q8K;                        integer dot against Q8_K activations
+//   static void load_act(Act&, const StreamArgs&, const Q8KView&, uint32_t u, bool valid)
 //   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
 //   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
 template <class F, int KL, bool SWIGLU>
-__global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
     constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
@@ -131,12 +156,47 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
     // ── consumers ──
     const uint32_t slot = warp / P, part = warp % P;
     pdl_wait();  // activations come from the previous kernel
+    Q8KView q8 = a.q8;
+    if (F::USES_Q8K && a.q8.qs == nullptr) {
+        // f32 input: the consumer warps quantize it to Q8_K once per CTA into shared memory
+        // (one warp per 256-element block, exactly the stand-alone quantizer), then every lane
+        // picks up its own positions from there.
+        const uint32_t nb = a.cols / QK_K;
+        uint8_t* area = smem_raw + a.q8_off;
+        int8_t* qs_s = reinterpret_cast<int8_t*>(area);
+        int16_t* bs_s = reinterpret_cast<int16_t*>(area + (size_t)nb * 256);  // 8-byte aligned for any nb
+        float* d_s = reinterpret_cast<float*>(area + (size_t)nb * 288);
+        // four blocks per warp at a time: their loads are in flight together and their
+        // (independent) reduction chains interleave
+        for (uint32_t b0 = warp; b0 < nb; b0 += 4 * NCW) {
+            Q8KLaneInput in[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) in[i] = q8k_load_lane(a.x + (size_t)blk * QK_K, lane);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) q8k_quantize_block_warp(in[i], lane, qs_s + (size_t)blk * QK_K, d_s + blk, bs_s + (size_t)blk * 16);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        q8.qs = qs_s; q8.d = d_s; q8.bsums = bs_s; q8.nb = nb;
+    }
     typename F::Act act[KL];
 #pragma unroll
     for (int k = 0; k < KL; k++) {
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-        F::load_act(act[k], a, u, u < a.units);
+        F::load_act(act[k], a, q8, u, u < a.units);
     }
+
+    // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
+    // and one butterfly reduces all of them (NV-1 + log2(32/NV) shuffles instead of 5*NV).
+    constexpr int M = SWIGLU ? 2 : 1;
+    constexpr int RB = KL == 1 ? (SWIGLU ? 2 : 4) : (KL == 2 ? (SWIGLU ? 1 : 2) : 1);
+    constexpr int NV = RB * M;
+    constexpr uint32_t LANES_PER_VALUE = 32 / NV;
 
     for (uint32_t c = 0; c < nchunks; c++) {
         const uint32_t s = c % a.nstages, ph = (c / a.nstages) & 1;
@@ -146,38 +206,37 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const St
         const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
         const uint32_t nrow = r0 + set0 < a.rows ? min(rps, a.rows - r0 - set0) : 0;
         const uint32_t sb = ring + s * stage_bytes + pad + set0 * a.row_bytes;
-        float keep0 = 0.0f, keep1 = 0.0f;                 // finalizer warp: lane rr keeps row rr's own partial
-        for (uint32_t rr = 0; rr < nrow; rr++) {
-            const uint32_t rb = sb + rr * a.row_bytes;
-            float v0 = 0.0f, v1 = 0.0f;
+        for (uint32_t rr0 = 0; rr0 < nrow; rr0 += RB) {
+            float v[NV];
 #pragma unroll
-            for (int k = 0; k < KL; k++) {
-                const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-                if (u < a.units) {
-                    v0 += F::unit(rb, u, act[k], a);
-                    if (SWIGLU) v1 += F::unit(rb + a.cap, u, act[k], a);
+            for (int i = 0; i < NV; i++) v[i] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < RB; j++) {
+                if (rr0 + j < nrow) {
+                    const uint32_t rb = sb + (rr0 + j) * a.row_bytes;
+#pragma unroll
+                    for (int k = 0; k < KL; k++) {
+                        const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
+                        if (u < a.units) {
+                            v[j * M] += F::unit(rb, u, act[k], a);
+                            if (SWIGLU) v[j * M + M - 1] += F::unit(rb + a.cap, u, act[k], a);
+                        }
+                    }
                 }
             }
-            v0 = warp_sum(v0);
-            if (SWIGLU) v1 = warp_sum(v1);
-            if (part != 0) {
-                if (lane == 0) {
-                    sm->partial[s][warp][rr][0] = v0;
-                    if (SWIGLU) sm->partial[s][warp][rr][1] = v1;
-                }
-            } else if (lane == (rr & 31)) {
-                keep0 = v0;
-                keep1 = v1;
-            }
+            const float tot = reduce_values<NV>(v, lane);
+            const uint32_t vi = lane / LANES_PER_VALUE;   // which of the NV values this lane now holds
+            if ((lane % LANES_PER_VALUE) == 0 && rr0 + vi / M < nrow) sm->partial[s][warp][rr0 + vi / M][vi % M] = tot;
         }
+        __syncwarp();
         if (nrow > 0) {
             if (part != 0) {
                 if (lane == 0) mbar_arrive(smem_u32(&sm->red[s][slot]));
             } else {
                 if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status)) break;
                 if (lane < nrow) {
-                    float v0 = keep0, v1 = keep1;
-                    for (uint32_t p = 1; p < P; p++) {
+                    float v0 = 0.0f, v1 = 0.0f;
+                    for (uint32_t p = 0; p < P; p++) {
                         v0 += sm->partial[s][warp + p][lane][0];
                         if (SWIGLU) v1 += sm->partial[s][warp + p][lane][1];
                     }

@@ -109,6 +109,27 @@ def test_matvec_preq_matches_oracle(eng, oracle, qtype):
     assert_close(got, oracle.matvec_preq(qtype, data, rows, cols, q8), synth.TYPE_NAMES[qtype])
 
 
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K])
+def test_fused_quantization_equals_prequantized_path(eng, oracle, qtype):
+    """alice_matvec quantizes x to Q8_K inside the kernel; the result must be bit-identical to
+    alice_matvec_preq fed with the oracle's Q8_K blocks of the same x (same kernel arithmetic)."""
+    rng = np.random.default_rng(900 + qtype)
+    for rows, cols in [(50, 4096), (9, 14336), (4, 256)]:
+        data = synth.make_weights(qtype, rng, rows, cols)
+        x = synth.make_x(rng, cols)
+        x[:256] = 0.0
+        if cols > 512:
+            x[300], x[301], x[700] = 5.5, -5.5, -9.25
+        w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
+        fused = eng.matvec(w, x)
+        q = eng.upload_q8k(*oracle.quantize_row_q8_k(x), cols, 1)
+        y = eng.alloc_f32(rows)
+        eng.matvec_preq_dev(w, q, y)
+        pre = eng.read_f32(y)
+        eng.sync()
+        assert np.array_equal(bits(fused), bits(pre)), (synth.TYPE_NAMES[qtype], rows, cols)
+
+
 @pytest.mark.parametrize("qtype,rows,cols", [(Q4_K, 300, 4096), (Q4_K, 17, 512), (Q1_0, 200, 5120), (Q6_K, 33, 1024),
                                              (Q8_0, 40, 1024)])
 def test_swiglu_matches_oracle(eng, oracle, qtype, rows, cols):
