@@ -8,6 +8,7 @@ Nothing here computes on the CPU; every method is a call into libalice_cuda.so.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from enum import Enum
 
 import numpy as np
@@ -41,6 +42,7 @@ class GpuBuffer:
 
     def __init__(self, engine, handle, length):
         self.engine, self._h, self.len = engine, handle, length
+        engine._children.add(self)
 
     def free(self):
         if self._h:
@@ -59,6 +61,7 @@ class GpuWeightBuffer:
 
     def __init__(self, engine, handle, rows, cols, quant):
         self.engine, self._h, self.rows, self.cols, self.quant = engine, handle, rows, cols, quant
+        engine._children.add(self)
 
     def free(self):
         if self._h:
@@ -77,6 +80,7 @@ class Q8KBuffer:
 
     def __init__(self, engine, handle, cols, batch):
         self.engine, self._h, self.cols, self.batch = engine, handle, cols, batch
+        engine._children.add(self)
 
     def read(self):
         """-> (d[batch, nb], qs[batch, nb, 256], bsums[batch, nb, 16])"""
@@ -104,13 +108,17 @@ class GpuEngine:
 
     def __init__(self, device: int = 0):
         self._lib = _lib.load()
+        self._children = weakref.WeakSet()
         h = C.c_void_p()
         check(self._lib.alice_engine_create(device, C.byref(h)))
         self._h = h
         self.device = device
 
     def close(self):
+        """Frees every buffer still alive on this engine (their C handles point at it), then the engine."""
         if getattr(self, "_h", None):
+            for child in list(self._children):
+                child.free()
             self._lib.alice_engine_destroy(self._h)
             self._h = None
 
