@@ -51,6 +51,7 @@ SIGNATURES = {
     "alice_swiglu": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "alice_swiglu_preq": (C.c_int32, [_vp, _vp, _vp, _vp, _vp]),
     "alice_dequantize": (C.c_int32, [_vp, _vp, _vp]),
+    "alice_matvec_preq_noalloc": (C.c_int32, [_vp, _vp, _vp, _vp]),
     "alice_matvec_host": (C.c_int32, [C.c_uint32, _vp, C.c_size_t, C.c_uint32, C.c_uint32, _vp, _vp]),
     "alice_dequantize_host": (C.c_int32, [C.c_uint32, _vp, C.c_size_t, _vp, C.c_size_t]),
 }

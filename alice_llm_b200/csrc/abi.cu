@@ -51,6 +51,8 @@ struct alice_q8k {
 
 namespace {
 
+__device__ __forceinline__ void pdl_wait_abi() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 thread_local std::string g_err;
 
 int fail(int code, const char* fmt, ...) {
@@ -546,6 +548,67 @@ int32_t alice_dequantize_host(uint32_t type, const uint8_t* data, size_t nbytes,
     if (!rc) rc = alice_buf_read_f32(e, bo, out, n_out);
     alice_buf_free(bo); alice_weights_free(w);
     return rc;
+}
+
+// ---- pre-quantized Q1_0 / Q2_0 matvec without any allocation -------------------------------------
+//
+// alice_matvec_preq turns the Q8_K blocks back into f32 (src/gguf.rs:4593-4605) in a scratch
+// buffer that the engine obtains with cudaMalloc and grows on demand. Some callers must not reach
+// the allocator at all: a serving process that has handed every byte of HBM to its own pool
+// (KV-cache arena, a framework's caching allocator) so that cudaMalloc fails; or a decode thread
+// that cannot afford cudaMalloc / cudaFree because both synchronise the whole device. For them the
+// variant below keeps the f32 scratch in a fixed array that is part of the library image: every
+// GPU that loads the library holds ALICE_NOALLOC_MAX_FLOATS * 4 bytes (256 KiB) until the process
+// exits.
+
+static __device__ __align__(256) float g_noalloc_scratch[ALICE_NOALLOC_MAX_FLOATS];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address; the
+// address of each device's copy is looked up once, with that device current, and cached here.
+static float* g_noalloc_ptr[64] = {};
+static std::mutex g_noalloc_mu;
+
+static __global__ void q8k_to_f32_noalloc_kernel(Q8KView q, uint32_t total) {
+    pdl_wait_abi();
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+        g_noalloc_scratch[i] = __fmul_rn(q.d[i >> 8], (float)q.qs[i]);
+}
+
+static int noalloc_scratch_for(alice_engine* e, float** out) {
+    if (e->device < 0 || e->device >= 64) return fail(ALICE_E_INVALID, "alice_matvec_preq_noalloc: device index %d", e->device);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[e->device]) {
+        void* p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // current device = e->device (set by the caller)
+        if (err != cudaSuccess || !p) return cuda_fail(err, "alice_matvec_preq_noalloc: cudaGetSymbolAddress");
+        g_noalloc_ptr[e->device] = static_cast<float*>(p);
+    }
+    *out = g_noalloc_ptr[e->device];
+    return ALICE_OK;
+}
+
+int32_t alice_matvec_preq_noalloc(alice_engine* e, const alice_weights* w, const alice_q8k* q, alice_buf* y) {
+    const char* who = "alice_matvec_preq_noalloc";
+    if (!e || !w || !q || !y) return fail(ALICE_E_INVALID, "%s: null argument", who);
+    const WeightDesc& d = w->d;
+    if (d.fmt != WF_Q1_0 && d.fmt != WF_Q2_0)
+        return fail(ALICE_E_UNSUPPORTED, "%s: only Q1_0 / Q2_0 weights need the f32 scratch; use alice_matvec_preq", who);
+    if (q->cols != d.cols) return fail(ALICE_E_SHAPE, "%s: Q8_K input has %u columns, weights %u", who, q->cols, d.cols);
+    if (q->batch == 0 || q->batch > 8) return fail(ALICE_E_SHAPE, "%s: batch %u outside 1..8", who, q->batch);
+    const size_t total = (size_t)q->batch * d.cols;
+    if (total > (size_t)ALICE_NOALLOC_MAX_FLOATS)
+        return fail(ALICE_E_SHAPE, "%s: batch * cols = %zu floats exceeds the fixed scratch of %d floats", who, total,
+                    (int)ALICE_NOALLOC_MAX_FLOATS);
+    if (y->len < (size_t)q->batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output too small", who);
+    CU(cudaSetDevice(e->device));
+    float* scratch = nullptr;
+    int rc = noalloc_scratch_for(e, &scratch);
+    if (rc) return rc;
+    // Every element the matvec reads is rewritten first, so nothing has to be cleared between calls.
+    const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 8);
+    q8k_to_f32_noalloc_kernel<<<blocks, 256, 0, e->stream>>>(view_of(q, 0), (uint32_t)total);
+    CU(cudaGetLastError());
+    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, who);
 }
 
 }  // extern "C"

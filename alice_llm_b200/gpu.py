@@ -239,6 +239,11 @@ class GpuEngine:
     def matvec_preq_dev(self, w: GpuWeightBuffer, q: Q8KBuffer, y: GpuBuffer):
         check(self._lib.alice_matvec_preq(self._h, w._h, q._h, y._h))
 
+    def matvec_preq_noalloc_dev(self, w: GpuWeightBuffer, q: Q8KBuffer, y: GpuBuffer):
+        """alice_matvec_preq_noalloc: the Q1_0 / Q2_0 pre-quantized matvec for callers that cannot
+        allocate device memory; its f32 scratch is a fixed 65536-float array inside the library."""
+        check(self._lib.alice_matvec_preq_noalloc(self._h, w._h, q._h, y._h))
+
     def swiglu_dev(self, gate: GpuWeightBuffer, up: GpuWeightBuffer, x: GpuBuffer, y: GpuBuffer, batch: int = 1):
         check(self._lib.alice_swiglu(self._h, gate._h, up._h, x._h, y._h, batch))
 

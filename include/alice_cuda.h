@@ -129,6 +129,23 @@ int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alic
 /* dequantize_weight_row / GgufFile::tensor_to_f32 (src/gguf.rs:6168, 574): out[r*cols + c], bit-exact. */
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out);
 
+/* ---- no-allocation variant ---------------------------------------------------------------- */
+/* Has no counterpart in the reference. alice_matvec_preq for Q1_0 / Q2_0 weights needs an f32 copy
+ * of the Q8_K input and takes it from engine scratch obtained with cudaMalloc. This variant is for
+ * callers that cannot allocate: a process whose HBM is entirely owned by its own pool (so cudaMalloc
+ * would fail), or a decode thread that must not trigger the device-wide synchronisation cudaMalloc /
+ * cudaFree imply. The f32 scratch is a fixed array inside the library image instead:
+ * ALICE_NOALLOC_MAX_FLOATS floats (256 KiB) resident on every GPU that loads the library, for the
+ * life of the process. batch * cols beyond that limit is rejected with ALICE_E_SHAPE; weights other
+ * than Q1_0 / Q2_0 with ALICE_E_UNSUPPORTED. The call itself performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine. The first call on a device looks up the address of that
+ * device's copy of the array (cudaGetSymbolAddress); make that first call before starting any stream
+ * capture. All calls share the one array and it keeps the previous call's contents (each call
+ * rewrites every element it reads, so nothing needs clearing); two calls whose GPU work overlaps -
+ * different streams or engines on one device - race on it. Results equal alice_matvec_preq's. */
+#define ALICE_NOALLOC_MAX_FLOATS 65536
+int32_t alice_matvec_preq_noalloc(alice_engine* e, const alice_weights* w, const alice_q8k* q, alice_buf* y);
+
 /* ---- host-pointer convenience (the gguf.rs-level signatures) ------------------------------- */
 /* quantized_matvec(input, data, qtype, rows, cols, output) (src/gguf.rs:4214): uploads, runs on
  * device 0 through a process-wide engine, reads back. */
