@@ -51,10 +51,35 @@ SIGNATURES = {
     "alice_swiglu": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "alice_swiglu_preq": (C.c_int32, [_vp, _vp, _vp, _vp, _vp]),
     "alice_dequantize": (C.c_int32, [_vp, _vp, _vp]),
+    "alice_model_create": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _pp]),
+    "alice_model_destroy": (C.c_int32, [_vp]),
+    "alice_model_forward": (C.c_int32, [_vp, C.c_uint32]),
+    "alice_model_forward_read": (C.c_int32, [_vp, C.c_uint32, _vp]),
+    "alice_model_decode_greedy": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp]),
+    "alice_model_read_logits": (C.c_int32, [_vp, _vp]),
+    "alice_model_position": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),
+    "alice_model_vocab_size": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),
+    "alice_model_rollback_to": (C.c_int32, [_vp, C.c_uint32]),
+    "alice_model_reset": (C.c_int32, [_vp]),
+    "alice_model_kv_write": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
+    "alice_model_kv_read": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, C.c_uint32, _vp, _vp]),
+    "alice_model_set_position": (C.c_int32, [_vp, C.c_uint32]),
     "alice_matvec_preq_noalloc": (C.c_int32, [_vp, _vp, _vp, _vp]),
     "alice_matvec_host": (C.c_int32, [C.c_uint32, _vp, C.c_size_t, C.c_uint32, C.c_uint32, _vp, _vp]),
     "alice_dequantize_host": (C.c_int32, [C.c_uint32, _vp, C.c_size_t, _vp, C.c_size_t]),
 }
+
+
+class ModelConfig(C.Structure):
+    """alice_model_config"""
+    _fields_ = [(n, C.c_uint32) for n in ("num_layers", "hidden_dim", "intermediate_dim", "num_heads", "num_kv_heads",
+                                          "head_dim", "vocab_size", "max_seq_len")] + \
+               [("rope_theta", C.c_float), ("eps", C.c_float), ("neox_rope", C.c_uint32)]
+
+
+class LayerWeights(C.Structure):
+    """alice_layer_weights"""
+    _fields_ = [(n, C.c_void_p) for n in ("q", "k", "v", "o", "gate", "up", "down", "attn_norm", "ffn_norm")]
 
 
 class AliceError(RuntimeError):

@@ -10,44 +10,9 @@
 #include <string>
 #include <vector>
 
-#include "../../include/alice_cuda.h"
-#include "gemv_launch.cuh"
-#include "q8k.cuh"
+#include "abi_internal.cuh"
 
 using namespace alice;
-
-struct alice_engine {
-    int device = 0;
-    int num_sms = 0;
-    cudaStream_t stream = nullptr;
-    bool own_stream = false;
-    bool pdl = true;
-    int force_rps = 0, force_stages = 0;
-    int* status = nullptr;        // device status word
-    void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
-    size_t scratch_bytes = 0;
-};
-
-struct alice_weights {
-    alice_engine* e;
-    WeightDesc d;
-    void* owned_data = nullptr;
-    void* owned_scales = nullptr;
-};
-
-struct alice_buf {
-    alice_engine* e;
-    float* p;
-    size_t len;
-    bool owned;
-};
-
-struct alice_q8k {
-    alice_engine* e;
-    void* base;
-    uint32_t cols, batch, nb;
-    Q8KLayout lay;
-};
 
 namespace {
 
@@ -77,12 +42,29 @@ int cuda_fail(cudaError_t err, const char* what) {
 
 bool known_ggml(uint32_t t) { return ggml_block_bytes((WeightFormat)t) != 0; }
 
-LaunchCfg cfg_of(const alice_engine* e) {
+LaunchCfg cfg_of(const alice_engine* e) { return alice_cfg_of(e); }
+
+}  // namespace
+
+LaunchCfg alice_cfg_of(const alice_engine* e) {
     LaunchCfg c;
     c.stream = e->stream; c.num_sms = e->num_sms; c.status = e->status; c.pdl = e->pdl;
     c.force_rps = e->force_rps; c.force_stages = e->force_stages;
     return c;
 }
+
+int alice_fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+int alice_cuda_fail(cudaError_t err, const char* what) { return cuda_fail(err, what); }
+
+namespace {
 
 Q8KView view_of(const alice_q8k* q, uint32_t k) {
     auto* p = static_cast<uint8_t*>(q->base);

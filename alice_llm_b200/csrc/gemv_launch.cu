@@ -91,17 +91,37 @@ int launch_fmt(const StreamArgs& a, uint32_t kl, bool sw, uint32_t grid, size_t 
 
 int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
                        const LaunchCfg& cfg) {
+    GemvOp op;
+    op.w[0] = &w0; op.up = w1; op.q8 = q8; op.x = x; op.y = y;
+    return launch_stream_gemv_op(op, cfg);
+}
+
+int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
+    if (op.nw < 1 || op.nw > 3 || !op.w[0] || !op.y) return ALICE_E_INVALID;
+    const WeightDesc& w0 = *op.w[0];
+    const WeightDesc* w1 = op.up;
+    const Q8KView* q8 = op.q8;
+    const float* x = op.x;
     const bool sw = w1 != nullptr;
-    if (w0.rows == 0 || w0.cols == 0 || !w0.data || !y) return ALICE_E_INVALID;
+    if (sw && op.nw != 1) return ALICE_E_INVALID;
+    if (w0.rows == 0 || w0.cols == 0 || !w0.data) return ALICE_E_INVALID;
     if (sw && (w1->fmt != w0.fmt || w1->rows != w0.rows || w1->cols != w0.cols || w1->row_bytes != w0.row_bytes))
         return ALICE_E_SHAPE;
     if (((uintptr_t)w0.data & 15) || (sw && ((uintptr_t)w1->data & 15))) return ALICE_E_INVALID;
+    uint32_t total_rows = 0;
+    for (uint32_t i = 0; i < op.nw; i++) {
+        const WeightDesc* wi = op.w[i];
+        if (!wi || !wi->data || ((uintptr_t)wi->data & 15) || wi->rows == 0) return ALICE_E_INVALID;
+        if (wi->fmt != w0.fmt || wi->cols != w0.cols || wi->row_bytes != w0.row_bytes) return ALICE_E_SHAPE;
+        total_rows += wi->rows;
+    }
     if (format_uses_q8k(w0.fmt)) {
         // K-quants take either pre-quantized Q8_K blocks or the f32 vector (quantized in the prologue)
         if (q8 ? q8->nb * 256u != w0.cols : x == nullptr) return q8 ? ALICE_E_SHAPE : ALICE_E_INVALID;
     } else if (!x) {
         return ALICE_E_INVALID;
     }
+    if (op.norm_w && (!x || q8)) return ALICE_E_INVALID;  // the norm needs the f32 vector
     const uint32_t units = units_per_row(w0.fmt, w0.cols);
     if (units == 0) return ALICE_E_UNSUPPORTED;
 
@@ -109,8 +129,10 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
     a.w0 = w0.data; a.w1 = sw ? w1->data : nullptr;
     if (q8) a.q8 = *q8;
     a.x = x; a.aux0 = w0.scales; a.aux1 = sw ? w1->scales : nullptr;
-    a.y = y; a.status = cfg.status;
-    a.rows = w0.rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
+    a.y = op.y; a.status = cfg.status;
+    a.rows = total_rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
+    a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid;
+    if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
 
     // warps per row: just enough lanes for one unit each, at most all eight
     uint32_t P = 1;
@@ -123,15 +145,18 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
     const uint32_t nmat = sw ? 2 : 1;
     static const char* env_cps = getenv("ALICE_CTAS_PER_SM");  // experiment knob
     const uint32_t per_sm = env_cps ? (uint32_t)atoi(env_cps) : (kl <= 2 ? 2 : 1);
-    // in-kernel Q8_K area: qs[cols] + d[nb] f32 + bsums[nb][16] i16
+    // in-kernel Q8_K area: qs[cols] + bsums[nb][16] i16 + d[nb] f32; normalised input: f32[cols]
     const uint32_t q8_bytes = (format_uses_q8k(w0.fmt) && !q8) ? ((w0.cols / 256u) * 292u + 127u) & ~127u : 0u;
-    const uint32_t budget = (kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1) - HDR_BYTES - q8_bytes;
+    const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
+    const uint32_t full_budget = kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1;
+    if (HDR_BYTES + q8_bytes + xn_bytes + 4096 > full_budget) return ALICE_E_SHAPE;
+    const uint32_t budget = full_budget - HDR_BYTES - q8_bytes - xn_bytes;
     const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
     uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
     // rows per warp set per stage: as many as the ring allows (per-stage costs are amortised over
     // them) while every CTA still gets at least ~4 stages of work
     uint32_t rps_bytes = std::max<uint32_t>(1, (budget / nst - 256) / std::max<uint32_t>(1, a.slots * a.row_bytes * nmat));
-    uint32_t rps_bal = std::max<uint32_t>(1, a.rows / (a.slots * ctas * 4));
+    uint32_t rps_bal = std::max<uint32_t>(1, total_rows / (a.slots * ctas * 4));
     uint32_t rps = std::min<uint32_t>(std::min(rps_bytes, rps_bal), MAX_RPS);
     if (cfg.force_rps > 0) rps = std::min<uint32_t>(cfg.force_rps, MAX_RPS);
     uint32_t cap, stage;
@@ -144,10 +169,18 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
         return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
     }
     a.rps = rps; a.cap = cap; a.nstages = nst;
-    a.groups = (a.rows + a.slots * rps - 1) / (a.slots * rps);
+    a.nseg = op.nw;
+    a.groups = 0;
+    for (uint32_t i = 0; i < op.nw; i++) {
+        a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i];
+        a.seg_g0[i] = a.groups;
+        a.groups += (op.w[i]->rows + a.slots * rps - 1) / (a.slots * rps);
+    }
+    a.seg_g0[op.nw] = a.groups;
     const uint32_t grid = std::min(ctas, a.groups);
     a.q8_off = HDR_BYTES + nst * stage;
-    const size_t smem = HDR_BYTES + (size_t)nst * stage + q8_bytes;
+    a.xn_off = a.q8_off + q8_bytes;
+    const size_t smem = HDR_BYTES + (size_t)nst * stage + q8_bytes + xn_bytes;
 
     switch (w0.fmt) {
         case WF_Q4_K: return launch_fmt<FmtQ4K>(a, kl, sw, grid, smem, cfg);

@@ -37,6 +37,21 @@ struct LaunchCfg {
     int force_stages; // 0 = automatic
 };
 
+// One launch of the streaming matvec with its optional fused stages.
+struct GemvOp {
+    const WeightDesc* w[3] = {nullptr, nullptr, nullptr};  // 1..3 matrices of one format and width sharing the input
+    uint32_t nw = 1;
+    uint32_t y_off[3] = {0, 0, 0};                         // output offset (floats) of each matrix inside y
+    const WeightDesc* up = nullptr;                        // fused SwiGLU: w[0] = gate, up = up (nw must be 1)
+    const Q8KView* q8 = nullptr;                           // pre-quantized input (K-quants), else x
+    const float* x = nullptr;                              // f32 input vector
+    const float* norm_w = nullptr;                         // fused RMSNorm of x with these weights
+    float norm_eps = 0.0f;
+    const float* resid = nullptr;                          // y = resid + result
+    float* y = nullptr;
+};
+int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
+
 // y[r] = W[r,:] . x  (or silu(W0 x) * (W1 x) when w1 != null). K-quant formats read `q8`,
 // the others read the f32 vector `x`. Returns 0 or a negative ALICE_E_* code.
 int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,

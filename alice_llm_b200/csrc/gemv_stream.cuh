@@ -42,6 +42,19 @@ struct StreamArgs {
     uint32_t nstages;
     uint32_t cap;        // bytes reserved per matrix per stage (multiple of 128)
     uint32_t q8_off;     // shared-memory offset of the in-kernel Q8_K area (K-quants with f32 input)
+    uint32_t xn_off;     // shared-memory offset of the normalised f32 input (RMSNorm prologue)
+    // Optional fused RMSNorm of the input (rms_norm, src/llama3.rs:5244): x <- x * rsqrt(mean(x^2) + eps) * norm_w
+    const float* norm_w;
+    float norm_eps;
+    // Optional residual epilogue: y[row] = resid[row] + result (resid may alias y)
+    const float* resid;
+    // Up to three matrices of the same format and width share one launch (q, k, v): segment s owns
+    // row groups [seg_g0[s], seg_g0[s+1]) and writes y + seg_y[s]. nseg == 1 for a single matrix.
+    uint32_t nseg;
+    const uint8_t* seg_w[3];
+    uint32_t seg_rows[3];
+    uint32_t seg_g0[4];
+    uint32_t seg_y[3];
 };
 
 // Shared-memory header in front of the ring.
@@ -50,6 +63,7 @@ struct StreamSmem {
     unsigned long long empty[MAX_STAGES];
     unsigned long long red[MAX_STAGES][NCW];  // per (stage, slot): partials of the P-1 helper warps posted
     float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
+    double norm_part[NCW];
     int abort_flag;
 };
 
@@ -93,7 +107,7 @@ __device__ __forceinline__ float reduce_values(float (&v)[NV], uint32_t lane) {
 // F supplies:
 //   struct Act;                                            per-position activation registers
 //   static constexpr bool USES_Q8K;                        integer dot against Q8_K activations
-//   static void load_act(Act&, const StreamArgs&, const Q8KView&, uint32_t u, bool valid)
+//   static void load_act(Act&, const StreamArgs&, const float* x, const Q8KView&, uint32_t u, bool valid)
 //   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
 //   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
 template <class F, int KL, bool SWIGLU>
@@ -132,14 +146,17 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
             for (uint32_t c = 0; c < nchunks; c++) {
                 const uint32_t s = c % a.nstages, use = c / a.nstages;
                 if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status)) break;
-                const uint32_t r0 = (g0 + c) * rows_per_group;
-                const uint32_t nrow = min(rows_per_group, a.rows - r0);
+                const uint32_t g = g0 + c;
+                uint32_t sg = 0;
+                while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+                const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
+                const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
                 const uint64_t off = (uint64_t)r0 * a.row_bytes;
                 const uint64_t a0 = off & ~uint64_t(15);
                 const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
                 const uint32_t fb = smem_u32(&sm->full[s]);
                 mbar_arrive_expect_tx(fb, SWIGLU ? 2 * cb : cb);
-                bulk_g2s(ring + s * stage_bytes, a.w0 + a0, cb, fb);
+                bulk_g2s(ring + s * stage_bytes, a.seg_w[sg] + a0, cb, fb);
                 if (SWIGLU) bulk_g2s(ring + s * stage_bytes + a.cap, a.w1 + a0, cb, fb);
                 issued = c + 1;
             }
@@ -156,6 +173,27 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     // ── consumers ──
     const uint32_t slot = warp / P, part = warp % P;
     pdl_wait();  // activations come from the previous kernel
+    const float* x_src = a.x;
+    if (a.norm_w != nullptr) {
+        // rms_norm (src/llama3.rs:5244-5256): f64 sum of squares, mean and scale in f32, then
+        // (x * scale) * w; the normalised vector is kept in shared memory for this CTA only.
+        float* xn = reinterpret_cast<float*>(smem_raw + a.xn_off);
+        const uint32_t tid = threadIdx.x;  // consumer threads are 0 .. NCW*32-1
+        double ss = 0.0;
+        for (uint32_t i = tid; i < a.cols; i += NCW * 32) { const float v = a.x[i]; ss += (double)v * (double)v; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sm->norm_part[warp] = ss;
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        double tot = 0.0;
+#pragma unroll
+        for (int w = 0; w < NCW; w++) tot += sm->norm_part[w];
+        const float mean = (float)(tot / (double)a.cols);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.norm_eps)));
+        for (uint32_t i = tid; i < a.cols; i += NCW * 32) xn[i] = __fmul_rn(__fmul_rn(a.x[i], scale), a.norm_w[i]);
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        x_src = xn;
+    }
     Q8KView q8 = a.q8;
     if (F::USES_Q8K && a.q8.qs == nullptr) {
         // f32 input: the consumer warps quantize it to Q8_K once per CTA into shared memory
@@ -173,7 +211,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint32_t blk = b0 + i * NCW;
-                if (blk < nb) in[i] = q8k_load_lane(a.x + (size_t)blk * QK_K, lane);
+                if (blk < nb) in[i] = q8k_load_lane(x_src + (size_t)blk * QK_K, lane);
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -188,7 +226,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
 #pragma unroll
     for (int k = 0; k < KL; k++) {
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-        F::load_act(act[k], a, q8, u, u < a.units);
+        F::load_act(act[k], a, x_src, q8, u, u < a.units);
     }
 
     // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
@@ -201,10 +239,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     for (uint32_t c = 0; c < nchunks; c++) {
         const uint32_t s = c % a.nstages, ph = (c / a.nstages) & 1;
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status)) break;
-        const uint32_t r0 = (g0 + c) * rows_per_group;
+        const uint32_t g = g0 + c;
+        uint32_t sg = 0;
+        while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+        const uint32_t seg_rows = a.seg_rows[sg];
+        const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
         const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
         const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
-        const uint32_t nrow = r0 + set0 < a.rows ? min(rps, a.rows - r0 - set0) : 0;
+        const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         const uint32_t sb = ring + s * stage_bytes + pad + set0 * a.row_bytes;
         for (uint32_t rr0 = 0; rr0 < nrow; rr0 += RB) {
             float v[NV];
@@ -240,10 +282,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
                         v0 += sm->partial[s][warp + p][lane][0];
                         if (SWIGLU) v1 += sm->partial[s][warp + p][lane][1];
                     }
-                    const uint32_t row = r0 + set0 + lane;
+                    const uint32_t row = r0 + set0 + lane;      // row inside its matrix
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
-                    a.y[row] = r;
+                    const uint32_t yi = a.seg_y[sg] + row;
+                    if (a.resid != nullptr) r = __fadd_rn(a.resid[yi], r);
+                    a.y[yi] = r;
                 }
             }
         }

@@ -1,0 +1,358 @@
+// Device-resident Llama-style decode model over the streaming matvec (alice_model_* of
+// include/alice_cuda.h): the GpuModel of ALICE-LLM src/gpu.rs:2348 with the arithmetic of the CPU
+// forward (src/llama3.rs:13632-13687, 14167-14613).
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "abi_internal.cuh"
+#include "glue.cuh"
+
+using namespace alice;
+
+struct alice_model {
+    alice_engine* e = nullptr;
+    alice_model_config cfg{};
+    struct Layer {
+        WeightDesc q, k, v, o, gate, up, down;
+        float* attn_norm = nullptr;
+        float* ffn_norm = nullptr;
+    };
+    std::vector<Layer> layers;
+    WeightDesc emb{}, out{};
+    float* out_norm = nullptr;
+    // activations
+    float *hidden = nullptr, *qkv = nullptr, *attn_out = nullptr, *ffn_h = nullptr, *logits = nullptr;
+    float *kcache = nullptr, *vcache = nullptr;  // [layer][max_seq][kv_dim]
+    float* attn_part = nullptr;
+    uint32_t nsplit = 1;
+    // device-side state: position, current token, tokens chosen per position
+    int *d_pos = nullptr, *d_token = nullptr, *d_trace = nullptr;
+    uint32_t pos = 0;  // host mirror of *d_pos
+    cudaGraphExec_t graph_greedy = nullptr;
+    bool graph_tried = false;
+    std::vector<void*> owned;
+};
+
+namespace {
+
+#define MCU(call)                                                       \
+    do {                                                                \
+        cudaError_t err__ = (call);                                     \
+        if (err__ != cudaSuccess) return alice_cuda_fail(err__, #call); \
+    } while (0)
+
+template <class T>
+int dev_alloc(alice_model* m, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t err = cudaMalloc(&q, std::max<size_t>(n, 1) * sizeof(T));
+    if (err != cudaSuccess) return alice_cuda_fail(err, "alice_model_create: cudaMalloc");
+    m->owned.push_back(q);
+    *p = static_cast<T*>(q);
+    return ALICE_OK;
+}
+
+int upload_norm(alice_model* m, float** dst, const float* host, size_t n) {
+    int rc = dev_alloc(m, dst, n);
+    if (rc) return rc;
+    MCU(cudaMemcpy(*dst, host, n * sizeof(float), cudaMemcpyHostToDevice));
+    return ALICE_OK;
+}
+
+int gemv(alice_model* m, const GemvOp& op, const char* what) {
+    const int rc = launch_stream_gemv_op(op, alice_cfg_of(m->e));
+    if (rc == ALICE_OK) return rc;
+    return alice_fail(rc, "alice_model: %s matvec failed (%d): %s", what, rc, cudaGetErrorString(cudaGetLastError()));
+}
+
+// Queues one decode step on the engine's stream. The token is read from *d_token.
+int enqueue_step(alice_model* m, bool greedy_feed) {
+    const alice_model_config& c = m->cfg;
+    cudaStream_t st = m->e->stream;
+    const bool pdl = m->e->pdl;
+    const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
+    const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
+    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, st, pdl));
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const alice_model::Layer& L = m->layers[l];
+        float* kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim;
+        float* vc = m->vcache + (size_t)l * c.max_seq_len * kv_dim;
+        if (L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt && !L.q.scales) {
+            // attention norm + q, k, v projections in one launch (src/llama3.rs:14178-14217)
+            GemvOp op;
+            op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
+            op.y_off[0] = 0; op.y_off[1] = q_dim; op.y_off[2] = q_dim + kv_dim;
+            op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
+            int rc = gemv(m, op, "qkv");
+            if (rc) return rc;
+        } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
+            const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
+            const uint32_t offs[3] = {0, q_dim, q_dim + kv_dim};
+            for (int i = 0; i < 3; i++) {
+                GemvOp op;
+                op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
+                op.y = m->qkv + offs[i];
+                int rc = gemv(m, op, "q/k/v");
+                if (rc) return rc;
+            }
+        }
+        MCU(launch_rope_kv(m->qkv, m->d_pos, shape, c.rope_theta, (int)c.neox_rope, kc, vc, st, pdl));
+        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->nsplit, m->attn_part, m->attn_out, st, pdl));
+        {   // output projection + residual (src/llama3.rs:14423, 14468)
+            GemvOp op;
+            op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden;
+            int rc = gemv(m, op, "o_proj");
+            if (rc) return rc;
+        }
+        {   // FFN norm + fused SwiGLU gate/up (src/llama3.rs:14497-14534)
+            GemvOp op;
+            op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
+            op.y = m->ffn_h;
+            int rc = gemv(m, op, "gate/up");
+            if (rc) return rc;
+        }
+        {   // down projection + residual (src/llama3.rs:14536-14555)
+            GemvOp op;
+            op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden;
+            int rc = gemv(m, op, "down_proj");
+            if (rc) return rc;
+        }
+    }
+    {   // output norm + head (src/llama3.rs:14590-14604)
+        GemvOp op;
+        op.w[0] = &m->out; op.x = m->hidden; op.norm_w = m->out_norm; op.norm_eps = c.eps; op.y = m->logits;
+        int rc = gemv(m, op, "output head");
+        if (rc) return rc;
+    }
+    MCU(launch_argmax_advance(m->logits, c.vocab_size, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
+    return ALICE_OK;
+}
+
+int check_room(const alice_model* m, uint32_t steps, const char* who) {
+    if ((uint64_t)m->pos + steps > m->cfg.max_seq_len)
+        return alice_fail(ALICE_E_SHAPE, "%s: position %u + %u steps exceeds max_seq_len %u", who, m->pos, steps,
+                          m->cfg.max_seq_len);
+    return ALICE_OK;
+}
+
+bool same_shape(const WeightDesc& w, uint32_t rows, uint32_t cols) { return w.rows == rows && w.cols == cols; }
+
+}  // namespace
+
+extern "C" {
+
+int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const alice_layer_weights* layers,
+                           const alice_weights* embedding, const float* output_norm, const alice_weights* output,
+                           alice_model** out) {
+    const char* who = "alice_model_create";
+    if (!e || !cfg || !layers || !embedding || !output_norm || !output || !out) return alice_fail(ALICE_E_INVALID, "%s: null argument", who);
+    *out = nullptr;
+    const alice_model_config& c = *cfg;
+    if (!c.num_layers || !c.hidden_dim || !c.intermediate_dim || !c.num_heads || !c.num_kv_heads || !c.vocab_size || !c.max_seq_len)
+        return alice_fail(ALICE_E_SHAPE, "%s: zero dimension in config", who);
+    if (c.head_dim != 128) return alice_fail(ALICE_E_SHAPE, "%s: head_dim %u (the attention kernel is built for 128)", who, c.head_dim);
+    if (c.num_heads % c.num_kv_heads) return alice_fail(ALICE_E_SHAPE, "%s: num_heads %% num_kv_heads != 0", who);
+    const uint32_t group = c.num_heads / c.num_kv_heads;
+    if (group != 1 && group != 2 && group != 4 && group != 5 && group != 8)
+        return alice_fail(ALICE_E_SHAPE, "%s: %u query heads per KV head not supported (1, 2, 4, 5, 8)", who, group);
+    const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
+    if (embedding->d.fmt != WF_Q8_0 || !same_shape(embedding->d, c.vocab_size, c.hidden_dim))
+        return alice_fail(ALICE_E_SHAPE, "%s: embedding must be Q8_0 [vocab x hidden]", who);
+    if (!same_shape(output->d, c.vocab_size, c.hidden_dim)) return alice_fail(ALICE_E_SHAPE, "%s: output head shape", who);
+    MCU(cudaSetDevice(e->device));
+    auto* m = new alice_model();
+    m->e = e; m->cfg = c; m->emb = embedding->d; m->out = output->d;
+    int rc = ALICE_OK;
+    for (uint32_t l = 0; l < c.num_layers && !rc; l++) {
+        const alice_layer_weights& s = layers[l];
+        if (!s.q || !s.k || !s.v || !s.o || !s.gate || !s.up || !s.down || !s.attn_norm || !s.ffn_norm) {
+            rc = alice_fail(ALICE_E_INVALID, "%s: layer %u has a null weight", who, l);
+            break;
+        }
+        if (!same_shape(s.q->d, q_dim, c.hidden_dim) || !same_shape(s.k->d, kv_dim, c.hidden_dim) ||
+            !same_shape(s.v->d, kv_dim, c.hidden_dim) || !same_shape(s.o->d, c.hidden_dim, q_dim) ||
+            !same_shape(s.gate->d, c.intermediate_dim, c.hidden_dim) || !same_shape(s.up->d, c.intermediate_dim, c.hidden_dim) ||
+            !same_shape(s.down->d, c.hidden_dim, c.intermediate_dim) || s.gate->d.fmt != s.up->d.fmt) {
+            rc = alice_fail(ALICE_E_SHAPE, "%s: layer %u weight shapes do not match the config", who, l);
+            break;
+        }
+        alice_model::Layer L;
+        L.q = s.q->d; L.k = s.k->d; L.v = s.v->d; L.o = s.o->d; L.gate = s.gate->d; L.up = s.up->d; L.down = s.down->d;
+        rc = upload_norm(m, &L.attn_norm, s.attn_norm, c.hidden_dim);
+        if (!rc) rc = upload_norm(m, &L.ffn_norm, s.ffn_norm, c.hidden_dim);
+        m->layers.push_back(L);
+    }
+    m->nsplit = std::max<uint32_t>(1, std::min<uint32_t>(64, (2 * (uint32_t)e->num_sms) / c.num_kv_heads));
+    const size_t kv_elems = (size_t)c.num_layers * c.max_seq_len * kv_dim;
+    if (!rc) rc = upload_norm(m, &m->out_norm, output_norm, c.hidden_dim);
+    if (!rc) rc = dev_alloc(m, &m->hidden, c.hidden_dim);
+    if (!rc) rc = dev_alloc(m, &m->qkv, q_dim + 2 * kv_dim);
+    if (!rc) rc = dev_alloc(m, &m->attn_out, q_dim);
+    if (!rc) rc = dev_alloc(m, &m->ffn_h, c.intermediate_dim);
+    if (!rc) rc = dev_alloc(m, &m->logits, c.vocab_size);
+    if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
+    if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
+    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * c.num_heads * (c.head_dim + 2));
+    if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
+    if (!rc) rc = dev_alloc(m, &m->d_token, 1);
+    if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
+    if (!rc) {
+        cudaError_t err = cudaMemsetAsync(m->kcache, 0, kv_elems * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
+        if (err != cudaSuccess) rc = alice_cuda_fail(err, "alice_model_create: clearing state");
+    }
+    if (rc) { alice_model_destroy(m); return rc; }
+    *out = m;
+    return ALICE_OK;
+}
+
+int32_t alice_model_destroy(alice_model* m) {
+    if (!m) return ALICE_OK;
+    cudaSetDevice(m->e->device);
+    cudaStreamSynchronize(m->e->stream);
+    if (m->graph_greedy) cudaGraphExecDestroy(m->graph_greedy);
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    return ALICE_OK;
+}
+
+static int set_token(alice_model* m, uint32_t token) {
+    if (token >= m->cfg.vocab_size) return alice_fail(ALICE_E_INVALID, "alice_model: token %u >= vocab %u", token, m->cfg.vocab_size);
+    const int t = (int)token;
+    MCU(cudaMemcpyAsync(m->d_token, &t, 4, cudaMemcpyHostToDevice, m->e->stream));
+    MCU(cudaStreamSynchronize(m->e->stream));  // `t` lives on this stack frame
+    return ALICE_OK;
+}
+
+int32_t alice_model_forward(alice_model* m, uint32_t token) {
+    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_forward: null model");
+    MCU(cudaSetDevice(m->e->device));
+    int rc = check_room(m, 1, "alice_model_forward");
+    if (!rc) rc = set_token(m, token);
+    if (!rc) rc = enqueue_step(m, false);
+    if (!rc) m->pos += 1;
+    return rc;
+}
+
+int32_t alice_model_read_logits(alice_model* m, float* logits) {
+    if (!m || !logits) return alice_fail(ALICE_E_INVALID, "alice_model_read_logits: null argument");
+    MCU(cudaMemcpyAsync(logits, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->e->stream));
+    MCU(cudaStreamSynchronize(m->e->stream));
+    return alice_sync(m->e);
+}
+
+int32_t alice_model_forward_read(alice_model* m, uint32_t token, float* logits) {
+    int rc = alice_model_forward(m, token);
+    if (rc) return rc;
+    return alice_model_read_logits(m, logits);
+}
+
+int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t n, uint32_t* out_tokens) {
+    const char* who = "alice_model_decode_greedy";
+    if (!m || (!out_tokens && n)) return alice_fail(ALICE_E_INVALID, "%s: null argument", who);
+    if (n == 0) return ALICE_OK;
+    MCU(cudaSetDevice(m->e->device));
+    int rc = check_room(m, n, who);
+    if (!rc) rc = set_token(m, first_token);
+    if (rc) return rc;
+    cudaStream_t st = m->e->stream;
+    const uint32_t pos0 = m->pos;
+    if (!m->graph_tried) {
+        // Capture one step (every kernel reads position and token from device memory) and replay it.
+        m->graph_tried = true;
+        rc = enqueue_step(m, true);   // eager first step: also sets per-kernel attributes outside capture
+        if (rc) return rc;
+        m->pos += 1;
+        cudaGraph_t g = nullptr;
+        if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            const int crc = enqueue_step(m, true);
+            cudaError_t err = cudaStreamEndCapture(st, &g);
+            if (crc == ALICE_OK && err == cudaSuccess && g) {
+                if (cudaGraphInstantiate(&m->graph_greedy, g, 0) != cudaSuccess) m->graph_greedy = nullptr;
+            }
+            if (g) cudaGraphDestroy(g);
+            cudaGetLastError();  // a failed capture only means the steps are launched one by one
+        }
+    }
+    while (m->pos < pos0 + n) {
+        if (m->graph_greedy) {
+            MCU(cudaGraphLaunch(m->graph_greedy, st));
+        } else {
+            rc = enqueue_step(m, true);
+            if (rc) return rc;
+        }
+        m->pos += 1;
+    }
+    static_assert(sizeof(uint32_t) == sizeof(int), "token trace is copied as 32-bit words");
+    MCU(cudaMemcpyAsync(out_tokens, m->d_trace + pos0, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    MCU(cudaStreamSynchronize(st));
+    return alice_sync(m->e);
+}
+
+int32_t alice_model_position(const alice_model* m, uint32_t* pos) {
+    if (!m || !pos) return alice_fail(ALICE_E_INVALID, "alice_model_position: null argument");
+    *pos = m->pos;
+    return ALICE_OK;
+}
+
+int32_t alice_model_vocab_size(const alice_model* m, uint32_t* vocab) {
+    if (!m || !vocab) return alice_fail(ALICE_E_INVALID, "alice_model_vocab_size: null argument");
+    *vocab = m->cfg.vocab_size;
+    return ALICE_OK;
+}
+
+int32_t alice_model_set_position(alice_model* m, uint32_t pos) {
+    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_set_position: null model");
+    if (pos > m->cfg.max_seq_len) return alice_fail(ALICE_E_SHAPE, "alice_model_set_position: %u > max_seq_len %u", pos, m->cfg.max_seq_len);
+    const int p = (int)pos;
+    MCU(cudaMemcpyAsync(m->d_pos, &p, 4, cudaMemcpyHostToDevice, m->e->stream));
+    MCU(cudaStreamSynchronize(m->e->stream));
+    m->pos = pos;
+    return ALICE_OK;
+}
+
+int32_t alice_model_rollback_to(alice_model* m, uint32_t pos) {
+    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_rollback_to: null model");
+    if (pos > m->pos) return ALICE_OK;  // only ever lowers the counter (src/gpu.rs:5645-5652)
+    return alice_model_set_position(m, pos);
+}
+
+int32_t alice_model_reset(alice_model* m) {
+    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_reset: null model");
+    const size_t kv_bytes = (size_t)m->cfg.num_layers * m->cfg.max_seq_len * m->cfg.num_kv_heads * m->cfg.head_dim * 4;
+    MCU(cudaMemsetAsync(m->kcache, 0, kv_bytes, m->e->stream));
+    MCU(cudaMemsetAsync(m->vcache, 0, kv_bytes, m->e->stream));
+    return alice_model_set_position(m, 0);
+}
+
+static int kv_copy(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos, float* k, float* v, bool to_device) {
+    if (!m || !k || !v) return alice_fail(ALICE_E_INVALID, "alice_model_kv: null argument");
+    const alice_model_config& c = m->cfg;
+    if (layer >= c.num_layers || (uint64_t)pos0 + npos > c.max_seq_len) return alice_fail(ALICE_E_SHAPE, "alice_model_kv: layer / position out of range");
+    const size_t kv_dim = (size_t)c.num_kv_heads * c.head_dim;
+    const size_t off = ((size_t)layer * c.max_seq_len + pos0) * kv_dim, bytes = (size_t)npos * kv_dim * 4;
+    cudaStream_t st = m->e->stream;
+    if (to_device) {
+        MCU(cudaMemcpyAsync(m->kcache + off, k, bytes, cudaMemcpyHostToDevice, st));
+        MCU(cudaMemcpyAsync(m->vcache + off, v, bytes, cudaMemcpyHostToDevice, st));
+    } else {
+        MCU(cudaMemcpyAsync(k, m->kcache + off, bytes, cudaMemcpyDeviceToHost, st));
+        MCU(cudaMemcpyAsync(v, m->vcache + off, bytes, cudaMemcpyDeviceToHost, st));
+    }
+    MCU(cudaStreamSynchronize(st));
+    return ALICE_OK;
+}
+
+int32_t alice_model_kv_write(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos, const float* k, const float* v) {
+    return kv_copy(m, layer, pos0, npos, const_cast<float*>(k), const_cast<float*>(v), true);
+}
+
+int32_t alice_model_kv_read(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos, float* k, float* v) {
+    return kv_copy(m, layer, pos0, npos, k, v, false);
+}
+
+}  // extern "C"

@@ -117,7 +117,8 @@ class GpuEngine:
     def close(self):
         """Frees every buffer still alive on this engine (their C handles point at it), then the engine."""
         if getattr(self, "_h", None):
-            for child in list(self._children):
+            children = list(self._children)
+            for child in [c for c in children if isinstance(c, GpuModel)] + [c for c in children if not isinstance(c, GpuModel)]:
                 child.free()
             self._lib.alice_engine_destroy(self._h)
             self._h = None
@@ -328,3 +329,125 @@ class GpuPass:
         out = self.engine.read_f32(buf)
         self.engine.sync()
         return out
+
+
+class GpuModelConfig:
+    """GpuModelConfig (src/gpu.rs:2111-2151), the fields the Llama-style layer stack uses."""
+
+    def __init__(self, num_layers, hidden_dim, intermediate_dim, num_heads, num_kv_heads, head_dim, rope_theta, eps,
+                 max_seq_len, vocab_size, neox_rope=False):
+        self.num_layers, self.hidden_dim, self.intermediate_dim = num_layers, hidden_dim, intermediate_dim
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.rope_theta, self.eps, self.max_seq_len = rope_theta, eps, max_seq_len
+        self.vocab_size, self.neox_rope = vocab_size, neox_rope
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["num_layers"], d["hidden_dim"], d["intermediate_dim"], d["num_heads"], d["num_kv_heads"],
+                   d["head_dim"], d["rope_theta"], d["eps"], d["max_seq_len"], d["vocab_size"], bool(d.get("neox_rope", 0)))
+
+
+class GpuModel:
+    """GpuModel (src/gpu.rs:2348): the pre-built decode graph of a Llama-style model on one device.
+
+    ``GpuModel.load(engine, model, config)`` takes the raw quantized tensors (a dict as built by
+    ``synth.make_llama``, standing in for the GgufFile of src/gpu.rs:2831) and uploads them verbatim."""
+
+    def __init__(self, engine: GpuEngine, handle, config: GpuModelConfig, keep):
+        self.engine, self._h, self._config, self._keep = engine, handle, config, keep
+        engine._children.add(self)
+
+    @classmethod
+    def load(cls, engine: GpuEngine, model: dict, config: GpuModelConfig | None = None, device_tensors=None) -> "GpuModel":
+        cfg = config or GpuModelConfig.from_dict(model["config"])
+        q_dim, kv_dim = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        H, F = cfg.hidden_dim, cfg.intermediate_dim
+        shapes = {"q": (q_dim, H), "k": (kv_dim, H), "v": (kv_dim, H), "o": (H, q_dim), "gate": (F, H), "up": (F, H),
+                  "down": (H, F)}
+        keep = []
+
+        def up(entry, rows, cols):
+            t, data = entry
+            w = engine.upload_weights_typed(data, rows, cols, GpuQuantType(t))
+            keep.append(w)
+            return w
+
+        layers = (_lib.LayerWeights * cfg.num_layers)()
+        for i, L in enumerate(model["layers"]):
+            for n, (r, c) in shapes.items():
+                setattr(layers[i], n, up(L[n], r, c)._h)
+            an, fn = _np(L["attn_norm"], np.float32), _np(L["ffn_norm"], np.float32)
+            keep += [an, fn]
+            layers[i].attn_norm, layers[i].ffn_norm = an.ctypes.data, fn.ctypes.data
+        emb = up(model["embedding"], cfg.vocab_size, H)
+        out = up(model["output"], cfg.vocab_size, H)
+        onorm = _np(model["output_norm"], np.float32)
+        c = _lib.ModelConfig(cfg.num_layers, H, F, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.vocab_size,
+                             cfg.max_seq_len, cfg.rope_theta, cfg.eps, int(cfg.neox_rope))
+        h = C.c_void_p()
+        check(engine._lib.alice_model_create(engine._h, C.byref(c), C.byref(layers), emb._h, _ptr(onorm), out._h,
+                                             C.byref(h)))
+        return cls(engine, h, cfg, keep)
+
+    def config(self) -> GpuModelConfig:
+        return self._config
+
+    def free(self):
+        if self._h:
+            self.engine._lib.alice_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    # -- src/gpu.rs:5010-5052 --
+    def forward(self, token_id: int):
+        check(self.engine._lib.alice_model_forward(self._h, token_id))
+
+    def forward_and_read(self, token_id: int) -> np.ndarray:
+        out = np.empty(self._config.vocab_size, np.float32)
+        check(self.engine._lib.alice_model_forward_read(self._h, token_id, _ptr(out)))
+        return out
+
+    def read_logits(self) -> np.ndarray:
+        out = np.empty(self._config.vocab_size, np.float32)
+        check(self.engine._lib.alice_model_read_logits(self._h, _ptr(out)))
+        return out
+
+    def decode_greedy(self, first_token: int, n: int) -> np.ndarray:
+        out = np.empty(n, np.uint32)
+        check(self.engine._lib.alice_model_decode_greedy(self._h, first_token, n, _ptr(out)))
+        return out
+
+    # -- src/gpu.rs:5618-5662 --
+    def position(self) -> int:
+        p = C.c_uint32()
+        check(self.engine._lib.alice_model_position(self._h, C.byref(p)))
+        return p.value
+
+    def vocab_size(self) -> int:
+        return self._config.vocab_size
+
+    def rollback_to(self, pos: int):
+        check(self.engine._lib.alice_model_rollback_to(self._h, pos))
+
+    def reset(self):
+        check(self.engine._lib.alice_model_reset(self._h))
+
+    # -- pre-filled context (no reference counterpart: the benchmark starts from a filled KV cache) --
+    def kv_write(self, layer: int, pos0: int, k, v):
+        k, v = _np(k, np.float32), _np(v, np.float32)
+        kv_dim = self._config.num_kv_heads * self._config.head_dim
+        check(self.engine._lib.alice_model_kv_write(self._h, layer, pos0, k.size // kv_dim, _ptr(k), _ptr(v)))
+
+    def kv_read(self, layer: int, pos0: int, npos: int):
+        kv_dim = self._config.num_kv_heads * self._config.head_dim
+        k, v = np.empty((npos, kv_dim), np.float32), np.empty((npos, kv_dim), np.float32)
+        check(self.engine._lib.alice_model_kv_read(self._h, layer, pos0, npos, _ptr(k), _ptr(v)))
+        return k, v
+
+    def set_position(self, pos: int):
+        check(self.engine._lib.alice_model_set_position(self._h, pos))

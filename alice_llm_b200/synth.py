@@ -132,3 +132,31 @@ def ternary_to_sparse(pos: np.ndarray, neg: np.ndarray, cols: int):
 def make_x(rng, n: int, batch: int = 1) -> np.ndarray:
     """Activations ~ N(0,1), f32, layout x[k*n + c]."""
     return rng.standard_normal(batch * n, dtype=np.float32)
+
+
+def make_llama(rng, cfg: dict, mix: dict | None = None) -> dict:
+    """Random-init Llama-architecture model as raw quantized blocks.
+
+    cfg keys: num_layers, hidden_dim, intermediate_dim, num_heads, num_kv_heads, head_dim, vocab_size,
+    max_seq_len, rope_theta, eps. ``mix`` maps tensor role -> GGML type; the default is the Q4_K_M mix
+    of the 8B benchmark configuration: q/k/v/o/gate/up Q4_K, down and output head Q6_K, embedding Q8_0.
+    RMSNorm weights are 1 + N(0, 0.02)."""
+    mix = {"q": Q4_K, "k": Q4_K, "v": Q4_K, "o": Q4_K, "gate": Q4_K, "up": Q4_K, "down": Q6_K, "output": Q6_K,
+           **(mix or {})}
+    H, F = cfg["hidden_dim"], cfg["intermediate_dim"]
+    q_dim, kv_dim = cfg["num_heads"] * cfg["head_dim"], cfg["num_kv_heads"] * cfg["head_dim"]
+    shapes = {"q": (q_dim, H), "k": (kv_dim, H), "v": (kv_dim, H), "o": (H, q_dim), "gate": (F, H), "up": (F, H),
+              "down": (H, F)}
+
+    def norm():
+        return (1.0 + 0.02 * rng.standard_normal(H, dtype=np.float32)).astype(np.float32)
+
+    layers = []
+    for _ in range(cfg["num_layers"]):
+        L = {n: (mix[n], make_weights(mix[n], rng, *shapes[n])) for n in shapes}
+        L["attn_norm"], L["ffn_norm"] = norm(), norm()
+        layers.append(L)
+    return {"config": dict(cfg), "layers": layers,
+            "embedding": (Q8_0, make_q8_0(rng, cfg["vocab_size"], H)),
+            "output_norm": norm(),
+            "output": (mix["output"], make_weights(mix["output"], rng, cfg["vocab_size"], H))}

@@ -129,6 +129,50 @@ int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alic
 /* dequantize_weight_row / GgufFile::tensor_to_f32 (src/gguf.rs:6168, 574): out[r*cols + c], bit-exact. */
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out);
 
+/* ---- decode model ------------------------------------------------------------------------- */
+/* GpuModel (src/gpu.rs:2348) for the Llama-style attention + SwiGLU layer stack, i.e. the Llama branch
+ * of Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613): per layer
+ * rms_norm -> q/k/v matvec -> RoPE -> KV append -> GQA attention -> o matvec + residual ->
+ * rms_norm -> fused SwiGLU gate/up -> down matvec + residual; then output norm and head.
+ * One decode step is ~7 kernels per layer replayed from a CUDA graph; position and token live on
+ * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations). */
+typedef struct alice_model alice_model;
+typedef struct {                       /* GpuModelConfig, src/gpu.rs:2111-2151 */
+    uint32_t num_layers, hidden_dim, intermediate_dim, num_heads, num_kv_heads, head_dim;
+    uint32_t vocab_size, max_seq_len;
+    float rope_theta, eps;
+    uint32_t neox_rope;                /* 0 = pairs (i, i+1) (Llama), 1 = (i, i + d/2) */
+} alice_model_config;
+typedef struct {                       /* one transformer layer; norms are host arrays of hidden_dim floats */
+    const alice_weights *q, *k, *v, *o, *gate, *up, *down;
+    const float *attn_norm, *ffn_norm;
+} alice_layer_weights;
+/* GpuModel::load (src/gpu.rs:2831). Weight handles are borrowed and must outlive the model. The
+ * embedding is a Q8_0 table [vocab][hidden] kept quantized; a row is dequantized per token. */
+int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const alice_layer_weights* layers,
+                           const alice_weights* embedding, const float* output_norm, const alice_weights* output,
+                           alice_model** out);
+int32_t alice_model_destroy(alice_model* m);
+/* GpuModel::forward / forward_and_read (src/gpu.rs:5010, 5033): one token at the current position. */
+int32_t alice_model_forward(alice_model* m, uint32_t token);
+int32_t alice_model_forward_read(alice_model* m, uint32_t token, float* logits);
+/* Greedy decode loop (Llama3Model::generate's decode loop, src/llama3.rs:16084, with argmax sampling):
+ * feeds first_token, then n-1 times the argmax of the previous logits; out_tokens[i] = argmax after
+ * step i. No host round trip between steps. */
+int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t n, uint32_t* out_tokens);
+int32_t alice_model_read_logits(alice_model* m, float* logits);
+/* position / vocab_size / rollback_to / reset (src/gpu.rs:5655, 5660, 5645, 5618). rollback only lowers
+ * the position; reset also zeroes the KV cache. */
+int32_t alice_model_position(const alice_model* m, uint32_t* pos);
+int32_t alice_model_vocab_size(const alice_model* m, uint32_t* vocab);
+int32_t alice_model_rollback_to(alice_model* m, uint32_t pos);
+int32_t alice_model_reset(alice_model* m);
+/* Write / read KV rows of one layer, layout [pos][num_kv_heads * head_dim] as KvCache (src/llama3.rs:4731),
+ * and set the position: used to start from a pre-filled context. */
+int32_t alice_model_kv_write(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos, const float* k, const float* v);
+int32_t alice_model_kv_read(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos, float* k, float* v);
+int32_t alice_model_set_position(alice_model* m, uint32_t pos);
+
 /* ---- no-allocation variant ---------------------------------------------------------------- */
 /* Has no counterpart in the reference. alice_matvec_preq for Q1_0 / Q2_0 weights needs an f32 copy
  * of the Q8_K input and takes it from engine scratch obtained with cudaMalloc. This variant is for

@@ -451,9 +451,139 @@ float sparse_ternary_dot_scalar(const uint16_t* active, const uint16_t* sign, fl
 // src/llama3.rs:5767
 inline float silu(float x) { return x / (1.0f + std::exp(-x)); }
 
+// ── model glue (src/llama3.rs) ──────────────────────────────────────────────
+// rms_norm, src/llama3.rs:5244-5256
+void rms_norm(const float* x, const float* w, float eps, float* out, size_t n) {
+    double ss = 0.0;
+    for (size_t i = 0; i < n; i++) ss += (double)x[i] * (double)x[i];
+    float mean = (float)(ss / (double)n);
+    float scale = 1.0f / std::sqrt(mean + eps);
+    for (size_t i = 0; i < n; i++) out[i] = x[i] * scale * w[i];
+}
+
+// apply_rope / apply_rope_neox, src/llama3.rs:5323-5333, 5367-5378
+void apply_rope(float* v, size_t pos, size_t head_dim, float theta, bool neox) {
+    if (!neox) {
+        for (size_t i = 0; i < head_dim; i += 2) {
+            float freq = 1.0f / std::pow(theta, (float)i / (float)head_dim);
+            float angle = (float)pos * freq;
+            float sn = std::sin(angle), cs = std::cos(angle);
+            float x0 = v[i], x1 = v[i + 1];
+            v[i] = x0 * cs - x1 * sn;
+            v[i + 1] = x0 * sn + x1 * cs;
+        }
+    } else {
+        size_t half = head_dim / 2;
+        for (size_t i = 0; i < half; i++) {
+            float freq = 1.0f / std::pow(theta, 2.0f * (float)i / (float)head_dim);
+            float angle = (float)pos * freq;
+            float sn = std::sin(angle), cs = std::cos(angle);
+            float x0 = v[i], x1 = v[i + half];
+            v[i] = x0 * cs - x1 * sn;
+            v[i + half] = x0 * sn + x1 * cs;
+        }
+    }
+}
+
+// gqa_attention, default two-pass branch, src/llama3.rs:5560-5689 (no sliding window, no softcap).
+// kc / vc: this layer's cache, [pos][kv_dim].
+void gqa_attention(const float* q, const float* kc, const float* vc, size_t pos, size_t num_heads,
+                   size_t num_kv_heads, size_t head_dim, float* out) {
+    size_t seq_len = pos + 1, per_kv = num_heads / num_kv_heads, kv_dim = num_kv_heads * head_dim;
+    float inv_sqrt_d = 1.0f / std::sqrt((float)head_dim);
+    std::fill(out, out + num_heads * head_dim, 0.0f);
+    std::vector<float> scores(seq_len);
+    for (size_t h = 0; h < num_heads; h++) {
+        size_t kvh = h / per_kv;
+        const float* qh = q + h * head_dim;
+        for (size_t t = 0; t < seq_len; t++) {
+            const float* k = kc + t * kv_dim + kvh * head_dim;
+            float acc = 0.0f;
+            for (size_t d = 0; d < head_dim; d++) acc += qh[d] * k[d];
+            scores[t] = acc * inv_sqrt_d;
+        }
+        float mx = -INFINITY;
+        for (size_t t = 0; t < seq_len; t++) mx = std::max(mx, scores[t]);
+        float sum = 0.0f;
+        for (size_t t = 0; t < seq_len; t++) { scores[t] = std::exp(scores[t] - mx); sum += scores[t]; }
+        if (sum > 0.0f) { float inv = 1.0f / sum; for (size_t t = 0; t < seq_len; t++) scores[t] *= inv; }
+        for (size_t t = 0; t < seq_len; t++) {
+            const float* v = vc + t * kv_dim + kvh * head_dim;
+            float w = scores[t];
+            for (size_t d = 0; d < head_dim; d++) out[h * head_dim + d] += w * v[d];
+        }
+    }
+}
+
+}  // namespace
+
+// Plain-C description of a model for orc_llama_forward (shared with the CUDA tests through ctypes).
+extern "C" {
+struct OrcLayer {
+    const uint8_t *q, *k, *v, *o, *gate, *up, *down;
+    uint32_t tq, tk, tv, to, tgate, tup, tdown;   // GGML type ids
+    const float *attn_norm, *ffn_norm;
+};
+struct OrcModel {
+    uint32_t num_layers, hidden, ffn, num_heads, num_kv_heads, head_dim, vocab, max_seq;
+    float theta, eps;
+    uint32_t neox;
+    const OrcLayer* layers;
+    const uint8_t* emb_q8_0;      // [vocab][hidden] Q8_0
+    const float* out_norm;
+    const uint8_t* out;           // [vocab][hidden]
+    uint32_t tout;
+    float *kcache, *vcache;       // [layer][max_seq][kv_dim], written at `pos`
+};
+}
+
+namespace {
+
+size_t mat_bytes(uint32_t t, size_t rows, size_t cols) { return rows * (cols / elements_per_block(t)) * block_bytes(t); }
+
+// Llama branch of Llama3Model::forward_with_layer_hook (src/llama3.rs:13681-13687, 14167-14613).
+// MV(type, x, data, nbytes, rows, cols, y) = WeightRef::matvec; MVP(..., d8, q8, bs, y) = matvec_preq.
+template <class MV, class MVP>
+int llama_forward(const OrcModel& m, uint32_t token, uint32_t pos, float* logits, MV mv, MVP mvp) {
+    const size_t H = m.hidden, F = m.ffn, hd = m.head_dim, q_dim = (size_t)m.num_heads * hd, kv_dim = (size_t)m.num_kv_heads * hd;
+    if (token >= m.vocab || pos >= m.max_seq || H % QK_K) return -1;
+    std::vector<float> hidden(H), norm(H), q(q_dim), k(kv_dim), v(kv_dim), attn(q_dim), o(H), gate(F), up(F), down(H);
+    dequantize_q8_0(m.emb_q8_0 + (size_t)token * (H / 32) * 34, (H / 32) * 34, hidden.data());
+    const size_t nb = H / QK_K;
+    std::vector<float> d8(nb); std::vector<int8_t> q8(nb * QK_K); std::vector<int16_t> bs(nb * 16);
+    for (uint32_t l = 0; l < m.num_layers; l++) {
+        const OrcLayer& L = m.layers[l];
+        float* kc = m.kcache + (size_t)l * m.max_seq * kv_dim;
+        float* vc = m.vcache + (size_t)l * m.max_seq * kv_dim;
+        rms_norm(hidden.data(), L.attn_norm, m.eps, norm.data(), H);
+        quantize_row_q8_k(norm.data(), H, d8.data(), q8.data(), bs.data());   // once for q, k, v (:14206)
+        if (mvp(L.tq, L.q, mat_bytes(L.tq, q_dim, H), q_dim, H, d8.data(), q8.data(), bs.data(), q.data())) return -2;
+        if (mvp(L.tk, L.k, mat_bytes(L.tk, kv_dim, H), kv_dim, H, d8.data(), q8.data(), bs.data(), k.data())) return -2;
+        if (mvp(L.tv, L.v, mat_bytes(L.tv, kv_dim, H), kv_dim, H, d8.data(), q8.data(), bs.data(), v.data())) return -2;
+        for (uint32_t h = 0; h < m.num_heads; h++) apply_rope(q.data() + h * hd, pos, hd, m.theta, m.neox != 0);
+        for (uint32_t h = 0; h < m.num_kv_heads; h++) apply_rope(k.data() + h * hd, pos, hd, m.theta, m.neox != 0);
+        std::memcpy(kc + (size_t)pos * kv_dim, k.data(), kv_dim * 4);
+        std::memcpy(vc + (size_t)pos * kv_dim, v.data(), kv_dim * 4);
+        gqa_attention(q.data(), kc, vc, pos, m.num_heads, m.num_kv_heads, hd, attn.data());
+        if (mv(L.to, attn.data(), L.o, mat_bytes(L.to, H, q_dim), H, q_dim, o.data())) return -2;
+        for (size_t i = 0; i < H; i++) hidden[i] += o[i];
+        rms_norm(hidden.data(), L.ffn_norm, m.eps, norm.data(), H);
+        quantize_row_q8_k(norm.data(), H, d8.data(), q8.data(), bs.data());   // once for gate, up (:14519)
+        if (mvp(L.tgate, L.gate, mat_bytes(L.tgate, F, H), F, H, d8.data(), q8.data(), bs.data(), gate.data())) return -2;
+        if (mvp(L.tup, L.up, mat_bytes(L.tup, F, H), F, H, d8.data(), q8.data(), bs.data(), up.data())) return -2;
+        for (size_t i = 0; i < F; i++) gate[i] = silu(gate[i]) * up[i];
+        if (mv(L.tdown, gate.data(), L.down, mat_bytes(L.tdown, H, F), H, F, down.data())) return -2;
+        for (size_t i = 0; i < H; i++) hidden[i] += down[i];
+    }
+    rms_norm(hidden.data(), m.out_norm, m.eps, norm.data(), H);
+    if (mv(m.tout, norm.data(), m.out, mat_bytes(m.tout, m.vocab, H), m.vocab, H, logits)) return -2;
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
+
 
 float orc_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
 int orc_block_bytes(uint32_t t) { return block_bytes(t); }
@@ -646,5 +776,22 @@ void orc_ternary_swiglu(const uint8_t* gpos, const uint8_t* gneg, const float* g
 }
 
 float orc_silu(float x) { return silu(x); }
+
+void orc_rms_norm(const float* x, const float* w, float eps, float* out, size_t n) { rms_norm(x, w, eps, out, n); }
+void orc_apply_rope(float* v, size_t pos, size_t head_dim, float theta, int neox) { apply_rope(v, pos, head_dim, theta, neox != 0); }
+void orc_gqa_attention(const float* q, const float* kc, const float* vc, size_t pos, size_t num_heads, size_t num_kv_heads,
+                       size_t head_dim, float* out) {
+    gqa_attention(q, kc, vc, pos, num_heads, num_kv_heads, head_dim, out);
+}
+
+// One token through the Llama branch of the CPU forward; appends K/V at `pos` in m->kcache / vcache.
+int orc_llama_forward(const OrcModel* m, uint32_t token, uint32_t pos, float* logits) {
+    return llama_forward(*m, token, pos, logits,
+                         [](uint32_t t, const float* x, const uint8_t* d, size_t nb, size_t r, size_t c, float* y) {
+                             return orc_matvec(t, x, d, nb, r, c, y);
+                         },
+                         [](uint32_t t, const uint8_t* d, size_t nb, size_t r, size_t c, const float* d8, const int8_t* q8,
+                            const int16_t* bs, float* y) { return orc_matvec_preq(t, d, nb, r, c, d8, q8, bs, y); });
+}
 
 }  // extern "C"

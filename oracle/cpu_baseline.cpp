@@ -68,6 +68,24 @@ void base_ternary_matvec(const uint8_t* pos, const uint8_t* neg, const float* sc
     });
 }
 
+// Llama3Model::forward with the `parallel` feature: the oracle's forward with row-parallel matvecs.
+int base_llama_forward(const OrcModel* m, uint32_t token, uint32_t pos, float* logits, int nthreads) {
+    return llama_forward(
+        *m, token, pos, logits,
+        [nthreads](uint32_t t, const float* x, const uint8_t* d, size_t nb, size_t r, size_t c, float* y) {
+            return base_matvec(t, x, d, nb, r, c, y, nthreads);
+        },
+        [nthreads](uint32_t t, const uint8_t* d, size_t nb, size_t r, size_t c, const float* d8, const int8_t* q8,
+                   const int16_t* bs, float* y) {
+            const size_t row_bytes = nb / r;
+            int rc = 0;
+            par_rows(r, nthreads, [&](size_t r0, size_t r1) {
+                if (orc_matvec_preq(t, d + r0 * row_bytes, (r1 - r0) * row_bytes, r1 - r0, c, d8, q8, bs, y + r0)) rc = -1;
+            });
+            return rc;
+        });
+}
+
 int base_hw_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

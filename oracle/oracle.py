@@ -257,3 +257,72 @@ def base_ffn(gu_type: int, gate, up, down_type: int, down, hidden: int, ffn: int
                         _p(dn, _u8p), C.c_size_t(dn.size), C.c_size_t(hidden), C.c_size_t(ffn), _p(x, _f32p),
                         _p(y, _f32p), C.c_int(nthreads))
     return y
+
+
+# ── Llama forward (orc_llama_forward / base_llama_forward) ──────────────────
+class _OrcLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("q", "k", "v", "o", "gate", "up", "down")] + \
+               [(n, C.c_uint32) for n in ("tq", "tk", "tv", "to", "tgate", "tup", "tdown")] + \
+               [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)]
+
+
+class _OrcModel(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("num_layers", "hidden", "ffn", "num_heads", "num_kv_heads", "head_dim",
+                                          "vocab", "max_seq")] + \
+               [("theta", C.c_float), ("eps", C.c_float), ("neox", C.c_uint32), ("layers", C.c_void_p),
+                ("emb_q8_0", C.c_void_p), ("out_norm", C.c_void_p), ("out", C.c_void_p), ("tout", C.c_uint32),
+                ("kcache", C.c_void_p), ("vcache", C.c_void_p)]
+
+
+class LlamaOracle:
+    """CPU forward of a synthetic model dict (alice_llm_b200.synth.make_llama): Llama branch of
+    Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613)."""
+
+    def __init__(self, model: dict, threads: int = 0):
+        cfg = model["config"]
+        self.cfg, self.model, self.threads = cfg, model, threads
+        kv_dim = cfg["num_kv_heads"] * cfg["head_dim"]
+        self.kcache = np.zeros((cfg["num_layers"], cfg["max_seq_len"], kv_dim), np.float32)
+        self.vcache = np.zeros_like(self.kcache)
+        self.pos = 0
+        self._layers = (_OrcLayer * cfg["num_layers"])()
+        self._keep = []
+        for i, L in enumerate(model["layers"]):
+            for n in ("q", "k", "v", "o", "gate", "up", "down"):
+                t, data = L[n]
+                setattr(self._layers[i], n, data.ctypes.data)
+                setattr(self._layers[i], "t" + n, t)
+            self._layers[i].attn_norm = L["attn_norm"].ctypes.data
+            self._layers[i].ffn_norm = L["ffn_norm"].ctypes.data
+        m = _OrcModel()
+        m.num_layers, m.hidden, m.ffn = cfg["num_layers"], cfg["hidden_dim"], cfg["intermediate_dim"]
+        m.num_heads, m.num_kv_heads, m.head_dim = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+        m.vocab, m.max_seq = cfg["vocab_size"], cfg["max_seq_len"]
+        m.theta, m.eps, m.neox = cfg["rope_theta"], cfg["eps"], int(cfg.get("neox_rope", 0))
+        m.layers = C.addressof(self._layers)
+        m.emb_q8_0 = model["embedding"][1].ctypes.data
+        m.out_norm = model["output_norm"].ctypes.data
+        m.tout, out = model["output"]
+        m.out = out.ctypes.data
+        m.kcache, m.vcache = self.kcache.ctypes.data, self.vcache.ctypes.data
+        self._m = m
+
+    def forward(self, token: int) -> np.ndarray:
+        logits = np.empty(self.cfg["vocab_size"], np.float32)
+        if self.threads > 1:
+            rc = baseline().base_llama_forward(C.byref(self._m), C.c_uint32(token), C.c_uint32(self.pos),
+                                               _p(logits, _f32p), C.c_int(self.threads))
+        else:
+            rc = lib().orc_llama_forward(C.byref(self._m), C.c_uint32(token), C.c_uint32(self.pos), _p(logits, _f32p))
+        if rc:
+            raise ValueError(f"oracle forward failed: {rc}")
+        self.pos += 1
+        return logits
+
+
+def rms_norm(x, w, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    out = np.empty_like(x)
+    lib().orc_rms_norm(_p(x, _f32p), _p(w, _f32p), C.c_float(eps), _p(out, _f32p), C.c_size_t(x.size))
+    return out
