@@ -131,7 +131,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     a.x = x; a.aux0 = w0.scales; a.aux1 = sw ? w1->scales : nullptr;
     a.y = op.y; a.status = cfg.status;
     a.rows = total_rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
-    a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid;
+    a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
 
     // warps per row: just enough lanes for one unit each, at most all eight

@@ -48,6 +48,7 @@ struct GemvOp {
     const float* norm_w = nullptr;                         // fused RMSNorm of x with these weights
     float norm_eps = 0.0f;
     const float* resid = nullptr;                          // y = resid + result
+    unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs
     float* y = nullptr;
 };
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);

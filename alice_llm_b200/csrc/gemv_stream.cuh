@@ -48,6 +48,9 @@ struct StreamArgs {
     float norm_eps;
     // Optional residual epilogue: y[row] = resid[row] + result (resid may alias y)
     const float* resid;
+    // Optional greedy-argmax epilogue: atomicMax of (order-preserving bits of y[i]) << 32 | ~i, so the
+    // largest value wins and, among equal values, the lowest index. The caller clears it to 0.
+    unsigned long long* argmax_key;
     // Up to three matrices of the same format and width share one launch (q, k, v): segment s owns
     // row groups [seg_g0[s], seg_g0[s+1]) and writes y + seg_y[s]. nseg == 1 for a single matrix.
     uint32_t nseg;
@@ -276,6 +279,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
                 if (lane == 0) mbar_arrive(smem_u32(&sm->red[s][slot]));
             } else {
                 if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status)) break;
+                unsigned long long key = 0ull;
                 if (lane < nrow) {
                     float v0 = 0.0f, v1 = 0.0f;
                     for (uint32_t p = 0; p < P; p++) {
@@ -288,6 +292,17 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
                     const uint32_t yi = a.seg_y[sg] + row;
                     if (a.resid != nullptr) r = __fadd_rn(a.resid[yi], r);
                     a.y[yi] = r;
+                    const uint32_t b = __float_as_uint(r);
+                    const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+                    if (r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
+                }
+                if (a.argmax_key != nullptr) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+                        key = other > key ? other : key;
+                    }
+                    if (lane == 0) atomicMax(a.argmax_key, key);
                 }
             }
         }

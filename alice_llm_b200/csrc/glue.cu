@@ -25,73 +25,93 @@ __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* 
     }
 }
 
-// RoPE on the q and k heads of qkv = [q | k | v] in place (pairs (i, i+1), or (i, i+d/2) for the
-// NeoX layout), then K and V of this position go into the cache at [pos][kv_dim].
-__global__ void rope_kv_kernel(float* __restrict__ qkv, const int* __restrict__ pos_ptr, AttnShape s, float theta,
-                               int neox, float* __restrict__ kcache, float* __restrict__ vcache) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const uint32_t pos = (uint32_t)*pos_ptr;
-    const uint32_t half = s.head_dim / 2;
-    const uint32_t q_pairs = s.num_heads * half, k_pairs = s.num_kv_heads * half;
-    const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
-    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
-    if (tid < q_pairs + k_pairs) {
-        const bool is_k = tid >= q_pairs;
-        const uint32_t p = is_k ? tid - q_pairs : tid;
-        const uint32_t h = p / half, j = p % half;
-        float* v = qkv + (is_k ? q_dim : 0) + h * s.head_dim;
-        const uint32_t i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
-        // freq = 1 / theta^(i / head_dim) with i the even index 2j (both layouts)
-        const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn((float)(2 * j), (float)s.head_dim)));
-        const float angle = __fmul_rn((float)pos, freq);
-        float sn, cs;
-        sincosf(angle, &sn, &cs);
-        const float x0 = v[i0], x1 = v[i1];
-        const float r0 = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
-        const float r1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
-        v[i0] = r0; v[i1] = r1;
-        if (is_k) {
-            float* kc = kcache + (size_t)pos * kv_dim + h * s.head_dim;
-            kc[i0] = r0; kc[i1] = r1;
-        }
-    } else if (tid < q_pairs + k_pairs + kv_dim) {
-        const uint32_t i = tid - q_pairs - k_pairs;
-        vcache[(size_t)pos * kv_dim + i] = qkv[q_dim + kv_dim + i];
+// RoPE of the 4 consecutive dims (4*lane .. 4*lane+3) a lane owns of one head vector (apply_rope /
+// apply_rope_neox, src/llama3.rs:5323-5333, 5367-5378): pairs (i, i+1), or (i, i + d/2) for NeoX,
+// freq = 1 / theta^(i_even / d), angle = pos * freq. head_dim = 128, so a NeoX partner sits in lane ^ 16.
+struct RopeCoef { float sn[4], cs[4]; };
+// sin / cos of the rotation angles of the dims a lane owns; they depend on the lane and the position
+// only, so a CTA computes them once and applies them to every head it touches.
+__device__ __forceinline__ RopeCoef rope_coef(uint32_t lane, uint32_t pos, float theta, int neox) {
+    const float hd = 128.0f;
+    RopeCoef c;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        // pairs layout: dims (4*lane + i) belong to pair with even index 4*lane + (i & ~1);
+        // NeoX layout: pair index j = 4*(lane & 15) + i, even index 2j
+        const float even = neox ? __fmul_rn(2.0f, (float)(4 * (lane & 15) + i)) : (float)(4 * lane + (i & ~1));
+        const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn(even, hd)));
+        sincosf(__fmul_rn((float)pos, freq), &c.sn[i], &c.cs[i]);
     }
+    return c;
+}
+__device__ __forceinline__ float4 rope4(float4 v, uint32_t lane, const RopeCoef& c, int neox) {
+    float r[4] = {v.x, v.y, v.z, v.w}, out[4];
+    if (!neox) {
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+            const float x0 = r[2 * p], x1 = r[2 * p + 1];
+            out[2 * p] = __fsub_rn(__fmul_rn(x0, c.cs[2 * p]), __fmul_rn(x1, c.sn[2 * p]));
+            out[2 * p + 1] = __fadd_rn(__fmul_rn(x0, c.sn[2 * p]), __fmul_rn(x1, c.cs[2 * p]));
+        }
+    } else {
+        const bool upper = lane >= 16;   // dims 64..127 are the second element of their pair
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float other = __shfl_xor_sync(0xffffffffu, r[i], 16);
+            const float x0 = upper ? other : r[i], x1 = upper ? r[i] : other;
+            out[i] = upper ? __fadd_rn(__fmul_rn(x0, c.sn[i]), __fmul_rn(x1, c.cs[i]))
+                           : __fsub_rn(__fmul_rn(x0, c.cs[i]), __fmul_rn(x1, c.sn[i]));
+        }
+    }
+    return make_float4(out[0], out[1], out[2], out[3]);
 }
 
+// GQA decode attention with RoPE, KV append and the split combine fused in.
 // One CTA = one KV head x one slice of positions; its GROUP = num_heads/num_kv_heads query heads share
 // every K and V row it reads. Each warp walks positions t, t+NW, ...; a lane owns 4 of the 128 dims.
-// Output per (split, head): running max m, sum l and the un-normalised accumulator acc[head_dim].
+// qkv = [q | k | v] of the current token, un-rotated: q and k are rotated here, the new K/V row is
+// used from registers and written to the cache at `pos` by the CTA whose slice contains it.
+// Per (split, head) the CTA leaves (max, sum, accumulator); the last CTA of a KV head to finish
+// (ticket counter) folds the splits into attn_out for its heads.
 template <int GROUP>
-__global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict__ qkv, const float* __restrict__ kcache,
-                                                         const float* __restrict__ vcache,
-                                                         const int* __restrict__ pos_ptr, AttnShape s, uint32_t nsplit,
-                                                         float* __restrict__ part) {
+__global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, float* __restrict__ kcache,
+                                                         float* __restrict__ vcache, const int* __restrict__ pos_ptr,
+                                                         AttnShape s, float theta, int neox, uint32_t nsplit,
+                                                         float* __restrict__ part, unsigned int* __restrict__ tickets,
+                                                         float* __restrict__ attn_out) {
     constexpr int NW = 8;
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t kvh = blockIdx.x, split = blockIdx.y;
-    const uint32_t seq = (uint32_t)*pos_ptr + 1;
+    const uint32_t pos = (uint32_t)*pos_ptr;
+    const uint32_t seq = pos + 1;
     const uint32_t per = (seq + nsplit - 1) / nsplit;
     const uint32_t t0 = split * per, t1 = min(seq, t0 + per);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t kv_dim = s.num_kv_heads * s.head_dim;
+    const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
     const float inv_sqrt_d = __fdiv_rn(1.0f, sqrtf((float)s.head_dim));
 
+    const RopeCoef rc = rope_coef(lane, pos, theta, neox);
     float4 q[GROUP];
 #pragma unroll
     for (int g = 0; g < GROUP; g++)
-        q[g] = reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim)[lane];
+        q[g] = rope4(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim)[lane], lane, rc, neox);
     float m[GROUP], l[GROUP];
     float4 acc[GROUP];
 #pragma unroll
     for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
 
     for (uint32_t t = t0 + warp; t < t1; t += NW) {
-        const float4 k = reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
-        const float4 v = reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
+        float4 k, v;
+        if (t == pos) {   // the token being decoded: rotate its K, append K and V (KvCache::append, src/llama3.rs:4773)
+            k = rope4(reinterpret_cast<const float4*>(qkv + q_dim + (size_t)kvh * s.head_dim)[lane], lane, rc, neox);
+            v = reinterpret_cast<const float4*>(qkv + q_dim + kv_dim + (size_t)kvh * s.head_dim)[lane];
+            reinterpret_cast<float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = k;
+            reinterpret_cast<float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = v;
+        } else {
+            k = reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
+            v = reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
+        }
         float sc[GROUP];
 #pragma unroll
         for (int g = 0; g < GROUP; g++) sc[g] = q[g].x * k.x + q[g].y * k.y + q[g].z * k.z + q[g].w * k.w;
@@ -113,12 +133,14 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict
     // combine the NW warps of the CTA
     __shared__ float sm_m[NW][GROUP], sm_l[NW][GROUP];
     __shared__ float4 sm_acc[NW][GROUP][32];
+    __shared__ unsigned int sm_last;
 #pragma unroll
     for (int g = 0; g < GROUP; g++) {
         if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
         sm_acc[warp][g][lane] = acc[g];
     }
     __syncthreads();
+    const uint32_t stride = s.head_dim + 4;   // (m, l, pad, pad, acc[128]): keeps acc 16-byte aligned
     if (warp < GROUP) {
         const int g = warp;
         float M = -INFINITY;
@@ -135,62 +157,71 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict
                 A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
             }
         }
-        const uint32_t head = kvh * GROUP + g;
-        float* out = part + ((size_t)split * s.num_heads + head) * (s.head_dim + 2);
+        float* out = part + ((size_t)split * s.num_heads + kvh * GROUP + g) * stride;
         if (lane == 0) { out[0] = M; out[1] = L; }
-        out[2 + 4 * lane] = A.x; out[3 + 4 * lane] = A.y; out[4 + 4 * lane] = A.z; out[5 + 4 * lane] = A.w;
+        reinterpret_cast<float4*>(out + 4)[lane] = A;
     }
-}
-
-// attn_out[head][d] = sum_s exp(m_s - M) acc_s[d] / sum_s exp(m_s - M) l_s
-__global__ void attn_combine_kernel(const float* __restrict__ part, AttnShape s, uint32_t nsplit,
-                                    float* __restrict__ attn_out) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const uint32_t head = blockIdx.x, d = threadIdx.x;
-    if (d >= s.head_dim) return;
-    const uint32_t stride = s.head_dim + 2;
-    float M = -INFINITY;
-    for (uint32_t sp = 0; sp < nsplit; sp++) M = fmaxf(M, part[((size_t)sp * s.num_heads + head) * stride]);
-    float L = 0.0f, A = 0.0f;
-    for (uint32_t sp = 0; sp < nsplit; sp++) {
-        const float* p = part + ((size_t)sp * s.num_heads + head) * stride;
-        if (p[0] == -INFINITY) continue;
-        const float c = expf(p[0] - M);
-        L += p[1] * c;
-        A += p[2 + d] * c;
-    }
-    attn_out[(size_t)head * s.head_dim + d] = L > 0.0f ? A / L : 0.0f;
-}
-
-// Greedy next token: index of the largest logit (lowest index on ties); also advances the position.
-__global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __restrict__ logits, uint32_t n,
-                                                              int* __restrict__ token, int* __restrict__ pos,
-                                                              int* __restrict__ trace, int write_token) {
-    pdl_wait();
-    pdl_launch_dependents();
-    float best = -INFINITY;
-    uint32_t bi = 0xFFFFFFFFu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = logits[i];
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-    }
-    __shared__ float sv[32];
-    __shared__ uint32_t si[32];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    // last CTA of this KV head folds the splits
+    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (uint32_t w = 1; w < (blockDim.x >> 5); w++)
-            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        const unsigned int ticket = atomicAdd(&tickets[kvh], 1u);
+        sm_last = (ticket == nsplit - 1) ? 1u : 0u;
+        if (sm_last) tickets[kvh] = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    if (warp < GROUP) {
+        // one warp per head; lane <-> split for the (max, sum) pairs, so all loads are in flight at once
+        const uint32_t head = kvh * GROUP + warp;
+        float ms[2], ls[2];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t sp = lane + 32 * i;
+            ms[i] = -INFINITY; ls[i] = 0.0f;
+            if (sp < nsplit) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part + ((size_t)sp * s.num_heads + head) * stride));
+                ms[i] = ml.x; ls[i] = ml.y;
+            }
+            M = fmaxf(M, ms[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float cs[2], L = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 2; i++) { cs[i] = ms[i] == -INFINITY ? 0.0f : expf(ms[i] - M); L += ls[i] * cs[i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (uint32_t sp = 0; sp < nsplit; sp++) {
+            const float c = __shfl_sync(0xffffffffu, sp < 32 ? cs[0] : cs[1], sp & 31);
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)sp * s.num_heads + head) * stride + 4) + lane);
+            A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+    }
+}
+
+// Turns the packed (ordered logit, ~row) maximum the output-head kernel accumulated into the next
+// token, records it, advances the position and clears the key for the next step.
+__global__ void finish_step_kernel(unsigned long long* __restrict__ key, int* __restrict__ token, int* __restrict__ pos,
+                                   int* __restrict__ trace, int write_token) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const unsigned long long k = *key;
         const int p = *pos;
-        if (write_token) { *token = (int)bi; if (trace) trace[p] = (int)bi; }
+        if (write_token) {
+            const int t = (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
+            *token = t;
+            if (trace) trace[p] = t;
+        }
         *pos = p + 1;
+        *key = 0ull;
     }
 }
 
@@ -209,39 +240,27 @@ cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t c
     return cudaLaunchKernelEx(&lc, embed_q8_0_kernel, table, token, cols, vocab, hidden);
 }
 
-cudaError_t launch_rope_kv(float* qkv, const int* pos, AttnShape s, float theta, int neox, float* kc, float* vc,
-                           cudaStream_t st, bool pdl) {
-    const uint32_t n = (s.num_heads + s.num_kv_heads) * (s.head_dim / 2) + s.num_kv_heads * s.head_dim;
-    cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
-    launch_cfg(lc, at, dim3((n + 255) / 256), dim3(256), st, pdl);
-    return cudaLaunchKernelEx(&lc, rope_kv_kernel, qkv, pos, s, theta, neox, kc, vc);
-}
-
-cudaError_t launch_attention(const float* qkv, const float* kc, const float* vc, const int* pos, AttnShape s,
-                             uint32_t nsplit, float* part, float* attn_out, cudaStream_t st, bool pdl) {
+cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, float theta, int neox,
+                             uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, cudaStream_t st, bool pdl) {
     if (s.head_dim != 128 || s.num_heads % s.num_kv_heads) return cudaErrorInvalidValue;
     const uint32_t group = s.num_heads / s.num_kv_heads;
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(s.num_kv_heads, nsplit), dim3(256), st, pdl);
-    cudaError_t err;
     switch (group) {
-        case 1: err = cudaLaunchKernelEx(&lc, attn_split_kernel<1>, qkv, kc, vc, pos, s, nsplit, part); break;
-        case 2: err = cudaLaunchKernelEx(&lc, attn_split_kernel<2>, qkv, kc, vc, pos, s, nsplit, part); break;
-        case 4: err = cudaLaunchKernelEx(&lc, attn_split_kernel<4>, qkv, kc, vc, pos, s, nsplit, part); break;
-        case 5: err = cudaLaunchKernelEx(&lc, attn_split_kernel<5>, qkv, kc, vc, pos, s, nsplit, part); break;
-        case 8: err = cudaLaunchKernelEx(&lc, attn_split_kernel<8>, qkv, kc, vc, pos, s, nsplit, part); break;
+        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
+        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
+        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
+        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
+        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
         default: return cudaErrorInvalidValue;
     }
-    if (err != cudaSuccess) return err;
-    launch_cfg(lc, at, dim3(s.num_heads), dim3(128), st, pdl);
-    return cudaLaunchKernelEx(&lc, attn_combine_kernel, (const float*)part, s, nsplit, attn_out);
 }
 
-cudaError_t launch_argmax_advance(const float* logits, uint32_t n, int* token, int* pos, int* trace, int write_token,
-                                  cudaStream_t st, bool pdl) {
+cudaError_t launch_finish_step(unsigned long long* key, int* token, int* pos, int* trace, int write_token, cudaStream_t st,
+                               bool pdl) {
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
-    launch_cfg(lc, at, dim3(1), dim3(1024), st, pdl);
-    return cudaLaunchKernelEx(&lc, argmax_advance_kernel, logits, n, token, pos, trace, write_token);
+    launch_cfg(lc, at, dim3(1), dim3(32), st, pdl);
+    return cudaLaunchKernelEx(&lc, finish_step_kernel, key, token, pos, trace, write_token);
 }
 
 }  // namespace alice

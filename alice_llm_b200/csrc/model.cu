@@ -25,6 +25,8 @@ struct alice_model {
     float *hidden = nullptr, *qkv = nullptr, *attn_out = nullptr, *ffn_h = nullptr, *logits = nullptr;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][max_seq][kv_dim]
     float* attn_part = nullptr;
+    unsigned int* attn_tickets = nullptr;
+    unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
     // device-side state: position, current token, tokens chosen per position
     int *d_pos = nullptr, *d_token = nullptr, *d_trace = nullptr;
@@ -96,8 +98,9 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
                 if (rc) return rc;
             }
         }
-        MCU(launch_rope_kv(m->qkv, m->d_pos, shape, c.rope_theta, (int)c.neox_rope, kc, vc, st, pdl));
-        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->nsplit, m->attn_part, m->attn_out, st, pdl));
+        // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
+        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, c.rope_theta, (int)c.neox_rope, m->nsplit, m->attn_part,
+                             m->attn_tickets, m->attn_out, st, pdl));
         {   // output projection + residual (src/llama3.rs:14423, 14468)
             GemvOp op;
             op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden;
@@ -121,10 +124,11 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
     {   // output norm + head (src/llama3.rs:14590-14604)
         GemvOp op;
         op.w[0] = &m->out; op.x = m->hidden; op.norm_w = m->out_norm; op.norm_eps = c.eps; op.y = m->logits;
+        op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum
         int rc = gemv(m, op, "output head");
         if (rc) return rc;
     }
-    MCU(launch_argmax_advance(m->logits, c.vocab_size, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
+    MCU(launch_finish_step(m->argmax_key, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
     return ALICE_OK;
 }
 
@@ -192,7 +196,9 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->logits, c.vocab_size);
     if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
-    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * c.num_heads * (c.head_dim + 2));
+    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * c.num_heads * (c.head_dim + 4));
+    if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads);
+    if (!rc) rc = dev_alloc(m, &m->argmax_key, 1);
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, 1);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
@@ -200,6 +206,8 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         cudaError_t err = cudaMemsetAsync(m->kcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)c.num_kv_heads * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->argmax_key, 0, 8, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
