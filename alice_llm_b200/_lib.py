@@ -56,6 +56,7 @@ SIGNATURES = {
     "alice_model_forward": (C.c_int32, [_vp, C.c_uint32]),
     "alice_model_forward_read": (C.c_int32, [_vp, C.c_uint32, _vp]),
     "alice_model_decode_greedy": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp]),
+    "alice_model_use_step_kernel": (C.c_int32, [_vp, C.c_int32]),
     "alice_model_read_logits": (C.c_int32, [_vp, _vp]),
     "alice_model_position": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),
     "alice_model_vocab_size": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),

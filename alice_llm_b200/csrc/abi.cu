@@ -170,7 +170,7 @@ int32_t alice_sync(alice_engine* e) {
     CU(cudaMemcpy(&st, e->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(e->status, 0, sizeof(int));
-        return fail(ALICE_E_KERNEL, "alice_sync: a kernel reported status %d (1 = barrier wait timed out)", st);
+        return fail(ALICE_E_KERNEL, "alice_sync: a kernel wait timed out (status 0x%x: low byte 2 = weights, 3 = partial sums, 4 = stage release, 5 = grid barrier; upper bits = op index)", st);
     }
     return ALICE_OK;
 }

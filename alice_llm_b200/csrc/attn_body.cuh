@@ -1,0 +1,197 @@
+// Device body of the fused decode attention (RoPE + KV append + split-KV GQA attention + split
+// combine), shared by the stand-alone kernel (csrc/glue.cu) and the whole-step kernel
+// (csrc/step_kernel.cu). Arithmetic: ALICE-LLM src/llama3.rs apply_rope :5323-5333, :5367-5378,
+// KvCache::append :4773, gqa_attention :5431-5690, evaluated as an online softmax over KV splits.
+#pragma once
+#include "common.cuh"
+#include "glue.cuh"
+
+namespace alice {
+
+struct RopeCoef { float sn[4], cs[4]; };
+// sin / cos of the rotation angles of the dims a lane owns; they depend on the lane and the position
+// only, so a CTA computes them once and applies them to every head it touches.
+__device__ __forceinline__ RopeCoef rope_coef(uint32_t lane, uint32_t pos, float theta, int neox) {
+    const float hd = 128.0f;
+    RopeCoef c;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        // pairs layout: dims (4*lane + i) belong to pair with even index 4*lane + (i & ~1);
+        // NeoX layout: pair index j = 4*(lane & 15) + i, even index 2j
+        const float even = neox ? __fmul_rn(2.0f, (float)(4 * (lane & 15) + i)) : (float)(4 * lane + (i & ~1));
+        const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn(even, hd)));
+        sincosf(__fmul_rn((float)pos, freq), &c.sn[i], &c.cs[i]);
+    }
+    return c;
+}
+__device__ __forceinline__ float4 rope4(float4 v, uint32_t lane, const RopeCoef& c, int neox) {
+    float r[4] = {v.x, v.y, v.z, v.w}, out[4];
+    if (!neox) {
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+            const float x0 = r[2 * p], x1 = r[2 * p + 1];
+            out[2 * p] = __fsub_rn(__fmul_rn(x0, c.cs[2 * p]), __fmul_rn(x1, c.sn[2 * p]));
+            out[2 * p + 1] = __fadd_rn(__fmul_rn(x0, c.sn[2 * p]), __fmul_rn(x1, c.cs[2 * p]));
+        }
+    } else {
+        const bool upper = lane >= 16;   // dims 64..127 are the second element of their pair
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float other = __shfl_xor_sync(0xffffffffu, r[i], 16);
+            const float x0 = upper ? other : r[i], x1 = upper ? r[i] : other;
+            out[i] = upper ? __fadd_rn(__fmul_rn(x0, c.sn[i]), __fmul_rn(x1, c.cs[i]))
+                           : __fsub_rn(__fmul_rn(x0, c.cs[i]), __fmul_rn(x1, c.sn[i]));
+        }
+    }
+    return make_float4(out[0], out[1], out[2], out[3]);
+}
+
+// GQA decode attention with RoPE, KV append and the split combine fused in.
+// One CTA = one KV head x one slice of positions; its GROUP = num_heads/num_kv_heads query heads share
+// every K and V row it reads. Each warp walks positions t, t+NW, ...; a lane owns 4 of the 128 dims.
+// qkv = [q | k | v] of the current token, un-rotated: q and k are rotated here, the new K/V row is
+// used from registers and written to the cache at `pos` by the CTA whose slice contains it.
+// Per (split, head) the CTA leaves (max, sum, accumulator); the last CTA of a KV head to finish
+// (ticket counter) folds the splits into attn_out for its heads.
+template <int GROUP>
+struct AttnSmem {
+    float m[8][GROUP], l[8][GROUP];
+    float4 acc[8][GROUP][32];
+    unsigned int last;
+};
+
+// CONSUMER_BAR: the 256 threads are the consumer warps of a larger CTA and meet on named barrier 1
+// instead of __syncthreads().
+template <bool CONSUMER_BAR>
+__device__ __forceinline__ void attn_sync() {
+    if (CONSUMER_BAR) asm volatile("bar.sync 1, 256;" ::: "memory");
+    else __syncthreads();
+}
+
+template <int GROUP, bool CONSUMER_BAR>
+__device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, float* __restrict__ kcache,
+                                                float* __restrict__ vcache, uint32_t pos, AttnShape s, float theta,
+                                                int neox, uint32_t nsplit, float* __restrict__ part,
+                                                unsigned int* __restrict__ tickets, float* __restrict__ attn_out,
+                                                uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh) {
+    constexpr int NW = 8;
+    const uint32_t seq = pos + 1;
+    const uint32_t per = (seq + nsplit - 1) / nsplit;
+    const uint32_t t0 = split * per, t1 = min(seq, t0 + per);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
+    const float inv_sqrt_d = __fdiv_rn(1.0f, sqrtf((float)s.head_dim));
+
+    const RopeCoef rc = rope_coef(lane, pos, theta, neox);
+    float4 q[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; g++)
+        q[g] = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim) + lane), lane, rc, neox);
+    float m[GROUP], l[GROUP];
+    float4 acc[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
+
+    for (uint32_t t = t0 + warp; t < t1; t += NW) {
+        float4 k, v;
+        if (t == pos) {   // the token being decoded: rotate its K, append K and V (KvCache::append, src/llama3.rs:4773)
+            k = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + q_dim + (size_t)kvh * s.head_dim) + lane), lane, rc, neox);
+            v = __ldcg(reinterpret_cast<const float4*>(qkv + q_dim + kv_dim + (size_t)kvh * s.head_dim) + lane);
+            reinterpret_cast<float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = k;
+            reinterpret_cast<float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = v;
+        } else {
+            k = __ldcg(reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
+            v = __ldcg(reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
+        }
+        float sc[GROUP];
+#pragma unroll
+        for (int g = 0; g < GROUP; g++) sc[g] = q[g].x * k.x + q[g].y * k.y + q[g].z * k.z + q[g].w * k.w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int g = 0; g < GROUP; g++) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+#pragma unroll
+        for (int g = 0; g < GROUP; g++) {
+            const float x = sc[g] * inv_sqrt_d;
+            const float mn = fmaxf(m[g], x);
+            const float corr = expf(m[g] - mn), p = expf(x - mn);
+            l[g] = l[g] * corr + p;
+            acc[g].x = acc[g].x * corr + p * v.x; acc[g].y = acc[g].y * corr + p * v.y;
+            acc[g].z = acc[g].z * corr + p * v.z; acc[g].w = acc[g].w * corr + p * v.w;
+            m[g] = mn;
+        }
+    }
+    // combine the NW warps of the CTA
+#pragma unroll
+    for (int g = 0; g < GROUP; g++) {
+        if (lane == 0) { sh->m[warp][g] = m[g]; sh->l[warp][g] = l[g]; }
+        sh->acc[warp][g][lane] = acc[g];
+    }
+    attn_sync<CONSUMER_BAR>();
+    const uint32_t stride = s.head_dim + 4;   // (m, l, pad, pad, acc[128]): keeps acc 16-byte aligned
+    if (warp < GROUP) {
+        const int g = warp;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; w++) M = fmaxf(M, sh->m[w][g]);
+        float L = 0.0f;
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < NW; w++) {
+                const float c = expf(sh->m[w][g] - M);   // exp(-inf) = 0 for warps that saw no position
+                L += sh->l[w][g] * c;
+                const float4 a = sh->acc[w][g][lane];
+                A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
+            }
+        }
+        float* out = part + ((size_t)split * s.num_heads + kvh * GROUP + g) * stride;
+        if (lane == 0) { out[0] = M; out[1] = L; }
+        reinterpret_cast<float4*>(out + 4)[lane] = A;
+    }
+    // last CTA of this KV head folds the splits
+    __threadfence();
+    attn_sync<CONSUMER_BAR>();
+    if (threadIdx.x == 0) {
+        const unsigned int ticket = atomicAdd(&tickets[kvh], 1u);
+        sh->last = (ticket == nsplit - 1) ? 1u : 0u;
+        if (sh->last) tickets[kvh] = 0;   // ready for the next launch
+    }
+    attn_sync<CONSUMER_BAR>();
+    if (!sh->last) return;
+    __threadfence();
+    if (warp < GROUP) {
+        // one warp per head; lane <-> split for the (max, sum) pairs, so all loads are in flight at once
+        const uint32_t head = kvh * GROUP + warp;
+        float ms[2], ls[2];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t sp = lane + 32 * i;
+            ms[i] = -INFINITY; ls[i] = 0.0f;
+            if (sp < nsplit) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part + ((size_t)sp * s.num_heads + head) * stride));
+                ms[i] = ml.x; ls[i] = ml.y;
+            }
+            M = fmaxf(M, ms[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float cs[2], L = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 2; i++) { cs[i] = ms[i] == -INFINITY ? 0.0f : expf(ms[i] - M); L += ls[i] * cs[i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (uint32_t sp = 0; sp < nsplit; sp++) {
+            const float c = __shfl_sync(0xffffffffu, sp < 32 ? cs[0] : cs[1], sp & 31);
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)sp * s.num_heads + head) * stride + 4) + lane);
+            A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+    }
+}
+
+}  // namespace alice

@@ -9,7 +9,12 @@ namespace alice {
 constexpr int QK_K = 256;
 
 // Status codes written by kernels into the engine's device status word.
-constexpr int KERR_WAIT_TIMEOUT = 1;   // an mbarrier wait ran out of its cycle budget
+// low byte: which wait ran out of its cycle budget; higher bits: index of the op inside a multi-op kernel
+constexpr int KERR_WAIT_TIMEOUT = 1;   // unspecified wait
+constexpr int KERR_WAIT_FULL = 2;      // consumer waiting for a weight stage to land
+constexpr int KERR_WAIT_PARTIALS = 3;  // row finalizer waiting for the other warps' partial sums
+constexpr int KERR_WAIT_EMPTY = 4;     // producer waiting for a stage to be released
+constexpr int KERR_WAIT_GRID = 5;      // grid-wide barrier
 
 // A wait that has not been satisfied after this many SM clock cycles (about one second) gives
 // up, records KERR_WAIT_TIMEOUT and lets the CTA drain and return instead of spinning forever.

@@ -6,6 +6,7 @@
 #include "../../include/alice_cuda.h"
 #include "formats.cuh"
 #include "gemv_launch.cuh"
+#include "gemv_plan.cuh"
 
 namespace alice {
 
@@ -96,7 +97,7 @@ int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView
     return launch_stream_gemv_op(op, cfg);
 }
 
-int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
+int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* lim, StreamPlan& pl) {
     if (op.nw < 1 || op.nw > 3 || !op.w[0] || !op.y) return ALICE_E_INVALID;
     const WeightDesc& w0 = *op.w[0];
     const WeightDesc* w1 = op.up;
@@ -143,16 +144,17 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     a.P = P; a.slots = NCW / P;
 
     const uint32_t nmat = sw ? 2 : 1;
-    static const char* env_cps = getenv("ALICE_CTAS_PER_SM");  // experiment knob
-    const uint32_t per_sm = env_cps ? (uint32_t)atoi(env_cps) : (kl <= 2 ? 2 : 1);
+    const uint32_t per_sm = kl <= 2 ? 2 : 1;
     // in-kernel Q8_K area: qs[cols] + bsums[nb][16] i16 + d[nb] f32; normalised input: f32[cols]
     const uint32_t q8_bytes = (format_uses_q8k(w0.fmt) && !q8) ? ((w0.cols / 256u) * 292u + 127u) & ~127u : 0u;
     const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
     const uint32_t full_budget = kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1;
-    if (HDR_BYTES + q8_bytes + xn_bytes + 4096 > full_budget) return ALICE_E_SHAPE;
-    const uint32_t budget = full_budget - HDR_BYTES - q8_bytes - xn_bytes;
-    const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
+    if (!lim && HDR_BYTES + q8_bytes + xn_bytes + 4096 > full_budget) return ALICE_E_SHAPE;
     uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
+    if (lim) nst = lim->nstages;
+    // bytes the ring may use: the CTA's budget, or nstages * the fixed stage stride of a multi-matvec kernel
+    const uint32_t budget = lim ? lim->nstages * lim->stage_stride : full_budget - HDR_BYTES - q8_bytes - xn_bytes;
+    const uint32_t ctas = lim ? lim->ctas : (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
     // rows per warp set per stage: as many as the ring allows (per-stage costs are amortised over
     // them) while every CTA still gets at least ~4 stages of work
     uint32_t rps_bytes = std::max<uint32_t>(1, (budget / nst - 256) / std::max<uint32_t>(1, a.slots * a.row_bytes * nmat));
@@ -165,7 +167,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         stage = cap * nmat;
         if (stage * nst <= budget) break;
         if (rps > 1) { rps--; continue; }
-        if (nst > 2) { nst--; continue; }
+        if (nst > 2 && !lim) { nst--; continue; }
         return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
     }
     a.rps = rps; a.cap = cap; a.nstages = nst;
@@ -177,10 +179,24 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         a.groups += (op.w[i]->rows + a.slots * rps - 1) / (a.slots * rps);
     }
     a.seg_g0[op.nw] = a.groups;
-    const uint32_t grid = std::min(ctas, a.groups);
+    pl.grid = std::min(ctas, a.groups);
     a.q8_off = HDR_BYTES + nst * stage;
     a.xn_off = a.q8_off + q8_bytes;
-    const size_t smem = HDR_BYTES + (size_t)nst * stage + q8_bytes + xn_bytes;
+    pl.smem = HDR_BYTES + (size_t)nst * stage + q8_bytes + xn_bytes;
+    pl.kl = kl; pl.swiglu = sw; pl.stage = stage; pl.q8_bytes = q8_bytes; pl.xn_bytes = xn_bytes;
+    pl.args = a;
+    return ALICE_OK;
+}
+
+int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
+    StreamPlan pl;
+    const int prc = plan_stream_gemv(op, cfg, nullptr, pl);
+    if (prc) return prc;
+    const StreamArgs& a = pl.args;
+    const WeightDesc& w0 = *op.w[0];
+    const uint32_t kl = pl.kl, grid = pl.grid;
+    const bool sw = pl.swiglu;
+    const size_t smem = pl.smem;
 
     switch (w0.fmt) {
         case WF_Q4_K: return launch_fmt<FmtQ4K>(a, kl, sw, grid, smem, cfg);

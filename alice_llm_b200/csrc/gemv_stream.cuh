@@ -68,16 +68,20 @@ struct StreamSmem {
     float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
     double norm_part[NCW];
     int abort_flag;
+    // multi-matvec kernels keep the arguments of the matvec in flight here (one copy for the consumer
+    // warps, one for the producer, which runs ahead) instead of re-reading them from global memory
+    StreamArgs cargs, pargs;
 };
 
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                              int code = KERR_WAIT_TIMEOUT, long long limit = WAIT_CYCLE_LIMIT) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
-            atomicExch(status, KERR_WAIT_TIMEOUT);
+            atomicCAS(status, 0, code);   // keep the first report
             return false;
         }
     }
@@ -110,80 +114,116 @@ __device__ __forceinline__ float reduce_values(float (&v)[NV], uint32_t lane) {
 // F supplies:
 //   struct Act;                                            per-position activation registers
 //   static constexpr bool USES_Q8K;                        integer dot against Q8_K activations
-//   static void load_act(Act&, const StreamArgs&, const float* x, const Q8KView&, uint32_t u, bool valid)
+//   static void load_act(Act&, const StreamArgs&, const float* x, bool x_cg, const Q8KView&, uint32_t u, bool valid)
 //   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
 //   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
-template <class F, int KL, bool SWIGLU>
-__global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
-    constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
-    const uint32_t ring = smem_u32(smem_raw) + HDR;
-    const uint32_t stage_bytes = a.cap * (SWIGLU ? 2u : 1u);
+// Per-CTA streaming state that outlives one matvec when several run back to back inside one
+// kernel: the ring and its full / empty barriers are shared, `cc` counts the chunks ever pushed
+// through it (stage = cc % nstages, phase from cc / nstages).
+struct StreamCtx {
+    StreamSmem* sm;
+    uint8_t* smem_raw;
+    uint32_t ring;          // shared address of stage 0
+    uint32_t stage_stride;  // bytes between stages
+    uint32_t nstages;
+    uint32_t cc;            // chunks streamed so far (producer and consumers keep separate copies in step)
+    int op;                 // index of the matvec inside a multi-op kernel (error reports)
+    bool acts_cg;           // read global activations with ld.global.cg (other SMs rewrite them inside this kernel)
+};
 
+// The per-(stage, warp set) barriers collect the P-1 helper warps of a row set. P changes from matvec
+// to matvec inside a multi-matvec kernel, so instead of re-initialising them each barrier expects
+// RED_COUNT = lcm(1, 3, 7) arrivals and every helper arrives with weight RED_COUNT / (P - 1). A barrier
+// that a stage does not use (no such row set, or no rows left for it) is completed by its own warp, so
+// every barrier finishes exactly one phase per stage use and shares the phase of the `full` barrier.
+constexpr uint32_t RED_COUNT = 21;
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t n) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(n) : "memory");
+}
+
+__device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstages) {
+    for (uint32_t s = 0; s < nstages; s++) {
+        mbar_init(smem_u32(&sm->full[s]), 1);
+        mbar_init(smem_u32(&sm->empty[s]), NCW);
+        for (uint32_t q = 0; q < NCW; q++) mbar_init(smem_u32(&sm->red[s][q]), RED_COUNT);
+    }
+    sm->abort_flag = 0;
+    mbar_fence_init();
+}
+
+__device__ __forceinline__ float ld_act(const float* p, bool cg) { return cg ? __ldcg(p) : *p; }
+
+// Producer side of one matvec: streams this CTA's row groups of `a` through the ring. One thread.
+__device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& cx) {
+    StreamSmem* sm = cx.sm;
+    volatile int* abort_flag = &sm->abort_flag;
+    const uint32_t rows_per_group = a.slots * a.rps;
+    const bool two = a.w1 != nullptr;
+    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
+    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
+    for (uint32_t g = g0; g < g1; g++) {
+        const uint32_t s = cx.cc % cx.nstages, use = cx.cc / cx.nstages;
+        if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status, KERR_WAIT_EMPTY + (cx.op << 8), 2 * WAIT_CYCLE_LIMIT)) return;
+        uint32_t sg = 0;
+        while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+        const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
+        const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
+        const uint64_t off = (uint64_t)r0 * a.row_bytes;
+        const uint64_t a0 = off & ~uint64_t(15);
+        const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
+        const uint32_t fb = smem_u32(&sm->full[s]);
+        mbar_arrive_expect_tx(fb, two ? 2 * cb : cb);
+        bulk_g2s(cx.ring + s * cx.stage_stride, a.seg_w[sg] + a0, cb, fb);
+        if (two) bulk_g2s(cx.ring + s * cx.stage_stride + a.cap, a.w1 + a0, cb, fb);
+        cx.cc++;
+    }
+}
+
+// After an abort: let copies already issued land before the CTA gives its shared memory back.
+__device__ __forceinline__ void stream_drain(StreamCtx& cx) {
+    const uint32_t first = cx.cc > cx.nstages ? cx.cc - cx.nstages : 0;
+    for (uint32_t c = first; c < cx.cc; c++) mbar_wait(smem_u32(&cx.sm->full[c % cx.nstages]), (c / cx.nstages) & 1);
+}
+
+// Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
+// Returns false after an abort.
+template <class F, int KL, bool SWIGLU>
+__device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
+    StreamSmem* sm = cx.sm;
+    uint8_t* smem_raw = cx.smem_raw;
+    volatile int* abort_flag = &sm->abort_flag;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;
     const uint32_t rows_per_group = slots * rps;
-
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < a.nstages; s++) {
-            mbar_init(smem_u32(&sm->full[s]), 1);
-            mbar_init(smem_u32(&sm->empty[s]), NCW);
-            for (uint32_t q = 0; q < slots; q++) mbar_init(smem_u32(&sm->red[s][q]), P > 1 ? P - 1 : 1);
-        }
-        sm->abort_flag = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-
-    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
-    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t nchunks = g1 - g0;
-    volatile int* abort_flag = &sm->abort_flag;
-
-    if (warp == NCW) {
-        // ── producer: weights do not depend on the previous kernel, so copies start at once ──
-        if (lane == 0) {
-            uint32_t issued = 0;
-            for (uint32_t c = 0; c < nchunks; c++) {
-                const uint32_t s = c % a.nstages, use = c / a.nstages;
-                if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status)) break;
-                const uint32_t g = g0 + c;
-                uint32_t sg = 0;
-                while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
-                const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
-                const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
-                const uint64_t off = (uint64_t)r0 * a.row_bytes;
-                const uint64_t a0 = off & ~uint64_t(15);
-                const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
-                const uint32_t fb = smem_u32(&sm->full[s]);
-                mbar_arrive_expect_tx(fb, SWIGLU ? 2 * cb : cb);
-                bulk_g2s(ring + s * stage_bytes, a.seg_w[sg] + a0, cb, fb);
-                if (SWIGLU) bulk_g2s(ring + s * stage_bytes + a.cap, a.w1 + a0, cb, fb);
-                issued = c + 1;
-            }
-            if (*abort_flag) {
-                // Drain: let copies already issued land before the CTA gives its shared memory back.
-                const uint32_t first = issued > a.nstages ? issued - a.nstages : 0;
-                for (uint32_t c = first; c < issued; c++)
-                    mbar_wait(smem_u32(&sm->full[c % a.nstages]), (c / a.nstages) & 1);
-            }
-        }
-        return;
-    }
-
-    // ── consumers ──
     const uint32_t slot = warp / P, part = warp % P;
-    pdl_wait();  // activations come from the previous kernel
+    const bool cg = cx.acts_cg;
+
     const float* x_src = a.x;
+    bool x_global = true;
     if (a.norm_w != nullptr) {
         // rms_norm (src/llama3.rs:5244-5256): f64 sum of squares, mean and scale in f32, then
         // (x * scale) * w; the normalised vector is kept in shared memory for this CTA only.
         float* xn = reinterpret_cast<float*>(smem_raw + a.xn_off);
-        const uint32_t tid = threadIdx.x;  // consumer threads are 0 .. NCW*32-1
+        const uint32_t tid = threadIdx.x;
+        // every thread keeps its share of x in registers (all loads in flight at once); cols is a
+        // multiple of 4 for every format here, rows wider than NCW*32*4*NORM_V floats take more rounds
+        constexpr int NORM_V = 8;
+        const uint32_t nvec = a.cols / 4;
+        const float4* xg = reinterpret_cast<const float4*>(a.x);
+        float4 xv[NORM_V];
         double ss = 0.0;
-        for (uint32_t i = tid; i < a.cols; i += NCW * 32) { const float v = a.x[i]; ss += (double)v * (double)v; }
+        for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++) {
+                const uint32_t i = base + k * NCW * 32 + tid;
+                xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < nvec) xv[k] = cg ? __ldcg(xg + i) : xg[i];
+            }
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++)
+                ss += (double)xv[k].x * (double)xv[k].x + (double)xv[k].y * (double)xv[k].y +
+                      (double)xv[k].z * (double)xv[k].z + (double)xv[k].w * (double)xv[k].w;
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) sm->norm_part[warp] = ss;
@@ -193,10 +233,24 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
         for (int w = 0; w < NCW; w++) tot += sm->norm_part[w];
         const float mean = (float)(tot / (double)a.cols);
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.norm_eps)));
-        for (uint32_t i = tid; i < a.cols; i += NCW * 32) xn[i] = __fmul_rn(__fmul_rn(a.x[i], scale), a.norm_w[i]);
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        const float4* wg = reinterpret_cast<const float4*>(a.norm_w);
+        const bool one_round = nvec <= NCW * 32 * NORM_V;   // then xv still holds this thread's whole share
+        for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++) {
+                const uint32_t i = base + k * NCW * 32 + tid;
+                if (i < nvec) {
+                    const float4 v = one_round ? xv[k] : (cg ? __ldcg(xg + i) : xg[i]);
+                    const float4 w = __ldg(wg + i);
+                    reinterpret_cast<float4*>(xn)[i] = make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
+                                                                   __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
+                }
+            }
+        }
         x_src = xn;
+        x_global = false;
     }
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // xn complete
     Q8KView q8 = a.q8;
     if (F::USES_Q8K && a.q8.qs == nullptr) {
         // f32 input: the consumer warps quantize it to Q8_K once per CTA into shared memory
@@ -214,7 +268,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint32_t blk = b0 + i * NCW;
-                if (blk < nb) in[i] = q8k_load_lane(x_src + (size_t)blk * QK_K, lane);
+                if (blk < nb) in[i] = q8k_load_lane(x_src + (size_t)blk * QK_K, lane, x_global && cg);
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -229,7 +283,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
 #pragma unroll
     for (int k = 0; k < KL; k++) {
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-        F::load_act(act[k], a, x_src, q8, u, u < a.units);
+        F::load_act(act[k], a, x_src, x_global && cg, q8, u, u < a.units);
     }
 
     // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
@@ -239,10 +293,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     constexpr int NV = RB * M;
     constexpr uint32_t LANES_PER_VALUE = 32 / NV;
 
-    for (uint32_t c = 0; c < nchunks; c++) {
-        const uint32_t s = c % a.nstages, ph = (c / a.nstages) & 1;
-        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status)) break;
-        const uint32_t g = g0 + c;
+    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
+    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
+    for (uint32_t g = g0; g < g1; g++) {
+        const uint32_t s = cx.cc % cx.nstages, ph = (cx.cc / cx.nstages) & 1;
+        cx.cc++;
+        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         uint32_t sg = 0;
         while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t seg_rows = a.seg_rows[sg];
@@ -250,7 +306,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
         const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
         const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
-        const uint32_t sb = ring + s * stage_bytes + pad + set0 * a.row_bytes;
+        const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_bytes;
         for (uint32_t rr0 = 0; rr0 < nrow; rr0 += RB) {
             float v[NV];
 #pragma unroll
@@ -274,11 +330,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
             if ((lane % LANES_PER_VALUE) == 0 && rr0 + vi / M < nrow) sm->partial[s][warp][rr0 + vi / M][vi % M] = tot;
         }
         __syncwarp();
+        {   // barrier red[s][warp] completes one phase per stage use even when no row set needs it
+            const uint32_t own0 = warp * rps;
+            const bool used = P > 1 && warp < slots && r0 + own0 < seg_rows;
+            if (!used && lane == 0) mbar_arrive_n(smem_u32(&sm->red[s][warp]), RED_COUNT);
+        }
         if (nrow > 0) {
             if (part != 0) {
-                if (lane == 0) mbar_arrive(smem_u32(&sm->red[s][slot]));
+                if (lane == 0) mbar_arrive_n(smem_u32(&sm->red[s][slot]), RED_COUNT / (P - 1));
             } else {
-                if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status)) break;
+                if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status, KERR_WAIT_PARTIALS + (cx.op << 8))) return false;
                 unsigned long long key = 0ull;
                 if (lane < nrow) {
                     float v0 = 0.0f, v1 = 0.0f;
@@ -290,7 +351,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr) r = __fadd_rn(a.resid[yi], r);
+                    if (a.resid != nullptr) r = __fadd_rn(ld_act(a.resid + yi, cg), r);
                     a.y[yi] = r;
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -309,6 +370,31 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
     }
+    return true;
+}
+
+// One matvec per launch.
+template <class F, int KL, bool SWIGLU>
+__global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
+    constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
+    StreamCtx cx;
+    cx.sm = sm; cx.smem_raw = smem_raw; cx.ring = smem_u32(smem_raw) + HDR;
+    cx.stage_stride = a.cap * (SWIGLU ? 2u : 1u); cx.nstages = a.nstages; cx.cc = 0; cx.op = 0; cx.acts_cg = false;
+    if (threadIdx.x == 0) stream_init_ring(sm, a.nstages);
+    __syncthreads();
+    pdl_launch_dependents();
+    if ((threadIdx.x >> 5) == NCW) {
+        // producer: weights do not depend on the previous kernel, so copies start at once
+        if ((threadIdx.x & 31) == 0) {
+            stream_produce(a, cx);
+            if (sm->abort_flag) stream_drain(cx);
+        }
+        return;
+    }
+    pdl_wait();  // activations come from the previous kernel
+    stream_consume<F, KL, SWIGLU>(a, cx);
 }
 
 }  // namespace alice

@@ -6,6 +6,7 @@
 // the f32 sums but not the math).
 #include "common.cuh"
 #include "glue.cuh"
+#include "attn_body.cuh"
 
 namespace alice {
 
@@ -28,182 +29,17 @@ __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* 
 // RoPE of the 4 consecutive dims (4*lane .. 4*lane+3) a lane owns of one head vector (apply_rope /
 // apply_rope_neox, src/llama3.rs:5323-5333, 5367-5378): pairs (i, i+1), or (i, i + d/2) for NeoX,
 // freq = 1 / theta^(i_even / d), angle = pos * freq. head_dim = 128, so a NeoX partner sits in lane ^ 16.
-struct RopeCoef { float sn[4], cs[4]; };
-// sin / cos of the rotation angles of the dims a lane owns; they depend on the lane and the position
-// only, so a CTA computes them once and applies them to every head it touches.
-__device__ __forceinline__ RopeCoef rope_coef(uint32_t lane, uint32_t pos, float theta, int neox) {
-    const float hd = 128.0f;
-    RopeCoef c;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        // pairs layout: dims (4*lane + i) belong to pair with even index 4*lane + (i & ~1);
-        // NeoX layout: pair index j = 4*(lane & 15) + i, even index 2j
-        const float even = neox ? __fmul_rn(2.0f, (float)(4 * (lane & 15) + i)) : (float)(4 * lane + (i & ~1));
-        const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn(even, hd)));
-        sincosf(__fmul_rn((float)pos, freq), &c.sn[i], &c.cs[i]);
-    }
-    return c;
-}
-__device__ __forceinline__ float4 rope4(float4 v, uint32_t lane, const RopeCoef& c, int neox) {
-    float r[4] = {v.x, v.y, v.z, v.w}, out[4];
-    if (!neox) {
-#pragma unroll
-        for (int p = 0; p < 2; p++) {
-            const float x0 = r[2 * p], x1 = r[2 * p + 1];
-            out[2 * p] = __fsub_rn(__fmul_rn(x0, c.cs[2 * p]), __fmul_rn(x1, c.sn[2 * p]));
-            out[2 * p + 1] = __fadd_rn(__fmul_rn(x0, c.sn[2 * p]), __fmul_rn(x1, c.cs[2 * p]));
-        }
-    } else {
-        const bool upper = lane >= 16;   // dims 64..127 are the second element of their pair
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float other = __shfl_xor_sync(0xffffffffu, r[i], 16);
-            const float x0 = upper ? other : r[i], x1 = upper ? r[i] : other;
-            out[i] = upper ? __fadd_rn(__fmul_rn(x0, c.sn[i]), __fmul_rn(x1, c.cs[i]))
-                           : __fsub_rn(__fmul_rn(x0, c.cs[i]), __fmul_rn(x1, c.sn[i]));
-        }
-    }
-    return make_float4(out[0], out[1], out[2], out[3]);
-}
-
-// GQA decode attention with RoPE, KV append and the split combine fused in.
-// One CTA = one KV head x one slice of positions; its GROUP = num_heads/num_kv_heads query heads share
-// every K and V row it reads. Each warp walks positions t, t+NW, ...; a lane owns 4 of the 128 dims.
-// qkv = [q | k | v] of the current token, un-rotated: q and k are rotated here, the new K/V row is
-// used from registers and written to the cache at `pos` by the CTA whose slice contains it.
-// Per (split, head) the CTA leaves (max, sum, accumulator); the last CTA of a KV head to finish
-// (ticket counter) folds the splits into attn_out for its heads.
 template <int GROUP>
 __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, float* __restrict__ kcache,
                                                          float* __restrict__ vcache, const int* __restrict__ pos_ptr,
                                                          AttnShape s, float theta, int neox, uint32_t nsplit,
                                                          float* __restrict__ part, unsigned int* __restrict__ tickets,
                                                          float* __restrict__ attn_out) {
-    constexpr int NW = 8;
+    __shared__ AttnSmem<GROUP> sh;
     pdl_wait();
     pdl_launch_dependents();
-    const uint32_t kvh = blockIdx.x, split = blockIdx.y;
-    const uint32_t pos = (uint32_t)*pos_ptr;
-    const uint32_t seq = pos + 1;
-    const uint32_t per = (seq + nsplit - 1) / nsplit;
-    const uint32_t t0 = split * per, t1 = min(seq, t0 + per);
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
-    const float inv_sqrt_d = __fdiv_rn(1.0f, sqrtf((float)s.head_dim));
-
-    const RopeCoef rc = rope_coef(lane, pos, theta, neox);
-    float4 q[GROUP];
-#pragma unroll
-    for (int g = 0; g < GROUP; g++)
-        q[g] = rope4(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim)[lane], lane, rc, neox);
-    float m[GROUP], l[GROUP];
-    float4 acc[GROUP];
-#pragma unroll
-    for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
-
-    for (uint32_t t = t0 + warp; t < t1; t += NW) {
-        float4 k, v;
-        if (t == pos) {   // the token being decoded: rotate its K, append K and V (KvCache::append, src/llama3.rs:4773)
-            k = rope4(reinterpret_cast<const float4*>(qkv + q_dim + (size_t)kvh * s.head_dim)[lane], lane, rc, neox);
-            v = reinterpret_cast<const float4*>(qkv + q_dim + kv_dim + (size_t)kvh * s.head_dim)[lane];
-            reinterpret_cast<float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = k;
-            reinterpret_cast<float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = v;
-        } else {
-            k = reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
-            v = reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane];
-        }
-        float sc[GROUP];
-#pragma unroll
-        for (int g = 0; g < GROUP; g++) sc[g] = q[g].x * k.x + q[g].y * k.y + q[g].z * k.z + q[g].w * k.w;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int g = 0; g < GROUP; g++) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
-#pragma unroll
-        for (int g = 0; g < GROUP; g++) {
-            const float x = sc[g] * inv_sqrt_d;
-            const float mn = fmaxf(m[g], x);
-            const float corr = expf(m[g] - mn), p = expf(x - mn);
-            l[g] = l[g] * corr + p;
-            acc[g].x = acc[g].x * corr + p * v.x; acc[g].y = acc[g].y * corr + p * v.y;
-            acc[g].z = acc[g].z * corr + p * v.z; acc[g].w = acc[g].w * corr + p * v.w;
-            m[g] = mn;
-        }
-    }
-    // combine the NW warps of the CTA
-    __shared__ float sm_m[NW][GROUP], sm_l[NW][GROUP];
-    __shared__ float4 sm_acc[NW][GROUP][32];
-    __shared__ unsigned int sm_last;
-#pragma unroll
-    for (int g = 0; g < GROUP; g++) {
-        if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
-        sm_acc[warp][g][lane] = acc[g];
-    }
-    __syncthreads();
-    const uint32_t stride = s.head_dim + 4;   // (m, l, pad, pad, acc[128]): keeps acc 16-byte aligned
-    if (warp < GROUP) {
-        const int g = warp;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NW; w++) M = fmaxf(M, sm_m[w][g]);
-        float L = 0.0f;
-        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (M > -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < NW; w++) {
-                const float c = expf(sm_m[w][g] - M);   // exp(-inf) = 0 for warps that saw no position
-                L += sm_l[w][g] * c;
-                const float4 a = sm_acc[w][g][lane];
-                A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
-            }
-        }
-        float* out = part + ((size_t)split * s.num_heads + kvh * GROUP + g) * stride;
-        if (lane == 0) { out[0] = M; out[1] = L; }
-        reinterpret_cast<float4*>(out + 4)[lane] = A;
-    }
-    // last CTA of this KV head folds the splits
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int ticket = atomicAdd(&tickets[kvh], 1u);
-        sm_last = (ticket == nsplit - 1) ? 1u : 0u;
-        if (sm_last) tickets[kvh] = 0;   // ready for the next launch
-    }
-    __syncthreads();
-    if (!sm_last) return;
-    __threadfence();
-    if (warp < GROUP) {
-        // one warp per head; lane <-> split for the (max, sum) pairs, so all loads are in flight at once
-        const uint32_t head = kvh * GROUP + warp;
-        float ms[2], ls[2];
-        float M = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint32_t sp = lane + 32 * i;
-            ms[i] = -INFINITY; ls[i] = 0.0f;
-            if (sp < nsplit) {
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part + ((size_t)sp * s.num_heads + head) * stride));
-                ms[i] = ml.x; ls[i] = ml.y;
-            }
-            M = fmaxf(M, ms[i]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        float cs[2], L = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 2; i++) { cs[i] = ms[i] == -INFINITY ? 0.0f : expf(ms[i] - M); L += ls[i] * cs[i]; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (uint32_t sp = 0; sp < nsplit; sp++) {
-            const float c = __shfl_sync(0xffffffffu, sp < 32 ? cs[0] : cs[1], sp & 31);
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)sp * s.num_heads + head) * stride + 4) + lane);
-            A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
-        }
-        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-        reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
-    }
+    attn_fused_body<GROUP, false>(qkv, kcache, vcache, (uint32_t)*pos_ptr, s, theta, neox, nsplit, part, tickets, attn_out,
+                                  blockIdx.x, blockIdx.y, &sh);
 }
 
 // Turns the packed (ordered logit, ~row) maximum the output-head kernel accumulated into the next

@@ -2,11 +2,15 @@
 // include/alice_cuda.h): the GpuModel of ALICE-LLM src/gpu.rs:2348 with the arithmetic of the CPU
 // forward (src/llama3.rs:13632-13687, 14167-14613).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
 #include "abi_internal.cuh"
+#include "attn_body.cuh"
 #include "glue.cuh"
+#include "step_kernel.cuh"
 
 using namespace alice;
 
@@ -33,6 +37,12 @@ struct alice_model {
     uint32_t pos = 0;  // host mirror of *d_pos
     cudaGraphExec_t graph_greedy = nullptr;
     bool graph_tried = false;
+    // whole-step kernel (csrc/step_kernel.cu): op table on the device, its launch geometry
+    bool use_step_kernel = true, step_ready = false, step_tried = false;
+    StepOp* d_ops = nullptr;
+    uint32_t step_nops = 0, step_grid = 0, step_stride = 0, step_aux_off = 0;
+    size_t step_smem = 0;
+    unsigned int* d_barrier = nullptr;
     std::vector<void*> owned;
 };
 
@@ -129,6 +139,106 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         if (rc) return rc;
     }
     MCU(launch_finish_step(m->argmax_key, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
+    return ALICE_OK;
+}
+
+// The same ops as enqueue_step, as a device-resident list for the whole-step kernel. Leaves
+// step_ready false (and the model on the one-launch-per-op path) when an op has no instance there.
+static int step_skip(int why) {
+    if (getenv("ALICE_DEBUG")) fprintf(stderr, "[alice] whole-step kernel not used (reason %d)\n", why);
+    return ALICE_OK;
+}
+
+int build_step_ops(alice_model* m) {
+    const alice_model_config& c = m->cfg;
+    const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
+    const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
+    const uint32_t group = c.num_heads / c.num_kv_heads;
+    if (group != 1 && group != 2 && group != 4) return step_skip(1);
+    std::vector<GemvOp> gops;
+    std::vector<int> kind;   // -1 embed, -2 attention(layer), >= 0 index into gops
+    std::vector<uint32_t> attn_layer;
+    kind.push_back(-1);
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const alice_model::Layer& L = m->layers[l];
+        if (!(L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt)) return step_skip(2);
+        GemvOp qkv; qkv.w[0] = &L.q; qkv.w[1] = &L.k; qkv.w[2] = &L.v; qkv.nw = 3;
+        qkv.y_off[1] = q_dim; qkv.y_off[2] = q_dim + kv_dim;
+        qkv.x = m->hidden; qkv.norm_w = L.attn_norm; qkv.norm_eps = c.eps; qkv.y = m->qkv;
+        kind.push_back((int)gops.size()); gops.push_back(qkv);
+        kind.push_back(-2); attn_layer.push_back(l);
+        GemvOp o; o.w[0] = &L.o; o.x = m->attn_out; o.resid = m->hidden; o.y = m->hidden;
+        kind.push_back((int)gops.size()); gops.push_back(o);
+        GemvOp gu; gu.w[0] = &L.gate; gu.up = &L.up; gu.x = m->hidden; gu.norm_w = L.ffn_norm; gu.norm_eps = c.eps; gu.y = m->ffn_h;
+        kind.push_back((int)gops.size()); gops.push_back(gu);
+        GemvOp dn; dn.w[0] = &L.down; dn.x = m->ffn_h; dn.resid = m->hidden; dn.y = m->hidden;
+        kind.push_back((int)gops.size()); gops.push_back(dn);
+    }
+    GemvOp head; head.w[0] = &m->out; head.x = m->hidden; head.norm_w = m->out_norm; head.norm_eps = c.eps;
+    head.y = m->logits; head.argmax_key = m->argmax_key;
+    kind.push_back((int)gops.size()); gops.push_back(head);
+
+    const LaunchCfg cfg = alice_cfg_of(m->e);
+    const uint32_t grid = 2u * (uint32_t)m->e->num_sms;
+    // first pass: the auxiliary area (normalised input + in-kernel Q8_K, or the attention scratch)
+    uint32_t aux = (uint32_t)((group == 4 ? sizeof(AttnSmem<4>) : group == 2 ? sizeof(AttnSmem<2>) : sizeof(AttnSmem<1>)) + 127) & ~127u;
+    PlanLimits probe{2, 48 * 1024, grid};
+    for (const GemvOp& g : gops) {
+        StreamPlan pl;
+        if (plan_stream_gemv(g, cfg, &probe, pl)) return step_skip(3);
+        if (pl.kl > 2) return step_skip(4);
+        aux = std::max(aux, pl.q8_bytes + pl.xn_bytes);
+    }
+    const uint32_t stride = ((STEP_SMEM_BUDGET - STREAM_HDR_BYTES - aux) / 2) & ~127u;
+    PlanLimits lim{2, stride, grid};
+    const uint32_t aux_off = STREAM_HDR_BYTES + 2 * stride;
+    std::vector<StepOp> ops;
+    size_t ai = 0;
+    for (int k : kind) {
+        StepOp op{};
+        if (k == -1) {
+            op.type = SOP_EMBED; op.table = m->emb.data; op.hidden = m->hidden; op.cols = c.hidden_dim; op.vocab = c.vocab_size;
+        } else if (k == -2) {
+            const uint32_t l = attn_layer[ai++];
+            op.type = SOP_ATTN; op.qkv = m->qkv;
+            op.kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim; op.vc = m->vcache + (size_t)l * c.max_seq_len * kv_dim;
+            op.part = m->attn_part; op.tickets = m->attn_tickets; op.attn_out = m->attn_out;
+            op.shape = shape; op.theta = c.rope_theta; op.neox = (int)c.neox_rope; op.nsplit = m->nsplit;
+        } else {
+            StreamPlan pl;
+            if (plan_stream_gemv(gops[k], cfg, &lim, pl)) return step_skip(5);
+            const int v = step_variant(gops[k].w[0]->fmt, pl.kl, pl.swiglu);
+            if (v < 0) return step_skip(6);
+            op.type = SOP_GEMV; op.variant = v; op.g = pl.args;
+            op.g.xn_off = aux_off; op.g.q8_off = aux_off + pl.xn_bytes;
+        }
+        ops.push_back(op);
+    }
+    int per_sm = 0;
+    const size_t smem = aux_off + aux;
+    if (decode_step_max_ctas_per_sm(smem, &per_sm) != cudaSuccess || per_sm < 2) { cudaGetLastError(); return step_skip(7); }
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->e->device);
+    if (!coop) return step_skip(8);
+    int rc = dev_alloc(m, &m->d_ops, ops.size());
+    if (!rc) rc = dev_alloc(m, &m->d_barrier, 1);
+    if (rc) return rc;
+    MCU(cudaMemcpy(m->d_ops, ops.data(), ops.size() * sizeof(StepOp), cudaMemcpyHostToDevice));
+    m->step_nops = (uint32_t)ops.size(); m->step_grid = grid; m->step_stride = stride; m->step_aux_off = aux_off;
+    m->step_smem = smem; m->step_ready = true;
+    return ALICE_OK;
+}
+
+// n decode steps in one cooperative launch of the whole-step kernel.
+int run_step_kernel(alice_model* m, uint32_t n, bool greedy_feed) {
+    cudaStream_t st = m->e->stream;
+    MCU(cudaMemsetAsync(m->d_barrier, 0, sizeof(unsigned int), st));
+    StepArgs sa{};
+    sa.ops = m->d_ops; sa.nops = m->step_nops; sa.nsteps = n;
+    sa.pos = m->d_pos; sa.token = m->d_token; sa.trace = m->d_trace; sa.key = m->argmax_key;
+    sa.barrier = m->d_barrier; sa.status = m->e->status; sa.write_token = greedy_feed ? 1 : 0;
+    sa.nstages = 2; sa.stage_stride = m->step_stride; sa.aux_off = m->step_aux_off;
+    MCU(launch_decode_steps(sa, m->step_grid, m->step_smem, st));
     return ALICE_OK;
 }
 
@@ -269,6 +379,19 @@ int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t
     if (rc) return rc;
     cudaStream_t st = m->e->stream;
     const uint32_t pos0 = m->pos;
+    if (m->use_step_kernel && !m->step_tried) {
+        m->step_tried = true;
+        rc = build_step_ops(m);
+        if (rc) return rc;
+    }
+    if (m->use_step_kernel && m->step_ready) {
+        rc = run_step_kernel(m, n, true);
+        if (rc) return rc;
+        m->pos += n;
+        MCU(cudaMemcpyAsync(out_tokens, m->d_trace + pos0, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+        MCU(cudaStreamSynchronize(st));
+        return alice_sync(m->e);
+    }
     if (!m->graph_tried) {
         // Capture one step (every kernel reads position and token from device memory) and replay it.
         m->graph_tried = true;
@@ -299,6 +422,12 @@ int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t
     MCU(cudaMemcpyAsync(out_tokens, m->d_trace + pos0, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     MCU(cudaStreamSynchronize(st));
     return alice_sync(m->e);
+}
+
+int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled) {
+    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_use_step_kernel: null model");
+    m->use_step_kernel = enabled != 0;
+    return ALICE_OK;
 }
 
 int32_t alice_model_position(const alice_model* m, uint32_t* pos) {

@@ -39,8 +39,11 @@ struct Q8KLayout {
 //   * bsums[j] = sum of 16 consecutive q; an all-zero block gives d = 0, q = 0.
 // qs / bsums / d may point to global or shared memory.
 struct Q8KLaneInput { float4 a, b; };  // the 8 consecutive elements one lane owns
-__device__ __forceinline__ Q8KLaneInput q8k_load_lane(const float* __restrict__ xb, uint32_t lane) {
+// `cg`: read through L2 only (ld.global.cg) - for a global vector that other SMs rewrite while this
+// kernel runs; must be false for a shared-memory source.
+__device__ __forceinline__ Q8KLaneInput q8k_load_lane(const float* xb, uint32_t lane, bool cg = false) {
     const float4* src = reinterpret_cast<const float4*>(xb + lane * 8);
+    if (cg) return Q8KLaneInput{__ldcg(src), __ldcg(src + 1)};
     return Q8KLaneInput{src[0], src[1]};
 }
 __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, uint32_t lane, int8_t* qs, float* d,

@@ -417,6 +417,10 @@ class GpuModel:
         check(self.engine._lib.alice_model_read_logits(self._h, _ptr(out)))
         return out
 
+    def use_step_kernel(self, enabled: bool):
+        """decode_greedy inside one cooperative kernel (default) or one launch per op from a CUDA graph."""
+        check(self.engine._lib.alice_model_use_step_kernel(self._h, int(enabled)))
+
     def decode_greedy(self, first_token: int, n: int) -> np.ndarray:
         out = np.empty(n, np.uint32)
         check(self.engine._lib.alice_model_decode_greedy(self._h, first_token, n, _ptr(out)))

@@ -115,3 +115,36 @@ def test_rollback_reset_and_limits(eng, oracle):
     with pytest.raises(AliceError):
         gm.forward_and_read(CFG["vocab_size"])
     gm.free()
+
+
+# the second shape makes several warps share a row (hidden 2304 -> 36 Q4_K units) and gives the down
+# projection two activation positions per lane (ffn 8704 -> 272 Q6_K units over 8 warps)
+@pytest.mark.parametrize("shape", [dict(), dict(hidden_dim=2304, intermediate_dim=8704, vocab_size=700)])
+def test_step_kernel_equals_per_op_launches(eng, oracle, shape):
+    """decode_greedy inside the one cooperative whole-step kernel must give the tokens, the logits and
+    the KV rows of the one-launch-per-op path (same arithmetic, different scheduling)."""
+    from alice_llm_b200.gpu import GpuModel
+    rng = np.random.default_rng(8)
+    cfg = dict(CFG, num_layers=3, **shape)
+    model = synth.make_llama(rng, cfg)
+    kv_dim = cfg["num_kv_heads"] * cfg["head_dim"]
+    pre = [(rng.standard_normal((50, kv_dim), dtype=np.float32), rng.standard_normal((50, kv_dim), dtype=np.float32))
+           for _ in range(cfg["num_layers"])]
+    outs = []
+    for step_kernel in (True, False):
+        gm = GpuModel.load(eng, model)
+        gm.use_step_kernel(step_kernel)
+        for l, (k, v) in enumerate(pre):
+            gm.kv_write(l, 0, k, v)
+        gm.set_position(50)
+        toks = gm.decode_greedy(3, 10)
+        logits = gm.read_logits()
+        toks2 = gm.decode_greedy(int(toks[-1]), 5)       # second launch continues from device state
+        kv = gm.kv_read(cfg["num_layers"] - 1, 50, 15)
+        outs.append((toks, logits, toks2, kv))
+        assert gm.position() == 65
+        gm.free()
+    a, b = outs
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[2], b[2])
+    assert np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+    assert np.array_equal(a[3][0], b[3][0]) and np.array_equal(a[3][1], b[3][1])
