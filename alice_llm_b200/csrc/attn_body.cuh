@@ -9,18 +9,28 @@
 namespace alice {
 
 struct RopeCoef { float sn[4], cs[4]; };
-// sin / cos of the rotation angles of the dims a lane owns; they depend on the lane and the position
-// only, so a CTA computes them once and applies them to every head it touches.
-__device__ __forceinline__ RopeCoef rope_coef(uint32_t lane, uint32_t pos, float theta, int neox) {
-    const float hd = 128.0f;
+// Rotation table of one position: tab[2*j] = sin, tab[2*j + 1] = cos of pos * theta^(-2j / head_dim),
+// j = 0 .. head_dim/2 - 1 (head_dim = 128). It depends on the position only, so it is computed once per
+// decode step (by the embedding stage) and every layer's attention reads it.
+__device__ __forceinline__ void rope_table_entry(float* tab, uint32_t j, uint32_t pos, float theta) {
+    const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn((float)(2 * j), 128.0f)));
+    float sn, cs;
+    sincosf(__fmul_rn((float)pos, freq), &sn, &cs);
+    tab[2 * j] = sn; tab[2 * j + 1] = cs;
+}
+// sin / cos of the rotation angles of the 4 dims a lane owns, fetched from the table (L2 reads: another
+// SM wrote it). Pairs layout: dims 4*lane + i belong to pair 2*lane + i/2; NeoX: pair 4*(lane & 15) + i.
+__device__ __forceinline__ RopeCoef rope_coef(const float* __restrict__ tab, uint32_t lane, int neox) {
     RopeCoef c;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        // pairs layout: dims (4*lane + i) belong to pair with even index 4*lane + (i & ~1);
-        // NeoX layout: pair index j = 4*(lane & 15) + i, even index 2j
-        const float even = neox ? __fmul_rn(2.0f, (float)(4 * (lane & 15) + i)) : (float)(4 * lane + (i & ~1));
-        const float freq = __fdiv_rn(1.0f, powf(theta, __fdiv_rn(even, hd)));
-        sincosf(__fmul_rn((float)pos, freq), &c.sn[i], &c.cs[i]);
+    if (!neox) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(tab) + lane);   // pairs 2*lane, 2*lane + 1
+        c.sn[0] = c.sn[1] = t.x; c.cs[0] = c.cs[1] = t.y;
+        c.sn[2] = c.sn[3] = t.z; c.cs[2] = c.cs[3] = t.w;
+    } else {
+        const float4 t0 = __ldcg(reinterpret_cast<const float4*>(tab) + 2 * (lane & 15));
+        const float4 t1 = __ldcg(reinterpret_cast<const float4*>(tab) + 2 * (lane & 15) + 1);
+        c.sn[0] = t0.x; c.cs[0] = t0.y; c.sn[1] = t0.z; c.cs[1] = t0.w;
+        c.sn[2] = t1.x; c.cs[2] = t1.y; c.sn[3] = t1.z; c.cs[3] = t1.w;
     }
     return c;
 }
@@ -70,10 +80,10 @@ __device__ __forceinline__ void attn_sync() {
 
 template <int GROUP, bool CONSUMER_BAR>
 __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, float* __restrict__ kcache,
-                                                float* __restrict__ vcache, uint32_t pos, AttnShape s, float theta,
-                                                int neox, uint32_t nsplit, float* __restrict__ part,
+                                                float* __restrict__ vcache, uint32_t pos, AttnShape s,
+                                                const float* __restrict__ rope_tab, int neox, uint32_t nsplit, float* __restrict__ part,
                                                 unsigned int* __restrict__ tickets, float* __restrict__ attn_out,
-                                                uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh) {
+                                                uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh, long long* prof = nullptr) {
     constexpr int NW = 8;
     const uint32_t seq = pos + 1;
     const uint32_t per = (seq + nsplit - 1) / nsplit;
@@ -82,45 +92,62 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
     const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
     const float inv_sqrt_d = __fdiv_rn(1.0f, sqrtf((float)s.head_dim));
 
-    const RopeCoef rc = rope_coef(lane, pos, theta, neox);
+    const RopeCoef rc = rope_coef(rope_tab, lane, neox);
     float4 q[GROUP];
 #pragma unroll
     for (int g = 0; g < GROUP; g++)
         q[g] = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim) + lane), lane, rc, neox);
+    if (prof && threadIdx.x == 0) prof[1] = clock64();
     float m[GROUP], l[GROUP];
     float4 acc[GROUP];
 #pragma unroll
     for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
 
-    for (uint32_t t = t0 + warp; t < t1; t += NW) {
-        float4 k, v;
-        if (t == pos) {   // the token being decoded: rotate its K, append K and V (KvCache::append, src/llama3.rs:4773)
-            k = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + q_dim + (size_t)kvh * s.head_dim) + lane), lane, rc, neox);
-            v = __ldcg(reinterpret_cast<const float4*>(qkv + q_dim + kv_dim + (size_t)kvh * s.head_dim) + lane);
-            reinterpret_cast<float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = k;
-            reinterpret_cast<float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = v;
-        } else {
-            k = __ldcg(reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
-            v = __ldcg(reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
+    // KB positions per warp round: their 2*KB row loads are issued before the first is used, so a round
+    // costs one memory round trip instead of KB (positions are still folded in ascending order)
+    constexpr int KB = CONSUMER_BAR ? 2 : 4;   // inside the whole-step kernel registers are scarce
+    for (uint32_t tb = t0 + warp; tb < t1; tb += NW * KB) {
+        float4 k[KB], v[KB];
+#pragma unroll
+        for (int j = 0; j < KB; j++) {
+            const uint32_t t = tb + j * NW;
+            k[j] = v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < t1 && t != pos) {
+                k[j] = __ldcg(reinterpret_cast<const float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
+                v[j] = __ldcg(reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
+            }
         }
-        float sc[GROUP];
 #pragma unroll
-        for (int g = 0; g < GROUP; g++) sc[g] = q[g].x * k.x + q[g].y * k.y + q[g].z * k.z + q[g].w * k.w;
+        for (int j = 0; j < KB; j++) {
+            const uint32_t t = tb + j * NW;
+            if (t < t1) {
+                if (t == pos) {   // the token being decoded: rotate its K, append K and V (KvCache::append, src/llama3.rs:4773)
+                    k[j] = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + q_dim + (size_t)kvh * s.head_dim) + lane), lane, rc, neox);
+                    v[j] = __ldcg(reinterpret_cast<const float4*>(qkv + q_dim + kv_dim + (size_t)kvh * s.head_dim) + lane);
+                    reinterpret_cast<float4*>(kcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = k[j];
+                    reinterpret_cast<float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim)[lane] = v[j];
+                }
+                float sc[GROUP];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
+                for (int g = 0; g < GROUP; g++) sc[g] = q[g].x * k[j].x + q[g].y * k[j].y + q[g].z * k[j].z + q[g].w * k[j].w;
 #pragma unroll
-            for (int g = 0; g < GROUP; g++) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+                for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-        for (int g = 0; g < GROUP; g++) {
-            const float x = sc[g] * inv_sqrt_d;
-            const float mn = fmaxf(m[g], x);
-            const float corr = expf(m[g] - mn), p = expf(x - mn);
-            l[g] = l[g] * corr + p;
-            acc[g].x = acc[g].x * corr + p * v.x; acc[g].y = acc[g].y * corr + p * v.y;
-            acc[g].z = acc[g].z * corr + p * v.z; acc[g].w = acc[g].w * corr + p * v.w;
-            m[g] = mn;
+                    for (int g = 0; g < GROUP; g++) sc[g] += __shfl_xor_sync(0xffffffffu, sc[g], o);
+#pragma unroll
+                for (int g = 0; g < GROUP; g++) {
+                    const float x = sc[g] * inv_sqrt_d;
+                    const float mn = fmaxf(m[g], x);
+                    const float corr = expf(m[g] - mn), p = expf(x - mn);
+                    l[g] = l[g] * corr + p;
+                    acc[g].x = acc[g].x * corr + p * v[j].x; acc[g].y = acc[g].y * corr + p * v[j].y;
+                    acc[g].z = acc[g].z * corr + p * v[j].z; acc[g].w = acc[g].w * corr + p * v[j].w;
+                    m[g] = mn;
+                }
+            }
         }
     }
+    if (prof && threadIdx.x == 0) prof[2] = clock64();
     // combine the NW warps of the CTA
 #pragma unroll
     for (int g = 0; g < GROUP; g++) {
@@ -150,6 +177,7 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
         reinterpret_cast<float4*>(out + 4)[lane] = A;
     }
     // last CTA of this KV head folds the splits
+    if (prof && threadIdx.x == 0) prof[3] = clock64();
     __threadfence();
     attn_sync<CONSUMER_BAR>();
     if (threadIdx.x == 0) {
@@ -158,6 +186,7 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
         if (sh->last) tickets[kvh] = 0;   // ready for the next launch
     }
     attn_sync<CONSUMER_BAR>();
+    if (prof && threadIdx.x == 0) prof[6] = clock64();
     if (!sh->last) return;
     __threadfence();
     if (warp < GROUP) {
@@ -183,11 +212,19 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
         float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (uint32_t sp = 0; sp < nsplit; sp++) {
-            const float c = __shfl_sync(0xffffffffu, sp < 32 ? cs[0] : cs[1], sp & 31);
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)sp * s.num_heads + head) * stride + 4) + lane);
-            A.x += a.x * c; A.y += a.y * c; A.z += a.z * c; A.w += a.w * c;
+        constexpr int SB = CONSUMER_BAR ? 8 : 16;   // split accumulators fetched per round trip
+        for (uint32_t sp0 = 0; sp0 < nsplit; sp0 += SB) {
+            float4 a[SB];
+#pragma unroll
+            for (int j = 0; j < SB; j++)
+                if (sp0 + j < nsplit)
+                    a[j] = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)(sp0 + j) * s.num_heads + head) * stride + 4) + lane);
+#pragma unroll
+            for (int j = 0; j < SB; j++) {
+                const uint32_t sp = sp0 + j;
+                const float c = __shfl_sync(0xffffffffu, sp < 32 ? cs[0] : cs[1], sp & 31);
+                if (sp < nsplit) { A.x += a[j].x * c; A.y += a[j].y * c; A.z += a[j].z * c; A.w += a[j].w * c; }
+            }
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
         reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);

@@ -68,9 +68,9 @@ struct StreamSmem {
     float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
     double norm_part[NCW];
     int abort_flag;
-    // multi-matvec kernels keep the arguments of the matvec in flight here (one copy for the consumer
-    // warps, one for the producer, which runs ahead) instead of re-reading them from global memory
-    StreamArgs cargs, pargs;
+    // multi-matvec kernels: the producer (which runs ahead of the consumers) keeps the arguments of the
+    // matvec it is streaming here instead of re-reading them from global memory
+    StreamArgs pargs;
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
@@ -129,6 +129,7 @@ struct StreamCtx {
     uint32_t cc;            // chunks streamed so far (producer and consumers keep separate copies in step)
     int op;                 // index of the matvec inside a multi-op kernel (error reports)
     bool acts_cg;           // read global activations with ld.global.cg (other SMs rewrite them inside this kernel)
+    long long* prof = nullptr;  // optional clock64 stamps of this matvec: [1] prologue done, [2] first stage landed, [3] rows done, [8..15] stage g done
 };
 
 // The per-(stage, warp set) barriers collect the P-1 helper warps of a row set. P changes from matvec
@@ -185,39 +186,45 @@ __device__ __forceinline__ void stream_drain(StreamCtx& cx) {
     for (uint32_t c = first; c < cx.cc; c++) mbar_wait(smem_u32(&cx.sm->full[c % cx.nstages]), (c / cx.nstages) & 1);
 }
 
-// Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
-// Returns false after an abort.
-template <class F, int KL, bool SWIGLU>
-__device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
-    StreamSmem* sm = cx.sm;
-    uint8_t* smem_raw = cx.smem_raw;
-    volatile int* abort_flag = &sm->abort_flag;
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t P = a.P, slots = a.slots, rps = a.rps;
-    const uint32_t rows_per_group = slots * rps;
-    const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg;
-
-    const float* x_src = a.x;
-    bool x_global = true;
-    if (a.norm_w != nullptr) {
-        // rms_norm (src/llama3.rs:5244-5256): f64 sum of squares, mean and scale in f32, then
-        // (x * scale) * w; the normalised vector is kept in shared memory for this CTA only.
-        float* xn = reinterpret_cast<float*>(smem_raw + a.xn_off);
-        const uint32_t tid = threadIdx.x;
-        // every thread keeps its share of x in registers (all loads in flight at once); cols is a
-        // multiple of 4 for every format here, rows wider than NCW*32*4*NORM_V floats take more rounds
-        constexpr int NORM_V = 8;
-        const uint32_t nvec = a.cols / 4;
-        const float4* xg = reinterpret_cast<const float4*>(a.x);
-        float4 xv[NORM_V];
+// Input prologue of one matvec, run by the NCW consumer warps. A real function call on purpose: it runs
+// once per matvec, so its code is fetched cold every time, and one shared compact copy (rolled loops)
+// costs far fewer instruction-cache misses than a copy unrolled into every format's kernel body.
+//   norm_w != null: rms_norm (src/llama3.rs:5244-5256) - f64 sum of squares, mean and scale in f32, then
+//                   (x * scale) * w - into the f32 area at xn_off;
+//   quant:          the (normalised) vector -> Q8_K in shared memory at q8_off (qs | bsums | d), one warp
+//                   per 256-element block, exactly the stand-alone quantizer.
+// cg: read x with ld.global.cg (other SMs rewrote it inside this kernel).
+static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
+                                                    float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
+                                                    bool quant, bool cg) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const float* src = x;
+    bool src_global = true;
+    if (norm_w != nullptr) {
+        float* xn = reinterpret_cast<float*>(smem_raw + xn_off);
+        // a thread's share of x stays in registers between the two passes when it fits in NORM_V float4
+        // (cols <= NCW*32*4*NORM_V); the norm weights ride the same memory round trip as x
+        constexpr int NORM_V = 4;
+        const uint32_t nvec = cols / 4;
+        const float4* xg = reinterpret_cast<const float4*>(x);
+        const float4* wg = reinterpret_cast<const float4*>(norm_w);
+        const bool one_round = nvec <= NCW * 32 * NORM_V;
+        float4 xv[NORM_V], wv[NORM_V];
         double ss = 0.0;
+#pragma unroll 1
         for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
 #pragma unroll
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (i < nvec) xv[k] = cg ? __ldcg(xg + i) : xg[i];
+            }
+            if (one_round) {
+#pragma unroll
+                for (int k = 0; k < NORM_V; k++) {
+                    const uint32_t i = k * NCW * 32 + tid;
+                    if (i < nvec) wv[k] = __ldg(wg + i);
+                }
             }
 #pragma unroll
             for (int k = 0; k < NORM_V; k++)
@@ -231,53 +238,75 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         double tot = 0.0;
 #pragma unroll
         for (int w = 0; w < NCW; w++) tot += sm->norm_part[w];
-        const float mean = (float)(tot / (double)a.cols);
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.norm_eps)));
-        const float4* wg = reinterpret_cast<const float4*>(a.norm_w);
-        const bool one_round = nvec <= NCW * 32 * NORM_V;   // then xv still holds this thread's whole share
+        const float mean = (float)(tot / (double)cols);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, norm_eps)));
+#pragma unroll 1
         for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
 #pragma unroll
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 if (i < nvec) {
                     const float4 v = one_round ? xv[k] : (cg ? __ldcg(xg + i) : xg[i]);
-                    const float4 w = __ldg(wg + i);
+                    const float4 w = one_round ? wv[k] : __ldg(wg + i);
                     reinterpret_cast<float4*>(xn)[i] = make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
                                                                    __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
                 }
             }
         }
-        x_src = xn;
-        x_global = false;
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // xn complete
+        src = xn;
+        src_global = false;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // xn complete
-    Q8KView q8 = a.q8;
-    if (F::USES_Q8K && a.q8.qs == nullptr) {
-        // f32 input: the consumer warps quantize it to Q8_K once per CTA into shared memory
-        // (one warp per 256-element block, exactly the stand-alone quantizer), then every lane
-        // picks up its own positions from there.
-        const uint32_t nb = a.cols / QK_K;
-        uint8_t* area = smem_raw + a.q8_off;
+    if (quant) {
+        const uint32_t nb = cols / QK_K;
+        uint8_t* area = smem_raw + q8_off;
         int8_t* qs_s = reinterpret_cast<int8_t*>(area);
         int16_t* bs_s = reinterpret_cast<int16_t*>(area + (size_t)nb * 256);  // 8-byte aligned for any nb
         float* d_s = reinterpret_cast<float*>(area + (size_t)nb * 288);
-        // four blocks per warp at a time: their loads are in flight together and their
-        // (independent) reduction chains interleave
-        for (uint32_t b0 = warp; b0 < nb; b0 += 4 * NCW) {
-            Q8KLaneInput in[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t blk = b0 + i * NCW;
-                if (blk < nb) in[i] = q8k_load_lane(x_src + (size_t)blk * QK_K, lane, x_global && cg);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t blk = b0 + i * NCW;
-                if (blk < nb) q8k_quantize_block_warp(in[i], lane, qs_s + (size_t)blk * QK_K, d_s + blk, bs_s + (size_t)blk * 16);
-            }
+        // two blocks per warp per round: their loads travel together and their reduction chains interleave
+        const bool lcg = src_global && cg;
+#pragma unroll 1
+        for (uint32_t b0 = warp; b0 < nb; b0 += 2 * NCW) {
+            const uint32_t b1 = b0 + NCW;
+            const Q8KLaneInput in0 = q8k_load_lane(src + (size_t)b0 * QK_K, lane, lcg);
+            Q8KLaneInput in1 = in0;
+            if (b1 < nb) in1 = q8k_load_lane(src + (size_t)b1 * QK_K, lane, lcg);
+            q8k_quantize_block_warp(in0, lane, qs_s + (size_t)b0 * QK_K, d_s + b0, bs_s + (size_t)b0 * 16);
+            if (b1 < nb) q8k_quantize_block_warp(in1, lane, qs_s + (size_t)b1 * QK_K, d_s + b1, bs_s + (size_t)b1 * 16);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        q8.qs = qs_s; q8.d = d_s; q8.bsums = bs_s; q8.nb = nb;
+    }
+}
+
+// Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
+// Returns false after an abort.
+template <class F, int KL, bool SWIGLU>
+__device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
+    StreamSmem* sm = cx.sm;
+    uint8_t* smem_raw = cx.smem_raw;
+    volatile int* abort_flag = &sm->abort_flag;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t P = a.P, slots = a.slots, rps = a.rps;
+    const uint32_t rows_per_group = slots * rps;
+    const uint32_t slot = warp / P, part = warp % P;
+    const bool cg = cx.acts_cg;
+
+    // input prologue (shared by every format, one copy of the code per kernel): RMSNorm into shared
+    // memory and / or Q8_K quantization into shared memory
+    const bool norm = a.norm_w != nullptr;
+    const bool quant = F::USES_Q8K && a.q8.qs == nullptr;
+    if (norm || quant)
+        stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant, cg);
+    const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
+    const bool x_global = !norm;
+    Q8KView q8 = a.q8;
+    if (quant) {
+        const uint32_t nb = a.cols / QK_K;
+        const uint8_t* area = smem_raw + a.q8_off;
+        q8.qs = reinterpret_cast<const int8_t*>(area);
+        q8.bsums = reinterpret_cast<const int16_t*>(area + (size_t)nb * 256);
+        q8.d = reinterpret_cast<const float*>(area + (size_t)nb * 288);
+        q8.nb = nb;
     }
     typename F::Act act[KL];
 #pragma unroll
@@ -285,6 +314,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
         F::load_act(act[k], a, x_src, x_global && cg, q8, u, u < a.units);
     }
+    if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
 
     // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
     // and one butterfly reduces all of them (NV-1 + log2(32/NV) shuffles instead of 5*NV).
@@ -298,7 +328,6 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     for (uint32_t g = g0; g < g1; g++) {
         const uint32_t s = cx.cc % cx.nstages, ph = (cx.cc / cx.nstages) & 1;
         cx.cc++;
-        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         uint32_t sg = 0;
         while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t seg_rows = a.seg_rows[sg];
@@ -306,6 +335,11 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
         const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
+        // the residual this lane will add in the epilogue: requested now, needed after the rows are done
+        float res = 0.0f;
+        if (a.resid != nullptr && part == 0 && lane < nrow) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
+        if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
         const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_bytes;
         for (uint32_t rr0 = 0; rr0 < nrow; rr0 += RB) {
             float v[NV];
@@ -351,7 +385,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr) r = __fadd_rn(ld_act(a.resid + yi, cg), r);
+                    if (a.resid != nullptr) r = __fadd_rn(res, r);
                     a.y[yi] = r;
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -369,7 +403,9 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
+        if (cx.prof && threadIdx.x == 0 && g - g0 < 8) cx.prof[8 + g - g0] = clock64();
     }
+    if (cx.prof && threadIdx.x == 0) cx.prof[3] = clock64();
     return true;
 }
 

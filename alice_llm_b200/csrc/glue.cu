@@ -13,9 +13,11 @@ namespace alice {
 // hidden[c] = d * q of row `token` of a Q8_0 table (dequantize_q8_0, src/gguf.rs:990-1004); the
 // CPU model dequantizes the whole table at load (src/llama3.rs:12890) and copies a row per token.
 __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* __restrict__ token, uint32_t cols,
-                                  uint32_t vocab, float* __restrict__ hidden) {
+                                  uint32_t vocab, float* __restrict__ hidden, const int* __restrict__ pos, float theta,
+                                  float* __restrict__ rope_tab) {
     pdl_wait();
     pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x < 64) rope_table_entry(rope_tab, threadIdx.x, (uint32_t)*pos, theta);
     uint32_t t = (uint32_t)*token;
     if (t >= vocab) t = 0;
     const uint8_t* row = table + (size_t)t * (cols / 32) * 34;
@@ -26,19 +28,19 @@ __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* 
     }
 }
 
-// RoPE of the 4 consecutive dims (4*lane .. 4*lane+3) a lane owns of one head vector (apply_rope /
-// apply_rope_neox, src/llama3.rs:5323-5333, 5367-5378): pairs (i, i+1), or (i, i + d/2) for NeoX,
-// freq = 1 / theta^(i_even / d), angle = pos * freq. head_dim = 128, so a NeoX partner sits in lane ^ 16.
+// RoPE (apply_rope / apply_rope_neox, src/llama3.rs:5323-5333, 5367-5378): pairs (i, i+1), or (i, i + d/2)
+// for NeoX, freq = 1 / theta^(i_even / d), angle = pos * freq; a lane owns dims 4*lane .. 4*lane+3 of a
+// head vector (head_dim = 128, so a NeoX partner sits in lane ^ 16).
 template <int GROUP>
 __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, float* __restrict__ kcache,
                                                          float* __restrict__ vcache, const int* __restrict__ pos_ptr,
-                                                         AttnShape s, float theta, int neox, uint32_t nsplit,
+                                                         AttnShape s, const float* __restrict__ rope_tab, int neox, uint32_t nsplit,
                                                          float* __restrict__ part, unsigned int* __restrict__ tickets,
                                                          float* __restrict__ attn_out) {
     __shared__ AttnSmem<GROUP> sh;
     pdl_wait();
     pdl_launch_dependents();
-    attn_fused_body<GROUP, false>(qkv, kcache, vcache, (uint32_t)*pos_ptr, s, theta, neox, nsplit, part, tickets, attn_out,
+    attn_fused_body<GROUP, false>(qkv, kcache, vcache, (uint32_t)*pos_ptr, s, rope_tab, neox, nsplit, part, tickets, attn_out,
                                   blockIdx.x, blockIdx.y, &sh);
 }
 
@@ -70,24 +72,24 @@ static void launch_cfg(cudaLaunchConfig_t& lc, cudaLaunchAttribute* at, dim3 gri
 }
 
 cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t cols, uint32_t vocab, float* hidden,
-                              cudaStream_t st, bool pdl) {
+                              const int* pos, float theta, float* rope_tab, cudaStream_t st, bool pdl) {
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3((cols + 255) / 256), dim3(256), st, pdl);
-    return cudaLaunchKernelEx(&lc, embed_q8_0_kernel, table, token, cols, vocab, hidden);
+    return cudaLaunchKernelEx(&lc, embed_q8_0_kernel, table, token, cols, vocab, hidden, pos, theta, rope_tab);
 }
 
-cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, float theta, int neox,
+cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
                              uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, cudaStream_t st, bool pdl) {
     if (s.head_dim != 128 || s.num_heads % s.num_kv_heads) return cudaErrorInvalidValue;
     const uint32_t group = s.num_heads / s.num_kv_heads;
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(s.num_kv_heads, nsplit), dim3(256), st, pdl);
     switch (group) {
-        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
-        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
-        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
-        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
-        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, theta, neox, nsplit, part, tickets, attn_out);
+        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
+        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
+        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
+        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
+        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -7,12 +7,14 @@ namespace alice {
 
 struct AttnShape { uint32_t num_heads, num_kv_heads, head_dim; };
 
+// hidden <- dequantized row *token of the Q8_0 table; rope_tab (128 floats) <- (sin, cos) of *pos * theta^(-2j/128)
 cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t cols, uint32_t vocab, float* hidden,
-                              cudaStream_t st, bool pdl);
+                              const int* pos, float theta, float* rope_tab, cudaStream_t st, bool pdl);
 // qkv = [q (num_heads*head_dim) | k (kv_dim) | v (kv_dim)] of the current token, un-rotated; kc / vc = this
 // layer's cache [max_seq][kv_dim] (row `pos` is written). part: nsplit * num_heads * (head_dim + 4) floats,
-// tickets: num_kv_heads zero-initialised counters (left at zero).
-cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, float theta, int neox,
+// tickets: num_kv_heads zero-initialised counters (left at zero). rope_tab: the table launch_embed_q8_0 wrote
+// for this position.
+cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
                              uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, cudaStream_t st, bool pdl);
 // token <- index held in *key (packed maximum written by the output-head kernel) when write_token; pos <- pos + 1
 cudaError_t launch_finish_step(unsigned long long* key, int* token, int* pos, int* trace, int write_token, cudaStream_t st,

@@ -29,6 +29,7 @@ struct alice_model {
     float *hidden = nullptr, *qkv = nullptr, *attn_out = nullptr, *ffn_h = nullptr, *logits = nullptr;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][max_seq][kv_dim]
     float* attn_part = nullptr;
+    float* rope_tab = nullptr;   // (sin, cos) per rotation pair at the current position, rewritten every step
     unsigned int* attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
@@ -38,10 +39,11 @@ struct alice_model {
     cudaGraphExec_t graph_greedy = nullptr;
     bool graph_tried = false;
     // whole-step kernel (csrc/step_kernel.cu): op table on the device, its launch geometry
-    bool use_step_kernel = true, step_ready = false, step_tried = false;
+    bool use_step_kernel = false, step_ready = false, step_tried = false;
     StepOp* d_ops = nullptr;
     uint32_t step_nops = 0, step_grid = 0, step_stride = 0, step_aux_off = 0;
     size_t step_smem = 0;
+    std::vector<uint32_t> step_types;   // StepOpType per op (host copy, for the debug profile)
     unsigned int* d_barrier = nullptr;
     std::vector<void*> owned;
 };
@@ -84,7 +86,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
     const bool pdl = m->e->pdl;
     const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
     const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
-    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, st, pdl));
+    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, st, pdl));
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const alice_model::Layer& L = m->layers[l];
         float* kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim;
@@ -109,7 +111,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             }
         }
         // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
-        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, c.rope_theta, (int)c.neox_rope, m->nsplit, m->attn_part,
+        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
                              m->attn_tickets, m->attn_out, st, pdl));
         {   // output projection + residual (src/llama3.rs:14423, 14468)
             GemvOp op;
@@ -189,7 +191,8 @@ int build_step_ops(alice_model* m) {
         if (pl.kl > 2) return step_skip(4);
         aux = std::max(aux, pl.q8_bytes + pl.xn_bytes);
     }
-    const uint32_t stride = ((STEP_SMEM_BUDGET - STREAM_HDR_BYTES - aux) / 2) & ~127u;
+    const uint32_t ops_bytes = 2 * (uint32_t)sizeof(StepOp);   // the consumers' descriptor double buffer, after the auxiliary area
+    const uint32_t stride = ((STEP_SMEM_BUDGET - STREAM_HDR_BYTES - aux - ops_bytes) / 2) & ~127u;
     PlanLimits lim{2, stride, grid};
     const uint32_t aux_off = STREAM_HDR_BYTES + 2 * stride;
     std::vector<StepOp> ops;
@@ -197,13 +200,13 @@ int build_step_ops(alice_model* m) {
     for (int k : kind) {
         StepOp op{};
         if (k == -1) {
-            op.type = SOP_EMBED; op.table = m->emb.data; op.hidden = m->hidden; op.cols = c.hidden_dim; op.vocab = c.vocab_size;
+            op.type = SOP_EMBED; op.table = m->emb.data; op.hidden = m->hidden; op.cols = c.hidden_dim; op.vocab = c.vocab_size; op.theta = c.rope_theta; op.rope_tab = m->rope_tab;
         } else if (k == -2) {
             const uint32_t l = attn_layer[ai++];
             op.type = SOP_ATTN; op.qkv = m->qkv;
             op.kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim; op.vc = m->vcache + (size_t)l * c.max_seq_len * kv_dim;
             op.part = m->attn_part; op.tickets = m->attn_tickets; op.attn_out = m->attn_out;
-            op.shape = shape; op.theta = c.rope_theta; op.neox = (int)c.neox_rope; op.nsplit = m->nsplit;
+            op.shape = shape; op.rope_tab = m->rope_tab; op.neox = (int)c.neox_rope; op.nsplit = m->nsplit;
         } else {
             StreamPlan pl;
             if (plan_stream_gemv(gops[k], cfg, &lim, pl)) return step_skip(5);
@@ -215,7 +218,7 @@ int build_step_ops(alice_model* m) {
         ops.push_back(op);
     }
     int per_sm = 0;
-    const size_t smem = aux_off + aux;
+    const size_t smem = aux_off + aux + ops_bytes;
     if (decode_step_max_ctas_per_sm(smem, &per_sm) != cudaSuccess || per_sm < 2) { cudaGetLastError(); return step_skip(7); }
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->e->device);
@@ -224,6 +227,8 @@ int build_step_ops(alice_model* m) {
     if (!rc) rc = dev_alloc(m, &m->d_barrier, 1);
     if (rc) return rc;
     MCU(cudaMemcpy(m->d_ops, ops.data(), ops.size() * sizeof(StepOp), cudaMemcpyHostToDevice));
+    m->step_types.clear();
+    for (const StepOp& o : ops) m->step_types.push_back(o.type);
     m->step_nops = (uint32_t)ops.size(); m->step_grid = grid; m->step_stride = stride; m->step_aux_off = aux_off;
     m->step_smem = smem; m->step_ready = true;
     return ALICE_OK;
@@ -238,7 +243,36 @@ int run_step_kernel(alice_model* m, uint32_t n, bool greedy_feed) {
     sa.pos = m->d_pos; sa.token = m->d_token; sa.trace = m->d_trace; sa.key = m->argmax_key;
     sa.barrier = m->d_barrier; sa.status = m->e->status; sa.write_token = greedy_feed ? 1 : 0;
     sa.nstages = 2; sa.stage_stride = m->step_stride; sa.aux_off = m->step_aux_off;
+    sa.ops_off = (uint32_t)(m->step_smem - 2 * sizeof(StepOp));
+    // ALICE_STEP_PROF=1: per-op clock stamps of one CTA during the last step, printed after the launch (debug aid)
+    long long* prof = nullptr;
+    if (getenv("ALICE_STEP_PROF")) {
+        MCU(cudaMalloc(&prof, (size_t)m->step_nops * 16 * sizeof(long long)));
+        MCU(cudaMemset(prof, 0, (size_t)m->step_nops * 16 * sizeof(long long)));
+    }
+    sa.prof = prof;
     MCU(launch_decode_steps(sa, m->step_grid, m->step_smem, st));
+    if (prof) {
+        std::vector<long long> h((size_t)m->step_nops * 16);
+        MCU(cudaStreamSynchronize(st));
+        MCU(cudaMemcpy(h.data(), prof, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+        cudaFree(prof);
+        fprintf(stderr, "[alice] step profile of one CTA, SM clock cycles\n");
+        for (uint32_t i = 0; i < m->step_nops; i++) {
+            const long long* p = &h[(size_t)i * 16];
+            if (m->step_types[i] == SOP_GEMV) {
+                fprintf(stderr, "[alice] %3u matvec    prologue %6lld  first stage %6lld  rows %7lld  grid barrier %6lld  total %7lld  | stages:", i,
+                        p[1] - p[0], p[2] - p[1], p[3] - p[2], p[5] - p[4], p[5] - p[0]);
+                for (int c = 0; c < 8 && p[8 + c]; c++) fprintf(stderr, " %lld", p[8 + c] - (c ? p[7 + c] : p[2]));
+                fprintf(stderr, "\n");
+            } else if (m->step_types[i] == SOP_ATTN) {
+                fprintf(stderr, "[alice] %3u attention q+rope %6lld  positions %6lld  cta combine %6lld  ticket %6lld  fold %6lld  grid barrier %6lld  total %7lld\n", i,
+                        p[1] - p[0], p[2] - p[1], p[3] - p[2], p[6] - p[3], p[4] - p[6], p[5] - p[4], p[5] - p[0]);
+            } else {
+                fprintf(stderr, "[alice] %3u embedding %6lld  grid barrier %6lld\n", i, p[4] - p[0], p[5] - p[4]);
+            }
+        }
+    }
     return ALICE_OK;
 }
 
@@ -308,6 +342,7 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * c.num_heads * (c.head_dim + 4));
     if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads);
+    if (!rc) rc = dev_alloc(m, &m->rope_tab, 128);
     if (!rc) rc = dev_alloc(m, &m->argmax_key, 1);
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, 1);

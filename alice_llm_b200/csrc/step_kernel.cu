@@ -70,14 +70,25 @@ __device__ __forceinline__ void copy_args(StreamArgs* dst, const StreamArgs* src
     for (uint32_t i = tid; i < sizeof(StreamArgs) / 4; i += nthreads) d[i] = __ldg(s + i);
 }
 
+// Asynchronous copy (no register round trip, so the issuing warps carry on at once) of one op
+// descriptor into shared memory; complete for everybody after cp_async_wait_all() + a CTA barrier.
+__device__ __forceinline__ void prefetch_op(StepOp* dst, const StepOp* src, uint32_t tid) {
+    static_assert(sizeof(StepOp) % 16 == 0, "copied in 16-byte pieces");
+    if (tid < sizeof(StepOp) / 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(reinterpret_cast<uint8_t*>(dst) + tid * 16)),
+                     "l"(reinterpret_cast<const uint8_t*>(src) + tid * 16)
+                     : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <int GROUP>
-__device__ __noinline__ void run_attn(const StepOp& op, uint32_t pos, uint8_t* aux) {
+__device__ __noinline__ void run_attn(const StepOp& op, uint32_t pos, uint8_t* aux, long long* prof) {
     AttnSmem<GROUP>* sh = reinterpret_cast<AttnSmem<GROUP>*>(aux);
     const uint32_t items = op.shape.num_kv_heads * op.nsplit;
     for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
         asm volatile("bar.sync 1, 256;" ::: "memory");   // the scratch of the previous item is free
-        attn_fused_body<GROUP, true>(op.qkv, op.kc, op.vc, pos, op.shape, op.theta, op.neox, op.nsplit, op.part,
-                                     op.tickets, op.attn_out, it % op.shape.num_kv_heads, it / op.shape.num_kv_heads, sh);
+        attn_fused_body<GROUP, true>(op.qkv, op.kc, op.vc, pos, op.shape, op.rope_tab, op.neox, op.nsplit, op.part,
+                                     op.tickets, op.attn_out, it % op.shape.num_kv_heads, it / op.shape.num_kv_heads, sh, prof);
     }
 }
 
@@ -108,13 +119,24 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) decode_step_kernel(const St
     }
 
     uint8_t* aux = smem_raw + sa.aux_off;
-    uint32_t epoch = 0;
+    StepOp* sops = reinterpret_cast<StepOp*>(smem_raw + sa.ops_off);
+    static_assert(sizeof(StepOp) / 16 <= NCW * 32, "one 16-byte piece per consumer thread");
+    uint32_t epoch = 0, nop = 0;   // nop: ops started so far; descriptor of op number n sits in sops[n & 1]
+    prefetch_op(&sops[0], &sa.ops[0], threadIdx.x);
+    cp_async_wait_all();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     for (uint32_t step = 0; step < sa.nsteps; step++) {
         const uint32_t pos = (uint32_t)__ldcg(sa.pos);
-        for (uint32_t i = 0; i < sa.nops; i++) {
-            const StepOp& op = sa.ops[i];
+        for (uint32_t i = 0; i < sa.nops; i++, nop++) {
+            const StepOp& op = sops[nop & 1];
+            // the next descriptor travels while this op runs
+            if (i + 1 < sa.nops || step + 1 < sa.nsteps) prefetch_op(&sops[(nop + 1) & 1], &sa.ops[i + 1 < sa.nops ? i + 1 : 0], threadIdx.x);
+            long long* prof = (sa.prof && blockIdx.x == gridDim.x / 2) ? sa.prof + 16 * i : nullptr;
+            cx.prof = prof;
+            if (prof && threadIdx.x == 0) prof[0] = clock64();
             if (op.type == SOP_EMBED) {
                 // hidden = dequantized Q8_0 row of the current token (src/gguf.rs:990-1004)
+                if (blockIdx.x == gridDim.x - 1 && threadIdx.x < 64) rope_table_entry(op.rope_tab, threadIdx.x, pos, op.theta);
                 uint32_t t = (uint32_t)__ldcg(sa.token);
                 if (t >= op.vocab) t = 0;
                 const uint8_t* row = op.table + (size_t)t * (op.cols / 32) * 34;
@@ -125,18 +147,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) decode_step_kernel(const St
                 }
             } else if (op.type == SOP_GEMV) {
                 cx.op = (int)i;
-                copy_args(&sm->cargs, &op.g, threadIdx.x, 256);
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                run_gemv(op.variant, sm->cargs, cx);   // after an abort every warp still walks to the barrier below and leaves there
+                run_gemv(op.variant, op.g, cx);   // after an abort every warp still walks to the barrier below and leaves there
             } else if (op.type == SOP_ATTN) {
                 switch (op.shape.num_heads / op.shape.num_kv_heads) {
-                    case 1: run_attn<1>(op, pos, aux); break;
-                    case 2: run_attn<2>(op, pos, aux); break;
-                    case 4: run_attn<4>(op, pos, aux); break;
+                    case 1: run_attn<1>(op, pos, aux, prof); break;
+                    case 2: run_attn<2>(op, pos, aux, prof); break;
+                    case 4: run_attn<4>(op, pos, aux, prof); break;
                     default: break;
                 }
             }
+            if (prof && threadIdx.x == 0) prof[4] = clock64();
+            cp_async_wait_all();   // own pieces of the next descriptor; the barrier below publishes everybody's
             if (!grid_sync(sa.barrier, epoch, sm, sa.status)) return;
+            if (prof && threadIdx.x == 0) prof[5] = clock64();
         }
         // greedy hand-over: the head matvec left the packed maximum; one thread turns it into the next token
         if (blockIdx.x == 0 && threadIdx.x == 0) {

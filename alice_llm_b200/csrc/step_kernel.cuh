@@ -9,13 +9,15 @@ enum StepOpType : uint32_t { SOP_EMBED = 0, SOP_GEMV = 1, SOP_ATTN = 2 };
 // (format, activation positions per lane, fused SwiGLU) instances compiled into the step kernel
 enum StepVariant : int { SV_Q4K_1 = 0, SV_Q4K_1_SW, SV_Q4K_2, SV_Q6K_1, SV_Q6K_2, SV_Q8_0_1, SV_Q8_0_2 };
 
-struct StepOp {
+struct alignas(16) StepOp {
     uint32_t type;
     int variant;            // SOP_GEMV
     StreamArgs g;           // SOP_GEMV (planned against the step kernel's ring)
     // SOP_ATTN
     const float* qkv; float* kc; float* vc; float* part; unsigned int* tickets; float* attn_out;
-    AttnShape shape; float theta; int neox; uint32_t nsplit;
+    AttnShape shape; int neox; uint32_t nsplit;
+    float* rope_tab;        // SOP_EMBED writes it, SOP_ATTN reads it
+    float theta;            // SOP_EMBED
     // SOP_EMBED
     const uint8_t* table; float* hidden; uint32_t cols, vocab;
 };
@@ -29,6 +31,8 @@ struct StepArgs {
     int* status;
     int write_token;
     uint32_t nstages, stage_stride, aux_off;
+    uint32_t ops_off;       // shared-memory offset of the consumers' two-entry StepOp buffer
+    long long* prof;        // optional: 16 clock64 stamps per op, written by thread 0 of the middle CTA during the last step
 };
 
 constexpr uint32_t STEP_SMEM_BUDGET = 112 * 1024;   // two CTAs per SM

@@ -418,7 +418,8 @@ class GpuModel:
         return out
 
     def use_step_kernel(self, enabled: bool):
-        """decode_greedy inside one cooperative kernel (default) or one launch per op from a CUDA graph."""
+        """decode_greedy as one launch per op replayed from a CUDA graph (default) or, when enabled, inside one
+        cooperative whole-step kernel (same tokens; opt-in)."""
         check(self.engine._lib.alice_model_use_step_kernel(self._h, int(enabled)))
 
     def decode_greedy(self, first_token: int, n: int) -> np.ndarray:

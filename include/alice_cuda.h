@@ -161,9 +161,11 @@ int32_t alice_model_forward_read(alice_model* m, uint32_t token, float* logits);
  * step i. No host round trip between steps. */
 int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t n, uint32_t* out_tokens);
 int32_t alice_model_read_logits(alice_model* m, float* logits);
-/* alice_model_decode_greedy runs all its steps inside one cooperative kernel (every matvec, the attention and
- * the token hand-over; weights of the next matvec are prefetched across op boundaries) when every op of the
- * model has an instance there; 0 selects one launch per op replayed from a CUDA graph instead. Default 1. */
+/* alice_model_decode_greedy replays one launch per op from a CUDA graph (default, enabled = 0). enabled = 1
+ * selects the whole-step kernel instead: all steps inside one cooperative launch (every matvec, the
+ * attention and the token hand-over; weights of the next matvec are prefetched across op boundaries), used
+ * when every op of the model has an instance there. Same tokens either way; the graph path is the faster
+ * one at present, so the whole-step kernel is opt-in. */
 int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled);
 /* position / vocab_size / rollback_to / reset (src/gpu.rs:5655, 5660, 5645, 5618). rollback only lowers
  * the position; reset also zeroes the KV cache. */
