@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "abi_internal.cuh"
+#include "tp.cuh"
 
 using namespace alice;
 
@@ -136,6 +137,7 @@ int32_t alice_engine_destroy(alice_engine* e) {
     if (!e) return ALICE_OK;
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
+    alice::tp_release(e);
     if (e->scratch) cudaFree(e->scratch);
     if (e->status) cudaFree(e->status);
     if (e->own_stream) cudaStreamDestroy(e->stream);

@@ -17,6 +17,9 @@ struct alice_engine {
     int* status = nullptr;        // device status word
     void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
     size_t scratch_bytes = 0;
+    // tensor-parallel group (csrc/tp.cu): this engine is rank tp_rank of tp_world, one engine per GPU
+    uint32_t tp_rank = 0, tp_world = 1;
+    void* tp_comm = nullptr;      // ncclComm_t
 };
 
 struct alice_weights {

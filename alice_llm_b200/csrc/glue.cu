@@ -44,14 +44,16 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
                                   blockIdx.x, blockIdx.y, &sh);
 }
 
-// Turns the packed (ordered logit, ~row) maximum the output-head kernel accumulated into the next
-// token, records it, advances the position and clears the key for the next step.
-__global__ void finish_step_kernel(unsigned long long* __restrict__ key, int* __restrict__ token, int* __restrict__ pos,
-                                   int* __restrict__ trace, int write_token) {
+// Turns the packed (ordered logit, ~row) maxima the output-head kernels accumulated - one per rank of a
+// tensor-parallel group, each over that rank's rows, gathered to every rank - into the next token,
+// records it, advances the position and clears the keys for the next step.
+__global__ void finish_step_kernel(unsigned long long* __restrict__ keys, uint32_t nkeys, int* __restrict__ token,
+                                   int* __restrict__ pos, int* __restrict__ trace, int write_token) {
     pdl_wait();
     pdl_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
-        const unsigned long long k = *key;
+        unsigned long long k = 0ull;
+        for (uint32_t i = 0; i < nkeys; i++) { k = keys[i] > k ? keys[i] : k; keys[i] = 0ull; }
         const int p = *pos;
         if (write_token) {
             const int t = (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
@@ -59,7 +61,6 @@ __global__ void finish_step_kernel(unsigned long long* __restrict__ key, int* __
             if (trace) trace[p] = t;
         }
         *pos = p + 1;
-        *key = 0ull;
     }
 }
 
@@ -94,11 +95,11 @@ cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* 
     }
 }
 
-cudaError_t launch_finish_step(unsigned long long* key, int* token, int* pos, int* trace, int write_token, cudaStream_t st,
-                               bool pdl) {
+cudaError_t launch_finish_step(unsigned long long* keys, uint32_t nkeys, int* token, int* pos, int* trace, int write_token,
+                               cudaStream_t st, bool pdl) {
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(1), dim3(32), st, pdl);
-    return cudaLaunchKernelEx(&lc, finish_step_kernel, key, token, pos, trace, write_token);
+    return cudaLaunchKernelEx(&lc, finish_step_kernel, keys, nkeys, token, pos, trace, write_token);
 }
 
 }  // namespace alice

@@ -16,7 +16,8 @@ cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t c
 // for this position.
 cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
                              uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, cudaStream_t st, bool pdl);
-// token <- index held in *key (packed maximum written by the output-head kernel) when write_token; pos <- pos + 1
-cudaError_t launch_finish_step(unsigned long long* key, int* token, int* pos, int* trace, int write_token, cudaStream_t st,
-                               bool pdl);
+// token <- index held in the largest of keys[0 .. nkeys) (packed maxima written by the output-head kernels,
+// one per tensor-parallel rank) when write_token; pos <- pos + 1; keys <- 0
+cudaError_t launch_finish_step(unsigned long long* keys, uint32_t nkeys, int* token, int* pos, int* trace, int write_token,
+                               cudaStream_t st, bool pdl);
 }  // namespace alice

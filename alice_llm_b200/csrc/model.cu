@@ -11,6 +11,7 @@
 #include "attn_body.cuh"
 #include "glue.cuh"
 #include "step_kernel.cuh"
+#include "tp.cuh"
 
 using namespace alice;
 
@@ -33,6 +34,9 @@ struct alice_model {
     unsigned int* attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
+    // tensor parallel (engine's group): every projection holds rows [r*R/n, (r+1)*R/n); l* are the local sizes
+    uint32_t tp_n = 1, tp_r = 0, lq = 0, lkv = 0, lH = 0, lF = 0, lV = 0;
+    unsigned long long* argmax_keys = nullptr;   // one packed maximum per rank (argmax_key = &argmax_keys[tp_r])
     // device-side state: position, current token, tokens chosen per position
     int *d_pos = nullptr, *d_token = nullptr, *d_trace = nullptr;
     uint32_t pos = 0;  // host mirror of *d_pos
@@ -79,68 +83,78 @@ int gemv(alice_model* m, const GemvOp& op, const char* what) {
     return alice_fail(rc, "alice_model: %s matvec failed (%d): %s", what, rc, cudaGetErrorString(cudaGetLastError()));
 }
 
+// In-place all-gather of a row-sharded activation vector (no-op for a single GPU).
+int gather(alice_model* m, float* base, uint32_t floats_per_rank) {
+    return tp_all_gather(m->e, base, (size_t)floats_per_rank * sizeof(float));
+}
+
 // Queues one decode step on the engine's stream. The token is read from *d_token.
+// With a tensor-parallel group every matvec computes this rank's rows into its slice of the full vector
+// and an all-gather completes it on every rank; attention runs on the rank's own KV heads (its q, k, v
+// rows), so only its output needs gathering (it is the input of the output projection).
 int enqueue_step(alice_model* m, bool greedy_feed) {
     const alice_model_config& c = m->cfg;
     cudaStream_t st = m->e->stream;
     const bool pdl = m->e->pdl;
-    const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
-    const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
+    const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r;
+    const AttnShape shape{c.num_heads / m->tp_n, c.num_kv_heads / m->tp_n, c.head_dim};
+    int rc;
     MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, st, pdl));
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const alice_model::Layer& L = m->layers[l];
-        float* kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim;
-        float* vc = m->vcache + (size_t)l * c.max_seq_len * kv_dim;
+        float* kc = m->kcache + (size_t)l * c.max_seq_len * lkv;
+        float* vc = m->vcache + (size_t)l * c.max_seq_len * lkv;
         if (L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt && !L.q.scales) {
             // attention norm + q, k, v projections in one launch (src/llama3.rs:14178-14217)
             GemvOp op;
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
-            op.y_off[0] = 0; op.y_off[1] = q_dim; op.y_off[2] = q_dim + kv_dim;
+            op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
             op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
-            int rc = gemv(m, op, "qkv");
-            if (rc) return rc;
+            if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
             const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
-            const uint32_t offs[3] = {0, q_dim, q_dim + kv_dim};
+            const uint32_t offs[3] = {0, lq, lq + lkv};
             for (int i = 0; i < 3; i++) {
                 GemvOp op;
                 op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
                 op.y = m->qkv + offs[i];
-                int rc = gemv(m, op, "q/k/v");
-                if (rc) return rc;
+                if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
         }
         // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
         MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
-                             m->attn_tickets, m->attn_out, st, pdl));
+                             m->attn_tickets, m->attn_out + (size_t)r * lq, st, pdl));
+        if ((rc = gather(m, m->attn_out, lq))) return rc;
         {   // output projection + residual (src/llama3.rs:14423, 14468)
             GemvOp op;
-            op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden;
-            int rc = gemv(m, op, "o_proj");
-            if (rc) return rc;
+            op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
+            if ((rc = gemv(m, op, "o_proj"))) return rc;
+            if ((rc = gather(m, m->hidden, m->lH))) return rc;
         }
         {   // FFN norm + fused SwiGLU gate/up (src/llama3.rs:14497-14534)
             GemvOp op;
             op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
-            op.y = m->ffn_h;
-            int rc = gemv(m, op, "gate/up");
-            if (rc) return rc;
+            op.y = m->ffn_h; op.y_off[0] = r * m->lF;
+            if ((rc = gemv(m, op, "gate/up"))) return rc;
+            if ((rc = gather(m, m->ffn_h, m->lF))) return rc;
         }
         {   // down projection + residual (src/llama3.rs:14536-14555)
             GemvOp op;
-            op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden;
-            int rc = gemv(m, op, "down_proj");
-            if (rc) return rc;
+            op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
+            if ((rc = gemv(m, op, "down_proj"))) return rc;
+            if ((rc = gather(m, m->hidden, m->lH))) return rc;
         }
     }
     {   // output norm + head (src/llama3.rs:14590-14604)
         GemvOp op;
         op.w[0] = &m->out; op.x = m->hidden; op.norm_w = m->out_norm; op.norm_eps = c.eps; op.y = m->logits;
-        op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum
-        int rc = gemv(m, op, "output head");
-        if (rc) return rc;
+        op.y_off[0] = r * m->lV;
+        op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
+        if ((rc = gemv(m, op, "output head"))) return rc;
+        if ((rc = gather(m, m->logits, m->lV))) return rc;
+        if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
     }
-    MCU(launch_finish_step(m->argmax_key, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
+    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
     return ALICE_OK;
 }
 
@@ -157,6 +171,7 @@ int build_step_ops(alice_model* m) {
     const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
     const uint32_t group = c.num_heads / c.num_kv_heads;
     if (group != 1 && group != 2 && group != 4) return step_skip(1);
+    if (m->tp_n > 1) return step_skip(9);   // the whole-step kernel has no collective stage
     std::vector<GemvOp> gops;
     std::vector<int> kind;   // -1 embed, -2 attention(layer), >= 0 index into gops
     std::vector<uint32_t> attn_layer;
@@ -304,12 +319,19 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (group != 1 && group != 2 && group != 4 && group != 5 && group != 8)
         return alice_fail(ALICE_E_SHAPE, "%s: %u query heads per KV head not supported (1, 2, 4, 5, 8)", who, group);
     const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
+    // tensor-parallel group of the engine: the weight handles are this rank's row shards
+    const uint32_t n = e->tp_world;
+    if (c.num_kv_heads % n || c.hidden_dim % n || c.intermediate_dim % n || c.vocab_size % n)
+        return alice_fail(ALICE_E_SHAPE, "%s: kv heads %u, hidden %u, ffn %u and vocab %u must all divide by the group size %u", who,
+                          c.num_kv_heads, c.hidden_dim, c.intermediate_dim, c.vocab_size, n);
+    const uint32_t lq = q_dim / n, lkv = kv_dim / n, lH = c.hidden_dim / n, lF = c.intermediate_dim / n, lV = c.vocab_size / n;
     if (embedding->d.fmt != WF_Q8_0 || !same_shape(embedding->d, c.vocab_size, c.hidden_dim))
         return alice_fail(ALICE_E_SHAPE, "%s: embedding must be Q8_0 [vocab x hidden]", who);
-    if (!same_shape(output->d, c.vocab_size, c.hidden_dim)) return alice_fail(ALICE_E_SHAPE, "%s: output head shape", who);
+    if (!same_shape(output->d, lV, c.hidden_dim)) return alice_fail(ALICE_E_SHAPE, "%s: output head shape", who);
     MCU(cudaSetDevice(e->device));
     auto* m = new alice_model();
     m->e = e; m->cfg = c; m->emb = embedding->d; m->out = output->d;
+    m->tp_n = n; m->tp_r = e->tp_rank; m->lq = lq; m->lkv = lkv; m->lH = lH; m->lF = lF; m->lV = lV;
     int rc = ALICE_OK;
     for (uint32_t l = 0; l < c.num_layers && !rc; l++) {
         const alice_layer_weights& s = layers[l];
@@ -317,11 +339,11 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
             rc = alice_fail(ALICE_E_INVALID, "%s: layer %u has a null weight", who, l);
             break;
         }
-        if (!same_shape(s.q->d, q_dim, c.hidden_dim) || !same_shape(s.k->d, kv_dim, c.hidden_dim) ||
-            !same_shape(s.v->d, kv_dim, c.hidden_dim) || !same_shape(s.o->d, c.hidden_dim, q_dim) ||
-            !same_shape(s.gate->d, c.intermediate_dim, c.hidden_dim) || !same_shape(s.up->d, c.intermediate_dim, c.hidden_dim) ||
-            !same_shape(s.down->d, c.hidden_dim, c.intermediate_dim) || s.gate->d.fmt != s.up->d.fmt) {
-            rc = alice_fail(ALICE_E_SHAPE, "%s: layer %u weight shapes do not match the config", who, l);
+        if (!same_shape(s.q->d, lq, c.hidden_dim) || !same_shape(s.k->d, lkv, c.hidden_dim) ||
+            !same_shape(s.v->d, lkv, c.hidden_dim) || !same_shape(s.o->d, lH, q_dim) ||
+            !same_shape(s.gate->d, lF, c.hidden_dim) || !same_shape(s.up->d, lF, c.hidden_dim) ||
+            !same_shape(s.down->d, lH, c.intermediate_dim) || s.gate->d.fmt != s.up->d.fmt) {
+            rc = alice_fail(ALICE_E_SHAPE, "%s: layer %u weight shapes do not match the config (rows are this rank's 1/%u share)", who, l, n);
             break;
         }
         alice_model::Layer L;
@@ -330,20 +352,21 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         if (!rc) rc = upload_norm(m, &L.ffn_norm, s.ffn_norm, c.hidden_dim);
         m->layers.push_back(L);
     }
-    m->nsplit = std::max<uint32_t>(1, std::min<uint32_t>(64, (2 * (uint32_t)e->num_sms) / c.num_kv_heads));
-    const size_t kv_elems = (size_t)c.num_layers * c.max_seq_len * kv_dim;
+    m->nsplit = std::max<uint32_t>(1, std::min<uint32_t>(64, (2 * (uint32_t)e->num_sms) / (c.num_kv_heads / n)));
+    const size_t kv_elems = (size_t)c.num_layers * c.max_seq_len * lkv;
     if (!rc) rc = upload_norm(m, &m->out_norm, output_norm, c.hidden_dim);
     if (!rc) rc = dev_alloc(m, &m->hidden, c.hidden_dim);
-    if (!rc) rc = dev_alloc(m, &m->qkv, q_dim + 2 * kv_dim);
+    if (!rc) rc = dev_alloc(m, &m->qkv, lq + 2 * lkv);
     if (!rc) rc = dev_alloc(m, &m->attn_out, q_dim);
     if (!rc) rc = dev_alloc(m, &m->ffn_h, c.intermediate_dim);
     if (!rc) rc = dev_alloc(m, &m->logits, c.vocab_size);
     if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
-    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * c.num_heads * (c.head_dim + 4));
-    if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads);
+    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
+    if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads / n);
     if (!rc) rc = dev_alloc(m, &m->rope_tab, 128);
-    if (!rc) rc = dev_alloc(m, &m->argmax_key, 1);
+    if (!rc) rc = dev_alloc(m, &m->argmax_keys, n);
+    if (!rc) m->argmax_key = m->argmax_keys + m->tp_r;
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, 1);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
@@ -351,8 +374,8 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         cudaError_t err = cudaMemsetAsync(m->kcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)c.num_kv_heads * 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->argmax_key, 0, 8, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)(c.num_kv_heads / n) * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->argmax_keys, 0, 8 * (size_t)n, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
@@ -495,7 +518,7 @@ int32_t alice_model_rollback_to(alice_model* m, uint32_t pos) {
 
 int32_t alice_model_reset(alice_model* m) {
     if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_reset: null model");
-    const size_t kv_bytes = (size_t)m->cfg.num_layers * m->cfg.max_seq_len * m->cfg.num_kv_heads * m->cfg.head_dim * 4;
+    const size_t kv_bytes = (size_t)m->cfg.num_layers * m->cfg.max_seq_len * m->lkv * 4;
     MCU(cudaMemsetAsync(m->kcache, 0, kv_bytes, m->e->stream));
     MCU(cudaMemsetAsync(m->vcache, 0, kv_bytes, m->e->stream));
     return alice_model_set_position(m, 0);
@@ -505,7 +528,7 @@ static int kv_copy(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos,
     if (!m || !k || !v) return alice_fail(ALICE_E_INVALID, "alice_model_kv: null argument");
     const alice_model_config& c = m->cfg;
     if (layer >= c.num_layers || (uint64_t)pos0 + npos > c.max_seq_len) return alice_fail(ALICE_E_SHAPE, "alice_model_kv: layer / position out of range");
-    const size_t kv_dim = (size_t)c.num_kv_heads * c.head_dim;
+    const size_t kv_dim = m->lkv;   // this rank's KV heads
     const size_t off = ((size_t)layer * c.max_seq_len + pos0) * kv_dim, bytes = (size_t)npos * kv_dim * 4;
     cudaStream_t st = m->e->stream;
     if (to_device) {

@@ -139,6 +139,25 @@ class GpuEngine:
     def set_tuning(self, rows_per_set: int = 0, stages: int = 0):
         check(self._lib.alice_engine_set_tuning(self._h, rows_per_set, stages))
 
+    # -- tensor parallel: one engine (one process) per GPU, rows of every projection sharded over the group --
+    TP_ID_BYTES = 128
+
+    def tp_unique_id(self) -> bytes:
+        """Group id made by rank 0; hand it to the other ranks (e.g. torch.distributed.broadcast_object_list)."""
+        buf = C.create_string_buffer(self.TP_ID_BYTES)
+        check(self._lib.alice_tp_unique_id(buf, self.TP_ID_BYTES))
+        return bytes(buf.raw)
+
+    def tp_init(self, rank: int, world: int, unique_id: bytes):
+        """Joins the group (collective: every rank calls it with the same id)."""
+        buf = C.create_string_buffer(bytes(unique_id), self.TP_ID_BYTES)
+        check(self._lib.alice_engine_tp_init(self._h, rank, world, buf, self.TP_ID_BYTES))
+
+    def tp_info(self):
+        r, w = C.c_uint32(), C.c_uint32()
+        check(self._lib.alice_engine_tp_info(self._h, C.byref(r), C.byref(w)))
+        return r.value, w.value
+
     # -- weights: upload_weights* (src/gpu.rs:698-798) --
     def upload_weights_typed(self, data, rows: int, cols: int, quant: GpuQuantType) -> GpuWeightBuffer:
         d = _np(data, np.uint8)
@@ -347,18 +366,33 @@ class GpuModelConfig:
                    d["head_dim"], d["rope_theta"], d["eps"], d["max_seq_len"], d["vocab_size"], bool(d.get("neox_rope", 0)))
 
 
+def shard_rows(data, rows: int, rank: int, world: int):
+    """Rows [rank*rows/world, (rank+1)*rows/world) of a row-major tensor of raw blocks (or of any per-row
+    array): a contiguous byte range, since a row is a whole number of blocks. Returns (shard, shard_rows)."""
+    if rows % world:
+        raise AliceError(_lib.E_SHAPE, f"shard_rows: {rows} rows do not divide over {world} ranks")
+    a = np.ascontiguousarray(data).reshape(-1)
+    if a.size % rows:
+        raise AliceError(_lib.E_SHAPE, f"shard_rows: {a.size} elements are not {rows} equal rows")
+    per = a.size // rows
+    n = rows // world
+    return a[rank * n * per:(rank + 1) * n * per], n
+
+
 class GpuModel:
     """GpuModel (src/gpu.rs:2348): the pre-built decode graph of a Llama-style model on one device.
 
     ``GpuModel.load(engine, model, config)`` takes the raw quantized tensors (a dict as built by
-    ``synth.make_llama``, standing in for the GgufFile of src/gpu.rs:2831) and uploads them verbatim."""
+    ``synth.make_llama``, standing in for the GgufFile of src/gpu.rs:2831) and uploads them verbatim.
+    On an engine that belongs to a tensor-parallel group (``engine.tp_init``) it uploads this rank's row
+    shard of every projection; a tensor entry may also be a ready ``GpuWeightBuffer`` (already the shard)."""
 
     def __init__(self, engine: GpuEngine, handle, config: GpuModelConfig, keep):
         self.engine, self._h, self._config, self._keep = engine, handle, config, keep
         engine._children.add(self)
 
     @classmethod
-    def load(cls, engine: GpuEngine, model: dict, config: GpuModelConfig | None = None, device_tensors=None) -> "GpuModel":
+    def load(cls, engine: GpuEngine, model: dict, config: GpuModelConfig | None = None) -> "GpuModel":
         cfg = config or GpuModelConfig.from_dict(model["config"])
         q_dim, kv_dim = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
         H, F = cfg.hidden_dim, cfg.intermediate_dim
@@ -366,8 +400,15 @@ class GpuModel:
                   "down": (H, F)}
         keep = []
 
-        def up(entry, rows, cols):
+        rank, world = engine.tp_info()
+
+        def up(entry, rows, cols, shard=True):
+            if isinstance(entry, GpuWeightBuffer):
+                keep.append(entry)
+                return entry
             t, data = entry
+            if shard and world > 1:
+                data, rows = shard_rows(data, rows, rank, world)
             w = engine.upload_weights_typed(data, rows, cols, GpuQuantType(t))
             keep.append(w)
             return w
@@ -379,7 +420,7 @@ class GpuModel:
             an, fn = _np(L["attn_norm"], np.float32), _np(L["ffn_norm"], np.float32)
             keep += [an, fn]
             layers[i].attn_norm, layers[i].ffn_norm = an.ctypes.data, fn.ctypes.data
-        emb = up(model["embedding"], cfg.vocab_size, H)
+        emb = up(model["embedding"], cfg.vocab_size, H, shard=False)
         out = up(model["output"], cfg.vocab_size, H)
         onorm = _np(model["output_norm"], np.float32)
         c = _lib.ModelConfig(cfg.num_layers, H, F, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.vocab_size,

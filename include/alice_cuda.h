@@ -129,13 +129,31 @@ int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alic
 /* dequantize_weight_row / GgufFile::tensor_to_f32 (src/gguf.rs:6168, 574): out[r*cols + c], bit-exact. */
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out);
 
+/* ---- tensor parallel ------------------------------------------------------------------------ */
+/* One engine (one process) per GPU; output rows of every projection are sharded over the group and the
+ * full vector is rebuilt on every rank by an NCCL all-gather queued on the engine's stream (the row
+ * split is where the reference parallelises a matvec, src/gguf.rs:3664; the reference itself is single
+ * device). NCCL is loaded at run time (libnccl.so.2), only when a group is formed.
+ * alice_tp_unique_id: rank 0 fills `out` (ALICE_TP_ID_BYTES) and hands it to the other ranks by any
+ * means; every rank then calls alice_engine_tp_init (collective: returns when the group is formed).
+ * A model created on an engine that belongs to a group takes this rank's row shards (see below). */
+#define ALICE_TP_ID_BYTES 128
+int32_t alice_tp_unique_id(void* out, size_t nbytes);
+int32_t alice_engine_tp_init(alice_engine* e, uint32_t rank, uint32_t world, const void* unique_id, size_t nbytes);
+int32_t alice_engine_tp_info(const alice_engine* e, uint32_t* rank, uint32_t* world);
+
 /* ---- decode model ------------------------------------------------------------------------- */
 /* GpuModel (src/gpu.rs:2348) for the Llama-style attention + SwiGLU layer stack, i.e. the Llama branch
  * of Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613): per layer
  * rms_norm -> q/k/v matvec -> RoPE -> KV append -> GQA attention -> o matvec + residual ->
  * rms_norm -> fused SwiGLU gate/up -> down matvec + residual; then output norm and head.
  * One decode step is ~7 kernels per layer replayed from a CUDA graph; position and token live on
- * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations). */
+ * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations).
+ * On an engine that is rank r of a tensor-parallel group of n, the config stays the whole model's and the
+ * weight handles are row shards: rows [r*R/n, (r+1)*R/n) of q, k, v, o, gate, up, down and the output
+ * head (R = that matrix's row count; contiguous byte ranges of the raw blocks); the embedding table is
+ * whole on every rank. The rank keeps the KV cache of its num_kv_heads/n heads only (kv_write / kv_read
+ * move rows of kv_dim/n floats). All ranks must make the same calls in the same order. */
 typedef struct alice_model alice_model;
 typedef struct {                       /* GpuModelConfig, src/gpu.rs:2111-2151 */
     uint32_t num_layers, hidden_dim, intermediate_dim, num_heads, num_kv_heads, head_dim;
