@@ -133,6 +133,7 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.y = op.y; a.status = cfg.status;
     a.rows = total_rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
     a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
+    a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
 
     // warps per row: just enough lanes for one unit each, at most all eight

@@ -47,6 +47,7 @@ struct GemvOp {
     const float* x = nullptr;                              // f32 input vector
     const float* norm_w = nullptr;                         // fused RMSNorm of x with these weights
     float norm_eps = 0.0f;
+    bool q8k_roundtrip = false;                            // with norm_w, f32-activation formats: see StreamArgs
     const float* resid = nullptr;                          // y = resid + result
     unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs
     float* y = nullptr;

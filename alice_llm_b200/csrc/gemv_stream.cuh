@@ -46,6 +46,9 @@ struct StreamArgs {
     // Optional fused RMSNorm of the input (rms_norm, src/llama3.rs:5244): x <- x * rsqrt(mean(x^2) + eps) * norm_w
     const float* norm_w;
     float norm_eps;
+    // With norm_w, for f32-activation formats: round the normalised vector to the Q8_K grid (quantize, then
+    // d * q), as the CPU model does on projections it reaches through matvec_preq (src/gguf.rs:4593-4605)
+    uint32_t q8k_roundtrip;
     // Optional residual epilogue: y[row] = resid[row] + result (resid may alias y)
     const float* resid;
     // Optional greedy-argmax epilogue: atomicMax of (order-preserving bits of y[i]) << 32 | ~i, so the
@@ -192,11 +195,12 @@ __device__ __forceinline__ void stream_drain(StreamCtx& cx) {
 //   norm_w != null: rms_norm (src/llama3.rs:5244-5256) - f64 sum of squares, mean and scale in f32, then
 //                   (x * scale) * w - into the f32 area at xn_off;
 //   quant:          the (normalised) vector -> Q8_K in shared memory at q8_off (qs | bsums | d), one warp
-//                   per 256-element block, exactly the stand-alone quantizer.
+//                   per 256-element block, exactly the stand-alone quantizer;
+//   roundtrip:      (with norm_w) the normalised vector is replaced by d * q of its Q8_K quantization.
 // cg: read x with ld.global.cg (other SMs rewrote it inside this kernel).
 static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
                                                     float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
-                                                    bool quant, bool cg) {
+                                                    bool quant, bool roundtrip, bool cg) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const float* src = x;
     bool src_global = true;
@@ -256,6 +260,14 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* sme
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // xn complete
         src = xn;
         src_global = false;
+        if (roundtrip) {   // xn <- d * q of its own Q8_K quantization, block by block, in place
+#pragma unroll 1
+            for (uint32_t b = warp; b < cols / QK_K; b += NCW) {
+                const Q8KLaneInput in = q8k_load_lane(xn + (size_t)b * QK_K, lane, false);
+                q8k_quantize_block_warp<true>(in, lane, nullptr, nullptr, nullptr, xn + (size_t)b * QK_K);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        }
     }
     if (quant) {
         const uint32_t nb = cols / QK_K;
@@ -296,7 +308,8 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const bool norm = a.norm_w != nullptr;
     const bool quant = F::USES_Q8K && a.q8.qs == nullptr;
     if (norm || quant)
-        stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant, cg);
+        stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                        !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
     const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
     const bool x_global = !norm;
     Q8KView q8 = a.q8;

@@ -83,6 +83,11 @@ int gemv(alice_model* m, const GemvOp& op, const char* what) {
     return alice_fail(rc, "alice_model: %s matvec failed (%d): %s", what, rc, cudaGetErrorString(cudaGetLastError()));
 }
 
+// The CPU model reaches q/k/v and gate/up through matvec_preq with the Q8_K-quantized norm output; for
+// Q1_0 / Q2_0 weights that path turns the blocks back into f32 (src/gguf.rs:4593-4605), so those
+// projections see the vector rounded to the Q8_K grid.
+bool preq_roundtrip(const WeightDesc& w) { return w.fmt == WF_Q1_0 || w.fmt == WF_Q2_0; }
+
 // In-place all-gather of a row-sharded activation vector (no-op for a single GPU).
 int gather(alice_model* m, float* base, uint32_t floats_per_rank) {
     return tp_all_gather(m->e, base, (size_t)floats_per_rank * sizeof(float));
@@ -110,6 +115,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
             op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
+            op.q8k_roundtrip = preq_roundtrip(L.q);
             if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
             const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
@@ -117,6 +123,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             for (int i = 0; i < 3; i++) {
                 GemvOp op;
                 op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
+                op.q8k_roundtrip = preq_roundtrip(*ws[i]);
                 op.y = m->qkv + offs[i];
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
@@ -134,6 +141,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         {   // FFN norm + fused SwiGLU gate/up (src/llama3.rs:14497-14534)
             GemvOp op;
             op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
+            op.q8k_roundtrip = preq_roundtrip(L.gate);
             op.y = m->ffn_h; op.y_off[0] = r * m->lF;
             if ((rc = gemv(m, op, "gate/up"))) return rc;
             if ((rc = gather(m, m->ffn_h, m->lF))) return rc;

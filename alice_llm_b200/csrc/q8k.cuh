@@ -46,8 +46,11 @@ __device__ __forceinline__ Q8KLaneInput q8k_load_lane(const float* xb, uint32_t 
     if (cg) return Q8KLaneInput{__ldcg(src), __ldcg(src + 1)};
     return Q8KLaneInput{src[0], src[1]};
 }
+// ROUNDTRIP: instead of storing the block, write d * q back as f32 to `rt` (256 floats) - the vector as a
+// kernel sees it after quantized_matvec_preq turned the Q8_K blocks back into f32 (src/gguf.rs:4593-4605).
+template <bool ROUNDTRIP = false>
 __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, uint32_t lane, int8_t* qs, float* d,
-                                                        int16_t* bsums) {
+                                                        int16_t* bsums, float* rt = nullptr) {
     const float4 a = in.a, b = in.b;
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     // local first-maximum, then a warp max over (|x| bits, reversed index) keys
@@ -70,9 +73,9 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, u
     uint32_t w0 = 0, w1 = 0;
     int lsum = 0;
     float dval = 0.0f;
+    int q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (amax != 0.0f) {
         const float iscale = __fdiv_rn(128.0f, max_val);
-        int q[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const float t = __fadd_rn(__fmul_rn(iscale, v[i]), 12582912.0f);
@@ -83,6 +86,12 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, u
         w0 = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
         w1 = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
         dval = __fdiv_rn(1.0f, iscale);
+    }
+    if (ROUNDTRIP) {
+        float4* out = reinterpret_cast<float4*>(rt + lane * 8);
+        out[0] = make_float4(__fmul_rn(dval, (float)q[0]), __fmul_rn(dval, (float)q[1]), __fmul_rn(dval, (float)q[2]), __fmul_rn(dval, (float)q[3]));
+        out[1] = make_float4(__fmul_rn(dval, (float)q[4]), __fmul_rn(dval, (float)q[5]), __fmul_rn(dval, (float)q[6]), __fmul_rn(dval, (float)q[7]));
+        return;
     }
     reinterpret_cast<uint2*>(qs)[lane] = make_uint2(w0, w1);
     const int pair = lsum + __shfl_xor_sync(0xffffffffu, lsum, 1);

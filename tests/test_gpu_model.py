@@ -38,7 +38,12 @@ def prefill(rng, cfg, gm, orc, npos):
     orc.pos = npos
 
 
-@pytest.mark.parametrize("mix,heads", [(None, (4, 2)), ({"v": synth.Q6_K, "down": synth.Q4_K, "output": synth.Q8_0}, (8, 2))])
+Q1_MIX = {n: synth.Q1_0 for n in ("q", "k", "v", "o", "gate", "up", "down")}
+Q1_MIX["output"] = synth.Q8_0   # the 27B binary-weight configuration: Q1_0 projections, Q8_0 head, 5 query heads per KV head
+
+
+@pytest.mark.parametrize("mix,heads", [(None, (4, 2)), ({"v": synth.Q6_K, "down": synth.Q4_K, "output": synth.Q8_0}, (8, 2)),
+                                       (Q1_MIX, (10, 2)), ({**Q1_MIX, "k": synth.Q2_0, "gate": synth.Q2_0, "up": synth.Q2_0}, (4, 4))])
 def test_forward_logits_match_oracle(eng, oracle, mix, heads):
     from alice_llm_b200.gpu import GpuModel
     cfg = dict(CFG, num_heads=heads[0], num_kv_heads=heads[1])
