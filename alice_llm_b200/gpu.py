@@ -407,6 +407,14 @@ class GpuModel:
                 keep.append(entry)
                 return entry
             t, data = entry
+            if GpuQuantType(t) is GpuQuantType.Ternary:   # (pos planes, neg planes, per-row scales)
+                pos, neg, sc = data
+                if shard and world > 1:
+                    (pos, n), (neg, _), (sc, _) = (shard_rows(a, rows, rank, world) for a in (pos, neg, sc))
+                    rows = n
+                w = engine.upload_ternary(pos, neg, sc, rows, cols)
+                keep.append(w)
+                return w
             if shard and world > 1:
                 data, rows = shard_rows(data, rows, rank, world)
             w = engine.upload_weights_typed(data, rows, cols, GpuQuantType(t))

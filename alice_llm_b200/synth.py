@@ -16,6 +16,7 @@ QK_K = 256
 
 # GGML type ids (src/gguf.rs:101-122)
 Q8_0, Q4_K, Q5_K, Q6_K, Q1_0, Q2_0 = 8, 12, 13, 14, 41, 42
+TERNARY = 1000   # in-memory ternary bit planes (TernaryMatrix, src/gguf.rs:5198); not a GGML id
 BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q1_0: 18, Q2_0: 34}
 BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, Q1_0: 128, Q2_0: 128}
 TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", Q1_0: "Q1_0", Q2_0: "Q2_0"}
@@ -101,7 +102,10 @@ def make_q2_0(rng, rows: int, cols: int) -> np.ndarray:
 MAKERS = {Q4_K: make_q4k, Q5_K: make_q5k, Q6_K: make_q6k, Q8_0: make_q8_0, Q1_0: make_q1_0, Q2_0: make_q2_0}
 
 
-def make_weights(qtype: int, rng, rows: int, cols: int) -> np.ndarray:
+def make_weights(qtype: int, rng, rows: int, cols: int):
+    """Raw blocks of a GGML type, or (pos, neg, scales) for TERNARY."""
+    if qtype == TERNARY:
+        return make_ternary(rng, rows, cols)
     return MAKERS[qtype](rng, rows, cols)
 
 
@@ -140,7 +144,8 @@ def make_llama(rng, cfg: dict, mix: dict | None = None) -> dict:
     cfg keys: num_layers, hidden_dim, intermediate_dim, num_heads, num_kv_heads, head_dim, vocab_size,
     max_seq_len, rope_theta, eps. ``mix`` maps tensor role -> GGML type; the default is the Q4_K_M mix
     of the 8B benchmark configuration: q/k/v/o/gate/up Q4_K, down and output head Q6_K, embedding Q8_0.
-    RMSNorm weights are 1 + N(0, 0.02)."""
+    A role mapped to TERNARY carries (pos, neg, scales) bit planes instead of blocks (the 70B configuration:
+    every projection and the output head ternary). RMSNorm weights are 1 + N(0, 0.02)."""
     mix = {"q": Q4_K, "k": Q4_K, "v": Q4_K, "o": Q4_K, "gate": Q4_K, "up": Q4_K, "down": Q6_K, "output": Q6_K,
            **(mix or {})}
     H, F = cfg["hidden_dim"], cfg["intermediate_dim"]

@@ -539,12 +539,37 @@ struct OrcModel {
 
 namespace {
 
-size_t mat_bytes(uint32_t t, size_t rows, size_t cols) { return rows * (cols / elements_per_block(t)) * block_bytes(t); }
+// Model tensors in the in-memory ternary packing (TernaryMatrix, src/gguf.rs:5198) travel as one blob:
+// pos planes [rows][ceil(cols/8)] | neg planes | f32 scale per row; type id T_TERNARY (not a GGML id).
+constexpr uint32_t T_TERNARY = 1000;
+size_t mat_bytes(uint32_t t, size_t rows, size_t cols) {
+    if (t == T_TERNARY) return rows * (2 * ((cols + 7) / 8) + 4);
+    return rows * (cols / elements_per_block(t)) * block_bytes(t);
+}
+int ternary_blob_matvec(const uint8_t* blob, size_t rows, size_t cols, const float* x, float* y) {
+    const size_t pb = (cols + 7) / 8;
+    const uint8_t* pos = blob;
+    const uint8_t* neg = blob + rows * pb;
+    std::vector<float> scales(rows);
+    std::memcpy(scales.data(), blob + 2 * rows * pb, rows * 4);
+    for (size_t r = 0; r < rows; r++) y[r] = ternary_dot_row_scalar(pos + r * pb, neg + r * pb, scales[r], cols, x);
+    return 0;
+}
 
 // Llama branch of Llama3Model::forward_with_layer_hook (src/llama3.rs:13681-13687, 14167-14613).
 // MV(type, x, data, nbytes, rows, cols, y) = WeightRef::matvec; MVP(..., d8, q8, bs, y) = matvec_preq.
+// Tensors of type T_TERNARY take the forward_ternary skeleton instead (src/llama3.rs:16960-17062): the same
+// layer sequence with ternary_matvec on f32 activations everywhere, no Q8_K step.
 template <class MV, class MVP>
-int llama_forward(const OrcModel& m, uint32_t token, uint32_t pos, float* logits, MV mv, MVP mvp) {
+int llama_forward(const OrcModel& m, uint32_t token, uint32_t pos, float* logits, MV mv_g, MVP mvp_g) {
+    auto mv = [&](uint32_t t, const float* x, const uint8_t* d, size_t nb, size_t r, size_t c, float* y) {
+        return t == T_TERNARY ? ternary_blob_matvec(d, r, c, x, y) : mv_g(t, x, d, nb, r, c, y);
+    };
+    const float* cur_norm = nullptr;   // f32 vector behind the current Q8_K blocks
+    auto mvp = [&](uint32_t t, const uint8_t* d, size_t nb, size_t r, size_t c, const float* d8, const int8_t* q8,
+                   const int16_t* bs, float* y) {
+        return t == T_TERNARY ? ternary_blob_matvec(d, r, c, cur_norm, y) : mvp_g(t, d, nb, r, c, d8, q8, bs, y);
+    };
     const size_t H = m.hidden, F = m.ffn, hd = m.head_dim, q_dim = (size_t)m.num_heads * hd, kv_dim = (size_t)m.num_kv_heads * hd;
     if (token >= m.vocab || pos >= m.max_seq || H % QK_K) return -1;
     std::vector<float> hidden(H), norm(H), q(q_dim), k(kv_dim), v(kv_dim), attn(q_dim), o(H), gate(F), up(F), down(H);
@@ -556,6 +581,7 @@ int llama_forward(const OrcModel& m, uint32_t token, uint32_t pos, float* logits
         float* kc = m.kcache + (size_t)l * m.max_seq * kv_dim;
         float* vc = m.vcache + (size_t)l * m.max_seq * kv_dim;
         rms_norm(hidden.data(), L.attn_norm, m.eps, norm.data(), H);
+        cur_norm = norm.data();
         quantize_row_q8_k(norm.data(), H, d8.data(), q8.data(), bs.data());   // once for q, k, v (:14206)
         if (mvp(L.tq, L.q, mat_bytes(L.tq, q_dim, H), q_dim, H, d8.data(), q8.data(), bs.data(), q.data())) return -2;
         if (mvp(L.tk, L.k, mat_bytes(L.tk, kv_dim, H), kv_dim, H, d8.data(), q8.data(), bs.data(), k.data())) return -2;

@@ -8,6 +8,7 @@ its header states.
 from __future__ import annotations
 
 import ctypes as C
+import hashlib
 import os
 import subprocess
 
@@ -30,14 +31,35 @@ def _stale(lib, src):
     return not os.path.exists(lib) or (os.path.exists(src) and os.path.getmtime(src) > os.path.getmtime(lib))
 
 
+def _cpu_tag() -> str:
+    """Identifies the instruction set of this host: the baseline is built with -march=native, so a
+    library built on another machine must not be reused."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return hashlib.sha1(line.encode()).hexdigest()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def build(force: bool = False) -> None:
     """Compile the oracle (and the threaded CPU baseline when its source is present)."""
     if force or _stale(_LIB, _SRC):
         subprocess.check_call(["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-fno-fast-math",
                                "-fPIC", "-shared", "-o", _LIB, _SRC])
-    if os.path.exists(_BASE_SRC) and (force or _stale(_BASE_LIB, _BASE_SRC)):
+    tag_file = _BASE_LIB + ".host"
+    try:
+        with open(tag_file) as f:
+            same_host = f.read().strip() == _cpu_tag()
+    except OSError:
+        same_host = False
+    if os.path.exists(_BASE_SRC) and (force or not same_host or _stale(_BASE_LIB, _BASE_SRC) or _stale(_BASE_LIB, _SRC)):   # it includes _SRC
         subprocess.check_call(["g++", "-O3", "-std=c++17", "-march=native", "-ffp-contract=off",
                                "-fno-fast-math", "-fPIC", "-shared", "-pthread", "-o", _BASE_LIB, _BASE_SRC])
+        with open(tag_file, "w") as f:
+            f.write(_cpu_tag())
 
 
 _lib = None
@@ -274,6 +296,9 @@ class _OrcModel(C.Structure):
                 ("kcache", C.c_void_p), ("vcache", C.c_void_p)]
 
 
+TERNARY = 1000   # model-tensor type id of the in-memory ternary bit planes (not a GGML id)
+
+
 class LlamaOracle:
     """CPU forward of a synthetic model dict (alice_llm_b200.synth.make_llama): Llama branch of
     Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613)."""
@@ -289,7 +314,7 @@ class LlamaOracle:
         self._keep = []
         for i, L in enumerate(model["layers"]):
             for n in ("q", "k", "v", "o", "gate", "up", "down"):
-                t, data = L[n]
+                t, data = self._blob(L[n])
                 setattr(self._layers[i], n, data.ctypes.data)
                 setattr(self._layers[i], "t" + n, t)
             self._layers[i].attn_norm = L["attn_norm"].ctypes.data
@@ -302,10 +327,20 @@ class LlamaOracle:
         m.layers = C.addressof(self._layers)
         m.emb_q8_0 = model["embedding"][1].ctypes.data
         m.out_norm = model["output_norm"].ctypes.data
-        m.tout, out = model["output"]
+        m.tout, out = self._blob(model["output"])
         m.out = out.ctypes.data
         m.kcache, m.vcache = self.kcache.ctypes.data, self.vcache.ctypes.data
         self._m = m
+
+    def _blob(self, entry):
+        """(type, data) as the C side wants it; ternary (pos, neg, scales) -> one pos | neg | scales blob."""
+        t, data = entry
+        if t == TERNARY:
+            pos, neg, scales = data
+            data = np.concatenate([_u8(pos).reshape(-1), _u8(neg).reshape(-1),
+                                   np.ascontiguousarray(scales, np.float32).view(np.uint8).reshape(-1)])
+        self._keep.append(data)
+        return t, data
 
     def forward(self, token: int) -> np.ndarray:
         logits = np.empty(self.cfg["vocab_size"], np.float32)

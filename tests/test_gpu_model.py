@@ -43,6 +43,7 @@ Q1_MIX["output"] = synth.Q8_0   # the 27B binary-weight configuration: Q1_0 proj
 
 
 @pytest.mark.parametrize("mix,heads", [(None, (4, 2)), ({"v": synth.Q6_K, "down": synth.Q4_K, "output": synth.Q8_0}, (8, 2)),
+                                       ({n: synth.TERNARY for n in ("q", "k", "v", "o", "gate", "up", "down", "output")}, (8, 2)),
                                        (Q1_MIX, (10, 2)), ({**Q1_MIX, "k": synth.Q2_0, "gate": synth.Q2_0, "up": synth.Q2_0}, (4, 4))])
 def test_forward_logits_match_oracle(eng, oracle, mix, heads):
     from alice_llm_b200.gpu import GpuModel

@@ -63,3 +63,44 @@ def test_forward_is_deterministic_and_threaded_equals_serial(oracle):
     assert np.array_equal(a.kcache, b.kcache) and a.pos == 3
     # the first layer's appended K row is the RoPE'd K projection of the normalised embedding
     assert a.kcache[0, :3].any() and not a.kcache[0, 3:].any()
+
+
+def test_ternary_forward_is_the_same_skeleton_with_f32_ternary_matvec(oracle):
+    """forward_ternary (src/llama3.rs:16960-17062): every projection and the head through ternary_matvec on f32
+    activations. A one-layer model is recomputed here from the oracle's own pinned pieces (ternary_matvec,
+    rms_norm, RoPE, attention) and must equal the fused forward bit for bit."""
+    cfg = dict(CFG, num_layers=1)
+    rng = np.random.default_rng(4)
+    roles = ("q", "k", "v", "o", "gate", "up", "down", "output")
+    model = synth.make_llama(rng, cfg, {n: synth.TERNARY for n in roles})
+    H, F, D = cfg["hidden_dim"], cfg["intermediate_dim"], cfg["head_dim"]
+    nh, nkv = cfg["num_heads"], cfg["num_kv_heads"]
+    o = oracle.LlamaOracle(model)
+    got = o.forward(7)
+    lib, fp = oracle.lib(), C.POINTER(C.c_float)
+    L = model["layers"][0]
+
+    def tmv(entry, rows, cols, x):
+        pos, neg, sc = entry[1]
+        return oracle.ternary_matvec(pos, neg, sc, rows, cols, x)
+
+    hidden = oracle.dequantize(synth.Q8_0, model["embedding"][1][7 * (H // 32) * 34:8 * (H // 32) * 34])
+    norm = oracle.rms_norm(hidden, L["attn_norm"], cfg["eps"])
+    q, k, v = tmv(L["q"], nh * D, H, norm), tmv(L["k"], nkv * D, H, norm), tmv(L["v"], nkv * D, H, norm)
+    for vec, n in ((q, nh), (k, nkv)):
+        for h in range(n):
+            head = np.ascontiguousarray(vec[h * D:(h + 1) * D])
+            lib.orc_apply_rope(head.ctypes.data_as(fp), C.c_size_t(0), C.c_size_t(D), C.c_float(cfg["rope_theta"]), 0)
+            vec[h * D:(h + 1) * D] = head
+    assert np.array_equal(o.kcache[0, 0], k) and np.array_equal(o.vcache[0, 0], v)
+    attn = np.empty(nh * D, np.float32)
+    kc, vc = np.ascontiguousarray(k[None, :]), np.ascontiguousarray(v[None, :])
+    lib.orc_gqa_attention(q.ctypes.data_as(fp), kc.ctypes.data_as(fp), vc.ctypes.data_as(fp), C.c_size_t(0), C.c_size_t(nh),
+                          C.c_size_t(nkv), C.c_size_t(D), attn.ctypes.data_as(fp))
+    hidden = hidden + tmv(L["o"], H, nh * D, attn)
+    norm = oracle.rms_norm(hidden, L["ffn_norm"], cfg["eps"])
+    g, u = tmv(L["gate"], F, H, norm), tmv(L["up"], F, H, norm)
+    act = np.array([lib.orc_silu(C.c_float(float(x))) for x in g], np.float32) * u
+    hidden = hidden + tmv(L["down"], H, F, act)
+    want = tmv(model["output"], cfg["vocab_size"], H, oracle.rms_norm(hidden, model["output_norm"], cfg["eps"]))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
