@@ -56,6 +56,7 @@ SIGNATURES = {
     "alice_model_forward": (C.c_int32, [_vp, C.c_uint32]),
     "alice_model_forward_read": (C.c_int32, [_vp, C.c_uint32, _vp]),
     "alice_model_decode_greedy": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp]),
+    "alice_ternary_from_device": (C.c_int32, [_vp, _vp, _vp, C.c_uint32, C.c_uint32, _pp]),
     "alice_tp_unique_id": (C.c_int32, [_vp, C.c_size_t]),
     "alice_engine_tp_init": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, C.c_size_t]),
     "alice_engine_tp_info": (C.c_int32, [_vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),

@@ -262,6 +262,22 @@ int32_t alice_upload_ternary(alice_engine* e, const uint8_t* pos, const uint8_t*
     return upload_rows_and_scales(e, host, scales, d, out);
 }
 
+int32_t alice_ternary_from_device(alice_engine* e, const void* rows_dptr, const float* scales_dptr, uint32_t rows,
+                                  uint32_t cols, alice_weights** out) {
+    if (!e || !rows_dptr || !scales_dptr || !out) return fail(ALICE_E_INVALID, "alice_ternary_from_device: null argument");
+    if (rows == 0 || cols == 0) return fail(ALICE_E_SHAPE, "alice_ternary_from_device: empty matrix");
+    if ((uintptr_t)rows_dptr & 15) return fail(ALICE_E_INVALID, "alice_ternary_from_device: pointer not 16-byte aligned");
+    const uint32_t pb = ((cols + 31) / 32) * 4;
+    if (((size_t)rows * 2 * pb) & 15)
+        return fail(ALICE_E_SHAPE, "alice_ternary_from_device: rows * row bytes (%zu) must be a multiple of 16", (size_t)rows * 2 * pb);
+    WeightDesc d = {};
+    d.fmt = WF_TERNARY; d.rows = rows; d.cols = cols; d.row_bytes = 2 * pb;
+    d.data = static_cast<const uint8_t*>(rows_dptr);
+    d.scales = scales_dptr;
+    *out = new alice_weights{e, d, nullptr, nullptr};
+    return ALICE_OK;
+}
+
 int32_t alice_upload_sparse_ternary(alice_engine* e, const uint8_t* packed, const float* scales, uint32_t rows,
                                     uint32_t cols, alice_weights** out) {
     if (!e || !packed || !scales || !out) return fail(ALICE_E_INVALID, "alice_upload_sparse_ternary: null argument");

@@ -275,16 +275,23 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* sme
         int8_t* qs_s = reinterpret_cast<int8_t*>(area);
         int16_t* bs_s = reinterpret_cast<int16_t*>(area + (size_t)nb * 256);  // 8-byte aligned for any nb
         float* d_s = reinterpret_cast<float*>(area + (size_t)nb * 288);
-        // two blocks per warp per round: their loads travel together and their reduction chains interleave
+        // QB blocks per warp per round: their loads travel together (one memory round trip per round when
+        // the source is global memory) and their reduction chains interleave
+        constexpr int QB = 4;
         const bool lcg = src_global && cg;
 #pragma unroll 1
-        for (uint32_t b0 = warp; b0 < nb; b0 += 2 * NCW) {
-            const uint32_t b1 = b0 + NCW;
-            const Q8KLaneInput in0 = q8k_load_lane(src + (size_t)b0 * QK_K, lane, lcg);
-            Q8KLaneInput in1 = in0;
-            if (b1 < nb) in1 = q8k_load_lane(src + (size_t)b1 * QK_K, lane, lcg);
-            q8k_quantize_block_warp(in0, lane, qs_s + (size_t)b0 * QK_K, d_s + b0, bs_s + (size_t)b0 * 16);
-            if (b1 < nb) q8k_quantize_block_warp(in1, lane, qs_s + (size_t)b1 * QK_K, d_s + b1, bs_s + (size_t)b1 * 16);
+        for (uint32_t b0 = warp; b0 < nb; b0 += QB * NCW) {
+            Q8KLaneInput in[QB];
+#pragma unroll
+            for (int i = 0; i < QB; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) in[i] = q8k_load_lane(src + (size_t)blk * QK_K, lane, lcg);
+            }
+#pragma unroll
+            for (int i = 0; i < QB; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) q8k_quantize_block_warp(in[i], lane, qs_s + (size_t)blk * QK_K, d_s + blk, bs_s + (size_t)blk * 16);
+            }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
     }

@@ -198,6 +198,13 @@ class GpuEngine:
         check(self._lib.alice_upload_ternary(self._h, _ptr(p), _ptr(n), _ptr(s), rows, cols, C.byref(h)))
         return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.Ternary)
 
+    def ternary_from_device(self, rows_ptr: int, scales_ptr: int, rows, cols) -> GpuWeightBuffer:
+        """Borrowed device-resident ternary matrix: row = [pos plane | neg plane], planes of ceil(cols/32)*4 bytes."""
+        h = C.c_void_p()
+        check(self._lib.alice_ternary_from_device(self._h, C.c_void_p(rows_ptr), C.c_void_p(scales_ptr), rows, cols,
+                                                  C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.Ternary)
+
     def upload_sparse_ternary(self, packed_2bit, scales, rows, cols) -> GpuWeightBuffer:
         """SparseTernaryMatrix.packed_2bit (src/gguf.rs:5432) + per-row scale."""
         p, s = _np(packed_2bit, np.uint8), _np(scales, np.float32)

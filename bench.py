@@ -16,6 +16,12 @@ cycled so every step streams its weights from HBM.
   cpu_baseline  the C++ restatement of the reference CPU path on the host cores (the reference
           itself is Rust and cannot be built here)
 
+  decode  greedy decode of the synthetic whole-model configurations (128 tokens after a prefilled context):
+          the 8B Q4_K_M mix, the 27B Q1_0 model and the 70B ternary model on one GPU; with --gpus N > 1 the
+          27B and 70B models row-sharded over the N GPUs (one process per GPU, NCCL all-gather of every
+          projection output inside the library). tok/s, ms/token and the ratio to the pure weight-streaming
+          time at the measured HBM bandwidth. `--decode none` skips it.
+
 `--impl reference` times that CPU path alone, with all host threads, on the same block.
 """
 from __future__ import annotations
@@ -146,6 +152,39 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(eng, name, tokens, stream, world, dist, dev, peak):
+    """Greedy decode of one whole-model configuration; returns its report entry (device-timed, max over ranks)."""
+    import torch
+    from alice_llm_b200.synth_device import build_model
+    gm, info = build_model(eng, name)
+    ctx = info["context"]
+    gm.decode_greedy(1, 8)          # warm-up; also captures the step graph
+    gm.set_position(ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    toks = gm.decode_greedy(1, tokens)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    gm.free()
+    del gm
+    torch.cuda.empty_cache()
+    wb = info["weight_bytes_per_token"]
+    bound_ms = wb / world / (peak * 1e9) * 1e3
+    return {"config": name, "tokens": tokens, "context": ctx, "tok_s": tokens / (ms * 1e-3), "ms_per_token": ms / tokens,
+            "weight_bytes_per_token": wb, "kv_bytes_per_token_at_context": info["kv_bytes_per_token"],
+            "weight_gbs": wb * tokens / (ms * 1e-3) / 1e9, "stream_bound_ms_per_token": bound_ms,
+            "x_of_stream_bound": (ms / tokens) / bound_ms, "first_tokens": [int(t) for t in toks[:4]],
+            "parallelism": "single GPU" if world == 1 else f"tp{world}: rows of every projection sharded, NCCL all-gather"}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -232,11 +271,26 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop() if rank == 0 else None
     eng.sync()
 
+    peak, peak_src = measured_peak()
+    decode = []
+    if args.decode != "none":
+        names = (["c3_8b_q4km", "c4_27b_q1_0", "c5_70b_ternary"] if world == 1 else ["c4_27b_q1_0", "c5_70b_ternary"]) \
+            if args.decode == "auto" else args.decode.split(",")
+        for t in keep:      # the FFN weight copies are no longer needed
+            t.clear()
+        del copies, base
+        torch.cuda.empty_cache()
+        if world > 1:
+            ids = [eng.tp_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            eng.tp_init(rank, world, ids[0])
+        for name in names:
+            decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak))
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    peak, peak_src = measured_peak()
     value = STEP_BYTES * world * args.steps / (ms * 1e-3) / 1e9
     e2e = STEP_BYTES * world * args.steps / (ms_e2e * 1e-3) / 1e9
     k_gbs = 2 * GU_BYTES / (ms_k / args.steps * 1e-3) / 1e9
@@ -264,6 +318,7 @@ def run_ours(args, rank, world, local_rank):
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": KERNELS_PER_STEP * args.steps,
         "clocks": clocks,
+        "decode": decode,
     }
     if world == 1 and not args.no_cpu:
         from oracle import oracle as orc
@@ -286,6 +341,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--decode", default="auto", help="auto | none | comma list of c3_8b_q4km,c4_27b_q1_0,c5_70b_ternary")
+    ap.add_argument("--decode-tokens", type=int, default=128)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -84,6 +84,12 @@ int32_t alice_weights_from_device(alice_engine* e, const void* device_ptr, size_
  * (bit i%8 of byte i/8), one f32 scale per row. */
 int32_t alice_upload_ternary(alice_engine* e, const uint8_t* pos, const uint8_t* neg, const float* scales,
                              uint32_t rows, uint32_t cols, alice_weights** out);
+/* Borrowed device-resident ternary matrix in the layout alice_upload_ternary builds on the device: row r =
+ * [pos plane | neg plane], each plane ceil(cols/32)*4 bytes (bit c%8 of byte c/8, zero bits past cols), plus
+ * one f32 scale per row. No reference counterpart (the reference uploads from host memory only); it lets a
+ * host that already holds the planes on the device (or generates them there) skip the round trip. */
+int32_t alice_ternary_from_device(alice_engine* e, const void* rows_dptr, const float* scales_dptr, uint32_t rows,
+                                  uint32_t cols, alice_weights** out);
 /* SparseTernaryMatrix (src/gguf.rs:5425-5445): packed_2bit rows, 4 bytes per 16 columns
  * (00 = 0, 01 = +1, 11 = -1), [rows][ceil(cols/16)*4] bytes, one f32 scale per row. */
 int32_t alice_upload_sparse_ternary(alice_engine* e, const uint8_t* packed_2bit, const float* scales,
