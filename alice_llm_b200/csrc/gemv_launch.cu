@@ -5,6 +5,7 @@
 
 #include "../../include/alice_cuda.h"
 #include "formats.cuh"
+#include "gemv_mma.cuh"
 #include "gemv_launch.cuh"
 #include "gemv_plan.cuh"
 
@@ -88,6 +89,97 @@ int launch_fmt(const StreamArgs& a, uint32_t kl, bool sw, uint32_t grid, size_t 
     return launch_one<F, 4, false>(a, grid, smem, cfg);
 }
 
+// ALICE_NO_MMA=1 keeps the 1- and 2-bit formats on the per-lane kernels (A/B timing, debugging).
+bool mma_disabled() {
+    static const bool off = [] { const char* v = getenv("ALICE_NO_MMA"); return v && *v && *v != '0'; }();
+    return off;
+}
+
+// Geometry of the bit-plane tensor-core kernel: 16-row tiles, `slots` tiles per stage, the P = NCW / slots
+// warps of a tile split the row's 16-byte groups. Shared memory: header | ring | normalised input (optional) |
+// activation digit table (512 B per 128 columns) | per-block sums. Two CTAs per SM when that fits.
+constexpr uint32_t MMA_BUDGET_2 = 112 * 1024, MMA_BUDGET_1 = 225 * 1024;
+int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t total_rows, StreamPlan& pl) {
+    const WeightDesc& w0 = *op.w[0];
+    const bool sw = op.up != nullptr;
+    const uint32_t nmat = sw ? 2 : 1;
+    const uint32_t ngroups = (w0.cols + 127) / 128;
+    const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
+    const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
+    for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
+        const uint32_t budget = per_sm == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1;
+        if (HDR_BYTES + table_bytes + xn_bytes >= budget) continue;
+        const uint32_t avail = budget - HDR_BYTES - table_bytes - xn_bytes;
+        const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
+        uint32_t best = 0;
+        for (uint32_t slots = NCW; slots >= 1; slots /= 2) {
+            const uint32_t cap = (slots * 16 * a.row_bytes + 48 + 127) & ~127u;
+            if ((uint64_t)cap * nmat * 2 > avail) continue;
+            if (best == 0) best = slots;                       // largest that fits
+            uint32_t groups = 0;
+            for (uint32_t i = 0; i < op.nw; i++) groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
+            if (groups >= 2 * ctas) { best = slots; break; }   // largest that still gives every CTA two stages
+            best = slots;                                      // else keep shrinking: more, smaller stages
+        }
+        if (best == 0) continue;
+        const uint32_t slots = best;
+        a.slots = slots; a.P = NCW / slots; a.rps = 16;
+        a.cap = (slots * 16 * a.row_bytes + 48 + 127) & ~127u;
+        const uint32_t stage = a.cap * nmat;
+        // as deep a ring as fits: the bytes in flight per SM have to cover memory latency at full bandwidth
+        const uint32_t nst = std::min<uint32_t>(MAX_STAGES, avail / stage);
+        a.nstages = nst;
+        a.nseg = op.nw;
+        a.groups = 0;
+        for (uint32_t i = 0; i < op.nw; i++) {
+            a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i];
+            a.seg_g0[i] = a.groups;
+            a.groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
+        }
+        a.seg_g0[op.nw] = a.groups;
+        a.q8_off = HDR_BYTES + nst * stage;
+        a.xn_off = a.q8_off + table_bytes;
+        pl.grid = std::min(ctas, a.groups);
+        pl.smem = HDR_BYTES + nst * (size_t)stage + table_bytes + xn_bytes;
+        pl.kl = 1; pl.swiglu = sw; pl.stage = stage; pl.q8_bytes = table_bytes; pl.xn_bytes = xn_bytes;
+        pl.mma = true; pl.ctas_per_sm = per_sm;
+        pl.args = a;
+        (void)total_rows;
+        return ALICE_OK;
+    }
+    return ALICE_E_SHAPE;
+}
+
+template <class M, bool SW, int CTAS>
+int launch_mma_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+    static bool attr_set = false;  // per template instance
+    auto kern = stream_gemv_mma_kernel<M, SW, CTAS>;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CTAS == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1)) != cudaSuccess)
+            return ALICE_E_CUDA;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(STREAM_THREADS);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = cfg.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = cfg.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
+}
+
+template <class M>
+int launch_mma(const StreamPlan& pl, const LaunchCfg& cfg) {
+    if (pl.swiglu) return pl.ctas_per_sm == 2 ? launch_mma_one<M, true, 2>(pl.args, pl.grid, pl.smem, cfg)
+                                              : launch_mma_one<M, true, 1>(pl.args, pl.grid, pl.smem, cfg);
+    return pl.ctas_per_sm == 2 ? launch_mma_one<M, false, 2>(pl.args, pl.grid, pl.smem, cfg)
+                               : launch_mma_one<M, false, 1>(pl.args, pl.grid, pl.smem, cfg);
+}
+
 }  // namespace
 
 int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
@@ -135,6 +227,8 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
     a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
+    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma(op, cfg, a, total_rows, pl) == ALICE_OK)
+        return ALICE_OK;
 
     // warps per row: just enough lanes for one unit each, at most all eight
     uint32_t P = 1;
@@ -195,6 +289,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     if (prc) return prc;
     const StreamArgs& a = pl.args;
     const WeightDesc& w0 = *op.w[0];
+    if (pl.mma) return w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pl, cfg) : launch_mma<MmaTernary>(pl, cfg);
     const uint32_t kl = pl.kl, grid = pl.grid;
     const bool sw = pl.swiglu;
     const size_t smem = pl.smem;

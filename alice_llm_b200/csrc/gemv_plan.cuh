@@ -20,6 +20,8 @@ struct StreamPlan {
     size_t smem;        // dynamic shared memory for a stand-alone launch
     uint32_t stage;     // bytes one stage really uses
     uint32_t q8_bytes, xn_bytes;
+    bool mma = false;         // bit-plane tensor-core kernel (csrc/gemv_mma.cuh) instead of the per-lane one
+    uint32_t ctas_per_sm = 2; // resident CTAs per SM the launch was planned for (mma kernels)
 };
 
 // lim == nullptr: plan a stand-alone launch (ring sized from the CTA's own budget).
