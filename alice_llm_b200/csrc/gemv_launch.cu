@@ -98,12 +98,35 @@ bool mma_disabled() {
 // Geometry of the bit-plane tensor-core kernel: 16-row tiles, `slots` tiles per stage, the P = NCW / slots
 // warps of a tile split the row's 16-byte groups. Shared memory: header | ring | normalised input (optional) |
 // activation digit table (512 B per 128 columns) | per-block sums. Two CTAs per SM when that fits.
+// [col_lo, col_lo + col_n) selects a column sub-range of the matrix (the whole row when col_n == cols): a
+// matrix whose rows are too wide for shared memory runs as several such launches that accumulate into y.
 constexpr uint32_t MMA_BUDGET_2 = 112 * 1024, MMA_BUDGET_1 = 225 * 1024;
-int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t total_rows, StreamPlan& pl) {
+int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_lo, uint32_t col_n, StreamPlan& pl) {
     const WeightDesc& w0 = *op.w[0];
     const bool sw = op.up != nullptr;
     const uint32_t nmat = sw ? 2 : 1;
-    const uint32_t ngroups = (w0.cols + 127) / 128;
+    const bool whole = col_lo == 0 && col_n == w0.cols;
+    if (!whole && (op.norm_w || sw || col_lo % 128 || col_n % 128)) return ALICE_E_SHAPE;
+    // the sub-row as the consumer sees it, and where its pieces sit inside the global row
+    uint32_t sub_row, npieces, piece_len, piece_off[2] = {0, 0};
+    if (w0.fmt == WF_Q1_0) {
+        npieces = 1; piece_len = col_n / 128 * 18; piece_off[0] = col_lo / 128 * 18; sub_row = piece_len;
+    } else {
+        const uint32_t plane_full = w0.row_bytes / 2;
+        npieces = 2; piece_len = (col_n + 31) / 32 * 4; piece_off[0] = col_lo / 8; piece_off[1] = plane_full + col_lo / 8;
+        sub_row = 2 * piece_len;
+    }
+    const bool row_ok = piece_len % 16 == 0 && w0.row_bytes % 16 == 0 && piece_off[0] % 16 == 0 && piece_off[1] % 16 == 0;
+    if (!row_ok && !whole) return ALICE_E_SHAPE;
+    // shared-memory row stride: an odd number of 16-byte units, so the 8 rows x 4 words one A-fragment load
+    // touches fall into 32 different banks
+    uint32_t row_stride = sub_row;
+    if (row_ok) { row_stride = (sub_row + 15) & ~15u; if ((row_stride / 16) % 2 == 0) row_stride += 16; }
+    a.cols = col_n; a.row_bytes = sub_row; a.row_stride = row_stride; a.row_mode = row_ok ? 1u : 0u;
+    a.src_row_bytes = w0.row_bytes; a.npieces = npieces; a.piece_len = piece_len;
+    a.piece_off[0] = piece_off[0]; a.piece_off[1] = piece_off[1];
+    if (a.x) a.x += col_lo;
+    const uint32_t ngroups = (col_n + 127) / 128;
     const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
     const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
     for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
@@ -113,18 +136,17 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t tota
         const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
         uint32_t best = 0;
         for (uint32_t slots = NCW; slots >= 1; slots /= 2) {
-            const uint32_t cap = (slots * 16 * a.row_bytes + 48 + 127) & ~127u;
+            const uint32_t cap = (slots * 16 * row_stride + 48 + 127) & ~127u;
             if ((uint64_t)cap * nmat * 2 > avail) continue;
-            if (best == 0) best = slots;                       // largest that fits
+            best = slots;                                      // fits; keep shrinking while the CTAs are short of stages
             uint32_t groups = 0;
             for (uint32_t i = 0; i < op.nw; i++) groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
-            if (groups >= 2 * ctas) { best = slots; break; }   // largest that still gives every CTA two stages
-            best = slots;                                      // else keep shrinking: more, smaller stages
+            if (groups >= 2 * ctas) break;
         }
         if (best == 0) continue;
         const uint32_t slots = best;
         a.slots = slots; a.P = NCW / slots; a.rps = 16;
-        a.cap = (slots * 16 * a.row_bytes + 48 + 127) & ~127u;
+        a.cap = (slots * 16 * row_stride + 48 + 127) & ~127u;
         const uint32_t stage = a.cap * nmat;
         // as deep a ring as fits: the bytes in flight per SM have to cover memory latency at full bandwidth
         const uint32_t nst = std::min<uint32_t>(MAX_STAGES, avail / stage);
@@ -144,8 +166,35 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t tota
         pl.kl = 1; pl.swiglu = sw; pl.stage = stage; pl.q8_bytes = table_bytes; pl.xn_bytes = xn_bytes;
         pl.mma = true; pl.ctas_per_sm = per_sm;
         pl.args = a;
-        (void)total_rows;
         return ALICE_OK;
+    }
+    return ALICE_E_SHAPE;
+}
+
+// Column chunk c of ksplit: whole multiples of `unit` columns (Q1_0: 1024, so that a chunk of a row is a multiple
+// of 16 bytes; ternary planes: 128).
+void mma_chunk(const WeightDesc& w, uint32_t ksplit, uint32_t c, uint32_t& lo, uint32_t& n) {
+    const uint32_t unit = w.fmt == WF_Q1_0 ? 1024u : 128u, units = w.cols / unit;
+    lo = units * c / ksplit * unit;
+    n = units * (c + 1) / ksplit * unit - lo;
+}
+
+// Whole row if it fits, else the smallest number of column chunks that does (plain matvec only).
+int plan_mma_split(const GemvOp& op, const LaunchCfg& cfg, const StreamArgs& a, StreamPlan& pl) {
+    const WeightDesc& w0 = *op.w[0];
+    if (plan_mma(op, cfg, a, 0, w0.cols, pl) == ALICE_OK) { pl.ksplit = 1; return ALICE_OK; }
+    const uint32_t unit = w0.fmt == WF_Q1_0 ? 1024u : 128u;
+    if (w0.cols % unit || op.norm_w || op.up) return ALICE_E_SHAPE;
+    for (uint32_t ks = 2; ks <= 4; ks++) {
+        bool ok = true;
+        for (uint32_t c = 0; c < ks && ok; c++) {
+            uint32_t lo, n;
+            mma_chunk(w0, ks, c, lo, n);
+            StreamPlan tmp;
+            ok = n > 0 && plan_mma(op, cfg, a, lo, n, tmp) == ALICE_OK;
+            if (ok && c == 0) pl = tmp;
+        }
+        if (ok) { pl.ksplit = ks; return ALICE_OK; }
     }
     return ALICE_E_SHAPE;
 }
@@ -227,7 +276,8 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
     a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
-    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma(op, cfg, a, total_rows, pl) == ALICE_OK)
+    a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
+    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
         return ALICE_OK;
 
     // warps per row: just enough lanes for one unit each, at most all eight
@@ -289,7 +339,26 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     if (prc) return prc;
     const StreamArgs& a = pl.args;
     const WeightDesc& w0 = *op.w[0];
-    if (pl.mma) return w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pl, cfg) : launch_mma<MmaTernary>(pl, cfg);
+    if (pl.mma) {
+        // one launch per column chunk; a later chunk adds to what the earlier ones left in y, and only the last one
+        // sees the final values (greedy-argmax epilogue)
+        for (uint32_t c = 0; c < pl.ksplit; c++) {
+            StreamPlan pc = pl;
+            if (pl.ksplit > 1) {
+                uint32_t lo, n;
+                mma_chunk(w0, pl.ksplit, c, lo, n);
+                StreamArgs base = pl.args;
+                base.x = op.x; base.cols = w0.cols; base.row_bytes = w0.row_bytes;
+                const int rc = plan_mma(op, cfg, base, lo, n, pc);
+                if (rc) return rc;
+                if (c > 0) pc.args.resid = op.y;
+                if (c + 1 < pl.ksplit) pc.args.argmax_key = nullptr;
+            }
+            const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : launch_mma<MmaTernary>(pc, cfg);
+            if (rc) return rc;
+        }
+        return ALICE_OK;
+    }
     const uint32_t kl = pl.kl, grid = pl.grid;
     const bool sw = pl.swiglu;
     const size_t smem = pl.smem;

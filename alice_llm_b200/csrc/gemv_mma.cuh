@@ -305,17 +305,17 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t seg_rows = a.seg_rows[sg];
         const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
-        const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
+        const uint32_t pad = a.row_mode ? 0u : (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
         const uint32_t set0 = slot * rps;
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         float res = 0.0f;
         if (a.resid != nullptr && part == 0 && lane < nrow) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
-        const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_bytes;
+        const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_stride;
         if (nrow > 0) {
             // rows past nrow of a short last tile read whatever the stage holds; their results are never used
-            const uint32_t rowA = sb + rowsel_a * a.row_bytes, rowB = sb + rowsel_b * a.row_bytes;
+            const uint32_t rowA = sb + rowsel_a * a.row_stride, rowB = sb + rowsel_b * a.row_stride;
             float y0, y1, u0 = 0.0f, u1 = 0.0f;
             M::tile(rowA, rowB, g_lo, g_hi, tb, lane, a, y0, y1);
             if (SWIGLU) M::tile(rowA + a.cap, rowB + a.cap, g_lo, g_hi, tb, lane, a, u0, u1);
@@ -395,7 +395,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
     __syncthreads();
     pdl_launch_dependents();
     if ((threadIdx.x >> 5) == NCW) {
-        if ((threadIdx.x & 31) == 0) {
+        if (a.row_mode) {
+            stream_produce_rows(a, cx);
+            if ((threadIdx.x & 31) == 0 && sm->abort_flag) stream_drain(cx);
+        } else if ((threadIdx.x & 31) == 0) {
             stream_produce(a, cx);
             if (sm->abort_flag) stream_drain(cx);
         }

@@ -22,6 +22,7 @@ struct StreamPlan {
     uint32_t q8_bytes, xn_bytes;
     bool mma = false;         // bit-plane tensor-core kernel (csrc/gemv_mma.cuh) instead of the per-lane one
     uint32_t ctas_per_sm = 2; // resident CTAs per SM the launch was planned for (mma kernels)
+    uint32_t ksplit = 1;      // column chunks, one launch each, accumulating into y (mma kernels with rows too wide for shared memory)
 };
 
 // lim == nullptr: plan a stand-alone launch (ring sized from the CTA's own budget).

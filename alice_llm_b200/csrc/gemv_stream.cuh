@@ -61,6 +61,17 @@ struct StreamArgs {
     uint32_t seg_rows[3];
     uint32_t seg_g0[4];
     uint32_t seg_y[3];
+    // Row-wise staging (bit-plane tensor-core kernels): instead of one contiguous copy per stage every row is
+    // copied on its own, as npieces pieces of piece_len bytes taken at piece_off[p] inside the global row of
+    // src_row_bytes bytes, to shared memory rows row_stride bytes apart. That allows a padded (bank-conflict
+    // free) row stride and a matvec over a column sub-range of the matrix (row_bytes = npieces * piece_len
+    // then describes the sub-row). row_mode == 0: rows are row_bytes apart in both memories (contiguous copy).
+    uint32_t row_mode;
+    uint32_t row_stride;
+    uint32_t src_row_bytes;
+    uint32_t npieces;
+    uint32_t piece_off[2];
+    uint32_t piece_len;
 };
 
 // Shared-memory header in front of the ring.
@@ -179,6 +190,42 @@ __device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& c
         mbar_arrive_expect_tx(fb, two ? 2 * cb : cb);
         bulk_g2s(cx.ring + s * cx.stage_stride, a.seg_w[sg] + a0, cb, fb);
         if (two) bulk_g2s(cx.ring + s * cx.stage_stride + a.cap, a.w1 + a0, cb, fb);
+        cx.cc++;
+    }
+}
+
+// Producer side in row mode: the whole producer warp takes part, lane l copies rows l, l + 32, ... of the stage.
+__device__ __forceinline__ void stream_produce_rows(const StreamArgs& a, StreamCtx& cx) {
+    StreamSmem* sm = cx.sm;
+    volatile int* abort_flag = &sm->abort_flag;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rows_per_group = a.slots * a.rps;
+    const bool two = a.w1 != nullptr;
+    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
+    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
+    for (uint32_t g = g0; g < g1; g++) {
+        const uint32_t s = cx.cc % cx.nstages, use = cx.cc / cx.nstages;
+        int ok = 1;
+        if (lane == 0 && use > 0)
+            ok = wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status, KERR_WAIT_EMPTY + (cx.op << 8), 2 * WAIT_CYCLE_LIMIT) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;
+        uint32_t sg = 0;
+        while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+        const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
+        const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
+        const uint32_t fb = smem_u32(&sm->full[s]);
+        if (lane == 0) mbar_arrive_expect_tx(fb, nrow * a.npieces * a.piece_len * (two ? 2u : 1u));
+        __syncwarp();   // the byte count is posted before any copy can complete
+        const uint32_t stage = cx.ring + s * cx.stage_stride;
+        for (uint32_t r = lane; r < nrow; r += 32) {
+            const uint64_t src = (uint64_t)(r0 + r) * a.src_row_bytes;
+            const uint32_t dst = stage + r * a.row_stride;
+            for (uint32_t p = 0; p < a.npieces; p++) {
+                bulk_g2s(dst + p * a.piece_len, a.seg_w[sg] + src + a.piece_off[p], a.piece_len, fb);
+                if (two) bulk_g2s(dst + a.cap + p * a.piece_len, a.w1 + src + a.piece_off[p], a.piece_len, fb);
+            }
+        }
         cx.cc++;
     }
 }

@@ -46,7 +46,8 @@ SHAPES = {
     Q5_K: [(1, 256), (5, 768), (70, 4096), (16, 14336)],
     Q6_K: [(1, 256), (3, 512), (7, 768), (70, 4096), (40, 14336)],
     Q8_0: [(2, 32), (3, 96), (70, 4096), (50, 5120), (9, 14336)],
-    Q1_0: [(4, 256), (3, 128), (70, 5120), (20, 25600)],
+    # (1000, 5120): many 16-row tiles and stages per CTA; (40, 61440): rows too wide for shared memory, run as column chunks
+    Q1_0: [(4, 256), (3, 128), (70, 5120), (20, 25600), (1000, 5120), (40, 61440)],
     Q2_0: [(4, 256), (70, 5120), (10, 16384)],
 }
 
@@ -161,7 +162,7 @@ def test_batched_matvec_matches_oracle(eng, oracle, qtype, batch):
         assert_close(got[k], oracle.matvec(qtype, x[k * cols:(k + 1) * cols], data, rows, cols), f"batch {k}")
 
 
-@pytest.mark.parametrize("rows,cols", [(5, 128), (3, 100), (70, 8192), (12, 28672), (9, 1000)])
+@pytest.mark.parametrize("rows,cols", [(5, 128), (3, 100), (70, 8192), (12, 28672), (9, 1000), (600, 8192), (33, 14336 + 128)])
 def test_ternary_matvec_matches_oracle(eng, oracle, rows, cols):
     rng = np.random.default_rng(600 + cols)
     pos, neg, sc = synth.make_ternary(rng, rows, cols)
