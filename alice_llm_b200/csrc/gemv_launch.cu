@@ -54,10 +54,10 @@ uint32_t units_per_row(WeightFormat f, uint32_t cols) {
     }
 }
 
-template <class F, int KL, bool SW>
-int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+template <class F, int KL, bool SW, bool PLAIN>
+int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     static bool attr_set = false;  // per template instance
-    auto kern = stream_gemv_kernel<F, KL, SW>;
+    auto kern = stream_gemv_kernel<F, KL, SW, PLAIN>;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
@@ -75,6 +75,13 @@ int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg&
     lc.attrs = at;
     lc.numAttrs = cfg.pdl ? 1 : 0;
     return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
+}
+
+// The lean instance when the matvec uses none of the fused extras.
+template <class F, int KL, bool SW>
+int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1;
+    return plain ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
 }
 
 template <class F>

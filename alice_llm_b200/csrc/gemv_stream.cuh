@@ -169,6 +169,8 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
 __device__ __forceinline__ float ld_act(const float* p, bool cg) { return cg ? __ldcg(p) : *p; }
 
 // Producer side of one matvec: streams this CTA's row groups of `a` through the ring. One thread.
+// PLAIN: the matvec is known to be a single matrix (no q/k/v segments).
+template <bool PLAIN = false>
 __device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
     volatile int* abort_flag = &sm->abort_flag;
@@ -180,7 +182,7 @@ __device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& c
         const uint32_t s = cx.cc % cx.nstages, use = cx.cc / cx.nstages;
         if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status, KERR_WAIT_EMPTY + (cx.op << 8), 2 * WAIT_CYCLE_LIMIT)) return;
         uint32_t sg = 0;
-        while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+        if (!PLAIN) while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
         const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
         const uint64_t off = (uint64_t)r0 * a.row_bytes;
@@ -245,7 +247,7 @@ __device__ __forceinline__ void stream_drain(StreamCtx& cx) {
 //                   per 256-element block, exactly the stand-alone quantizer;
 //   roundtrip:      (with norm_w) the normalised vector is replaced by d * q of its Q8_K quantization.
 // cg: read x with ld.global.cg (other SMs rewrote it inside this kernel).
-static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
+static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
                                                     float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
                                                     bool quant, bool roundtrip, bool cg) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -344,9 +346,19 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* sme
     }
 }
 
+// The same as one shared out-of-line copy: for kernels that run many matvecs (every format instance calls it, and
+// a copy that stays warm in the instruction cache beats an inlined one that is cold every time).
+static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
+                                                    float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
+                                                    bool quant, bool roundtrip, bool cg) {
+    stream_prologue_body(sm, smem_raw, x, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip, cg);
+}
+
 // Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
 // Returns false after an abort.
-template <class F, int KL, bool SWIGLU>
+// PLAIN: the matvec is known to use none of the fused extras (RMSNorm prologue, residual / argmax epilogue,
+// q/k/v segments), so their code is compiled out - the stand-alone matvec entry points run this leaner instance.
+template <class F, int KL, bool SWIGLU, bool SHARED_PROLOGUE = false, bool PLAIN = false>
 __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
     uint8_t* smem_raw = cx.smem_raw;
@@ -359,11 +371,19 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
 
     // input prologue (shared by every format, one copy of the code per kernel): RMSNorm into shared
     // memory and / or Q8_K quantization into shared memory
-    const bool norm = a.norm_w != nullptr;
+    const bool norm = !PLAIN && a.norm_w != nullptr;
+    const float* const resid = PLAIN ? nullptr : a.resid;
+    unsigned long long* const argmax_key = PLAIN ? nullptr : a.argmax_key;
+    const uint32_t nseg = PLAIN ? 1u : a.nseg;
     const bool quant = F::USES_Q8K && a.q8.qs == nullptr;
-    if (norm || quant)
-        stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
-                        !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
+    if (norm || quant) {
+        if (SHARED_PROLOGUE)
+            stream_prologue(sm, smem_raw, a.x, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                            !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
+        else
+            stream_prologue_body(sm, smem_raw, a.x, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                                 !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
+    }
     const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
     const bool x_global = !norm;
     Q8KView q8 = a.q8;
@@ -396,7 +416,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         const uint32_t s = cx.cc % cx.nstages, ph = (cx.cc / cx.nstages) & 1;
         cx.cc++;
         uint32_t sg = 0;
-        while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
+        while (sg + 1 < nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t seg_rows = a.seg_rows[sg];
         const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
         const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
@@ -404,7 +424,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         // the residual this lane will add in the epilogue: requested now, needed after the rows are done
         float res = 0.0f;
-        if (a.resid != nullptr && part == 0 && lane < nrow) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        if (resid != nullptr && part == 0 && lane < nrow) res = ld_act(resid + a.seg_y[sg] + r0 + set0 + lane, cg);
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
         const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_bytes;
@@ -442,30 +462,38 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
             } else {
                 if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status, KERR_WAIT_PARTIALS + (cx.op << 8))) return false;
                 unsigned long long key = 0ull;
+                float v0 = 0.0f, v1 = 0.0f;
                 if (lane < nrow) {
-                    float v0 = 0.0f, v1 = 0.0f;
                     for (uint32_t p = 0; p < P; p++) {
                         v0 += sm->partial[s][warp + p][lane][0];
                         if (SWIGLU) v1 += sm->partial[s][warp + p][lane][1];
                     }
+                }
+                // everything this warp needed from the stage has been read: the producer may refill it while the
+                // epilogue runs
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
+                if (lane < nrow) {
                     const uint32_t row = r0 + set0 + lane;      // row inside its matrix
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr) r = __fadd_rn(res, r);
+                    if (resid != nullptr) r = __fadd_rn(res, r);
                     a.y[yi] = r;
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-                    if (r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
+                    if (argmax_key != nullptr && r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
                 }
-                if (a.argmax_key != nullptr) {
+                if (argmax_key != nullptr) {
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
                         const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
                         key = other > key ? other : key;
                     }
-                    if (lane == 0) atomicMax(a.argmax_key, key);
+                    if (lane == 0) atomicMax(argmax_key, key);
                 }
+                if (cx.prof && threadIdx.x == 0 && g - g0 < 8) cx.prof[8 + g - g0] = clock64();
+                continue;   // this warp has already released the stage
             }
         }
         __syncwarp();
@@ -477,7 +505,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
 }
 
 // One matvec per launch.
-template <class F, int KL, bool SWIGLU>
+template <class F, int KL, bool SWIGLU, bool PLAIN>
 __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
@@ -491,13 +519,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     if ((threadIdx.x >> 5) == NCW) {
         // producer: weights do not depend on the previous kernel, so copies start at once
         if ((threadIdx.x & 31) == 0) {
-            stream_produce(a, cx);
+            stream_produce<PLAIN>(a, cx);
             if (sm->abort_flag) stream_drain(cx);
         }
         return;
     }
     pdl_wait();  // activations come from the previous kernel
-    stream_consume<F, KL, SWIGLU>(a, cx);
+    stream_consume<F, KL, SWIGLU, false, PLAIN>(a, cx);
 }
 
 }  // namespace alice

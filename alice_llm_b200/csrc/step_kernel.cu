@@ -47,7 +47,7 @@ __device__ __forceinline__ bool grid_sync(unsigned int* counter, uint32_t& epoch
 // Each instance is a real function call, so its registers are allocated on their own instead of
 // the whole op interpreter paying for the widest one.
 template <class F, int KL, bool SW>
-__device__ __noinline__ bool consume_call(const StreamArgs& a, StreamCtx& cx) { return stream_consume<F, KL, SW>(a, cx); }
+__device__ __noinline__ bool consume_call(const StreamArgs& a, StreamCtx& cx) { return stream_consume<F, KL, SW, true>(a, cx); }
 
 __device__ __forceinline__ bool run_gemv(int variant, const StreamArgs& g, StreamCtx& cx) {
     switch (variant) {
