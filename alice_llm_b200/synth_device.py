@@ -1,6 +1,6 @@
 """Synthetic decode models generated directly in device memory (torch CUDA RNG), for timing runs.
 
-The numpy generators of ``synth.py`` feed the parity tests, where host copies are needed for the CPU oracle;
+The numpy generators of ``synth.py`` feed the parity tests, which need host copies of every tensor;
 a timing run of a 5-17 GB model only needs bytes of the right layout and value ranges on the device, so the
 tensors are drawn there and handed to the library as borrowed device pointers (no host round trip).
 Scale fields get the distributions of the benchmark configurations so activations stay finite.
