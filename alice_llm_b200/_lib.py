@@ -60,6 +60,8 @@ SIGNATURES = {
     "alice_tp_unique_id": (C.c_int32, [_vp, C.c_size_t]),
     "alice_engine_tp_init": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, C.c_size_t]),
     "alice_engine_tp_info": (C.c_int32, [_vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "alice_model_tp_export": (C.c_int32, [_vp, _vp, C.c_size_t]),
+    "alice_model_tp_connect": (C.c_int32, [_vp, _vp, C.c_size_t]),
     "alice_model_use_step_kernel": (C.c_int32, [_vp, C.c_int32]),
     "alice_model_read_logits": (C.c_int32, [_vp, _vp]),
     "alice_model_position": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),

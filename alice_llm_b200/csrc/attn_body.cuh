@@ -83,7 +83,8 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
                                                 float* __restrict__ vcache, uint32_t pos, AttnShape s,
                                                 const float* __restrict__ rope_tab, int neox, uint32_t nsplit, float* __restrict__ part,
                                                 unsigned int* __restrict__ tickets, float* __restrict__ attn_out,
-                                                uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh, long long* prof = nullptr) {
+                                                uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh, long long* prof = nullptr,
+                                                const AttnPeers* peers = nullptr) {
     constexpr int NW = 8;
     const uint32_t seq = pos + 1;
     const uint32_t per = (seq + nsplit - 1) / nsplit;
@@ -227,7 +228,15 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
             }
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-        reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+        const float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
+        reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = o;
+        if (peers)
+            for (uint32_t p = 0; p < peers->npeers; p++) reinterpret_cast<float4*>(peers->out[p] + (size_t)head * s.head_dim)[lane] = o;
+    }
+    if (peers && peers->npeers) {   // this KV head's output has been pushed: tell every peer
+        __threadfence_system();
+        attn_sync<CONSUMER_BAR>();
+        if (threadIdx.x < peers->npeers) red_release_sys_add_u32(peers->flag[threadIdx.x], 1u);
     }
 }
 

@@ -15,6 +15,7 @@ constexpr int KERR_WAIT_FULL = 2;      // consumer waiting for a weight stage to
 constexpr int KERR_WAIT_PARTIALS = 3;  // row finalizer waiting for the other warps' partial sums
 constexpr int KERR_WAIT_EMPTY = 4;     // producer waiting for a stage to be released
 constexpr int KERR_WAIT_GRID = 5;      // grid-wide barrier
+constexpr int KERR_WAIT_PEER = 6;      // rows another GPU pushes into this GPU's vector (tensor parallel)
 
 // A wait that has not been satisfied after this many SM clock cycles (about one second) gives
 // up, records KERR_WAIT_TIMEOUT and lets the CTA drain and return instead of spinning forever.
@@ -97,6 +98,29 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 // Programmatic dependent launch: wait for the producing grid / let the dependent grid start.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ── cross-GPU hand-over (tensor parallel): peers store rows straight into this GPU's vector and bump a
+// counter here; the reader waits (bounded) for the count before it touches the vector ─────────────────
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned int* p, unsigned int v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// One thread. true when *flag has reached `expected` (wrap-safe), false after WAIT_CYCLE_LIMIT cycles or when
+// another wait of this kernel already failed; records KERR_WAIT_PEER then.
+__device__ __forceinline__ bool peer_wait(const unsigned int* flag, unsigned int expected, int* status, int code) {
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys_u32(flag) - expected) < 0) {
+        if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
 
 // ── arithmetic helpers ──────────────────────────────────────────────────────
 // u8 x s8 dot of four byte lanes, accumulated into c.

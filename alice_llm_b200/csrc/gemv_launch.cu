@@ -80,7 +80,7 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
 // The lean instance when the matvec uses none of the fused extras.
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1;
+    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1 && !a.npeers && !a.wait_flag;
     return plain ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
 }
 
@@ -282,6 +282,11 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.rows = total_rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
     a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
     a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
+    if (op.push) {
+        a.npeers = std::min<uint32_t>(op.push->npeers, MAX_PEERS);
+        for (uint32_t p = 0; p < a.npeers; p++) { a.peer_y[p] = op.push->y[p]; a.peer_flag[p] = op.push->flag[p]; }
+    }
+    a.wait_flag = op.wait_flag; a.wait_mult = op.wait_mult; a.epoch = op.epoch;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
     a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
     if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
@@ -340,6 +345,26 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     return ALICE_OK;
 }
 
+// CTAs of the launch that stores the final rows of `op` (the last column chunk when the matvec runs as several):
+// the number of arrivals a tensor-parallel peer must expect from this GPU for this matvec.
+int stream_gemv_final_grid(const GemvOp& op, const LaunchCfg& cfg, uint32_t* grid) {
+    StreamPlan pl;
+    int rc = plan_stream_gemv(op, cfg, nullptr, pl);
+    if (rc) return rc;
+    if (pl.mma && pl.ksplit > 1) {
+        uint32_t lo, n;
+        mma_chunk(*op.w[0], pl.ksplit, pl.ksplit - 1, lo, n);
+        StreamArgs base = pl.args;
+        base.x = op.x; base.cols = op.w[0]->cols; base.row_bytes = op.w[0]->row_bytes;
+        StreamPlan pc;
+        rc = plan_mma(op, cfg, base, lo, n, pc);
+        if (rc) return rc;
+        pl.grid = pc.grid;
+    }
+    *grid = pl.grid;
+    return ALICE_OK;
+}
+
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     StreamPlan pl;
     const int prc = plan_stream_gemv(op, cfg, nullptr, pl);
@@ -359,7 +384,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
                 const int rc = plan_mma(op, cfg, base, lo, n, pc);
                 if (rc) return rc;
                 if (c > 0) pc.args.resid = op.y;
-                if (c + 1 < pl.ksplit) pc.args.argmax_key = nullptr;
+                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; }   // only the last chunk holds final rows
             }
             const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : launch_mma<MmaTernary>(pc, cfg);
             if (rc) return rc;

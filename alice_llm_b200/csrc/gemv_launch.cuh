@@ -38,6 +38,13 @@ struct LaunchCfg {
 };
 
 // One launch of the streaming matvec with its optional fused stages.
+// Where a matvec's rows also go on the other GPUs of a tensor-parallel group (see StreamArgs::peer_y).
+struct PeerPush {
+    uint32_t npeers = 0;
+    float* y[7] = {};             // the same vector as GemvOp::y in each peer's memory
+    unsigned int* flag[7] = {};   // arrival counter of this matvec on each peer
+};
+
 struct GemvOp {
     const WeightDesc* w[3] = {nullptr, nullptr, nullptr};  // 1..3 matrices of one format and width sharing the input
     uint32_t nw = 1;
@@ -51,8 +58,14 @@ struct GemvOp {
     const float* resid = nullptr;                          // y = resid + result
     unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs
     float* y = nullptr;
+    const PeerPush* push = nullptr;                        // tensor parallel: also store every row result on the peers
+    const unsigned int* wait_flag = nullptr;               // tensor parallel: x is complete when *wait_flag >= (*epoch + 1) * wait_mult
+    uint32_t wait_mult = 0;
+    const unsigned int* epoch = nullptr;
 };
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
+// CTAs of the launch that stores the final rows of `op` (what a tensor-parallel peer counts as arrivals).
+int stream_gemv_final_grid(const GemvOp& op, const LaunchCfg& cfg, uint32_t* grid);
 
 // y[r] = W[r,:] . x  (or silu(W0 x) * (W1 x) when w1 != null). K-quant formats read `q8`,
 // the others read the f32 vector `x`. Returns 0 or a negative ALICE_E_* code.

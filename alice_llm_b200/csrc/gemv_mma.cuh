@@ -278,7 +278,8 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;   // rps == 16
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg;
+    const bool cg = cx.acts_cg || a.wait_flag != nullptr;
+    if (!stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
 
     const bool norm = a.norm_w != nullptr;
     if (norm) stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, false, a.q8k_roundtrip != 0, cg);
@@ -361,6 +362,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
                     const uint32_t yi = a.seg_y[sg] + row;
                     if (a.resid != nullptr) r = __fadd_rn(res, r);
                     a.y[yi] = r;
+                    for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
                     if (r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
@@ -379,6 +381,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
     }
+    stream_signal_peers(a, sm);
     return true;
 }
 

@@ -72,6 +72,17 @@ struct StreamArgs {
     uint32_t npieces;
     uint32_t piece_off[2];
     uint32_t piece_len;
+    // Tensor parallel without a collective library: every row result is also stored at the same index of the
+    // vector of each of npeers other GPUs (peer_y, peer-mapped memory), and a CTA that has finished all its rows
+    // adds 1 to peer_flag[p] on every peer (release). wait_flag (in this GPU's memory) guards the INPUT vector:
+    // the consumers wait until it has reached (*epoch + 1) * wait_mult - the arrivals of all peers' producing
+    // CTAs up to and including this decode step - before reading x, and read x past L1.
+    uint32_t npeers;
+    float* peer_y[7];
+    unsigned int* peer_flag[7];
+    const unsigned int* wait_flag;
+    uint32_t wait_mult;
+    const unsigned int* epoch;
 };
 
 // Shared-memory header in front of the ring.
@@ -82,6 +93,7 @@ struct StreamSmem {
     float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
     double norm_part[NCW];
     int abort_flag;
+    unsigned int peer_done;   // consumer warps that have pushed all their rows to the peers (tensor parallel)
     // multi-matvec kernels: the producer (which runs ahead of the consumers) keeps the arguments of the
     // matvec it is streaming here instead of re-reading them from global memory
     StreamArgs pargs;
@@ -100,6 +112,35 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
         }
     }
     return true;
+}
+
+constexpr uint32_t MAX_PEERS = 7;
+
+// Consumer warps, before the input vector is read. false = gave up (status recorded).
+__device__ __forceinline__ bool stream_wait_input(const StreamArgs& a, StreamSmem* sm) {
+    if (a.wait_flag == nullptr) return true;
+    if (threadIdx.x == 0) {
+        const unsigned int expected = (ld_acquire_sys_u32(a.epoch) + 1u) * a.wait_mult;
+        if (!peer_wait(a.wait_flag, expected, a.status, KERR_WAIT_PEER)) sm->abort_flag = 1;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+    return sm->abort_flag == 0;
+}
+// Consumer warps, after their last row: make the pushed rows visible, then tell every peer. The warps meet on a
+// shared-memory counter with a bounded wait (no CTA barrier: after an abort some warps never get here).
+__device__ __forceinline__ void stream_signal_peers(const StreamArgs& a, StreamSmem* sm) {
+    if (a.npeers == 0) return;
+    __threadfence_system();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) atomicAdd(&sm->peer_done, 1u);
+    if (threadIdx.x == 0) {
+        volatile unsigned int* done = &sm->peer_done;
+        volatile int* abort_flag = &sm->abort_flag;
+        const long long t0 = clock64();
+        while (*done < NCW && !*abort_flag && clock64() - t0 < WAIT_CYCLE_LIMIT) {}
+        if (*done >= NCW)
+            for (uint32_t p = 0; p < a.npeers; p++) red_release_sys_add_u32(a.peer_flag[p], 1u);
+    }
 }
 
 // Sums NV per-lane values across the warp with one butterfly: each halving step trades half of
@@ -163,6 +204,7 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
         for (uint32_t q = 0; q < NCW; q++) mbar_init(smem_u32(&sm->red[s][q]), RED_COUNT);
     }
     sm->abort_flag = 0;
+    sm->peer_done = 0;
     mbar_fence_init();
 }
 
@@ -367,7 +409,8 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg;
+    const bool cg = cx.acts_cg || (!PLAIN && a.wait_flag != nullptr);
+    if (!PLAIN && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
 
     // input prologue (shared by every format, one copy of the code per kernel): RMSNorm into shared
     // memory and / or Q8_K quantization into shared memory
@@ -480,6 +523,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
                     const uint32_t yi = a.seg_y[sg] + row;
                     if (resid != nullptr) r = __fadd_rn(res, r);
                     a.y[yi] = r;
+                    if (!PLAIN) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
                     if (argmax_key != nullptr && r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
@@ -501,6 +545,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         if (cx.prof && threadIdx.x == 0 && g - g0 < 8) cx.prof[8 + g - g0] = clock64();
     }
     if (cx.prof && threadIdx.x == 0) cx.prof[3] = clock64();
+    if (!PLAIN) stream_signal_peers(a, sm);
     return true;
 }
 

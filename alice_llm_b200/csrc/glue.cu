@@ -36,24 +36,39 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
                                                          float* __restrict__ vcache, const int* __restrict__ pos_ptr,
                                                          AttnShape s, const float* __restrict__ rope_tab, int neox, uint32_t nsplit,
                                                          float* __restrict__ part, unsigned int* __restrict__ tickets,
-                                                         float* __restrict__ attn_out) {
+                                                         float* __restrict__ attn_out, const AttnPeers peers) {
     __shared__ AttnSmem<GROUP> sh;
     pdl_wait();
     pdl_launch_dependents();
     attn_fused_body<GROUP, false>(qkv, kcache, vcache, (uint32_t)*pos_ptr, s, rope_tab, neox, nsplit, part, tickets, attn_out,
-                                  blockIdx.x, blockIdx.y, &sh);
+                                  blockIdx.x, blockIdx.y, &sh, nullptr, &peers);
 }
 
 // Turns the packed (ordered logit, ~row) maxima the output-head kernels accumulated - one per rank of a
 // tensor-parallel group, each over that rank's rows, gathered to every rank - into the next token,
 // records it, advances the position and clears the keys for the next step.
 __global__ void finish_step_kernel(unsigned long long* __restrict__ keys, uint32_t nkeys, int* __restrict__ token,
-                                   int* __restrict__ pos, int* __restrict__ trace, int write_token) {
+                                   int* __restrict__ pos, int* __restrict__ trace, int write_token, const StepPeers peers) {
     pdl_wait();
     pdl_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
+        unsigned int e = 0;
+        if (peers.npeers) {
+            // publish this rank's maximum, then wait for the peers' maxima and for their rows of the logits vector
+            const unsigned long long mine = keys[peers.rank];
+            for (uint32_t p = 0; p < peers.npeers; p++) peers.keys[p][peers.rank] = mine;
+            __threadfence_system();
+            for (uint32_t p = 0; p < peers.npeers; p++) red_release_sys_add_u32(peers.key_flag[p], 1u);
+            e = *peers.epoch;
+            peer_wait(peers.my_key_flag, (e + 1u) * peers.npeers, peers.status, KERR_WAIT_PEER);
+            peer_wait(peers.my_logits_flag, (e + 1u) * peers.logits_mult, peers.status, KERR_WAIT_PEER);
+        }
         unsigned long long k = 0ull;
-        for (uint32_t i = 0; i < nkeys; i++) { k = keys[i] > k ? keys[i] : k; keys[i] = 0ull; }
+        for (uint32_t i = 0; i < nkeys; i++) {
+            const unsigned long long ki = peers.npeers ? __ldcg(keys + i) : keys[i];
+            k = ki > k ? ki : k;
+            keys[i] = 0ull;
+        }
         const int p = *pos;
         if (write_token) {
             const int t = (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
@@ -61,6 +76,7 @@ __global__ void finish_step_kernel(unsigned long long* __restrict__ keys, uint32
             if (trace) trace[p] = t;
         }
         *pos = p + 1;
+        if (peers.npeers) *peers.epoch = e + 1u;
     }
 }
 
@@ -80,26 +96,27 @@ cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t c
 }
 
 cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
-                             uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, cudaStream_t st, bool pdl) {
+                             uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, const AttnPeers& peers,
+                             cudaStream_t st, bool pdl) {
     if (s.head_dim != 128 || s.num_heads % s.num_kv_heads) return cudaErrorInvalidValue;
     const uint32_t group = s.num_heads / s.num_kv_heads;
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(s.num_kv_heads, nsplit), dim3(256), st, pdl);
     switch (group) {
-        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
-        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
-        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
-        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
-        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out);
+        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
+        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
+        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
+        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
+        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
         default: return cudaErrorInvalidValue;
     }
 }
 
 cudaError_t launch_finish_step(unsigned long long* keys, uint32_t nkeys, int* token, int* pos, int* trace, int write_token,
-                               cudaStream_t st, bool pdl) {
+                               const StepPeers& peers, cudaStream_t st, bool pdl) {
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(1), dim3(32), st, pdl);
-    return cudaLaunchKernelEx(&lc, finish_step_kernel, keys, nkeys, token, pos, trace, write_token);
+    return cudaLaunchKernelEx(&lc, finish_step_kernel, keys, nkeys, token, pos, trace, write_token, peers);
 }
 
 }  // namespace alice

@@ -37,6 +37,16 @@ struct alice_model {
     // tensor parallel (engine's group): every projection holds rows [r*R/n, (r+1)*R/n); l* are the local sizes
     uint32_t tp_n = 1, tp_r = 0, lq = 0, lkv = 0, lH = 0, lF = 0, lV = 0;
     unsigned long long* argmax_keys = nullptr;   // one packed maximum per rank (argmax_key = &argmax_keys[tp_r])
+    // Exchange region (tensor parallel): hidden | attn_out | ffn_h | logits | keys | flags | epoch in ONE allocation,
+    // so one IPC handle maps all of it into the peers. peer_base[p] = that region of the p-th other rank.
+    uint8_t* xchg = nullptr;
+    size_t xchg_bytes = 0;
+    unsigned int* flags = nullptr;      // arrival counters, one per op that has an exchanged output (4 per layer + head + keys)
+    unsigned int* epoch = nullptr;      // decode steps completed
+    bool peer_mode = false;             // peers connected: rows are pushed by the kernels, no collective calls
+    uint32_t npeers = 0;
+    uint32_t peer_rank[7] = {};
+    uint8_t* peer_base[7] = {};
     // device-side state: position, current token, tokens chosen per position
     int *d_pos = nullptr, *d_token = nullptr, *d_trace = nullptr;
     uint32_t pos = 0;  // host mirror of *d_pos
@@ -103,8 +113,32 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
     const bool pdl = m->e->pdl;
     const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r;
     const AttnShape shape{c.num_heads / m->tp_n, c.num_kv_heads / m->tp_n, c.head_dim};
+    const bool peer = m->peer_mode;
+    // Peer mode: the kernel that produces an exchanged vector stores its rows on every peer and bumps that op's
+    // arrival counter there; the kernel that consumes the vector waits for the counter. flag f of this GPU sits at
+    // the same offset of every peer's region.
+    auto flag_of = [&](uint32_t layer, uint32_t k) { return layer * 4 + k; };   // k: 0 attention, 1 o, 2 gate/up, 3 down
+    const uint32_t f_logits = 4 * c.num_layers, f_keys = f_logits + 1;
+    auto push_to = [&](PeerPush& pp, float* local_vec, uint32_t f) {
+        pp.npeers = m->npeers;
+        for (uint32_t p = 0; p < m->npeers; p++) {
+            pp.y[p] = reinterpret_cast<float*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(local_vec) - m->xchg));
+            pp.flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + f) - m->xchg));
+        }
+    };
+    auto wait_on = [&](GemvOp& op, uint32_t f, uint32_t arrivals_per_peer) {
+        op.wait_flag = m->flags + f; op.wait_mult = m->npeers * arrivals_per_peer; op.epoch = m->epoch;
+    };
+    // arrivals a matvec produces on a peer = the CTAs of its launch (the last one for a matvec run as column chunks)
+    // arrivals a matvec produces on a peer = the CTAs of the launch that stores its final rows
+    auto grid_of = [&](const GemvOp& op, uint32_t& grid) {
+        const int prc = stream_gemv_final_grid(op, alice_cfg_of(m->e), &grid);
+        if (prc) return alice_fail(prc, "alice_model: planning a matvec failed (%d)", prc);
+        return (int)ALICE_OK;
+    };
     int rc;
     MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, st, pdl));
+    uint32_t prev_grid = 0;   // CTAs of the matvec that produced the vector the next op reads (same on every rank)
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const alice_model::Layer& L = m->layers[l];
         float* kc = m->kcache + (size_t)l * c.max_seq_len * lkv;
@@ -116,6 +150,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
             op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
             op.q8k_roundtrip = preq_roundtrip(L.q);
+            if (peer && l > 0) wait_on(op, flag_of(l - 1, 3), prev_grid);   // hidden comes from the previous layer's down projection
             if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
             const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
@@ -125,44 +160,73 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
                 op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
                 op.q8k_roundtrip = preq_roundtrip(*ws[i]);
                 op.y = m->qkv + offs[i];
+                if (peer && l > 0) wait_on(op, flag_of(l - 1, 3), prev_grid);
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
         }
         // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
+        AttnPeers ap;
+        if (peer) {
+            ap.npeers = m->npeers;
+            for (uint32_t p = 0; p < m->npeers; p++) {
+                ap.out[p] = reinterpret_cast<float*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->attn_out) - m->xchg)) + (size_t)r * lq;
+                ap.flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + flag_of(l, 0)) - m->xchg));
+            }
+        }
         MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
-                             m->attn_tickets, m->attn_out + (size_t)r * lq, st, pdl));
-        if ((rc = gather(m, m->attn_out, lq))) return rc;
+                             m->attn_tickets, m->attn_out + (size_t)r * lq, ap, st, pdl));
+        if (!peer && (rc = gather(m, m->attn_out, lq))) return rc;
         {   // output projection + residual (src/llama3.rs:14423, 14468)
-            GemvOp op;
+            GemvOp op; PeerPush pp;
             op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
+            if (peer) { push_to(pp, m->hidden, flag_of(l, 1)); op.push = &pp; wait_on(op, flag_of(l, 0), shape.num_kv_heads); }
+            if (peer && (rc = grid_of(op, prev_grid))) return rc;
             if ((rc = gemv(m, op, "o_proj"))) return rc;
-            if ((rc = gather(m, m->hidden, m->lH))) return rc;
+            if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
         }
         {   // FFN norm + fused SwiGLU gate/up (src/llama3.rs:14497-14534)
-            GemvOp op;
+            GemvOp op; PeerPush pp;
             op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
             op.q8k_roundtrip = preq_roundtrip(L.gate);
             op.y = m->ffn_h; op.y_off[0] = r * m->lF;
+            if (peer) { push_to(pp, m->ffn_h, flag_of(l, 2)); op.push = &pp; wait_on(op, flag_of(l, 1), prev_grid); }
+            if (peer && (rc = grid_of(op, prev_grid))) return rc;
             if ((rc = gemv(m, op, "gate/up"))) return rc;
-            if ((rc = gather(m, m->ffn_h, m->lF))) return rc;
+            if (!peer && (rc = gather(m, m->ffn_h, m->lF))) return rc;
         }
         {   // down projection + residual (src/llama3.rs:14536-14555)
-            GemvOp op;
+            GemvOp op; PeerPush pp;
             op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
+            if (peer) { push_to(pp, m->hidden, flag_of(l, 3)); op.push = &pp; wait_on(op, flag_of(l, 2), prev_grid); }
+            if (peer && (rc = grid_of(op, prev_grid))) return rc;
             if ((rc = gemv(m, op, "down_proj"))) return rc;
-            if ((rc = gather(m, m->hidden, m->lH))) return rc;
+            if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
         }
     }
+    StepPeers sp;
     {   // output norm + head (src/llama3.rs:14590-14604)
-        GemvOp op;
+        GemvOp op; PeerPush pp;
         op.w[0] = &m->out; op.x = m->hidden; op.norm_w = m->out_norm; op.norm_eps = c.eps; op.y = m->logits;
         op.y_off[0] = r * m->lV;
         op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
+        uint32_t head_grid = 0;
+        if (peer) { push_to(pp, m->logits, f_logits); op.push = &pp; wait_on(op, flag_of(c.num_layers - 1, 3), prev_grid); }
+        if (peer && (rc = grid_of(op, head_grid))) return rc;
         if ((rc = gemv(m, op, "output head"))) return rc;
-        if ((rc = gather(m, m->logits, m->lV))) return rc;
-        if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
+        if (!peer) {
+            if ((rc = gather(m, m->logits, m->lV))) return rc;
+            if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
+        } else {
+            sp.npeers = m->npeers; sp.rank = r;
+            for (uint32_t p = 0; p < m->npeers; p++) {
+                sp.keys[p] = reinterpret_cast<unsigned long long*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->argmax_keys) - m->xchg));
+                sp.key_flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + f_keys) - m->xchg));
+            }
+            sp.my_key_flag = m->flags + f_keys; sp.my_logits_flag = m->flags + f_logits; sp.logits_mult = m->npeers * head_grid;
+            sp.epoch = m->epoch; sp.status = m->e->status;
+        }
     }
-    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, st, pdl));
+    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, sp, st, pdl));
     return ALICE_OK;
 }
 
@@ -363,18 +427,32 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     m->nsplit = std::max<uint32_t>(1, std::min<uint32_t>(64, (2 * (uint32_t)e->num_sms) / (c.num_kv_heads / n)));
     const size_t kv_elems = (size_t)c.num_layers * c.max_seq_len * lkv;
     if (!rc) rc = upload_norm(m, &m->out_norm, output_norm, c.hidden_dim);
-    if (!rc) rc = dev_alloc(m, &m->hidden, c.hidden_dim);
+    {   // the vectors other ranks need, the argmax keys and the hand-over counters share one allocation
+        auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+        const size_t o_hidden = 0, o_attn = o_hidden + up((size_t)c.hidden_dim * 4), o_ffn = o_attn + up((size_t)q_dim * 4),
+                     o_logits = o_ffn + up((size_t)c.intermediate_dim * 4), o_keys = o_logits + up((size_t)c.vocab_size * 4),
+                     o_flags = o_keys + up(8 * 8), o_epoch = o_flags + up(((size_t)4 * c.num_layers + 2) * 4);
+        m->xchg_bytes = o_epoch + 256;
+        if (!rc) rc = dev_alloc(m, &m->xchg, m->xchg_bytes);
+        if (!rc) {
+            const cudaError_t zerr = cudaMemset(m->xchg, 0, m->xchg_bytes);
+            if (zerr != cudaSuccess) rc = alice_cuda_fail(zerr, "alice_model_create: clearing the exchange region");
+            m->hidden = reinterpret_cast<float*>(m->xchg + o_hidden);
+            m->attn_out = reinterpret_cast<float*>(m->xchg + o_attn);
+            m->ffn_h = reinterpret_cast<float*>(m->xchg + o_ffn);
+            m->logits = reinterpret_cast<float*>(m->xchg + o_logits);
+            m->argmax_keys = reinterpret_cast<unsigned long long*>(m->xchg + o_keys);
+            m->argmax_key = m->argmax_keys + m->tp_r;
+            m->flags = reinterpret_cast<unsigned int*>(m->xchg + o_flags);
+            m->epoch = reinterpret_cast<unsigned int*>(m->xchg + o_epoch);
+        }
+    }
     if (!rc) rc = dev_alloc(m, &m->qkv, lq + 2 * lkv);
-    if (!rc) rc = dev_alloc(m, &m->attn_out, q_dim);
-    if (!rc) rc = dev_alloc(m, &m->ffn_h, c.intermediate_dim);
-    if (!rc) rc = dev_alloc(m, &m->logits, c.vocab_size);
     if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
     if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads / n);
     if (!rc) rc = dev_alloc(m, &m->rope_tab, 128);
-    if (!rc) rc = dev_alloc(m, &m->argmax_keys, n);
-    if (!rc) m->argmax_key = m->argmax_keys + m->tp_r;
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, 1);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
@@ -383,7 +461,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)(c.num_kv_heads / n) * 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->argmax_keys, 0, 8 * (size_t)n, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
@@ -399,6 +476,7 @@ int32_t alice_model_destroy(alice_model* m) {
     cudaSetDevice(m->e->device);
     cudaStreamSynchronize(m->e->stream);
     if (m->graph_greedy) cudaGraphExecDestroy(m->graph_greedy);
+    for (uint32_t p = 0; p < m->npeers; p++) cudaIpcCloseMemHandle(m->peer_base[p]);
     for (void* p : m->owned) cudaFree(p);
     delete m;
     return ALICE_OK;
@@ -488,6 +566,46 @@ int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t
     MCU(cudaMemcpyAsync(out_tokens, m->d_trace + pos0, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     MCU(cudaStreamSynchronize(st));
     return alice_sync(m->e);
+}
+
+int32_t alice_model_tp_export(alice_model* m, void* out, size_t nbytes) {
+    if (!m || !out) return alice_fail(ALICE_E_INVALID, "alice_model_tp_export: null argument");
+    if (nbytes < sizeof(cudaIpcMemHandle_t)) return alice_fail(ALICE_E_INVALID, "alice_model_tp_export: need %zu bytes", sizeof(cudaIpcMemHandle_t));
+    MCU(cudaSetDevice(m->e->device));
+    cudaIpcMemHandle_t h;
+    MCU(cudaIpcGetMemHandle(&h, m->xchg));
+    memset(out, 0, nbytes);
+    memcpy(out, &h, sizeof(h));
+    return ALICE_OK;
+}
+
+int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes_per_handle) {
+    if (!m || !handles) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: null argument");
+    if (bytes_per_handle < sizeof(cudaIpcMemHandle_t)) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: handles of %zu bytes, need %zu", bytes_per_handle, sizeof(cudaIpcMemHandle_t));
+    if (m->peer_mode) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: already connected");
+    if (m->tp_n <= 1) return ALICE_OK;
+    MCU(cudaSetDevice(m->e->device));
+    MCU(cudaStreamSynchronize(m->e->stream));
+    uint32_t k = 0;
+    for (uint32_t p = 0; p < m->tp_n; p++) {
+        if (p == m->tp_r) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)p * bytes_per_handle, sizeof(h));
+        void* base = nullptr;
+        const cudaError_t err = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+        if (err != cudaSuccess) {
+            for (uint32_t q = 0; q < k; q++) cudaIpcCloseMemHandle(m->peer_base[q]);
+            return alice_cuda_fail(err, "alice_model_tp_connect: cudaIpcOpenMemHandle (are the GPUs peer-accessible?)");
+        }
+        m->peer_base[k] = static_cast<uint8_t*>(base);
+        m->peer_rank[k] = p;
+        k++;
+    }
+    m->npeers = k;
+    m->peer_mode = true;
+    if (m->graph_greedy) { cudaGraphExecDestroy(m->graph_greedy); m->graph_greedy = nullptr; }
+    m->graph_tried = false;   // a step captured earlier holds the collective calls
+    return ALICE_OK;
 }
 
 int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled) {

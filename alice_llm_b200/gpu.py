@@ -473,6 +473,21 @@ class GpuModel:
         check(self.engine._lib.alice_model_read_logits(self._h, _ptr(out)))
         return out
 
+    TP_HANDLE_BYTES = 64
+
+    def tp_export(self) -> bytes:
+        """Handle to this rank's exchange region (CUDA IPC); gather the handles of all ranks, in rank order."""
+        buf = C.create_string_buffer(self.TP_HANDLE_BYTES)
+        check(self.engine._lib.alice_model_tp_export(self._h, buf, self.TP_HANDLE_BYTES))
+        return bytes(buf.raw)
+
+    def tp_connect(self, handles):
+        """handles[r] = tp_export() of rank r. Switches the sharded vectors from NCCL all-gathers to rows pushed by
+        the producing kernels into the peers' memory."""
+        blob = b"".join(bytes(h).ljust(self.TP_HANDLE_BYTES, b"\0") for h in handles)
+        buf = C.create_string_buffer(blob, len(blob))
+        check(self.engine._lib.alice_model_tp_connect(self._h, buf, self.TP_HANDLE_BYTES))
+
     def use_step_kernel(self, enabled: bool):
         """decode_greedy as one launch per op replayed from a CUDA graph (default) or, when enabled, inside one
         cooperative whole-step kernel (same tokens; opt-in)."""

@@ -191,6 +191,15 @@ int32_t alice_model_read_logits(alice_model* m, float* logits);
  * when every op of the model has an instance there. Same tokens either way; the graph path is the faster
  * one at present, so the whole-step kernel is opt-in. */
 int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled);
+/* Tensor parallel without collective calls: after every rank has created its model, each exports a handle to its
+ * exchange region (ALICE_TP_HANDLE_BYTES; CUDA IPC, same node), the host gathers the handles of all ranks in rank
+ * order and every rank connects. From then on the kernel that produces a sharded vector stores its rows straight
+ * into every peer's copy over NVLink and bumps an arrival counter there; the kernel that consumes the vector waits
+ * (bounded, ALICE_E_KERNEL on expiry) for the counter. No reference counterpart (the reference is single device).
+ * Without this call the same model runs with NCCL all-gathers. */
+#define ALICE_TP_HANDLE_BYTES 64
+int32_t alice_model_tp_export(alice_model* m, void* out, size_t nbytes);
+int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes_per_handle);
 /* position / vocab_size / rollback_to / reset (src/gpu.rs:5655, 5660, 5645, 5618). rollback only lowers
  * the position; reset also zeroes the KV cache. */
 int32_t alice_model_position(const alice_model* m, uint32_t* pos);

@@ -1,5 +1,6 @@
-"""Row-sharded tensor-parallel decode on 2 GPUs (one process per GPU, NCCL all-gather inside the library)
-against the CPU oracle's forward of the whole model. Skipped on a box with a single GPU."""
+"""Row-sharded tensor-parallel decode on 2 GPUs (one process per GPU) against the CPU oracle's forward of the whole
+model, once with NCCL all-gathers inside the library and once with the kernels pushing their rows into the peer's
+memory. Skipped on a box with a single GPU."""
 import json
 import os
 import socket
@@ -38,6 +39,7 @@ def test_tp_decode_matches_oracle(world):
     for r, (p, (so, se)) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{se[-3000:]}"
     res = json.loads(outs[0][0].strip().splitlines()[-1])
-    assert res[0]["max_rel_err"] <= 1e-3, res[0]
-    for r in res:
-        assert r["tokens"] == res[0]["oracle_tokens"], r
+    for mode in ("nccl", "peer"):
+        assert res[0][mode + "_max_rel_err"] <= 1e-3, (mode, res[0])
+        for r in res:
+            assert r[mode + "_tokens"] == res[0]["oracle_tokens"], (mode, r)

@@ -35,39 +35,47 @@ def main():
     dist.broadcast_object_list(ids, src=0)
     eng.tp_init(rank, world, ids[0])
     assert eng.tp_info() == (rank, world)
-    gm = GpuModel.load(eng, model)
     lkv = kv_dim // world
-    for l, (k, v) in enumerate(pre):   # this rank keeps the cache of its own KV heads
-        gm.kv_write(l, 0, np.ascontiguousarray(k[:, rank * lkv:(rank + 1) * lkv]),
-                    np.ascontiguousarray(v[:, rank * lkv:(rank + 1) * lkv]))
-    gm.set_position(npos)
-
-    logits = [gm.forward_and_read(t) for t in (1, 17, 999)]
-    toks = gm.decode_greedy(5, 12)
-    last = gm.read_logits()
-    result = {"rank": rank, "tokens": [int(t) for t in toks]}
-    if rank == 0:
-        from oracle import oracle as orc
-        orc.build()
-        o = orc.LlamaOracle(model)
-        for l, (k, v) in enumerate(pre):
-            o.kcache[l, :npos] = k
-            o.vcache[l, :npos] = v
-        o.pos = npos
-        errs = []
-        for t, got in zip((1, 17, 999), logits):
-            ref = o.forward(t)
-            errs.append(float((np.abs(got.astype(np.float64) - ref) / np.maximum(np.abs(ref), 1.0)).max()))
-        ref_toks, tok = [], 5
-        for _ in range(12):
-            ref = o.forward(tok)
-            tok = int(np.argmax(ref))
-            ref_toks.append(tok)
-        errs.append(float((np.abs(last.astype(np.float64) - ref) / np.maximum(np.abs(ref), 1.0)).max()))
-        result.update(max_rel_err=max(errs), oracle_tokens=ref_toks)
+    from oracle import oracle as orc
+    result = {"rank": rank}
+    # the same model twice: NCCL all-gathers, then rows pushed into the peers' memory by the kernels
+    for mode in ("nccl", "peer"):
+        gm = GpuModel.load(eng, model)
+        if mode == "peer":
+            handles = [None] * world
+            dist.all_gather_object(handles, gm.tp_export())
+            gm.tp_connect(handles)
+        for l, (k, v) in enumerate(pre):   # this rank keeps the cache of its own KV heads
+            gm.kv_write(l, 0, np.ascontiguousarray(k[:, rank * lkv:(rank + 1) * lkv]),
+                        np.ascontiguousarray(v[:, rank * lkv:(rank + 1) * lkv]))
+        gm.set_position(npos)
+        logits = [gm.forward_and_read(t) for t in (1, 17, 999)]
+        toks = gm.decode_greedy(5, 12)
+        last = gm.read_logits()
+        result[mode + "_tokens"] = [int(t) for t in toks]
+        if rank == 0:
+            orc.build()
+            o = orc.LlamaOracle(model)
+            for l, (k, v) in enumerate(pre):
+                o.kcache[l, :npos] = k
+                o.vcache[l, :npos] = v
+            o.pos = npos
+            errs = []
+            for t, got in zip((1, 17, 999), logits):
+                ref = o.forward(t)
+                errs.append(float((np.abs(got.astype(np.float64) - ref) / np.maximum(np.abs(ref), 1.0)).max()))
+            ref_toks, tok = [], 5
+            for _ in range(12):
+                ref = o.forward(tok)
+                tok = int(np.argmax(ref))
+                ref_toks.append(tok)
+            errs.append(float((np.abs(last.astype(np.float64) - ref) / np.maximum(np.abs(ref), 1.0)).max()))
+            result[mode + "_max_rel_err"] = max(errs)
+            result["oracle_tokens"] = ref_toks
+        dist.barrier()      # no rank frees memory its peers may still be writing into
+        gm.free()
     gathered = [None] * world
     dist.all_gather_object(gathered, result)
-    gm.free()
     eng.close()
     if rank == 0:
         print(json.dumps(gathered), flush=True)
