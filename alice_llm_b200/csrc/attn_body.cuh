@@ -230,10 +230,20 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
         const float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
         reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = o;
-        if (peers)
+        if (peers && peers->out_ll) {   // tagged vector: this GPU's copy and the peers'
+            const uint32_t tag = ld_acquire_sys_u32(peers->epoch) * peers->tag_n + peers->tag_seq + 1u;
+            const size_t e0 = (size_t)head * s.head_dim + lane * 4;
+            const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                ll_store(peers->out_ll + e0 + i, ov[i], tag);
+                for (uint32_t p = 0; p < peers->npeers; p++) ll_store(peers->peer_ll[p] + e0 + i, ov[i], tag);
+            }
+        } else if (peers) {
             for (uint32_t p = 0; p < peers->npeers; p++) reinterpret_cast<float4*>(peers->out[p] + (size_t)head * s.head_dim)[lane] = o;
+        }
     }
-    if (peers && peers->npeers) {   // this KV head's output has been pushed: tell every peer
+    if (peers && peers->npeers && !peers->out_ll) {   // this KV head's output has been pushed: tell every peer
         __threadfence_system();
         attn_sync<CONSUMER_BAR>();
         if (threadIdx.x < peers->npeers) red_release_sys_add_u32(peers->flag[threadIdx.x], 1u);

@@ -80,7 +80,7 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
 // The lean instance when the matvec uses none of the fused extras.
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1 && !a.npeers && !a.wait_flag;
+    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1 && !a.npeers && !a.wait_flag && !a.x_ll && !a.y_ll && !a.resid_ll;
     return plain ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
 }
 
@@ -133,6 +133,7 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     a.src_row_bytes = w0.row_bytes; a.npieces = npieces; a.piece_len = piece_len;
     a.piece_off[0] = piece_off[0]; a.piece_off[1] = piece_off[1];
     if (a.x) a.x += col_lo;
+    if (a.x_ll) a.x_ll += col_lo;
     const uint32_t ngroups = (col_n + 127) / 128;
     const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
     const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
@@ -266,11 +267,11 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     }
     if (format_uses_q8k(w0.fmt)) {
         // K-quants take either pre-quantized Q8_K blocks or the f32 vector (quantized in the prologue)
-        if (q8 ? q8->nb * 256u != w0.cols : x == nullptr) return q8 ? ALICE_E_SHAPE : ALICE_E_INVALID;
-    } else if (!x) {
+        if (q8 ? q8->nb * 256u != w0.cols : (x == nullptr && !op.x_ll)) return q8 ? ALICE_E_SHAPE : ALICE_E_INVALID;
+    } else if (!x && !op.x_ll) {
         return ALICE_E_INVALID;
     }
-    if (op.norm_w && (!x || q8)) return ALICE_E_INVALID;  // the norm needs the f32 vector
+    if (op.norm_w && ((!x && !op.x_ll) || q8)) return ALICE_E_INVALID;  // the norm needs the f32 vector
     const uint32_t units = units_per_row(w0.fmt, w0.cols);
     if (units == 0) return ALICE_E_UNSUPPORTED;
 
@@ -284,8 +285,11 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
     if (op.push) {
         a.npeers = std::min<uint32_t>(op.push->npeers, MAX_PEERS);
-        for (uint32_t p = 0; p < a.npeers; p++) { a.peer_y[p] = op.push->y[p]; a.peer_flag[p] = op.push->flag[p]; }
+        for (uint32_t p = 0; p < a.npeers; p++) { a.peer_y[p] = op.push->y[p]; a.peer_flag[p] = op.push->flag[p]; a.peer_y_ll[p] = op.push->y_ll[p]; }
     }
+    a.x_ll = op.x_ll; a.x_seq = op.x_seq; a.x_n = op.x_n; a.y_ll = op.y_ll; a.y_seq = op.y_seq; a.y_n = op.y_n; a.resid_ll = op.resid_ll;
+    if (op.x_ll && !op.norm_w && !format_uses_q8k(w0.fmt) && w0.fmt != WF_Q1_0 && w0.fmt != WF_TERNARY)
+        return ALICE_E_UNSUPPORTED;   // the per-lane f32 formats read x directly; only the prologues understand tagged vectors
     a.wait_flag = op.wait_flag; a.wait_mult = op.wait_mult; a.epoch = op.epoch;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
     a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
@@ -355,7 +359,7 @@ int stream_gemv_final_grid(const GemvOp& op, const LaunchCfg& cfg, uint32_t* gri
         uint32_t lo, n;
         mma_chunk(*op.w[0], pl.ksplit, pl.ksplit - 1, lo, n);
         StreamArgs base = pl.args;
-        base.x = op.x; base.cols = op.w[0]->cols; base.row_bytes = op.w[0]->row_bytes;
+        base.x = op.x; base.x_ll = op.x_ll; base.cols = op.w[0]->cols; base.row_bytes = op.w[0]->row_bytes;
         StreamPlan pc;
         rc = plan_mma(op, cfg, base, lo, n, pc);
         if (rc) return rc;
@@ -380,11 +384,11 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
                 uint32_t lo, n;
                 mma_chunk(w0, pl.ksplit, c, lo, n);
                 StreamArgs base = pl.args;
-                base.x = op.x; base.cols = w0.cols; base.row_bytes = w0.row_bytes;
+                base.x = op.x; base.x_ll = op.x_ll; base.cols = w0.cols; base.row_bytes = w0.row_bytes;
                 const int rc = plan_mma(op, cfg, base, lo, n, pc);
                 if (rc) return rc;
-                if (c > 0) pc.args.resid = op.y;
-                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; }   // only the last chunk holds final rows
+                if (c > 0) { pc.args.resid = op.y; pc.args.resid_ll = nullptr; }   // partial sums travel through the plain y
+                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.y_ll = nullptr; }   // only the last chunk holds final rows
             }
             const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : launch_mma<MmaTernary>(pc, cfg);
             if (rc) return rc;

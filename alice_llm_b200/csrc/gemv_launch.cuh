@@ -43,6 +43,7 @@ struct PeerPush {
     uint32_t npeers = 0;
     float* y[7] = {};             // the same vector as GemvOp::y in each peer's memory
     unsigned int* flag[7] = {};   // arrival counter of this matvec on each peer
+    uint2* y_ll[7] = {};          // tagged form (GemvOp::y_ll) of the vector in each peer's memory
 };
 
 struct GemvOp {
@@ -62,6 +63,12 @@ struct GemvOp {
     const unsigned int* wait_flag = nullptr;               // tensor parallel: x is complete when *wait_flag >= (*epoch + 1) * wait_mult
     uint32_t wait_mult = 0;
     const unsigned int* epoch = nullptr;
+    // tagged vectors (StreamArgs::x_ll ...): input, output (with push->y_ll on the peers) and residual
+    const uint2* x_ll = nullptr;
+    uint32_t x_seq = 0, x_n = 0;
+    uint2* y_ll = nullptr;
+    uint32_t y_seq = 0, y_n = 0;
+    const uint2* resid_ll = nullptr;
 };
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
 // CTAs of the launch that stores the final rows of `op` (what a tensor-parallel peer counts as arrivals).

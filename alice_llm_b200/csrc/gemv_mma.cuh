@@ -58,12 +58,10 @@ constexpr int MMA_FIX_BITS = 26;   // |x| / scale < 1 -> |fixed| < 2^26; digits 
 // instead of one per element. tsum_blocks > 0: also leave sum(x[128 b .. 128 b + 127]) for b < tsum_blocks
 // (a warp's 32 float4 of one round are exactly one such block).
 constexpr int TB_V = 8;
-__device__ __forceinline__ float4 ld_act4(const float4* p, bool cg) { return cg ? __ldcg(p) : *p; }
 
-static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float* x, bool cg, uint32_t cols, uint8_t* table,
+static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc xs, int* status, uint32_t cols, uint8_t* table,
                                                      float* tsum, uint32_t tsum_blocks) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const float4* xv = reinterpret_cast<const float4*>(x);
     const uint32_t nvec = cols / 4;
     const bool one_round = nvec <= NCW * 32 * TB_V;   // then the registers of the first pass serve the second
     const uint32_t half_bytes = ((cols + 127) / 128) * 256;
@@ -75,7 +73,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float
 #pragma unroll
         for (int k = 0; k < TB_V; k++) {
             const uint32_t i = base + k * NCW * 32 + tid;
-            v[k] = i < nvec ? ld_act4(xv + i, cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[k] = i < nvec ? x_load4(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int k = 0; k < TB_V; k++)
@@ -103,7 +101,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float
 #pragma unroll
             for (int k = 0; k < TB_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
-                v[k] = i < nvec ? ld_act4(xv + i, cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[k] = i < nvec ? x_load4(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -282,8 +280,12 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     if (!stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
 
     const bool norm = a.norm_w != nullptr;
-    if (norm) stream_prologue(sm, smem_raw, a.x, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, false, a.q8k_roundtrip != 0, cg);
-    const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
+    XSrc xs = xsrc_of(a, cg);
+    if (norm) {
+        stream_prologue(sm, smem_raw, xs, a.status, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, false, a.q8k_roundtrip != 0);
+        xs.x = reinterpret_cast<const float*>(smem_raw + a.xn_off); xs.ll = nullptr; xs.cg = false;   // the normalised vector, in shared memory
+    }
+    const uint32_t y_tag = a.y_ll != nullptr ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
     const uint32_t ngroups = (a.cols + 127) / 128;
     MmaTable tb;
     uint8_t* table = smem_raw + a.q8_off;
@@ -292,7 +294,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     tb.half = ngroups * 256u;
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
-    tb.kappa = mma_build_table(sm, x_src, !norm && cg, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u);
+    tb.kappa = mma_build_table(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u);
     if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
     const uint32_t g_lo = ngroups * part / P, g_hi = ngroups * (part + 1) / P;
     const uint32_t rowsel_a = lane >> 2, rowsel_b = (lane >> 2) + 8;
@@ -310,7 +312,10 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         const uint32_t set0 = slot * rps;
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         float res = 0.0f;
-        if (a.resid != nullptr && part == 0 && lane < nrow) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        if (part == 0 && lane < nrow) {
+            if (a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
+            else if (a.resid != nullptr) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        }
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
         const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_stride;
@@ -360,9 +365,14 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
                     float r = M::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * M::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr) r = __fadd_rn(res, r);
-                    a.y[yi] = r;
-                    for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                    if (a.resid != nullptr || a.resid_ll != nullptr) r = __fadd_rn(res, r);
+                    if (a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
+                        ll_store(a.y_ll + yi, r, y_tag);
+                        for (uint32_t p = 0; p < a.npeers; p++) ll_store(a.peer_y_ll[p] + yi, r, y_tag);
+                    } else {
+                        a.y[yi] = r;
+                        for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                    }
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
                     if (r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
@@ -381,7 +391,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
     }
-    stream_signal_peers(a, sm);
+    if (a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
     return true;
 }
 

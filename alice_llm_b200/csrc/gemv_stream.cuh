@@ -83,7 +83,31 @@ struct StreamArgs {
     const unsigned int* wait_flag;
     uint32_t wait_mult;
     const unsigned int* epoch;
+    // The per-layer vectors of a tensor-parallel model travel in tagged form instead (8-byte elements (value, tag),
+    // see ll_store): x_ll replaces x as the input, y_ll / peer_y_ll[p] receive the rows of this matvec (this GPU's
+    // copy and the peers'), resid_ll replaces resid. A vector is rewritten several times per decode step; write
+    // number seq of n per step carries tag *epoch * n + seq + 1, so a reader knows exactly which version it wants.
+    const uint2* x_ll;
+    uint32_t x_seq, x_n;
+    uint2* y_ll;
+    uint2* peer_y_ll[7];
+    uint32_t y_seq, y_n;
+    const uint2* resid_ll;
 };
+
+// Where the input vector of a matvec comes from: plain f32 (global, optionally past L1) or a tagged vector.
+struct XSrc {
+    const float* x;
+    const uint2* ll;
+    uint32_t tag;
+    bool cg;
+};
+__device__ __forceinline__ XSrc xsrc_of(const StreamArgs& a, bool cg) {
+    XSrc s;
+    s.x = a.x; s.ll = a.x_ll; s.cg = cg;
+    s.tag = a.x_ll ? ld_acquire_sys_u32(a.epoch) * a.x_n + a.x_seq + 1u : 0u;
+    return s;
+}
 
 // Shared-memory header in front of the ring.
 struct StreamSmem {
@@ -128,9 +152,9 @@ __device__ __forceinline__ bool stream_wait_input(const StreamArgs& a, StreamSme
 }
 // Consumer warps, after their last row: make the pushed rows visible, then tell every peer. The warps meet on a
 // shared-memory counter with a bounded wait (no CTA barrier: after an abort some warps never get here).
-__device__ __forceinline__ void stream_signal_peers(const StreamArgs& a, StreamSmem* sm) {
+__device__ __forceinline__ void stream_signal_peers(const StreamArgs& a, StreamSmem* sm, bool stored) {
     if (a.npeers == 0) return;
-    __threadfence_system();
+    if (stored) __threadfence_system();   // only the warps that finished rows have remote stores in flight
     __syncwarp();
     if ((threadIdx.x & 31) == 0) atomicAdd(&sm->peer_done, 1u);
     if (threadIdx.x == 0) {
@@ -209,6 +233,12 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
 }
 
 __device__ __forceinline__ float ld_act(const float* p, bool cg) { return cg ? __ldcg(p) : *p; }
+// float4 number i4 of the input vector (elements 4*i4 .. 4*i4+3)
+__device__ __forceinline__ float4 x_load4(const XSrc& s, uint32_t i4, StreamSmem* sm, int* status) {
+    if (s.ll) return ll_load4(s.ll + (size_t)i4 * 4, s.tag, &sm->abort_flag, status);
+    const float4* p = reinterpret_cast<const float4*>(s.x) + i4;
+    return s.cg ? __ldcg(p) : *p;
+}
 
 // Producer side of one matvec: streams this CTA's row groups of `a` through the ring. One thread.
 // PLAIN: the matvec is known to be a single matrix (no q/k/v segments).
@@ -289,11 +319,11 @@ __device__ __forceinline__ void stream_drain(StreamCtx& cx) {
 //                   per 256-element block, exactly the stand-alone quantizer;
 //   roundtrip:      (with norm_w) the normalised vector is replaced by d * q of its Q8_K quantization.
 // cg: read x with ld.global.cg (other SMs rewrote it inside this kernel).
-static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
-                                                    float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
-                                                    bool quant, bool roundtrip, bool cg) {
+static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint8_t* smem_raw, const XSrc xs, int* status,
+                                                         const float* norm_w, float norm_eps, uint32_t cols, uint32_t xn_off,
+                                                         uint32_t q8_off, bool quant, bool roundtrip) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const float* src = x;
+    const float* src = xs.x;
     bool src_global = true;
     if (norm_w != nullptr) {
         float* xn = reinterpret_cast<float*>(smem_raw + xn_off);
@@ -301,7 +331,6 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
         // (cols <= NCW*32*4*NORM_V); the norm weights ride the same memory round trip as x
         constexpr int NORM_V = 4;
         const uint32_t nvec = cols / 4;
-        const float4* xg = reinterpret_cast<const float4*>(x);
         const float4* wg = reinterpret_cast<const float4*>(norm_w);
         const bool one_round = nvec <= NCW * 32 * NORM_V;
         float4 xv[NORM_V], wv[NORM_V];
@@ -312,7 +341,7 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < nvec) xv[k] = cg ? __ldcg(xg + i) : xg[i];
+                if (i < nvec) xv[k] = x_load4(xs, i, sm, status);
             }
             if (one_round) {
 #pragma unroll
@@ -341,7 +370,7 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 if (i < nvec) {
-                    const float4 v = one_round ? xv[k] : (cg ? __ldcg(xg + i) : xg[i]);
+                    const float4 v = one_round ? xv[k] : x_load4(xs, i, sm, status);
                     const float4 w = one_round ? wv[k] : __ldg(wg + i);
                     reinterpret_cast<float4*>(xn)[i] = make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
                                                                    __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
@@ -369,14 +398,20 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
         // QB blocks per warp per round: their loads travel together (one memory round trip per round when
         // the source is global memory) and their reduction chains interleave
         constexpr int QB = 4;
-        const bool lcg = src_global && cg;
 #pragma unroll 1
         for (uint32_t b0 = warp; b0 < nb; b0 += QB * NCW) {
             Q8KLaneInput in[QB];
 #pragma unroll
             for (int i = 0; i < QB; i++) {
                 const uint32_t blk = b0 + i * NCW;
-                if (blk < nb) in[i] = q8k_load_lane(src + (size_t)blk * QK_K, lane, lcg);
+                if (blk < nb) {
+                    if (src_global) {   // the lane's 8 consecutive elements = float4 numbers 2*(blk*32 + lane), +1
+                        in[i].a = x_load4(xs, 2 * (blk * 32 + lane), sm, status);
+                        in[i].b = x_load4(xs, 2 * (blk * 32 + lane) + 1, sm, status);
+                    } else {
+                        in[i] = q8k_load_lane(src + (size_t)blk * QK_K, lane, false);
+                    }
+                }
             }
 #pragma unroll
             for (int i = 0; i < QB; i++) {
@@ -390,10 +425,10 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
 
 // The same as one shared out-of-line copy: for kernels that run many matvecs (every format instance calls it, and
 // a copy that stays warm in the instruction cache beats an inlined one that is cold every time).
-static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const float* x, const float* norm_w,
+static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const XSrc xs, int* status, const float* norm_w,
                                                     float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
-                                                    bool quant, bool roundtrip, bool cg) {
-    stream_prologue_body(sm, smem_raw, x, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip, cg);
+                                                    bool quant, bool roundtrip) {
+    stream_prologue_body(sm, smem_raw, xs, status, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip);
 }
 
 // Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
@@ -411,6 +446,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const uint32_t slot = warp / P, part = warp % P;
     const bool cg = cx.acts_cg || (!PLAIN && a.wait_flag != nullptr);
     if (!PLAIN && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
+    const uint32_t y_tag = (!PLAIN && a.y_ll != nullptr) ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
 
     // input prologue (shared by every format, one copy of the code per kernel): RMSNorm into shared
     // memory and / or Q8_K quantization into shared memory
@@ -420,12 +456,14 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const uint32_t nseg = PLAIN ? 1u : a.nseg;
     const bool quant = F::USES_Q8K && a.q8.qs == nullptr;
     if (norm || quant) {
+        XSrc xs;
+        if (PLAIN) { xs.x = a.x; xs.ll = nullptr; xs.tag = 0; xs.cg = cg; } else xs = xsrc_of(a, cg);
         if (SHARED_PROLOGUE)
-            stream_prologue(sm, smem_raw, a.x, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
-                            !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
+            stream_prologue(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                            !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
         else
-            stream_prologue_body(sm, smem_raw, a.x, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
-                                 !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0, cg);
+            stream_prologue_body(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                                 !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
     }
     const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
     const bool x_global = !norm;
@@ -467,7 +505,10 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         // the residual this lane will add in the epilogue: requested now, needed after the rows are done
         float res = 0.0f;
-        if (resid != nullptr && part == 0 && lane < nrow) res = ld_act(resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        if (part == 0 && lane < nrow) {
+            if (!PLAIN && a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
+            else if (resid != nullptr) res = ld_act(resid + a.seg_y[sg] + r0 + set0 + lane, cg);
+        }
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
         if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
         const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_bytes;
@@ -521,9 +562,14 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (resid != nullptr) r = __fadd_rn(res, r);
-                    a.y[yi] = r;
-                    if (!PLAIN) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                    if (resid != nullptr || (!PLAIN && a.resid_ll != nullptr)) r = __fadd_rn(res, r);
+                    if (!PLAIN && a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
+                        ll_store(a.y_ll + yi, r, y_tag);
+                        for (uint32_t p = 0; p < a.npeers; p++) ll_store(a.peer_y_ll[p] + yi, r, y_tag);
+                    } else {
+                        a.y[yi] = r;
+                        if (!PLAIN) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                    }
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
                     if (argmax_key != nullptr && r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
@@ -545,7 +591,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         if (cx.prof && threadIdx.x == 0 && g - g0 < 8) cx.prof[8 + g - g0] = clock64();
     }
     if (cx.prof && threadIdx.x == 0) cx.prof[3] = clock64();
-    if (!PLAIN) stream_signal_peers(a, sm);
+    if (!PLAIN && a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
     return true;
 }
 

@@ -14,7 +14,7 @@ namespace alice {
 // CPU model dequantizes the whole table at load (src/llama3.rs:12890) and copies a row per token.
 __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* __restrict__ token, uint32_t cols,
                                   uint32_t vocab, float* __restrict__ hidden, const int* __restrict__ pos, float theta,
-                                  float* __restrict__ rope_tab) {
+                                  float* __restrict__ rope_tab, const EmbedTag tag) {
     pdl_wait();
     pdl_launch_dependents();
     if (blockIdx.x == 0 && threadIdx.x < 64) rope_table_entry(rope_tab, threadIdx.x, (uint32_t)*pos, theta);
@@ -24,7 +24,9 @@ __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* 
     for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
         const uint8_t* b = row + (c >> 5) * 34;
         const float d = f16_bits_to_f32((uint32_t)b[0] | ((uint32_t)b[1] << 8));
-        hidden[c] = __fmul_rn(d, (float)(int8_t)b[2 + (c & 31)]);
+        const float v = __fmul_rn(d, (float)(int8_t)b[2 + (c & 31)]);
+        hidden[c] = v;
+        if (tag.hidden_ll) ll_store(tag.hidden_ll + c, v, ld_acquire_sys_u32(tag.epoch) * tag.tag_n + 1u);
     }
 }
 
@@ -89,10 +91,10 @@ static void launch_cfg(cudaLaunchConfig_t& lc, cudaLaunchAttribute* at, dim3 gri
 }
 
 cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t cols, uint32_t vocab, float* hidden,
-                              const int* pos, float theta, float* rope_tab, cudaStream_t st, bool pdl) {
+                              const int* pos, float theta, float* rope_tab, const EmbedTag& tag, cudaStream_t st, bool pdl) {
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3((cols + 255) / 256), dim3(256), st, pdl);
-    return cudaLaunchKernelEx(&lc, embed_q8_0_kernel, table, token, cols, vocab, hidden, pos, theta, rope_tab);
+    return cudaLaunchKernelEx(&lc, embed_q8_0_kernel, table, token, cols, vocab, hidden, pos, theta, rope_tab, tag);
 }
 
 cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,

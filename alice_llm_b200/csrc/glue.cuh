@@ -12,6 +12,18 @@ struct AttnPeers {
     uint32_t npeers = 0;
     float* out[7] = {};
     unsigned int* flag[7] = {};
+    // tagged form instead (see ll_store): this GPU's copy and the peers', both already offset to this GPU's heads;
+    // tag = *epoch * tag_n + tag_seq + 1
+    uint2* out_ll = nullptr;
+    uint2* peer_ll[7] = {};
+    const unsigned int* epoch = nullptr;
+    uint32_t tag_seq = 0, tag_n = 0;
+};
+// Tagged copy of the embedding output (the first input of the layer stack), tag = *epoch * tag_n + 1.
+struct EmbedTag {
+    uint2* hidden_ll = nullptr;
+    const unsigned int* epoch = nullptr;
+    uint32_t tag_n = 0;
 };
 // Tensor parallel token hand-over: every rank publishes the packed maximum of its vocabulary rows to all peers.
 struct StepPeers {
@@ -27,7 +39,7 @@ struct StepPeers {
 
 // hidden <- dequantized row *token of the Q8_0 table; rope_tab (128 floats) <- (sin, cos) of *pos * theta^(-2j/128)
 cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t cols, uint32_t vocab, float* hidden,
-                              const int* pos, float theta, float* rope_tab, cudaStream_t st, bool pdl);
+                              const int* pos, float theta, float* rope_tab, const EmbedTag& tag, cudaStream_t st, bool pdl);
 // qkv = [q (num_heads*head_dim) | k (kv_dim) | v (kv_dim)] of the current token, un-rotated; kc / vc = this
 // layer's cache [max_seq][kv_dim] (row `pos` is written). part: nsplit * num_heads * (head_dim + 4) floats,
 // tickets: num_kv_heads zero-initialised counters (left at zero). rope_tab: the table launch_embed_q8_0 wrote

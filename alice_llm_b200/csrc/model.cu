@@ -43,6 +43,7 @@ struct alice_model {
     size_t xchg_bytes = 0;
     unsigned int* flags = nullptr;      // arrival counters, one per op that has an exchanged output (4 per layer + head + keys)
     unsigned int* epoch = nullptr;      // decode steps completed
+    uint2 *hidden_ll = nullptr, *attn_ll = nullptr, *ffn_ll = nullptr;   // tagged forms of the per-layer vectors (peer mode)
     bool peer_mode = false;             // peers connected: rows are pushed by the kernels, no collective calls
     uint32_t npeers = 0;
     uint32_t peer_rank[7] = {};
@@ -111,35 +112,28 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
     const alice_model_config& c = m->cfg;
     cudaStream_t st = m->e->stream;
     const bool pdl = m->e->pdl;
-    const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r;
+    const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r, L_n = c.num_layers;
     const AttnShape shape{c.num_heads / m->tp_n, c.num_kv_heads / m->tp_n, c.head_dim};
     const bool peer = m->peer_mode;
-    // Peer mode: the kernel that produces an exchanged vector stores its rows on every peer and bumps that op's
-    // arrival counter there; the kernel that consumes the vector waits for the counter. flag f of this GPU sits at
-    // the same offset of every peer's region.
-    auto flag_of = [&](uint32_t layer, uint32_t k) { return layer * 4 + k; };   // k: 0 attention, 1 o, 2 gate/up, 3 down
-    const uint32_t f_logits = 4 * c.num_layers, f_keys = f_logits + 1;
-    auto push_to = [&](PeerPush& pp, float* local_vec, uint32_t f) {
+    // Peer mode. The per-layer vectors (hidden, attention output, SwiGLU output) travel as tagged vectors: the kernel
+    // that produces rows stores (value, tag) into this GPU's copy and every peer's, the kernel that consumes the vector
+    // polls for the tag of the version it wants - no fence, no counter. hidden is rewritten 2 L + 1 times per step
+    // (embedding, then o and down of every layer), the other two L times. The logits and the argmax keys (once per
+    // step) use plain stores + an arrival counter instead.
+    const uint32_t hid_n = 2 * L_n + 1;
+    auto on_peer = [&](uint32_t p, const void* local) { return m->peer_base[p] + (reinterpret_cast<const uint8_t*>(local) - m->xchg); };
+    auto push_ll = [&](GemvOp& op, PeerPush& pp, uint2* vec, uint32_t seq, uint32_t n) {
         pp.npeers = m->npeers;
-        for (uint32_t p = 0; p < m->npeers; p++) {
-            pp.y[p] = reinterpret_cast<float*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(local_vec) - m->xchg));
-            pp.flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + f) - m->xchg));
-        }
+        for (uint32_t p = 0; p < m->npeers; p++) pp.y_ll[p] = reinterpret_cast<uint2*>(on_peer(p, vec));
+        op.push = &pp; op.y_ll = vec; op.y_seq = seq; op.y_n = n; op.epoch = m->epoch;
     };
-    auto wait_on = [&](GemvOp& op, uint32_t f, uint32_t arrivals_per_peer) {
-        op.wait_flag = m->flags + f; op.wait_mult = m->npeers * arrivals_per_peer; op.epoch = m->epoch;
-    };
-    // arrivals a matvec produces on a peer = the CTAs of its launch (the last one for a matvec run as column chunks)
-    // arrivals a matvec produces on a peer = the CTAs of the launch that stores its final rows
-    auto grid_of = [&](const GemvOp& op, uint32_t& grid) {
-        const int prc = stream_gemv_final_grid(op, alice_cfg_of(m->e), &grid);
-        if (prc) return alice_fail(prc, "alice_model: planning a matvec failed (%d)", prc);
-        return (int)ALICE_OK;
-    };
+    auto read_ll = [&](GemvOp& op, const uint2* vec, uint32_t seq, uint32_t n) { op.x_ll = vec; op.x_seq = seq; op.x_n = n; op.epoch = m->epoch; };
+    const uint32_t f_logits = 4 * L_n, f_keys = f_logits + 1;
     int rc;
-    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, st, pdl));
-    uint32_t prev_grid = 0;   // CTAs of the matvec that produced the vector the next op reads (same on every rank)
-    for (uint32_t l = 0; l < c.num_layers; l++) {
+    EmbedTag et;
+    if (peer) { et.hidden_ll = m->hidden_ll; et.epoch = m->epoch; et.tag_n = hid_n; }
+    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, et, st, pdl));
+    for (uint32_t l = 0; l < L_n; l++) {
         const alice_model::Layer& L = m->layers[l];
         float* kc = m->kcache + (size_t)l * c.max_seq_len * lkv;
         float* vc = m->vcache + (size_t)l * c.max_seq_len * lkv;
@@ -150,7 +144,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
             op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
             op.q8k_roundtrip = preq_roundtrip(L.q);
-            if (peer && l > 0) wait_on(op, flag_of(l - 1, 3), prev_grid);   // hidden comes from the previous layer's down projection
+            if (peer) read_ll(op, m->hidden_ll, 2 * l, hid_n);
             if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
             const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
@@ -160,7 +154,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
                 op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
                 op.q8k_roundtrip = preq_roundtrip(*ws[i]);
                 op.y = m->qkv + offs[i];
-                if (peer && l > 0) wait_on(op, flag_of(l - 1, 3), prev_grid);
+                if (peer) read_ll(op, m->hidden_ll, 2 * l, hid_n);
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
         }
@@ -168,10 +162,8 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         AttnPeers ap;
         if (peer) {
             ap.npeers = m->npeers;
-            for (uint32_t p = 0; p < m->npeers; p++) {
-                ap.out[p] = reinterpret_cast<float*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->attn_out) - m->xchg)) + (size_t)r * lq;
-                ap.flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + flag_of(l, 0)) - m->xchg));
-            }
+            ap.out_ll = m->attn_ll + (size_t)r * lq; ap.epoch = m->epoch; ap.tag_seq = l; ap.tag_n = L_n;
+            for (uint32_t p = 0; p < m->npeers; p++) ap.peer_ll[p] = reinterpret_cast<uint2*>(on_peer(p, m->attn_ll)) + (size_t)r * lq;
         }
         MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
                              m->attn_tickets, m->attn_out + (size_t)r * lq, ap, st, pdl));
@@ -179,8 +171,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         {   // output projection + residual (src/llama3.rs:14423, 14468)
             GemvOp op; PeerPush pp;
             op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
-            if (peer) { push_to(pp, m->hidden, flag_of(l, 1)); op.push = &pp; wait_on(op, flag_of(l, 0), shape.num_kv_heads); }
-            if (peer && (rc = grid_of(op, prev_grid))) return rc;
+            if (peer) { read_ll(op, m->attn_ll, l, L_n); op.resid_ll = m->hidden_ll; push_ll(op, pp, m->hidden_ll, 2 * l + 1, hid_n); }
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
         }
@@ -189,16 +180,14 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
             op.q8k_roundtrip = preq_roundtrip(L.gate);
             op.y = m->ffn_h; op.y_off[0] = r * m->lF;
-            if (peer) { push_to(pp, m->ffn_h, flag_of(l, 2)); op.push = &pp; wait_on(op, flag_of(l, 1), prev_grid); }
-            if (peer && (rc = grid_of(op, prev_grid))) return rc;
+            if (peer) { read_ll(op, m->hidden_ll, 2 * l + 1, hid_n); push_ll(op, pp, m->ffn_ll, l, L_n); }
             if ((rc = gemv(m, op, "gate/up"))) return rc;
             if (!peer && (rc = gather(m, m->ffn_h, m->lF))) return rc;
         }
         {   // down projection + residual (src/llama3.rs:14536-14555)
             GemvOp op; PeerPush pp;
             op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
-            if (peer) { push_to(pp, m->hidden, flag_of(l, 3)); op.push = &pp; wait_on(op, flag_of(l, 2), prev_grid); }
-            if (peer && (rc = grid_of(op, prev_grid))) return rc;
+            if (peer) { read_ll(op, m->ffn_ll, l, L_n); op.resid_ll = m->hidden_ll; push_ll(op, pp, m->hidden_ll, 2 * l + 2, hid_n); }
             if ((rc = gemv(m, op, "down_proj"))) return rc;
             if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
         }
@@ -210,8 +199,17 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         op.y_off[0] = r * m->lV;
         op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
         uint32_t head_grid = 0;
-        if (peer) { push_to(pp, m->logits, f_logits); op.push = &pp; wait_on(op, flag_of(c.num_layers - 1, 3), prev_grid); }
-        if (peer && (rc = grid_of(op, head_grid))) return rc;
+        if (peer) {
+            read_ll(op, m->hidden_ll, 2 * L_n, hid_n);
+            pp.npeers = m->npeers;
+            for (uint32_t p = 0; p < m->npeers; p++) {
+                pp.y[p] = reinterpret_cast<float*>(on_peer(p, m->logits));
+                pp.flag[p] = reinterpret_cast<unsigned int*>(on_peer(p, m->flags + f_logits));
+            }
+            op.push = &pp;
+            const int prc = stream_gemv_final_grid(op, alice_cfg_of(m->e), &head_grid);
+            if (prc) return alice_fail(prc, "alice_model: planning the output head failed (%d)", prc);
+        }
         if ((rc = gemv(m, op, "output head"))) return rc;
         if (!peer) {
             if ((rc = gather(m, m->logits, m->lV))) return rc;
@@ -219,8 +217,8 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         } else {
             sp.npeers = m->npeers; sp.rank = r;
             for (uint32_t p = 0; p < m->npeers; p++) {
-                sp.keys[p] = reinterpret_cast<unsigned long long*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->argmax_keys) - m->xchg));
-                sp.key_flag[p] = reinterpret_cast<unsigned int*>(m->peer_base[p] + (reinterpret_cast<uint8_t*>(m->flags + f_keys) - m->xchg));
+                sp.keys[p] = reinterpret_cast<unsigned long long*>(on_peer(p, m->argmax_keys));
+                sp.key_flag[p] = reinterpret_cast<unsigned int*>(on_peer(p, m->flags + f_keys));
             }
             sp.my_key_flag = m->flags + f_keys; sp.my_logits_flag = m->flags + f_logits; sp.logits_mult = m->npeers * head_grid;
             sp.epoch = m->epoch; sp.status = m->e->status;
@@ -431,8 +429,9 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
         const size_t o_hidden = 0, o_attn = o_hidden + up((size_t)c.hidden_dim * 4), o_ffn = o_attn + up((size_t)q_dim * 4),
                      o_logits = o_ffn + up((size_t)c.intermediate_dim * 4), o_keys = o_logits + up((size_t)c.vocab_size * 4),
-                     o_flags = o_keys + up(8 * 8), o_epoch = o_flags + up(((size_t)4 * c.num_layers + 2) * 4);
-        m->xchg_bytes = o_epoch + 256;
+                     o_flags = o_keys + up(8 * 8), o_epoch = o_flags + up(((size_t)4 * c.num_layers + 2) * 4),
+                     o_hll = o_epoch + 256, o_all = o_hll + up((size_t)c.hidden_dim * 8), o_fll = o_all + up((size_t)q_dim * 8);
+        m->xchg_bytes = o_fll + up((size_t)c.intermediate_dim * 8);
         if (!rc) rc = dev_alloc(m, &m->xchg, m->xchg_bytes);
         if (!rc) {
             const cudaError_t zerr = cudaMemset(m->xchg, 0, m->xchg_bytes);
@@ -445,6 +444,9 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
             m->argmax_key = m->argmax_keys + m->tp_r;
             m->flags = reinterpret_cast<unsigned int*>(m->xchg + o_flags);
             m->epoch = reinterpret_cast<unsigned int*>(m->xchg + o_epoch);
+            m->hidden_ll = reinterpret_cast<uint2*>(m->xchg + o_hll);
+            m->attn_ll = reinterpret_cast<uint2*>(m->xchg + o_all);
+            m->ffn_ll = reinterpret_cast<uint2*>(m->xchg + o_fll);
         }
     }
     if (!rc) rc = dev_alloc(m, &m->qkv, lq + 2 * lkv);
@@ -584,6 +586,11 @@ int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes
     if (bytes_per_handle < sizeof(cudaIpcMemHandle_t)) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: handles of %zu bytes, need %zu", bytes_per_handle, sizeof(cudaIpcMemHandle_t));
     if (m->peer_mode) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: already connected");
     if (m->tp_n <= 1) return ALICE_OK;
+    for (const alice_model::Layer& L : m->layers)
+        for (const WeightDesc* w : {&L.o, &L.down})
+            if (w->fmt == WF_Q8_0 || w->fmt == WF_Q2_0 || w->fmt == WF_SPARSE_TERNARY)
+                return alice_fail(ALICE_E_UNSUPPORTED, "alice_model_tp_connect: o / down projections in Q8_0, Q2_0 or sparse ternary read their input "
+                                                       "directly and cannot take pushed vectors; the model keeps using NCCL all-gathers");
     MCU(cudaSetDevice(m->e->device));
     MCU(cudaStreamSynchronize(m->e->stream));
     uint32_t k = 0;

@@ -93,7 +93,9 @@ def build_model(engine: GpuEngine, name: str, seed: int = 0, extra_positions: in
         return (1.0 + 0.02 * np.random.default_rng(seed).standard_normal(H)).astype(np.float32)
 
     layers = [dict({r: tensor(r, *shapes[r]) for r in shapes}, attn_norm=norm(), ffn_norm=norm()) for _ in range(c["num_layers"])]
-    emb = _ggml_tensor(gen, dev, synth.Q8_0, V, H)          # whole table on every rank; a decode step reads one row
+    shared = torch.Generator(device=dev)
+    shared.manual_seed(seed)                                # the same table on every rank
+    emb = _ggml_tensor(shared, dev, synth.Q8_0, V, H)       # whole table on every rank; a decode step reads one row
     keep.append(emb)
     model = {"layers": layers, "embedding": engine.weights_from_device(emb.data_ptr(), emb.numel(), V, H, GpuQuantType.Q8_0),
              "output_norm": norm(), "output": tensor("output", V, H)}

@@ -194,9 +194,11 @@ int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled);
 /* Tensor parallel without collective calls: after every rank has created its model, each exports a handle to its
  * exchange region (ALICE_TP_HANDLE_BYTES; CUDA IPC, same node), the host gathers the handles of all ranks in rank
  * order and every rank connects. From then on the kernel that produces a sharded vector stores its rows straight
- * into every peer's copy over NVLink and bumps an arrival counter there; the kernel that consumes the vector waits
- * (bounded, ALICE_E_KERNEL on expiry) for the counter. No reference counterpart (the reference is single device).
- * Without this call the same model runs with NCCL all-gathers. */
+ * into every peer's copy over NVLink. The per-layer vectors travel as 8-byte (value, tag) elements written with one
+ * store each, and the consuming kernel polls (bounded, ALICE_E_KERNEL on expiry) for the tag of the version it wants:
+ * no fence, no counter, no extra launch. The logits and the argmax keys (once per step) use plain stores and an
+ * arrival counter. Refused (ALICE_E_UNSUPPORTED, the model keeps using NCCL) when an o / down projection is Q8_0,
+ * Q2_0 or sparse ternary. No reference counterpart (the reference is single device). */
 #define ALICE_TP_HANDLE_BYTES 64
 int32_t alice_model_tp_export(alice_model* m, void* out, size_t nbytes);
 int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes_per_handle);
