@@ -59,6 +59,7 @@ constexpr int MMA_FIX_BITS = 26;   // |x| / scale < 1 -> |fixed| < 2^26; digits 
 // (a warp's 32 float4 of one round are exactly one such block).
 constexpr int TB_V = 8;
 
+template <bool LL>
 static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc xs, int* status, uint32_t cols, uint8_t* table,
                                                      float* tsum, uint32_t tsum_blocks) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -73,7 +74,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
 #pragma unroll
         for (int k = 0; k < TB_V; k++) {
             const uint32_t i = base + k * NCW * 32 + tid;
-            v[k] = i < nvec ? x_load4(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[k] = i < nvec ? x_load4<LL>(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int k = 0; k < TB_V; k++)
@@ -101,7 +102,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
 #pragma unroll
             for (int k = 0; k < TB_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
-                v[k] = i < nvec ? x_load4(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[k] = i < nvec ? x_load4<LL>(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -294,7 +295,8 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     tb.half = ngroups * 256u;
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
-    tb.kappa = mma_build_table(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u);
+    tb.kappa = xs.ll ? mma_build_table<true>(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u)
+                     : mma_build_table<false>(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u);
     if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
     const uint32_t g_lo = ngroups * part / P, g_hi = ngroups * (part + 1) / P;
     const uint32_t rowsel_a = lane >> 2, rowsel_b = (lane >> 2) + 8;

@@ -233,9 +233,11 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
 }
 
 __device__ __forceinline__ float ld_act(const float* p, bool cg) { return cg ? __ldcg(p) : *p; }
-// float4 number i4 of the input vector (elements 4*i4 .. 4*i4+3)
+// float4 number i4 of the input vector (elements 4*i4 .. 4*i4+3). LL: the vector is in tagged form (the callers
+// are compiled twice, so that the plain instance carries none of the polling code).
+template <bool LL>
 __device__ __forceinline__ float4 x_load4(const XSrc& s, uint32_t i4, StreamSmem* sm, int* status) {
-    if (s.ll) return ll_load4(s.ll + (size_t)i4 * 4, s.tag, &sm->abort_flag, status);
+    if (LL) return ll_load4(s.ll + (size_t)i4 * 4, s.tag, &sm->abort_flag, status);
     const float4* p = reinterpret_cast<const float4*>(s.x) + i4;
     return s.cg ? __ldcg(p) : *p;
 }
@@ -319,6 +321,7 @@ __device__ __forceinline__ void stream_drain(StreamCtx& cx) {
 //                   per 256-element block, exactly the stand-alone quantizer;
 //   roundtrip:      (with norm_w) the normalised vector is replaced by d * q of its Q8_K quantization.
 // cg: read x with ld.global.cg (other SMs rewrote it inside this kernel).
+template <bool LL>
 static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint8_t* smem_raw, const XSrc xs, int* status,
                                                          const float* norm_w, float norm_eps, uint32_t cols, uint32_t xn_off,
                                                          uint32_t q8_off, bool quant, bool roundtrip) {
@@ -341,7 +344,7 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < nvec) xv[k] = x_load4(xs, i, sm, status);
+                if (i < nvec) xv[k] = x_load4<LL>(xs, i, sm, status);
             }
             if (one_round) {
 #pragma unroll
@@ -370,7 +373,7 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
             for (int k = 0; k < NORM_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
                 if (i < nvec) {
-                    const float4 v = one_round ? xv[k] : x_load4(xs, i, sm, status);
+                    const float4 v = one_round ? xv[k] : x_load4<LL>(xs, i, sm, status);
                     const float4 w = one_round ? wv[k] : __ldg(wg + i);
                     reinterpret_cast<float4*>(xn)[i] = make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
                                                                    __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
@@ -406,8 +409,8 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
                 const uint32_t blk = b0 + i * NCW;
                 if (blk < nb) {
                     if (src_global) {   // the lane's 8 consecutive elements = float4 numbers 2*(blk*32 + lane), +1
-                        in[i].a = x_load4(xs, 2 * (blk * 32 + lane), sm, status);
-                        in[i].b = x_load4(xs, 2 * (blk * 32 + lane) + 1, sm, status);
+                        in[i].a = x_load4<LL>(xs, 2 * (blk * 32 + lane), sm, status);
+                        in[i].b = x_load4<LL>(xs, 2 * (blk * 32 + lane) + 1, sm, status);
                     } else {
                         in[i] = q8k_load_lane(src + (size_t)blk * QK_K, lane, false);
                     }
@@ -428,7 +431,8 @@ static __device__ __forceinline__ void stream_prologue_body(StreamSmem* sm, uint
 static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* smem_raw, const XSrc xs, int* status, const float* norm_w,
                                                     float norm_eps, uint32_t cols, uint32_t xn_off, uint32_t q8_off,
                                                     bool quant, bool roundtrip) {
-    stream_prologue_body(sm, smem_raw, xs, status, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip);
+    if (xs.ll) stream_prologue_body<true>(sm, smem_raw, xs, status, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip);
+    else stream_prologue_body<false>(sm, smem_raw, xs, status, norm_w, norm_eps, cols, xn_off, q8_off, quant, roundtrip);
 }
 
 // Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1).
@@ -461,9 +465,12 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         if (SHARED_PROLOGUE)
             stream_prologue(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
                             !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
+        else if (!PLAIN && xs.ll)   // tagged input (tensor parallel): the shared out-of-line copy
+            stream_prologue(sm, smem_raw, xs, a.status, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                            !F::USES_Q8K && a.q8k_roundtrip != 0);
         else
-            stream_prologue_body(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
-                                 !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
+            stream_prologue_body<false>(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
+                                        !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
     }
     const float* x_src = norm ? reinterpret_cast<const float*>(smem_raw + a.xn_off) : a.x;
     const bool x_global = !norm;
