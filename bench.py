@@ -301,7 +301,11 @@ def run_ours(args, rank, world, local_rank):
             dist.broadcast_object_list(ids, src=0)
             eng.tp_init(rank, world, ids[0])
         for name in names:
-            decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak))
+            try:
+                decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak))
+            except Exception as exc:   # the headline line must still be printed; every wait in the library is bounded
+                decode.append({"config": name, "error": f"{type(exc).__name__}: {exc}"[:300]})
+                break
 
     if rank != 0:
         if world > 1:
