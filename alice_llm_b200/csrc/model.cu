@@ -120,6 +120,10 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
     // polls for the tag of the version it wants - no fence, no counter. hidden is rewritten 2 L + 1 times per step
     // (embedding, then o and down of every layer), the other two L times. The logits and the argmax keys (once per
     // step) use plain stores + an arrival counter instead.
+    // Why nobody overwrites a version that is still being read: a peer's next write into vector V is the epilogue of a
+    // matvec whose input needs rows this GPU produces only AFTER all its CTAs have read V (hidden -> peers' down needs
+    // this GPU's complete SwiGLU slice, whose CTAs read hidden in their prologue; attention output -> peers' next
+    // attention needs this GPU's o / SwiGLU / down rows; SwiGLU output -> peers' next SwiGLU needs this GPU's down rows).
     const uint32_t hid_n = 2 * L_n + 1;
     auto on_peer = [&](uint32_t p, const void* local) { return m->peer_base[p] + (reinterpret_cast<const uint8_t*>(local) - m->xchg); };
     auto push_ll = [&](GemvOp& op, PeerPush& pp, uint2* vec, uint32_t seq, uint32_t n) {
