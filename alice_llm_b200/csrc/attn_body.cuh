@@ -5,6 +5,7 @@
 #pragma once
 #include "common.cuh"
 #include "glue.cuh"
+#include "q8k.cuh"
 
 namespace alice {
 
@@ -84,7 +85,7 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
                                                 const float* __restrict__ rope_tab, int neox, uint32_t nsplit, float* __restrict__ part,
                                                 unsigned int* __restrict__ tickets, float* __restrict__ attn_out,
                                                 uint32_t kvh, uint32_t split, AttnSmem<GROUP>* sh, long long* prof = nullptr,
-                                                const AttnPeers* peers = nullptr) {
+                                                const AttnPeers* peers = nullptr, const AttnQ8Out* q8out = nullptr) {
     constexpr int NW = 8;
     const uint32_t seq = pos + 1;
     const uint32_t per = (seq + nsplit - 1) / nsplit;
@@ -190,6 +191,7 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
     if (prof && threadIdx.x == 0) prof[6] = clock64();
     if (!sh->last) return;
     __threadfence();
+    float4 o_keep = make_float4(0.f, 0.f, 0.f, 0.f);   // this warp's head, this lane's 4 dims
     if (warp < GROUP) {
         // one warp per head; lane <-> split for the (max, sum) pairs, so all loads are in flight at once
         const uint32_t head = kvh * GROUP + warp;
@@ -230,6 +232,7 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
         const float4 o = make_float4(A.x * inv, A.y * inv, A.z * inv, A.w * inv);
         reinterpret_cast<float4*>(attn_out + (size_t)head * s.head_dim)[lane] = o;
+        o_keep = o;
         if (peers && peers->out_ll) {   // tagged vector: this GPU's copy and the peers'
             const uint32_t tag = ld_acquire_sys_u32(peers->epoch) * peers->tag_n + peers->tag_seq + 1u;
             const size_t e0 = (size_t)head * s.head_dim + lane * 4;
@@ -241,6 +244,21 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
             }
         } else if (peers) {
             for (uint32_t p = 0; p < peers->npeers; p++) reinterpret_cast<float4*>(peers->out[p] + (size_t)head * s.head_dim)[lane] = o;
+        }
+    }
+    if (q8out && q8out->qs && (GROUP % 2) == 0) {
+        // Q8_K of this KV head's GROUP * 128 outputs = GROUP / 2 whole blocks (quantize_row_q8_k, src/gguf.rs:1323): the
+        // outputs go through shared memory so that a warp sees the two heads of its block
+        attn_sync<CONSUMER_BAR>();                      // the split accumulators in sh->acc are no longer needed
+        if (warp < GROUP) sh->acc[0][warp][lane] = o_keep;
+        attn_sync<CONSUMER_BAR>();
+        if (warp < GROUP / 2) {
+            const uint32_t blk = (kvh * GROUP) / 2 + warp;
+            const int hsel = 2 * (int)warp + (int)(lane >> 4);
+            Q8KLaneInput in;
+            in.a = sh->acc[0][hsel][(lane & 15) * 2];
+            in.b = sh->acc[0][hsel][(lane & 15) * 2 + 1];
+            q8k_quantize_block_warp(in, lane, q8out->qs + (size_t)blk * 256, q8out->d + blk, q8out->bsums + (size_t)blk * 16);
         }
     }
     if (peers && peers->npeers && !peers->out_ll) {   // this KV head's output has been pushed: tell every peer

@@ -38,12 +38,13 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
                                                          float* __restrict__ vcache, const int* __restrict__ pos_ptr,
                                                          AttnShape s, const float* __restrict__ rope_tab, int neox, uint32_t nsplit,
                                                          float* __restrict__ part, unsigned int* __restrict__ tickets,
-                                                         float* __restrict__ attn_out, const AttnPeers peers) {
+                                                         float* __restrict__ attn_out, const AttnPeers peers,
+                                                         const AttnQ8Out q8out) {
     __shared__ AttnSmem<GROUP> sh;
     pdl_wait();
     pdl_launch_dependents();
     attn_fused_body<GROUP, false>(qkv, kcache, vcache, (uint32_t)*pos_ptr, s, rope_tab, neox, nsplit, part, tickets, attn_out,
-                                  blockIdx.x, blockIdx.y, &sh, nullptr, &peers);
+                                  blockIdx.x, blockIdx.y, &sh, nullptr, &peers, &q8out);
 }
 
 // Turns the packed (ordered logit, ~row) maxima the output-head kernels accumulated - one per rank of a
@@ -99,17 +100,17 @@ cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t c
 
 cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
                              uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, const AttnPeers& peers,
-                             cudaStream_t st, bool pdl) {
+                             const AttnQ8Out& q8out, cudaStream_t st, bool pdl) {
     if (s.head_dim != 128 || s.num_heads % s.num_kv_heads) return cudaErrorInvalidValue;
     const uint32_t group = s.num_heads / s.num_kv_heads;
     cudaLaunchConfig_t lc; cudaLaunchAttribute at[1];
     launch_cfg(lc, at, dim3(s.num_kv_heads, nsplit), dim3(256), st, pdl);
     switch (group) {
-        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
-        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
-        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
-        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
-        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers);
+        case 1: return cudaLaunchKernelEx(&lc, attn_fused_kernel<1>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers, q8out);
+        case 2: return cudaLaunchKernelEx(&lc, attn_fused_kernel<2>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers, q8out);
+        case 4: return cudaLaunchKernelEx(&lc, attn_fused_kernel<4>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers, q8out);
+        case 5: return cudaLaunchKernelEx(&lc, attn_fused_kernel<5>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers, q8out);
+        case 8: return cudaLaunchKernelEx(&lc, attn_fused_kernel<8>, qkv, kc, vc, pos, s, rope_tab, neox, nsplit, part, tickets, attn_out, peers, q8out);
         default: return cudaErrorInvalidValue;
     }
 }

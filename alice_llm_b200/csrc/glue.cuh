@@ -6,6 +6,14 @@
 namespace alice {
 
 struct AttnShape { uint32_t num_heads, num_kv_heads, head_dim; };
+// Optional Q8_K copy of the attention output for a K-quant output projection: the CTA that finishes a KV head holds
+// whole 256-element blocks of it (when the heads of a KV head are an even number), so it quantizes them on the spot and
+// the projection starts from int8 activations instead of quantizing the whole vector in every CTA.
+struct AttnQ8Out {
+    int8_t* qs = nullptr;     // [q_dim]
+    float* d = nullptr;       // [q_dim / 256]
+    int16_t* bsums = nullptr; // [q_dim / 256][16]
+};
 // Tensor parallel: the attention output of this GPU's heads also goes to the same place of every peer's vector,
 // and the CTA that finished a KV head adds 1 to the arrival counter on every peer.
 struct AttnPeers {
@@ -45,8 +53,8 @@ cudaError_t launch_embed_q8_0(const uint8_t* table, const int* token, uint32_t c
 // tickets: num_kv_heads zero-initialised counters (left at zero). rope_tab: the table launch_embed_q8_0 wrote
 // for this position.
 cudaError_t launch_attention(const float* qkv, float* kc, float* vc, const int* pos, AttnShape s, const float* rope_tab, int neox,
-                             uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, const AttnPeers& peers, cudaStream_t st,
-                             bool pdl);
+                             uint32_t nsplit, float* part, unsigned int* tickets, float* attn_out, const AttnPeers& peers,
+                             const AttnQ8Out& q8out, cudaStream_t st, bool pdl);
 // token <- index held in the largest of keys[0 .. nkeys) (packed maxima written by the output-head kernels,
 // one per tensor-parallel rank) when write_token; pos <- pos + 1; keys <- 0
 cudaError_t launch_finish_step(unsigned long long* keys, uint32_t nkeys, int* token, int* pos, int* trace, int write_token,

@@ -31,6 +31,10 @@ struct alice_model {
     float *kcache = nullptr, *vcache = nullptr;  // [layer][max_seq][kv_dim]
     float* attn_part = nullptr;
     float* rope_tab = nullptr;   // (sin, cos) per rotation pair at the current position, rewritten every step
+    // Q8_K copy of the attention output, written by the attention kernel for K-quant output projections (single GPU)
+    uint8_t* attn_q8 = nullptr;
+    Q8KLayout attn_q8_lay{};
+    bool attn_q8_ok = false;
     unsigned int* attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
@@ -169,12 +173,23 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
             ap.out_ll = m->attn_ll + (size_t)r * lq; ap.epoch = m->epoch; ap.tag_seq = l; ap.tag_n = L_n;
             for (uint32_t p = 0; p < m->npeers; p++) ap.peer_ll[p] = reinterpret_cast<uint2*>(on_peer(p, m->attn_ll)) + (size_t)r * lq;
         }
+        // a K-quant output projection takes the attention output already in Q8_K (written by the attention kernel)
+        const bool o_preq = m->attn_q8_ok && !peer && (L.o.fmt == WF_Q4_K || L.o.fmt == WF_Q5_K || L.o.fmt == WF_Q6_K);
+        AttnQ8Out aq;
+        Q8KView o_view{};
+        if (o_preq) {
+            aq.qs = reinterpret_cast<int8_t*>(m->attn_q8 + m->attn_q8_lay.qs_off);
+            aq.d = reinterpret_cast<float*>(m->attn_q8 + m->attn_q8_lay.d_off);
+            aq.bsums = reinterpret_cast<int16_t*>(m->attn_q8 + m->attn_q8_lay.bsums_off);
+            o_view.qs = aq.qs; o_view.d = aq.d; o_view.bsums = aq.bsums; o_view.nb = (c.num_heads * c.head_dim) / 256;
+        }
         MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
-                             m->attn_tickets, m->attn_out + (size_t)r * lq, ap, st, pdl));
+                             m->attn_tickets, m->attn_out + (size_t)r * lq, ap, aq, st, pdl));
         if (!peer && (rc = gather(m, m->attn_out, lq))) return rc;
         {   // output projection + residual (src/llama3.rs:14423, 14468)
             GemvOp op; PeerPush pp;
             op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
+            if (o_preq) { op.q8 = &o_view; op.x = nullptr; }
             if (peer) { read_ll(op, m->attn_ll, l, L_n); op.resid_ll = m->hidden_ll; push_ll(op, pp, m->hidden_ll, 2 * l + 1, hid_n); }
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
@@ -459,6 +474,9 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
     if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads / n);
     if (!rc) rc = dev_alloc(m, &m->rope_tab, 128);
+    m->attn_q8_lay = Q8KLayout::make(q_dim / 256, 1);
+    m->attn_q8_ok = n == 1 && (group % 2) == 0 && q_dim % 256 == 0 && !getenv("ALICE_NO_ATTN_Q8");
+    if (!rc && m->attn_q8_ok) rc = dev_alloc(m, &m->attn_q8, m->attn_q8_lay.total);
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, 1);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
