@@ -445,6 +445,16 @@ class GpuModel:
                                              C.byref(h)))
         return cls(engine, h, cfg, keep)
 
+    @classmethod
+    def load_gguf(cls, engine: GpuEngine, path, max_seq_len=None) -> "GpuModel":
+        """GpuModel::load (src/gpu.rs:2831) from a GGUF file: the file is mapped, the raw blocks of every tensor of
+        the name table go to the device as they are (this rank's row shards on a tensor-parallel engine)."""
+        from .gguf_file import GgufFile
+        gf = GgufFile.open(path)
+        gm = cls.load(engine, gf.load_model(max_seq_len))
+        gm._keep.append(gf)
+        return gm
+
     def config(self) -> GpuModelConfig:
         return self._config
 
