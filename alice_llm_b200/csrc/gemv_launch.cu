@@ -116,8 +116,11 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     if (!whole && (op.norm_w || sw || col_lo % 128 || col_n % 128)) return ALICE_E_SHAPE;
     // the sub-row as the consumer sees it, and where its pieces sit inside the global row
     uint32_t sub_row, npieces, piece_len, piece_off[2] = {0, 0};
-    if (w0.fmt == WF_Q1_0) {
-        npieces = 1; piece_len = col_n / 128 * 18; piece_off[0] = col_lo / 128 * 18; sub_row = piece_len;
+    if (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0) {
+        const uint32_t bb = w0.fmt == WF_Q1_0 ? 18u : 34u;
+        npieces = 1; piece_len = col_n / 128 * bb; piece_off[0] = col_lo / 128 * bb; sub_row = piece_len;
+    } else if (w0.fmt == WF_SPARSE_TERNARY) {
+        npieces = 1; piece_len = (col_n + 15) / 16 * 4; piece_off[0] = col_lo / 16 * 4; sub_row = piece_len;
     } else {
         const uint32_t plane_full = w0.row_bytes / 2;
         npieces = 2; piece_len = (col_n + 31) / 32 * 4; piece_off[0] = col_lo / 8; piece_off[1] = plane_full + col_lo / 8;
@@ -134,7 +137,8 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     a.piece_off[0] = piece_off[0]; a.piece_off[1] = piece_off[1];
     if (a.x) a.x += col_lo;
     if (a.x_ll) a.x_ll += col_lo;
-    const uint32_t ngroups = (col_n + 127) / 128;
+    const uint32_t ge = (w0.fmt == WF_Q2_0 || w0.fmt == WF_SPARSE_TERNARY) ? 64u : 128u;   // elements per 16 weight bytes
+    const uint32_t ngroups = (col_n + ge - 1) / ge;
     const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
     const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
     for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
@@ -182,7 +186,7 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
 // Column chunk c of ksplit: whole multiples of `unit` columns (Q1_0: 1024, so that a chunk of a row is a multiple
 // of 16 bytes; ternary planes: 128).
 void mma_chunk(const WeightDesc& w, uint32_t ksplit, uint32_t c, uint32_t& lo, uint32_t& n) {
-    const uint32_t unit = w.fmt == WF_Q1_0 ? 1024u : 128u, units = w.cols / unit;
+    const uint32_t unit = (w.fmt == WF_Q1_0 || w.fmt == WF_Q2_0) ? 1024u : 128u, units = w.cols / unit;
     lo = units * c / ksplit * unit;
     n = units * (c + 1) / ksplit * unit - lo;
 }
@@ -191,7 +195,7 @@ void mma_chunk(const WeightDesc& w, uint32_t ksplit, uint32_t c, uint32_t& lo, u
 int plan_mma_split(const GemvOp& op, const LaunchCfg& cfg, const StreamArgs& a, StreamPlan& pl) {
     const WeightDesc& w0 = *op.w[0];
     if (plan_mma(op, cfg, a, 0, w0.cols, pl) == ALICE_OK) { pl.ksplit = 1; return ALICE_OK; }
-    const uint32_t unit = w0.fmt == WF_Q1_0 ? 1024u : 128u;
+    const uint32_t unit = (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0) ? 1024u : 128u;
     if (w0.cols % unit || op.norm_w || op.up) return ALICE_E_SHAPE;
     for (uint32_t ks = 2; ks <= 4; ks++) {
         bool ok = true;
@@ -288,12 +292,12 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
         for (uint32_t p = 0; p < a.npeers; p++) { a.peer_y[p] = op.push->y[p]; a.peer_flag[p] = op.push->flag[p]; a.peer_y_ll[p] = op.push->y_ll[p]; }
     }
     a.x_ll = op.x_ll; a.x_seq = op.x_seq; a.x_n = op.x_n; a.y_ll = op.y_ll; a.y_seq = op.y_seq; a.y_n = op.y_n; a.resid_ll = op.resid_ll;
-    if (op.x_ll && !op.norm_w && !format_uses_q8k(w0.fmt) && w0.fmt != WF_Q1_0 && w0.fmt != WF_TERNARY)
+    if (op.x_ll && !op.norm_w && w0.fmt == WF_Q8_0)
         return ALICE_E_UNSUPPORTED;   // the per-lane f32 formats read x directly; only the prologues understand tagged vectors
     a.wait_flag = op.wait_flag; a.wait_mult = op.wait_mult; a.epoch = op.epoch;
     if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
     a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
-    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
+    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
         return ALICE_OK;
 
     // warps per row: just enough lanes for one unit each, at most all eight
@@ -390,7 +394,8 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
                 if (c > 0) { pc.args.resid = op.y; pc.args.resid_ll = nullptr; }   // partial sums travel through the plain y
                 if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.y_ll = nullptr; }   // only the last chunk holds final rows
             }
-            const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : launch_mma<MmaTernary>(pc, cfg);
+            const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : w0.fmt == WF_Q2_0 ? launch_mma<MmaQ2_0>(pc, cfg)
+                         : w0.fmt == WF_TERNARY ? launch_mma<MmaTernary>(pc, cfg) : launch_mma<MmaSparseTernary>(pc, cfg);
             if (rc) return rc;
         }
         return ALICE_OK;

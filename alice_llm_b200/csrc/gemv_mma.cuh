@@ -59,13 +59,29 @@ constexpr int MMA_FIX_BITS = 26;   // |x| / scale < 1 -> |fixed| < 2^26; digits 
 // (a warp's 32 float4 of one round are exactly one such block).
 constexpr int TB_V = 8;
 
-template <bool LL>
+// CODE: how a weight byte maps to elements. 0: one bit per element (element 8*byte + j, bit j; Q1_0 signs, ternary
+// planes). 1 / 2: two bits per element (element 4*byte + q, bits 2q and 2q+1) worth +1 and +2 (Q2_0 slots) or +1 and -2
+// (sparse-ternary codes 00 = 0, 01 = +1, 11 = -1). A group is always 16 weight bytes, i.e. 128 or 64 elements.
+template <int CODE>
+__device__ __forceinline__ constexpr uint32_t mma_group_elems() { return CODE == 0 ? 128u : 64u; }
+
+// four signed base-128 digits of f (|f| < 2^27) into digit records 64 bytes apart
+__device__ __forceinline__ void mma_store_digits(uint8_t* w, int f) {
+    const int d3 = ((f + 64) & 127) - 64; f = (f - d3) >> 7;
+    const int d2 = ((f + 64) & 127) - 64; f = (f - d2) >> 7;
+    const int d1 = ((f + 64) & 127) - 64; f = (f - d1) >> 7;
+    w[0] = (uint8_t)f; w[64] = (uint8_t)d1; w[128] = (uint8_t)d2; w[192] = (uint8_t)d3;
+}
+
+template <bool LL, int CODE>
 static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc xs, int* status, uint32_t cols, uint8_t* table,
                                                      float* tsum, uint32_t tsum_blocks) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t nvec = cols / 4;
     const bool one_round = nvec <= NCW * 32 * TB_V;   // then the registers of the first pass serve the second
-    const uint32_t half_bytes = ((cols + 127) / 128) * 256;
+    constexpr uint32_t GE = mma_group_elems<CODE>();
+    const uint32_t groups = (cols + GE - 1) / GE;
+    const uint32_t half_bytes = groups * 256;
     float4 v[TB_V];
     // 1. power-of-two scale above max |x|
     float amax = 0.0f;
@@ -94,8 +110,8 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
     const int e = (ebits == 0u || ebits == 0xffu) ? 0 : (int)ebits - 126;
     const float to_fixed = ldexpf(1.0f, MMA_FIX_BITS - e);
     const float kappa = ldexpf(1.0f, e - MMA_FIX_BITS);
-    // 2. digits: element idx = 8 * byte + j sits at byte i = byte & 3 of word ((G*4 + t)*4 + d)*8 + j; a float4
-    //    covers j = 4h .. 4h + 3 of one byte
+    // 2. digits. Record of (group G, digit d, quad lane t) at ((G*4 + d)*4 + t)*16 in the half of its bit position;
+    //    word j & 3 of the record, byte `byte & 3` of the word.
 #pragma unroll 1
     for (uint32_t base = 0; base < nvec; base += NCW * 32 * TB_V) {
         if (!one_round) {
@@ -115,30 +131,47 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
                 if (lane == 0 && (i >> 5) < tsum_blocks) tsum[i >> 5] = ts;
             }
             if (i < nvec) {
-                const uint32_t byte = i >> 1, G = byte >> 4, t = (byte >> 2) & 3u, bi = byte & 3u;
-                // this float4 is bits 4h .. 4h+3 (h = i & 1) of one weight byte: one 16-byte record per digit
-                uint8_t* w = table + (size_t)(i & 1u) * half_bytes + ((size_t)(G * 4) * 4 + t) * 16 + bi;
-                const float xs[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                const float xq[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                if (CODE == 0) {
+                    // this float4 is bits 4h .. 4h+3 (h = i & 1) of one weight byte
+                    const uint32_t byte = i >> 1, G = byte >> 4, t = (byte >> 2) & 3u, bi = byte & 3u;
+                    uint8_t* w = table + (size_t)(i & 1u) * half_bytes + ((size_t)(G * 4) * 4 + t) * 16 + bi;
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int j = (int)(i & 1u) * 4 + q;
-                    int f = (__float2int_rn(xs[q] * to_fixed) + ((1 << j) >> 1)) >> j;   // fixed / 2^j, rounded to nearest
-                    const int d3 = ((f + 64) & 127) - 64; f = (f - d3) >> 7;
-                    const int d2 = ((f + 64) & 127) - 64; f = (f - d2) >> 7;
-                    const int d1 = ((f + 64) & 127) - 64; f = (f - d1) >> 7;
-                    uint8_t* wq = w + q * 4;       // next bit position: next word of the record
-                    wq[0] = (uint8_t)f; wq[64] = (uint8_t)d1; wq[128] = (uint8_t)d2; wq[192] = (uint8_t)d3;   // digit d: 4 records on
+                    for (int q = 0; q < 4; q++) {
+                        const int j = (int)(i & 1u) * 4 + q;
+                        mma_store_digits(w + q * 4, (__float2int_rn(xq[q] * to_fixed) + ((1 << j) >> 1)) >> j);   // fixed / 2^j, to nearest
+                    }
+                } else {
+                    // this float4 is the four elements of weight byte i: element q owns bits 2q (worth +1) and 2q+1
+                    // (worth +2 or -2), so both want fixed / 2^(2q) (negated for -2); bits 0..3 live in half 0
+                    const uint32_t byte = i, G = byte >> 4, t = (byte >> 2) & 3u, bi = byte & 3u;
+                    uint8_t* rec = table + ((size_t)(G * 4) * 4 + t) * 16 + bi;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int sh = 2 * q;
+                        const int f = (__float2int_rn(xq[q] * to_fixed) + ((1 << sh) >> 1)) >> sh;
+                        uint8_t* w = rec + (size_t)(q >> 1) * half_bytes + ((2 * q) & 3) * 4;
+                        mma_store_digits(w, f);
+                        mma_store_digits(w + 4, CODE == 1 ? f : -f);
+                    }
                 }
             }
         }
     }
-    // zero the part of the last group past `cols` (only a ragged ternary row has one; its plane bits there are zero,
+    // zero the part of the last group past `cols` (only a ragged ternary row has one; its weight bits there are zero,
     // so the table content only has to be finite)
-    const uint32_t groups = (cols + 127) / 128;
-    for (uint32_t idx = cols + tid; idx < groups * 128; idx += NCW * 32) {
-        const uint32_t j = idx & 7u, byte = idx >> 3, G = byte >> 4, t = (byte >> 2) & 3u, i = byte & 3u;
-        uint8_t* w = table + (size_t)(j >> 2) * half_bytes + ((size_t)(G * 4) * 4 + t) * 16 + (j & 3u) * 4 + i;
-        w[0] = 0; w[64] = 0; w[128] = 0; w[192] = 0;
+    for (uint32_t idx = cols + tid; idx < groups * GE; idx += NCW * 32) {
+        const uint32_t byte = CODE == 0 ? idx >> 3 : idx >> 2, G = byte >> 4, t = (byte >> 2) & 3u, bi = byte & 3u;
+        uint8_t* rec = table + ((size_t)(G * 4) * 4 + t) * 16 + bi;
+        if (CODE == 0) {
+            const uint32_t j = idx & 7u;
+            mma_store_digits(rec + (size_t)(j >> 2) * half_bytes + (j & 3u) * 4, 0);
+        } else {
+            const uint32_t q = idx & 3u;
+            uint8_t* w = rec + (size_t)(q >> 1) * half_bytes + ((2 * q) & 3) * 4;
+            mma_store_digits(w, 0);
+            mma_store_digits(w + 4, 0);
+        }
     }
     if (tid < 4) reinterpret_cast<uint32_t*>(table + 2 * (size_t)half_bytes)[tid] = 0u;   // the zero record
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
@@ -161,6 +194,8 @@ __device__ __forceinline__ float small_int_to_f32(int c) { return __int_as_float
 // the accumulator hold the four digit sums of both blocks: quad lanes 0, 1 finish block G, quad lanes 2, 3 block G + 1.
 struct MmaQ1_0 {
     static constexpr bool HAS_TSUM = true;
+    static constexpr int CODE = 0;
+    static constexpr uint32_t SPLIT_UNIT = 1;   // groups per unit the row may be split at between warps
     __device__ static void tile(uint32_t rowA, uint32_t rowB, uint32_t g_lo, uint32_t g_hi, const MmaTable& tb, uint32_t lane,
                                 const StreamArgs&, float& y0, float& y1) {
         const uint32_t t = lane & 3u, d = lane >> 2;
@@ -216,6 +251,8 @@ struct MmaQ1_0 {
 // Groups are taken two at a time (k = 32); integer accumulation over the whole group range.
 struct MmaTernary {
     static constexpr bool HAS_TSUM = false;
+    static constexpr int CODE = 0;
+    static constexpr uint32_t SPLIT_UNIT = 1;
     __device__ static void tile(uint32_t rowA, uint32_t rowB, uint32_t g_lo, uint32_t g_hi, const MmaTable& tb, uint32_t lane,
                                 const StreamArgs& a, float& y0, float& y1) {
         const uint32_t t = lane & 3u, d = lane >> 2;
@@ -265,6 +302,89 @@ struct MmaTernary {
     __device__ static float finish(float v, const StreamArgs&, const float* aux, uint32_t row) { return __ldg(aux + row) * v; }
 };
 
+// ── Q2_0 tile: 34-byte block = d f16 + 128 two-bit slots, value (slot - 1) * d (src/gguf.rs:1283-1300):
+// y = sum_b d_b * (S_b - T_b), S_b = sum slot * x. A block is two groups = one k = 32 step with the four digit columns.
+struct MmaQ2_0 {
+    static constexpr bool HAS_TSUM = true;
+    static constexpr int CODE = 1;
+    static constexpr uint32_t SPLIT_UNIT = 2;
+    __device__ static void tile(uint32_t rowA, uint32_t rowB, uint32_t g_lo, uint32_t g_hi, const MmaTable& tb, uint32_t lane,
+                                const StreamArgs&, float& y0, float& y1) {
+        const uint32_t t = lane & 3u, d = lane >> 2;
+        const bool has_b = d < 4;
+        const float w_lo = t == 0 ? 2097152.0f : (t == 1 ? 128.0f : 0.0f), w_hi = t == 0 ? 16384.0f : (t == 1 ? 1.0f : 0.0f);
+        y0 = 0.0f; y1 = 0.0f;
+        for (uint32_t b = g_lo / 2; b < g_hi / 2; b++) {
+            const uint32_t blkA = rowA + b * 34, blkB = rowB + b * 34;
+            const uint32_t a0 = lds32_u2(blkA + 2 + t * 4), a1 = lds32_u2(blkB + 2 + t * 4);
+            const uint32_t a2 = lds32_u2(blkA + 18 + t * 4), a3 = lds32_u2(blkB + 18 + t * 4);
+            const uint32_t rec = has_b ? tb.words + ((2 * b * 4 + d) * 4 + t) * 16 : tb.zero;
+            const uint32_t rech = has_b ? rec + tb.half : tb.zero, nxt = has_b ? 256u : 0u;
+            const uint4 x03 = lds128(rec), x47 = lds128(rech), z03 = lds128(rec + nxt), z47 = lds128(rech + nxt);
+            int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+#define ALICE_Q2(m, bx, bz, c) mma_u8s8_k32(c, a0 & (m), a1 & (m), a2 & (m), a3 & (m), (bx), (bz));
+            ALICE_Q2(0x01010101u, x03.x, z03.x, c0) ALICE_Q2(0x02020202u, x03.y, z03.y, c1)
+            ALICE_Q2(0x04040404u, x03.z, z03.z, c0) ALICE_Q2(0x08080808u, x03.w, z03.w, c1)
+            ALICE_Q2(0x10101010u, x47.x, z47.x, c0) ALICE_Q2(0x20202020u, x47.y, z47.y, c1)
+            ALICE_Q2(0x40404040u, x47.z, z47.z, c0) ALICE_Q2(0x80808080u, x47.w, z47.w, c1)
+#undef ALICE_Q2
+            // per-block sums stay below 2^22 (32 bytes x 8 bits x 2^j x |digit| <= 64)
+            const float sA = fmaf(small_int_to_f32(c0[0] + c1[0]), w_lo, small_int_to_f32(c0[1] + c1[1]) * w_hi);
+            const float sB = fmaf(small_int_to_f32(c0[2] + c1[2]), w_lo, small_int_to_f32(c0[3] + c1[3]) * w_hi);
+            const float tsum = t == 0 ? ldsf(tb.tsum + b * 4) : 0.0f;
+            y0 = fmaf(f16_bits_to_f32(lds16(blkA)), fmaf(sA, tb.kappa, -tsum), y0);
+            y1 = fmaf(f16_bits_to_f32(lds16(blkB)), fmaf(sB, tb.kappa, -tsum), y1);
+        }
+    }
+    __device__ static float finish(float v, const StreamArgs&, const float*, uint32_t) { return v; }
+};
+
+// ── Sparse-ternary tile: packed 2-bit codes, 4 bytes per 16 columns (SparseTernaryMatrix::packed_2bit,
+// src/gguf.rs:5560-5583), 00 = 0, 01 = +1, 11 = -1: the low bit of a code is worth +x, the high bit -2x.
+// y = scale_row * S; integer accumulation over the whole group range.
+struct MmaSparseTernary {
+    static constexpr bool HAS_TSUM = false;
+    static constexpr int CODE = 2;
+    static constexpr uint32_t SPLIT_UNIT = 1;
+    __device__ static void tile(uint32_t rowA, uint32_t rowB, uint32_t g_lo, uint32_t g_hi, const MmaTable& tb, uint32_t lane,
+                                const StreamArgs& a, float& y0, float& y1) {
+        const uint32_t t = lane & 3u, d = lane >> 2;
+        const bool has_b = d < 4;
+        const float w_lo = t == 0 ? 2097152.0f : (t == 1 ? 128.0f : 0.0f), w_hi = t == 0 ? 16384.0f : (t == 1 ? 1.0f : 0.0f);
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        const uint32_t whole = a.row_bytes / 16;   // whole 16-byte groups in a row
+        uint32_t G = g_lo;
+        for (; G + 2 <= g_hi && G + 2 <= whole; G += 2) {
+            const uint32_t off = G * 16 + t * 4;
+            const uint32_t a0 = lds32(rowA + off), a1 = lds32(rowB + off), a2 = lds32(rowA + off + 16), a3 = lds32(rowB + off + 16);
+            const uint32_t rec = has_b ? tb.words + ((G * 4 + d) * 4 + t) * 16 : tb.zero;
+            const uint32_t rech = has_b ? rec + tb.half : tb.zero, nxt = has_b ? 256u : 0u;
+            const uint4 x03 = lds128(rec), x47 = lds128(rech), z03 = lds128(rec + nxt), z47 = lds128(rech + nxt);
+#define ALICE_SP(m, bx, bz, c) mma_u8s8_k32(c, a0 & (m), a1 & (m), a2 & (m), a3 & (m), (bx), (bz));
+            ALICE_SP(0x01010101u, x03.x, z03.x, c0) ALICE_SP(0x02020202u, x03.y, z03.y, c1)
+            ALICE_SP(0x04040404u, x03.z, z03.z, c0) ALICE_SP(0x08080808u, x03.w, z03.w, c1)
+            ALICE_SP(0x10101010u, x47.x, z47.x, c0) ALICE_SP(0x20202020u, x47.y, z47.y, c1)
+            ALICE_SP(0x40404040u, x47.z, z47.z, c0) ALICE_SP(0x80808080u, x47.w, z47.w, c1)
+#undef ALICE_SP
+        }
+        for (; G < g_hi; G++) {   // odd group count, or the last partly filled group of a row
+            const uint32_t off = G * 16 + t * 4;
+            const bool in = off + 4 <= a.row_bytes;   // rows are multiples of 4 bytes
+            const uint32_t a0 = in ? lds32(rowA + off) : 0u, a1 = in ? lds32(rowB + off) : 0u;
+            const uint32_t rec = has_b ? tb.words + ((G * 4 + d) * 4 + t) * 16 : tb.zero;
+            const uint4 x03 = lds128(rec), x47 = lds128(has_b ? rec + tb.half : tb.zero);
+#define ALICE_SP16(m, bx, c) mma_u8s8_k16(c, a0 & (m), a1 & (m), (bx));
+            ALICE_SP16(0x01010101u, x03.x, c0) ALICE_SP16(0x02020202u, x03.y, c1) ALICE_SP16(0x04040404u, x03.z, c0)
+            ALICE_SP16(0x08080808u, x03.w, c1) ALICE_SP16(0x10101010u, x47.x, c0) ALICE_SP16(0x20202020u, x47.y, c1)
+            ALICE_SP16(0x40404040u, x47.z, c0) ALICE_SP16(0x80808080u, x47.w, c1)
+#undef ALICE_SP16
+        }
+        y0 = tb.kappa * digits_to_f32(c0[0] + c1[0], c0[1] + c1[1], w_lo, w_hi);
+        y1 = tb.kappa * digits_to_f32(c0[2] + c1[2], c0[3] + c1[3], w_lo, w_hi);
+    }
+    __device__ static float finish(float v, const StreamArgs&, const float* aux, uint32_t row) { return __ldg(aux + row) * v; }
+};
+
 // Consumer side of one matvec in bit-plane tensor-core form (the NCW consumer warps). Same ring, barriers,
 // partial-sum hand-over and epilogue as stream_consume; a stage holds slots * 16 rows and warp `part` of a
 // row set covers groups [groups * part / P, groups * (part + 1) / P) of every row of its 16-row tile.
@@ -287,7 +407,8 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         xs.x = reinterpret_cast<const float*>(smem_raw + a.xn_off); xs.ll = nullptr; xs.cg = false;   // the normalised vector, in shared memory
     }
     const uint32_t y_tag = a.y_ll != nullptr ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
-    const uint32_t ngroups = (a.cols + 127) / 128;
+    constexpr uint32_t GE = mma_group_elems<M::CODE>();
+    const uint32_t ngroups = (a.cols + GE - 1) / GE;
     MmaTable tb;
     uint8_t* table = smem_raw + a.q8_off;
     float* tsum = reinterpret_cast<float*>(table + ((mma_table_bytes(ngroups) + 15u) & ~15u));
@@ -295,10 +416,13 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     tb.half = ngroups * 256u;
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
-    tb.kappa = xs.ll ? mma_build_table<true>(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u)
-                     : mma_build_table<false>(sm, xs, a.status, a.cols, table, tsum, M::HAS_TSUM ? ngroups : 0u);
+    const uint32_t tsum_blocks = M::HAS_TSUM ? a.cols / 128 : 0u;
+    tb.kappa = xs.ll ? mma_build_table<true, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks)
+                     : mma_build_table<false, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks);
     if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
-    const uint32_t g_lo = ngroups * part / P, g_hi = ngroups * (part + 1) / P;
+    // the warps of a row set split the groups in whole SPLIT_UNITs (a Q2_0 block is two groups)
+    const uint32_t nunits = (ngroups + M::SPLIT_UNIT - 1) / M::SPLIT_UNIT;
+    const uint32_t g_lo = nunits * part / P * M::SPLIT_UNIT, g_hi = min(ngroups, nunits * (part + 1) / P * M::SPLIT_UNIT);
     const uint32_t rowsel_a = lane >> 2, rowsel_b = (lane >> 2) + 8;
 
     const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);

@@ -22,7 +22,8 @@ from .synth_device import _ggml_tensor, _ternary_tensor
 CASES = [("Q4_K", synth.Q4_K, 32768, 4096), ("Q5_K", synth.Q5_K, 32768, 4096), ("Q6_K", synth.Q6_K, 32768, 4096),
          ("Q8_0", synth.Q8_0, 32768, 4096), ("Q1_0", synth.Q1_0, 102400, 5120), ("Q2_0", synth.Q2_0, 51200, 5120),
          ("Q1_0_gate", synth.Q1_0, 25600, 5120), ("Q1_0_down", synth.Q1_0, 5120, 25600),
-         ("TERNARY", synth.TERNARY, 28672, 8192), ("TERNARY_down", synth.TERNARY, 8192, 28672)]
+         ("TERNARY", synth.TERNARY, 28672, 8192), ("TERNARY_down", synth.TERNARY, 8192, 28672),
+         ("SPARSE_TERNARY", "sparse", 28672, 8192)]
 
 
 def peak_gbs():
@@ -47,11 +48,20 @@ def main(argv):
     for name, qt, rows, cols in CASES:
         if only and name not in only:
             continue
-        per = rows * ((cols + 31) // 32 * 8) if qt == synth.TERNARY else rows * synth.row_bytes(qt, cols)
+        if qt == "sparse":
+            per = rows * ((cols + 15) // 16 * 4)
+        else:
+            per = rows * ((cols + 31) // 32 * 8) if qt == synth.TERNARY else rows * synth.row_bytes(qt, cols)
         ncopy = max(2, int(300e6 // per) + 1)
         keep, ws = [], []
         for _ in range(ncopy):
-            if qt == synth.TERNARY:
+            if qt == "sparse":
+                # packed 2-bit codes 00 / 01 / 11 with P(0) = 0.5, P(+1) = P(-1) = 0.25; uploaded through the host API
+                r1 = torch.randint(0, 256, (per,), dtype=torch.uint8, device=dev, generator=gen) & 0x55
+                r2 = torch.randint(0, 256, (per,), dtype=torch.uint8, device=dev, generator=gen) & r1
+                sc = (torch.randn(rows, device=dev, generator=gen).abs() * 0.01).float()
+                ws.append(eng.upload_sparse_ternary((r1 | (r2 << 1)).cpu().numpy(), sc.cpu().numpy(), rows, cols))
+            elif qt == synth.TERNARY:
                 planes, scales = _ternary_tensor(gen, dev, rows, cols)
                 keep += [planes, scales]
                 ws.append(eng.ternary_from_device(planes.data_ptr(), scales.data_ptr(), rows, cols))
