@@ -54,10 +54,10 @@ uint32_t units_per_row(WeightFormat f, uint32_t cols) {
     }
 }
 
-template <class F, int KL, bool SW, bool PLAIN>
+template <class F, int KL, bool SW, bool PLAIN, bool PEER>
 int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     static bool attr_set = false;  // per template instance
-    auto kern = stream_gemv_kernel<F, KL, SW, PLAIN>;
+    auto kern = stream_gemv_kernel<F, KL, SW, PLAIN, PEER>;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
@@ -80,8 +80,10 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
 // The lean instance when the matvec uses none of the fused extras.
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    const bool plain = !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1 && !a.npeers && !a.wait_flag && !a.x_ll && !a.y_ll && !a.resid_ll;
-    return plain ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
+    const bool peer = a.npeers || a.wait_flag || a.x_ll || a.y_ll || a.resid_ll;
+    const bool plain = !peer && !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1;
+    if (peer) return launch_one_v<F, KL, SW, false, true>(a, grid, smem, cfg);
+    return plain ? launch_one_v<F, KL, SW, true, false>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false, false>(a, grid, smem, cfg);
 }
 
 template <class F>
@@ -211,10 +213,10 @@ int plan_mma_split(const GemvOp& op, const LaunchCfg& cfg, const StreamArgs& a, 
     return ALICE_E_SHAPE;
 }
 
-template <class M, bool SW, int CTAS>
+template <class M, bool SW, int CTAS, bool PEER>
 int launch_mma_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     static bool attr_set = false;  // per template instance
-    auto kern = stream_gemv_mma_kernel<M, SW, CTAS>;
+    auto kern = stream_gemv_mma_kernel<M, SW, CTAS, PEER>;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CTAS == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1)) != cudaSuccess)
             return ALICE_E_CUDA;
@@ -233,12 +235,19 @@ int launch_mma_one(const StreamArgs& a, uint32_t grid, size_t smem, const Launch
     return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
 }
 
+template <class M, bool PEER>
+int launch_mma_p(const StreamPlan& pl, const LaunchCfg& cfg) {
+    if (pl.swiglu) return pl.ctas_per_sm == 2 ? launch_mma_one<M, true, 2, PEER>(pl.args, pl.grid, pl.smem, cfg)
+                                              : launch_mma_one<M, true, 1, PEER>(pl.args, pl.grid, pl.smem, cfg);
+    return pl.ctas_per_sm == 2 ? launch_mma_one<M, false, 2, PEER>(pl.args, pl.grid, pl.smem, cfg)
+                               : launch_mma_one<M, false, 1, PEER>(pl.args, pl.grid, pl.smem, cfg);
+}
+// the instance with the tensor-parallel hand-over only when the matvec takes part in one
 template <class M>
 int launch_mma(const StreamPlan& pl, const LaunchCfg& cfg) {
-    if (pl.swiglu) return pl.ctas_per_sm == 2 ? launch_mma_one<M, true, 2>(pl.args, pl.grid, pl.smem, cfg)
-                                              : launch_mma_one<M, true, 1>(pl.args, pl.grid, pl.smem, cfg);
-    return pl.ctas_per_sm == 2 ? launch_mma_one<M, false, 2>(pl.args, pl.grid, pl.smem, cfg)
-                               : launch_mma_one<M, false, 1>(pl.args, pl.grid, pl.smem, cfg);
+    const StreamArgs& a = pl.args;
+    const bool peer = a.npeers || a.wait_flag || a.x_ll || a.y_ll || a.resid_ll;
+    return peer ? launch_mma_p<M, true>(pl, cfg) : launch_mma_p<M, false>(pl, cfg);
 }
 
 }  // namespace

@@ -388,7 +388,7 @@ struct MmaSparseTernary {
 // Consumer side of one matvec in bit-plane tensor-core form (the NCW consumer warps). Same ring, barriers,
 // partial-sum hand-over and epilogue as stream_consume; a stage holds slots * 16 rows and warp `part` of a
 // row set covers groups [groups * part / P, groups * (part + 1) / P) of every row of its 16-row tile.
-template <class M, bool SWIGLU>
+template <class M, bool SWIGLU, bool PEER>
 __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
     uint8_t* smem_raw = cx.smem_raw;
@@ -397,16 +397,17 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;   // rps == 16
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg || a.wait_flag != nullptr;
-    if (!stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
+    const bool cg = cx.acts_cg || (PEER && a.wait_flag != nullptr);
+    if (PEER && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
 
     const bool norm = a.norm_w != nullptr;
-    XSrc xs = xsrc_of(a, cg);
+    XSrc xs;
+    if (PEER) xs = xsrc_of(a, cg); else { xs.x = a.x; xs.ll = nullptr; xs.tag = 0; xs.cg = cg; }
     if (norm) {
         stream_prologue(sm, smem_raw, xs, a.status, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, false, a.q8k_roundtrip != 0);
         xs.x = reinterpret_cast<const float*>(smem_raw + a.xn_off); xs.ll = nullptr; xs.cg = false;   // the normalised vector, in shared memory
     }
-    const uint32_t y_tag = a.y_ll != nullptr ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
+    const uint32_t y_tag = (PEER && a.y_ll != nullptr) ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
     constexpr uint32_t GE = mma_group_elems<M::CODE>();
     const uint32_t ngroups = (a.cols + GE - 1) / GE;
     MmaTable tb;
@@ -417,7 +418,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
     const uint32_t tsum_blocks = M::HAS_TSUM ? a.cols / 128 : 0u;
-    tb.kappa = xs.ll ? mma_build_table<true, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks)
+    tb.kappa = (PEER && xs.ll) ? mma_build_table<true, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks)
                      : mma_build_table<false, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks);
     if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
     // the warps of a row set split the groups in whole SPLIT_UNITs (a Q2_0 block is two groups)
@@ -439,7 +440,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         float res = 0.0f;
         if (part == 0 && lane < nrow) {
-            if (a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
+            if (PEER && a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
             else if (a.resid != nullptr) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
         }
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
@@ -491,13 +492,13 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
                     float r = M::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * M::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr || a.resid_ll != nullptr) r = __fadd_rn(res, r);
-                    if (a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
+                    if (a.resid != nullptr || (PEER && a.resid_ll != nullptr)) r = __fadd_rn(res, r);
+                    if (PEER && a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
                         ll_store(a.y_ll + yi, r, y_tag);
                         for (uint32_t p = 0; p < a.npeers; p++) ll_store(a.peer_y_ll[p] + yi, r, y_tag);
                     } else {
                         a.y[yi] = r;
-                        for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                        if (PEER) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
                     }
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -517,12 +518,12 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
     }
-    if (a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
+    if (PEER && a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
     return true;
 }
 
 // One matvec per launch, bit-plane tensor-core form. CTAS: resident CTAs per SM the launch is planned for.
-template <class M, bool SWIGLU, int CTAS>
+template <class M, bool SWIGLU, int CTAS, bool PEER>
 __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
@@ -544,7 +545,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
         return;
     }
     pdl_wait();
-    stream_consume_mma<M, SWIGLU>(a, cx);
+    stream_consume_mma<M, SWIGLU, PEER>(a, cx);
 }
 
 }  // namespace alice

@@ -439,7 +439,9 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, uint8_t* sme
 // Returns false after an abort.
 // PLAIN: the matvec is known to use none of the fused extras (RMSNorm prologue, residual / argmax epilogue,
 // q/k/v segments), so their code is compiled out - the stand-alone matvec entry points run this leaner instance.
-template <class F, int KL, bool SWIGLU, bool SHARED_PROLOGUE = false, bool PLAIN = false>
+// PEER: the tensor-parallel hand-over (pushed rows, tagged vectors, arrival counters) is compiled in; a single-GPU
+// model runs the instance without it.
+template <class F, int KL, bool SWIGLU, bool SHARED_PROLOGUE = false, bool PLAIN = false, bool PEER = false>
 __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
     uint8_t* smem_raw = cx.smem_raw;
@@ -448,9 +450,9 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg || (!PLAIN && a.wait_flag != nullptr);
-    if (!PLAIN && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
-    const uint32_t y_tag = (!PLAIN && a.y_ll != nullptr) ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
+    const bool cg = cx.acts_cg || (PEER && a.wait_flag != nullptr);
+    if (PEER && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
+    const uint32_t y_tag = (PEER && a.y_ll != nullptr) ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
 
     // input prologue (shared by every format, one copy of the code per kernel): RMSNorm into shared
     // memory and / or Q8_K quantization into shared memory
@@ -461,11 +463,11 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const bool quant = F::USES_Q8K && a.q8.qs == nullptr;
     if (norm || quant) {
         XSrc xs;
-        if (PLAIN) { xs.x = a.x; xs.ll = nullptr; xs.tag = 0; xs.cg = cg; } else xs = xsrc_of(a, cg);
+        if (!PEER) { xs.x = a.x; xs.ll = nullptr; xs.tag = 0; xs.cg = cg; } else xs = xsrc_of(a, cg);
         if (SHARED_PROLOGUE)
             stream_prologue(sm, smem_raw, xs, a.status, PLAIN ? nullptr : a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
                             !PLAIN && !F::USES_Q8K && a.q8k_roundtrip != 0);
-        else if (!PLAIN && xs.ll)   // tagged input (tensor parallel): the shared out-of-line copy
+        else if (PEER && xs.ll)   // tagged input (tensor parallel): the shared out-of-line copy
             stream_prologue(sm, smem_raw, xs, a.status, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, quant,
                             !F::USES_Q8K && a.q8k_roundtrip != 0);
         else
@@ -513,7 +515,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         // the residual this lane will add in the epilogue: requested now, needed after the rows are done
         float res = 0.0f;
         if (part == 0 && lane < nrow) {
-            if (!PLAIN && a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
+            if (PEER && a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
             else if (resid != nullptr) res = ld_act(resid + a.seg_y[sg] + r0 + set0 + lane, cg);
         }
         if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
@@ -569,13 +571,13 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
                     float r = F::finish(v0, a, a.aux0, row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
-                    if (resid != nullptr || (!PLAIN && a.resid_ll != nullptr)) r = __fadd_rn(res, r);
-                    if (!PLAIN && a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
+                    if (resid != nullptr || (PEER && a.resid_ll != nullptr)) r = __fadd_rn(res, r);
+                    if (PEER && a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
                         ll_store(a.y_ll + yi, r, y_tag);
                         for (uint32_t p = 0; p < a.npeers; p++) ll_store(a.peer_y_ll[p] + yi, r, y_tag);
                     } else {
                         a.y[yi] = r;
-                        if (!PLAIN) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
+                        if (PEER) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
                     }
                     const uint32_t b = __float_as_uint(r);
                     const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -598,12 +600,12 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
         if (cx.prof && threadIdx.x == 0 && g - g0 < 8) cx.prof[8 + g - g0] = clock64();
     }
     if (cx.prof && threadIdx.x == 0) cx.prof[3] = clock64();
-    if (!PLAIN && a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
+    if (PEER && a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
     return true;
 }
 
 // One matvec per launch.
-template <class F, int KL, bool SWIGLU, bool PLAIN>
+template <class F, int KL, bool SWIGLU, bool PLAIN, bool PEER>
 __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
@@ -623,7 +625,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
         return;
     }
     pdl_wait();  // activations come from the previous kernel
-    stream_consume<F, KL, SWIGLU, false, PLAIN>(a, cx);
+    stream_consume<F, KL, SWIGLU, false, PLAIN, PEER>(a, cx);
 }
 
 }  // namespace alice

@@ -34,7 +34,7 @@ __global__ void embed_q8_0_kernel(const uint8_t* __restrict__ table, const int* 
 // for NeoX, freq = 1 / theta^(i_even / d), angle = pos * freq; a lane owns dims 4*lane .. 4*lane+3 of a
 // head vector (head_dim = 128, so a NeoX partner sits in lane ^ 16).
 template <int GROUP>
-__global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, float* __restrict__ kcache,
+__global__ void __launch_bounds__(256, GROUP <= 5 ? 2 : 1) attn_fused_kernel(const float* __restrict__ qkv, float* __restrict__ kcache,
                                                          float* __restrict__ vcache, const int* __restrict__ pos_ptr,
                                                          AttnShape s, const float* __restrict__ rope_tab, int neox, uint32_t nsplit,
                                                          float* __restrict__ part, unsigned int* __restrict__ tickets,
