@@ -192,13 +192,22 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak):
     torch.cuda.empty_cache()
     wb = info["weight_bytes_per_token"]
     bound_ms = wb / world / (peak * 1e9) * 1e3
-    return {"config": name, "tokens": tokens, "context": ctx, "tok_s": tokens / (ms * 1e-3), "ms_per_token": ms / tokens,
-            "weight_bytes_per_token": wb, "kv_bytes_per_token_at_context": info["kv_bytes_per_token"],
-            "weight_gbs": wb * tokens / (ms * 1e-3) / 1e9, "stream_bound_ms_per_token": bound_ms,
-            "x_of_stream_bound": (ms / tokens) / bound_ms, "first_tokens": [int(t) for t in toks[:4]],
-            "parallelism": "single GPU" if world == 1 else
-            f"tp{world}: rows of every projection sharded; rows pushed into the peers' vectors by the producing kernels (NVLink stores + arrival counters)",
-            **({"nccl_all_gather_ms_per_token": nccl_ms / tokens} if nccl_ms is not None else {})}
+    entry = {"config": name, "tokens": tokens, "context": ctx, "weight_bytes_per_token": wb,
+             "kv_bytes_per_token_at_context": info["kv_bytes_per_token"], "stream_bound_ms_per_token": bound_ms,
+             "first_tokens": [int(t) for t in toks[:4]]}
+    if world == 1:
+        entry["parallelism"] = "single GPU"
+    else:
+        # both exchange mechanisms were timed; the entry's headline is the faster one, both are listed
+        entry["parallelism"] = f"tp{world}: rows of every projection sharded"
+        entry["pushed_rows_ms_per_token"] = ms / tokens
+        entry["nccl_all_gather_ms_per_token"] = nccl_ms / tokens
+        entry["exchange"] = "rows pushed into the peers' vectors by the producing kernels (NVLink stores, tagged elements)" \
+            if ms <= nccl_ms else "NCCL all-gather issued by the library"
+        ms = min(ms, nccl_ms)
+    entry.update({"tok_s": tokens / (ms * 1e-3), "ms_per_token": ms / tokens, "weight_gbs": wb * tokens / (ms * 1e-3) / 1e9,
+                  "x_of_stream_bound": (ms / tokens) / bound_ms})
+    return entry
 
 
 def run_ours(args, rank, world, local_rank):
