@@ -168,7 +168,7 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
         a.nseg = op.nw;
         a.groups = 0;
         for (uint32_t i = 0; i < op.nw; i++) {
-            a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i];
+            a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i]; a.seg_aux[i] = op.w[i]->scales;
             a.seg_g0[i] = a.groups;
             a.groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
         }
@@ -304,7 +304,6 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     if (op.x_ll && !op.norm_w && w0.fmt == WF_Q8_0)
         return ALICE_E_UNSUPPORTED;   // the per-lane f32 formats read x directly; only the prologues understand tagged vectors
     a.wait_flag = op.wait_flag; a.wait_mult = op.wait_mult; a.epoch = op.epoch;
-    if (op.nw > 1 && w0.scales) return ALICE_E_UNSUPPORTED;  // per-row scales are not segmented
     a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
     if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
         return ALICE_OK;
@@ -348,7 +347,7 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.nseg = op.nw;
     a.groups = 0;
     for (uint32_t i = 0; i < op.nw; i++) {
-        a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i];
+        a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i]; a.seg_aux[i] = op.w[i]->scales;
         a.seg_g0[i] = a.groups;
         a.groups += (op.w[i]->rows + a.slots * rps - 1) / (a.slots * rps);
     }

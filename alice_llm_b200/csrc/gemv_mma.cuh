@@ -489,7 +489,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
                 if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
                 if (lane < nrow) {
                     const uint32_t row = r0 + set0 + lane;
-                    float r = M::finish(v0, a, a.aux0, row);
+                    float r = M::finish(v0, a, a.seg_aux[sg], row);
                     if (SWIGLU) r = silu_ref(r) * M::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
                     if (a.resid != nullptr || (PEER && a.resid_ll != nullptr)) r = __fadd_rn(res, r);

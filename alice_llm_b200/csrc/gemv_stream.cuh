@@ -61,6 +61,7 @@ struct StreamArgs {
     uint32_t seg_rows[3];
     uint32_t seg_g0[4];
     uint32_t seg_y[3];
+    const float* seg_aux[3];   // per-row scales of each segment's matrix (formats that have them), else null
     // Row-wise staging (bit-plane tensor-core kernels): instead of one contiguous copy per stage every row is
     // copied on its own, as npieces pieces of piece_len bytes taken at piece_off[p] inside the global row of
     // src_row_bytes bytes, to shared memory rows row_stride bytes apart. That allows a padded (bank-conflict
@@ -568,7 +569,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
                 if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
                 if (lane < nrow) {
                     const uint32_t row = r0 + set0 + lane;      // row inside its matrix
-                    float r = F::finish(v0, a, a.aux0, row);
+                    float r = F::finish(v0, a, PLAIN ? a.aux0 : a.seg_aux[sg], row);
                     if (SWIGLU) r = silu_ref(r) * F::finish(v1, a, a.aux1, row);
                     const uint32_t yi = a.seg_y[sg] + row;
                     if (resid != nullptr || (PEER && a.resid_ll != nullptr)) r = __fadd_rn(res, r);

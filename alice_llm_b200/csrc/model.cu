@@ -145,7 +145,7 @@ int enqueue_step(alice_model* m, bool greedy_feed) {
         const alice_model::Layer& L = m->layers[l];
         float* kc = m->kcache + (size_t)l * c.max_seq_len * lkv;
         float* vc = m->vcache + (size_t)l * c.max_seq_len * lkv;
-        if (L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt && !L.q.scales) {
+        if (L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt) {
             // attention norm + q, k, v projections in one launch (src/llama3.rs:14178-14217)
             GemvOp op;
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
