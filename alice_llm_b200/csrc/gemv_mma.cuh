@@ -1,11 +1,11 @@
-// Bit-plane tensor-core consumer for the 1- and 2-bit formats (Q1_0, ternary bit planes).
+// Bit-plane tensor-core consumer for the 1- and 2-bit formats (Q1_0, Q2_0, ternary bit planes, sparse-ternary codes).
 //
 // At one or two bits per weight the CUDA-core path spends an instruction per weight per lane and is
 // ALU-bound at a fraction of HBM speed. Here the raw weight bytes ARE the A operand of an int8
 // mma.sync: for bit position j = 0..7 the fragment A_j = bytes & (0x01 << j) (one LOP per four
 // weights, values 0 or 2^j) multiplies a B fragment that holds the activation of the element that
 // bit j of each byte stands for, pre-divided by 2^j. The f32 activations are turned once per CTA into
-// 28-bit fixed point (one power-of-two scale per vector) and split into four signed base-128 digits,
+// 26-bit fixed point (one power-of-two scale per vector) and split into four signed base-128 digits,
 // which are the first four of the eight B columns; the integer accumulators of the four digit
 // columns are recombined in f32. The fixed-point step costs at most 2^-20 of max|x| per element,
 // far below f32 summation error at these row lengths.

@@ -3,7 +3,7 @@
     python -m alice_llm_b200.format_rates [NAME ...]
 
 For each case several distinct copies of the matrix (together > 300 MB, far above the 126 MB L2) are cycled, so
-every launch streams its weights from HBM; CUDA events on the launching stream around 60 launches after 10 warm-up
+every launch streams its weights from HBM; CUDA events on the launching stream bracket 60 launches that follow 10 warm-up
 launches. Prints rows x cols, bytes per launch, microseconds per launch, GB/s and the fraction of the measured copy
 bandwidth (MEASURED_PEAKS.json next to the repository root when present, else 6650 GB/s)."""
 from __future__ import annotations
