@@ -94,22 +94,12 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
     const uint32_t q_dim = s.num_heads * s.head_dim, kv_dim = s.num_kv_heads * s.head_dim;
     const float inv_sqrt_d = __fdiv_rn(1.0f, sqrtf((float)s.head_dim));
 
-    const RopeCoef rc = rope_coef(rope_tab, lane, neox);
-    float4 q[GROUP];
-#pragma unroll
-    for (int g = 0; g < GROUP; g++)
-        q[g] = rope4(__ldcg(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim) + lane), lane, rc, neox);
-    if (prof && threadIdx.x == 0) prof[1] = clock64();
-    float m[GROUP], l[GROUP];
-    float4 acc[GROUP];
-#pragma unroll
-    for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
-
-    // KB positions per warp round: their 2*KB row loads are issued before the first is used, so a round
-    // costs one memory round trip instead of KB (positions are still folded in ascending order)
+    // KB positions per warp round: their 2*KB row loads are issued before the first is used, so a round costs one
+    // memory round trip instead of KB (positions are still folded in ascending order). The first round is requested
+    // before q and the rotation table are looked at: none of these loads depends on another.
     constexpr int KB = CONSUMER_BAR ? 2 : 4;   // inside the whole-step kernel registers are scarce
-    for (uint32_t tb = t0 + warp; tb < t1; tb += NW * KB) {
-        float4 k[KB], v[KB];
+    float4 k[KB], v[KB];
+    auto load_round = [&](uint32_t tb) {
 #pragma unroll
         for (int j = 0; j < KB; j++) {
             const uint32_t t = tb + j * NW;
@@ -119,6 +109,22 @@ __device__ __forceinline__ void attn_fused_body(const float* __restrict__ qkv, f
                 v[j] = __ldcg(reinterpret_cast<const float4*>(vcache + (size_t)t * kv_dim + kvh * s.head_dim) + lane);
             }
         }
+    };
+    float4 q[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; g++) q[g] = __ldcg(reinterpret_cast<const float4*>(qkv + (size_t)(kvh * GROUP + g) * s.head_dim) + lane);
+    if (t0 + warp < t1) load_round(t0 + warp);
+    const RopeCoef rc = rope_coef(rope_tab, lane, neox);
+#pragma unroll
+    for (int g = 0; g < GROUP; g++) q[g] = rope4(q[g], lane, rc, neox);
+    if (prof && threadIdx.x == 0) prof[1] = clock64();
+    float m[GROUP], l[GROUP];
+    float4 acc[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; g++) { m[g] = -INFINITY; l[g] = 0.0f; acc[g] = make_float4(0.f, 0.f, 0.f, 0.f); }
+
+    for (uint32_t tb = t0 + warp; tb < t1; tb += NW * KB) {
+        if (tb != t0 + warp) load_round(tb);
 #pragma unroll
         for (int j = 0; j < KB; j++) {
             const uint32_t t = tb + j * NW;
