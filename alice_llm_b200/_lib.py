@@ -30,6 +30,7 @@ SIGNATURES = {
     "alice_sync": (C.c_int32, [_vp]),
     "alice_engine_set_pdl": (C.c_int32, [_vp, C.c_int32]),
     "alice_engine_set_tuning": (C.c_int32, [_vp, C.c_int32, C.c_int32]),
+    "alice_engine_set_wait_limit": (C.c_int32, [_vp, C.c_uint64]),
     "alice_upload_weights": (C.c_int32, [_vp, _vp, C.c_size_t, C.c_uint32, C.c_uint32, C.c_uint32, _pp]),
     "alice_weights_from_device": (C.c_int32, [_vp, _vp, C.c_size_t, C.c_uint32, C.c_uint32, C.c_uint32, _pp]),
     "alice_upload_ternary": (C.c_int32, [_vp, _vp, _vp, _vp, C.c_uint32, C.c_uint32, _pp]),
@@ -51,6 +52,7 @@ SIGNATURES = {
     "alice_swiglu": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "alice_swiglu_preq": (C.c_int32, [_vp, _vp, _vp, _vp, _vp]),
     "alice_dequantize": (C.c_int32, [_vp, _vp, _vp]),
+    "alice_plan_query": (C.c_int32, [_vp, _vp, C.c_int32, C.c_int32, _vp, C.c_uint32]),
     "alice_model_create": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _pp]),
     "alice_model_destroy": (C.c_int32, [_vp]),
     "alice_model_forward": (C.c_int32, [_vp, C.c_uint32]),
@@ -62,7 +64,8 @@ SIGNATURES = {
     "alice_engine_tp_info": (C.c_int32, [_vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "alice_model_tp_export": (C.c_int32, [_vp, _vp, C.c_size_t]),
     "alice_model_tp_connect": (C.c_int32, [_vp, _vp, C.c_size_t]),
-    "alice_model_use_step_kernel": (C.c_int32, [_vp, C.c_int32]),
+    "alice_model_forward_batch": (C.c_int32, [_vp, _vp, C.c_uint32]),
+    "alice_model_forward_batch_read": (C.c_int32, [_vp, _vp, C.c_uint32, _vp]),
     "alice_model_read_logits": (C.c_int32, [_vp, _vp]),
     "alice_model_position": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),
     "alice_model_vocab_size": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "abi_internal.cuh"
+#include "gemv_plan.cuh"
 #include "tp.cuh"
 
 using namespace alice;
@@ -46,6 +47,17 @@ bool known_ggml(uint32_t t) { return ggml_block_bytes((WeightFormat)t) != 0; }
 LaunchCfg cfg_of(const alice_engine* e) { return alice_cfg_of(e); }
 
 }  // namespace
+
+void alice_engine_retain(alice_engine* e) { e->refs++; }
+void alice_engine_release(alice_engine* e) {
+    if (--e->refs == 0) delete e;
+}
+// Before a handle frees device memory the engine's queued work must be done - unless the engine is already gone
+// (its destroy synchronised the stream).
+static void quiesce(alice_engine* e) {
+    cudaSetDevice(e->device);
+    if (!e->dead) cudaStreamSynchronize(e->stream);
+}
 
 LaunchCfg alice_cfg_of(const alice_engine* e) {
     LaunchCfg c;
@@ -128,20 +140,31 @@ int32_t alice_engine_create(int32_t device, alice_engine** out) {
     e->own_stream = true;
     err = cudaMalloc(&e->status, sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(e->status, 0, sizeof(int));
-    if (err != cudaSuccess) { cudaStreamDestroy(e->stream); delete e; return cuda_fail(err, "status word"); }
+    if (err == cudaSuccess) err = cudaMalloc(&e->tickets, ALICE_ENGINE_TICKETS * sizeof(unsigned int));
+    if (err == cudaSuccess) err = cudaMemset(e->tickets, 0, ALICE_ENGINE_TICKETS * sizeof(unsigned int));
+    if (err != cudaSuccess) {
+        if (e->status) cudaFree(e->status);
+        cudaStreamDestroy(e->stream); delete e;
+        return cuda_fail(err, "status word");
+    }
     *out = e;
     return ALICE_OK;
 }
 
 int32_t alice_engine_destroy(alice_engine* e) {
-    if (!e) return ALICE_OK;
+    if (!e || e->dead) return ALICE_OK;
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     alice::tp_release(e);
     if (e->scratch) cudaFree(e->scratch);
+    if (e->shadow) cudaFree(e->shadow);
+    if (e->tickets) cudaFree(e->tickets);
     if (e->status) cudaFree(e->status);
     if (e->own_stream) cudaStreamDestroy(e->stream);
-    delete e;
+    e->scratch = e->shadow = nullptr; e->tickets = nullptr; e->status = nullptr; e->stream = nullptr;
+    e->shadow_of = nullptr;
+    e->dead = true;               // handles created on this engine may outlive it: they only free their own memory
+    alice_engine_release(e);
     return ALICE_OK;
 }
 
@@ -165,6 +188,12 @@ int32_t alice_engine_set_tuning(alice_engine* e, int32_t rps, int32_t stages) {
     return ALICE_OK;
 }
 
+int32_t alice_engine_set_wait_limit(alice_engine* e, uint64_t sm_cycles) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_engine_set_wait_limit: null engine");
+    e->wait_limit = (long long)std::min<uint64_t>(sm_cycles, (uint64_t)1 << 40);
+    return ALICE_OK;
+}
+
 int32_t alice_sync(alice_engine* e) {
     if (!e) return fail(ALICE_E_INVALID, "alice_sync: null engine");
     CU(cudaStreamSynchronize(e->stream));
@@ -172,7 +201,11 @@ int32_t alice_sync(alice_engine* e) {
     CU(cudaMemcpy(&st, e->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(e->status, 0, sizeof(int));
-        return fail(ALICE_E_KERNEL, "alice_sync: a kernel wait timed out (status 0x%x: low byte 2 = weights, 3 = partial sums, 4 = stage release, 5 = grid barrier; upper bits = op index)", st);
+        static const char* const what[] = {"?", "unspecified wait", "weights did not land in shared memory", "partial sums of a row", "stage release",
+                                           "grid barrier", "rows from a tensor-parallel peer"};
+        const int code = st & 0xff;
+        return fail(ALICE_E_KERNEL, "alice_sync: a kernel wait ran out of its cycle budget (status %d: %s); results of the queued work are void",
+                    st, code >= 1 && code <= 6 ? what[code] : what[0]);
     }
     return ALICE_OK;
 }
@@ -207,6 +240,7 @@ int32_t alice_upload_weights(alice_engine* e, const uint8_t* data, size_t nbytes
     if (err != cudaSuccess) { cudaFree(p); return cuda_fail(err, "alice_upload_weights copy"); }
     d.data = static_cast<const uint8_t*>(p);
     *out = new alice_weights{e, d, p, nullptr};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
@@ -221,6 +255,7 @@ int32_t alice_weights_from_device(alice_engine* e, const void* dptr, size_t nbyt
         return fail(ALICE_E_SHAPE, "alice_weights_from_device: byte size %zu must be a multiple of 16", nbytes);
     d.data = static_cast<const uint8_t*>(dptr);
     *out = new alice_weights{e, d, nullptr, nullptr};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
@@ -239,6 +274,7 @@ static int upload_rows_and_scales(alice_engine* e, const std::vector<uint8_t>& h
     d.data = static_cast<const uint8_t*>(p);
     d.scales = static_cast<const float*>(s);
     *out = new alice_weights{e, d, p, s};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
@@ -275,6 +311,7 @@ int32_t alice_ternary_from_device(alice_engine* e, const void* rows_dptr, const 
     d.data = static_cast<const uint8_t*>(rows_dptr);
     d.scales = scales_dptr;
     *out = new alice_weights{e, d, nullptr, nullptr};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
@@ -291,10 +328,10 @@ int32_t alice_upload_sparse_ternary(alice_engine* e, const uint8_t* packed, cons
 
 int32_t alice_weights_free(alice_weights* w) {
     if (!w) return ALICE_OK;
-    cudaSetDevice(w->e->device);
-    cudaStreamSynchronize(w->e->stream);
+    if (w->owned_data || w->owned_scales) quiesce(w->e);
     if (w->owned_data) cudaFree(w->owned_data);
     if (w->owned_scales) cudaFree(w->owned_scales);
+    alice_engine_release(w->e);
     delete w;
     return ALICE_OK;
 }
@@ -309,12 +346,14 @@ int32_t alice_buf_alloc_f32(alice_engine* e, size_t len, alice_buf** out) {
     cudaError_t err = cudaMemsetAsync(p, 0, std::max<size_t>(len, 1) * sizeof(float), e->stream);
     if (err != cudaSuccess) { cudaFree(p); return cuda_fail(err, "alice_buf_alloc_f32 memset"); }
     *out = new alice_buf{e, static_cast<float*>(p), len, true};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
 int32_t alice_buf_write_f32(alice_engine* e, alice_buf* b, const float* data, size_t len) {
     if (!e || !b || (!data && len)) return fail(ALICE_E_INVALID, "alice_buf_write_f32: null argument");
     if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_write_f32: %zu floats into a buffer of %zu", len, b->len);
+    if (e->shadow_of == b) e->shadow_of = nullptr;
     CU(cudaMemcpyAsync(b->p, data, len * sizeof(float), cudaMemcpyHostToDevice, e->stream));
     CU(cudaStreamSynchronize(e->stream));  // the host slice is only borrowed for the call
     return ALICE_OK;
@@ -340,16 +379,18 @@ int32_t alice_buf_from_device(alice_engine* e, void* dptr, size_t len, alice_buf
     if (!e || !dptr || !out) return fail(ALICE_E_INVALID, "alice_buf_from_device: null argument");
     if ((uintptr_t)dptr & 15) return fail(ALICE_E_INVALID, "alice_buf_from_device: pointer not 16-byte aligned");
     *out = new alice_buf{e, static_cast<float*>(dptr), len, false};
+    alice_engine_retain(e);
     return ALICE_OK;
 }
 
 int32_t alice_buf_free(alice_buf* b) {
     if (!b) return ALICE_OK;
+    if (b->e->shadow_of == b) b->e->shadow_of = nullptr;
     if (b->owned) {
-        cudaSetDevice(b->e->device);
-        cudaStreamSynchronize(b->e->stream);
+        quiesce(b->e);
         cudaFree(b->p);
     }
+    alice_engine_release(b->e);
     delete b;
     return ALICE_OK;
 }
@@ -364,6 +405,7 @@ int32_t alice_q8k_alloc(alice_engine* e, uint32_t cols, uint32_t batch, alice_q8
     auto* q = new alice_q8k{e, nullptr, cols, batch, cols / 256, Q8KLayout::make(cols / 256, batch)};
     cudaError_t err = cudaMalloc(&q->base, q->lay.total);
     if (err != cudaSuccess) { delete q; return cuda_fail(err, "alice_q8k_alloc"); }
+    alice_engine_retain(e);
     *out = q;
     return ALICE_OK;
 }
@@ -372,7 +414,7 @@ int32_t alice_quantize_q8k(alice_engine* e, const alice_buf* x, alice_q8k* q) {
     if (!e || !x || !q) return fail(ALICE_E_INVALID, "alice_quantize_q8k: null argument");
     if (x->len < (size_t)q->cols * q->batch)
         return fail(ALICE_E_SHAPE, "alice_quantize_q8k: input has %zu floats, need %zu", x->len, (size_t)q->cols * q->batch);
-    launch_quantize_q8k(x->p, q->cols, q->batch, q->base, e->stream);
+    launch_quantize_q8k(x->p, q->cols, q->batch, q->base, e->stream, e->pdl);
     CU(cudaGetLastError());
     return ALICE_OK;
 }
@@ -406,27 +448,34 @@ int32_t alice_q8k_upload(alice_engine* e, const float* d, const int8_t* qs, cons
 
 int32_t alice_q8k_free(alice_q8k* q) {
     if (!q) return ALICE_OK;
-    cudaSetDevice(q->e->device);
-    cudaStreamSynchronize(q->e->stream);
+    quiesce(q->e);
     cudaFree(q->base);
+    alice_engine_release(q->e);
     delete q;
     return ALICE_OK;
 }
 
 // ---- the hot path --------------------------------------------------------------------------
 
-// Shared body of matvec / swiglu on already prepared activations: one launch per batch vector.
-static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_q8k* q,
-                    const float* xf, float* y, uint32_t batch, const char* who) {
-    const LaunchCfg cfg = cfg_of(e);
-    for (uint32_t k = 0; k < batch; k++) {
-        Q8KView v;
-        if (q) v = view_of(q, k);
-        int rc = launch_stream_gemv(w0->d, w1 ? &w1->d : nullptr, q ? &v : nullptr,
-                                    xf ? xf + (size_t)k * w0->d.cols : nullptr, y + (size_t)k * w0->d.rows, cfg);
-        if (rc) return launch_rc(rc, who);
-    }
-    return ALICE_OK;
+Q8KView view_at(void* base, uint32_t nb, uint32_t batch) {
+    const Q8KLayout l = Q8KLayout::make(nb, batch);
+    auto* p = static_cast<uint8_t*>(base);
+    Q8KView v;
+    v.qs = reinterpret_cast<const int8_t*>(p + l.qs_off);
+    v.d = reinterpret_cast<const float*>(p + l.d_off);
+    v.bsums = reinterpret_cast<const int16_t*>(p + l.bsums_off);
+    v.nb = nb;
+    return v;
+}
+
+// One matvec / fused SwiGLU over `batch` prepared input vectors.
+static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const Q8KView* q8, const float* xf,
+                    float* y, uint32_t batch, const Publish* pub, const char* who) {
+    GemvOp op;
+    op.w[0] = &w0->d; op.up = w1 ? &w1->d : nullptr;
+    op.q8 = q8; op.x = xf; op.y = y; op.batch = batch; op.pub = pub;
+    op.wait_limit = e->wait_limit;
+    return launch_rc(launch_stream_gemv_op(op, cfg_of(e)), who);
 }
 
 static int check_pair(const alice_weights* g, const alice_weights* u, const char* who) {
@@ -435,6 +484,19 @@ static int check_pair(const alice_weights* g, const alice_weights* u, const char
     return ALICE_OK;
 }
 
+static int ensure_shadow(alice_engine* e, size_t bytes) {
+    if (bytes <= e->shadow_bytes) return ALICE_OK;
+    CU(cudaStreamSynchronize(e->stream));
+    if (e->shadow) CU(cudaFree(e->shadow));
+    e->shadow = nullptr; e->shadow_bytes = 0; e->shadow_of = nullptr;
+    CU(cudaMalloc(&e->shadow, bytes));
+    e->shadow_bytes = bytes;
+    return ALICE_OK;
+}
+
+// f32 input of a matvec. K-quant weights want it as Q8_K blocks (q4k_matvec = quantize_row_q8_k + q4k_matvec_preq,
+// src/gguf.rs:3600-3603): either the blocks the kernel that produced x left behind (the fused SwiGLU does that for its
+// output, which only ever feeds a down projection), or a small quantizer kernel into engine scratch, ahead of the matvec.
 static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_buf* x,
                          alice_buf* y, uint32_t batch, const char* who) {
     if (!e || !w0 || !x || !y) return fail(ALICE_E_INVALID, "%s: null argument", who);
@@ -444,9 +506,33 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
     if (x->len < (size_t)batch * d.cols) return fail(ALICE_E_SHAPE, "%s: input has %zu floats, need %zu", who, x->len, (size_t)batch * d.cols);
     if (y->len < (size_t)batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output has %zu floats, need %zu", who, y->len, (size_t)batch * d.rows);
     CU(cudaSetDevice(e->device));
-    // K-quant kernels quantize x to Q8_K in their prologue: q4k_matvec = quantize_row_q8_k +
-    // q4k_matvec_preq (src/gguf.rs:3600-3603) in one launch.
-    return run_gemv(e, w0, w1, nullptr, x->p, y->p, batch, who);
+    Q8KView v{};
+    const bool kq = format_uses_q8k(d.fmt);
+    if (kq) {
+        const uint32_t nb = d.cols / 256;
+        if (e->shadow_of == x && e->shadow_cols == d.cols && e->shadow_batch == batch) {
+            v = view_at(e->shadow, nb, batch);
+        } else {
+            int rc = ensure_scratch(e, Q8KLayout::make(nb, batch).total);
+            if (rc) return rc;
+            launch_quantize_q8k(x->p, d.cols, batch, e->scratch, e->stream, e->pdl);
+            CU(cudaGetLastError());
+            v = view_at(e->scratch, nb, batch);
+        }
+    }
+    if (e->shadow_of == y) e->shadow_of = nullptr;   // y is about to be rewritten
+    Publish pub{};
+    const bool leave_q8 = w1 && kq && y->owned && d.rows % 256 == 0 && d.rows / 256 <= ALICE_ENGINE_TICKETS && y->len == (size_t)batch * d.rows;
+    if (leave_q8) {
+        int rc = ensure_shadow(e, Q8KLayout::make(d.rows / 256, batch).total);
+        if (rc) return rc;
+        const Q8KView sv = view_at(e->shadow, d.rows / 256, batch);
+        pub.mode = PUB_BLOCKS; pub.n = d.rows; pub.batch = batch; pub.src = y->p; pub.tickets = e->tickets;
+        pub.dst.qs = const_cast<int8_t*>(sv.qs); pub.dst.d = const_cast<float*>(sv.d); pub.dst.bsums = const_cast<int16_t*>(sv.bsums);
+    }
+    int rc = run_gemv(e, w0, w1, kq ? &v : nullptr, kq ? nullptr : x->p, y->p, batch, leave_q8 ? &pub : nullptr, who);
+    if (!rc && leave_q8) { e->shadow_of = y; e->shadow_cols = d.rows; e->shadow_batch = batch; }
+    return rc;
 }
 
 static int preq_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_q8k* q,
@@ -458,13 +544,17 @@ static int preq_common(alice_engine* e, const alice_weights* w0, const alice_wei
     if (q->batch > 8) return fail(ALICE_E_SHAPE, "%s: batch %u outside 1..8", who, q->batch);
     if (y->len < (size_t)q->batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output too small", who);
     CU(cudaSetDevice(e->device));
-    if (format_uses_q8k(d.fmt)) return run_gemv(e, w0, w1, q, nullptr, y->p, q->batch, who);
+    if (e->shadow_of == y) e->shadow_of = nullptr;
+    if (format_uses_q8k(d.fmt)) {
+        const Q8KView v = view_of(q, 0);
+        return run_gemv(e, w0, w1, &v, nullptr, y->p, q->batch, nullptr, who);
+    }
     if (d.fmt == WF_Q1_0 || d.fmt == WF_Q2_0) {
         const size_t total = (size_t)q->batch * d.cols;
         int rc = ensure_scratch(e, total * sizeof(float));
         if (rc) return rc;
         launch_q8k_to_f32(view_of(q, 0), total, static_cast<float*>(e->scratch), e->stream);
-        return run_gemv(e, w0, w1, nullptr, static_cast<float*>(e->scratch), y->p, q->batch, who);
+        return run_gemv(e, w0, w1, nullptr, static_cast<float*>(e->scratch), y->p, q->batch, nullptr, who);
     }
     // quantized_matvec_preq panics for every other type (src/gguf.rs:4606)
     return fail(ALICE_E_UNSUPPORTED, "%s: pre-quantized input only for Q4_K/Q5_K/Q6_K/Q1_0/Q2_0", who);
@@ -490,10 +580,31 @@ int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alic
     return preq_common(e, gate, up, q, y, "alice_swiglu_preq");
 }
 
+int32_t alice_plan_query(alice_engine* e, const alice_weights* w, int32_t swiglu, int32_t preq, uint32_t* out, uint32_t n_out) {
+    if (!e || !w || !out || n_out < 10) return fail(ALICE_E_INVALID, "alice_plan_query: null argument or fewer than 10 outputs");
+    GemvOp op;
+    op.w[0] = &w->d;
+    if (swiglu) op.up = &w->d;
+    alignas(16) static float dummy[4];
+    Q8KView v{};
+    (void)preq;     // the input always reaches the kernel prepared; the plan does not depend on who prepared it
+    if (format_uses_q8k(w->d.fmt)) { v.qs = reinterpret_cast<const int8_t*>(dummy); v.nb = w->d.cols / 256; op.q8 = &v; }
+    else op.x = dummy;
+    op.y = dummy;   // planning never dereferences the vectors
+    StreamPlan pl;
+    const int rc = plan_stream_gemv(op, cfg_of(e), pl);
+    if (rc) return launch_rc(rc, "alice_plan_query");
+    const StreamArgs& a = pl.args;
+    out[0] = pl.grid; out[1] = a.P; out[2] = a.slots; out[3] = a.rps; out[4] = a.groups; out[5] = a.nstages;
+    out[6] = pl.kl; out[7] = pl.mma ? 1u : 0u; out[8] = pl.ksplit; out[9] = pl.ctas_per_sm;
+    return ALICE_OK;
+}
+
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out) {
     if (!e || !w || !out) return fail(ALICE_E_INVALID, "alice_dequantize: null argument");
     if (out->len < (size_t)w->d.rows * w->d.cols) return fail(ALICE_E_SHAPE, "alice_dequantize: output too small");
     CU(cudaSetDevice(e->device));
+    if (e->shadow_of == out) e->shadow_of = nullptr;
     return launch_rc(launch_dequantize(w->d, out->p, e->stream), "alice_dequantize");
 }
 
@@ -608,7 +719,8 @@ int32_t alice_matvec_preq_noalloc(alice_engine* e, const alice_weights* w, const
     const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 8);
     q8k_to_f32_noalloc_kernel<<<blocks, 256, 0, e->stream>>>(view_of(q, 0), (uint32_t)total);
     CU(cudaGetLastError());
-    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, who);
+    if (e->shadow_of == y) e->shadow_of = nullptr;
+    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, nullptr, who);
 }
 
 }  // extern "C"

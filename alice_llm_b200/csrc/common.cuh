@@ -109,50 +109,18 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p
 __device__ __forceinline__ void red_release_sys_add_u32(unsigned int* p, unsigned int v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// One thread. true when *flag has reached `expected` (wrap-safe), false after WAIT_CYCLE_LIMIT cycles or when
-// another wait of this kernel already failed; records KERR_WAIT_PEER then.
-__device__ __forceinline__ bool peer_wait(const unsigned int* flag, unsigned int expected, int* status, int code) {
+// One thread. true when *flag has reached `expected` (wrap-safe), false after `limit` SM cycles; records `code` in the
+// status word then (the first report is kept).
+__device__ __forceinline__ bool peer_wait(const unsigned int* flag, unsigned int expected, int* status, int code,
+                                          long long limit = WAIT_CYCLE_LIMIT) {
     const long long t0 = clock64();
     while ((int)(ld_acquire_sys_u32(flag) - expected) < 0) {
-        if (clock64() - t0 > WAIT_CYCLE_LIMIT) {
+        if (clock64() - t0 > limit) {
             atomicCAS(status, 0, code);
             return false;
         }
     }
     return true;
-}
-
-// Tagged vectors: an element is 8 bytes (f32 bits, tag) written with one store, so a reader that sees the tag
-// it expects also sees the value - no fence, no counter (the idea of NCCL's low-latency protocol). Used for the
-// vectors tensor-parallel ranks push into each other's memory.
-__device__ __forceinline__ void ll_store(uint2* p, float v, uint32_t tag) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-// value of one element, whatever its tag (for data this GPU wrote itself in an earlier kernel)
-__device__ __forceinline__ float ll_value(const uint2* p) {
-    uint32_t v, t;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v), "=r"(t) : "l"(p) : "memory");
-    return __uint_as_float(v);
-}
-__device__ __forceinline__ uint4 ll_load_pair(const uint2* p) {   // two consecutive elements, 16-byte aligned
-    uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-// Four consecutive elements (p 32-byte aligned) once all four carry `tag`. On expiry of the cycle budget the caller's
-// abort flag and the status word are set and whatever is there is returned (the kernel finishes, its result is void).
-__device__ __forceinline__ float4 ll_load4(const uint2* p, uint32_t tag, volatile int* abort_flag, int* status) {
-    uint4 a = ll_load_pair(p), b = ll_load_pair(p + 2);
-    if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
-        const long long t0 = clock64();
-        for (;;) {
-            a = ll_load_pair(p); b = ll_load_pair(p + 2);
-            if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
-            if (*abort_flag) break;
-            if (clock64() - t0 > WAIT_CYCLE_LIMIT) { *abort_flag = 1; atomicCAS(status, 0, KERR_WAIT_PEER); break; }
-        }
-    }
-    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
 }
 
 // ── arithmetic helpers ──────────────────────────────────────────────────────

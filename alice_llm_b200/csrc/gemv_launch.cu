@@ -54,16 +54,17 @@ uint32_t units_per_row(WeightFormat f, uint32_t cols) {
     }
 }
 
-template <class F, int KL, bool SW, bool PLAIN, bool PEER>
-int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    static bool attr_set = false;  // per template instance
-    auto kern = stream_gemv_kernel<F, KL, SW, PLAIN, PEER>;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
-            return ALICE_E_CUDA;
-        attr_set = true;
-    }
+// cudaFuncSetAttribute is per device: remember, per kernel instance, the devices it has been raised on.
+bool attr_needed(bool (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+}
+
+template <class K>
+int launch_kernel(K kern, const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(grid);
     lc.blockDim = dim3(STREAM_THREADS);
@@ -77,13 +78,21 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
     return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
 }
 
-// The lean instance when the matvec uses none of the fused extras.
+template <class F, int KL, bool SW, bool PEER>
+int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
+    static bool attr_done[64] = {};  // per template instance
+    auto kern = stream_gemv_kernel<F, KL, SW, PEER>;
+    if (attr_needed(attr_done) &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
+        return ALICE_E_CUDA;
+    return launch_kernel(kern, a, grid, smem, cfg);
+}
+
+// The instance with the tensor-parallel row push only when the matvec takes part in one.
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    const bool peer = a.npeers || a.wait_flag || a.x_ll || a.y_ll || a.resid_ll;
-    const bool plain = !peer && !a.norm_w && !a.resid && !a.argmax_key && a.nseg == 1;
-    if (peer) return launch_one_v<F, KL, SW, false, true>(a, grid, smem, cfg);
-    return plain ? launch_one_v<F, KL, SW, true, false>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false, false>(a, grid, smem, cfg);
+    const bool peer = a.npeers || a.pub.npeers;
+    return peer ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
 }
 
 template <class F>
@@ -98,12 +107,6 @@ int launch_fmt(const StreamArgs& a, uint32_t kl, bool sw, uint32_t grid, size_t 
     return launch_one<F, 4, false>(a, grid, smem, cfg);
 }
 
-// ALICE_NO_MMA=1 keeps the 1- and 2-bit formats on the per-lane kernels (A/B timing, debugging).
-bool mma_disabled() {
-    static const bool off = [] { const char* v = getenv("ALICE_NO_MMA"); return v && *v && *v != '0'; }();
-    return off;
-}
-
 // Geometry of the bit-plane tensor-core kernel: 16-row tiles, `slots` tiles per stage, the P = NCW / slots
 // warps of a tile split the row's 16-byte groups. Shared memory: header | ring | normalised input (optional) |
 // activation digit table (512 B per 128 columns) | per-block sums. Two CTAs per SM when that fits.
@@ -115,7 +118,7 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     const bool sw = op.up != nullptr;
     const uint32_t nmat = sw ? 2 : 1;
     const bool whole = col_lo == 0 && col_n == w0.cols;
-    if (!whole && (op.norm_w || sw || col_lo % 128 || col_n % 128)) return ALICE_E_SHAPE;
+    if (!whole && (sw || col_lo % 128 || col_n % 128)) return ALICE_E_SHAPE;
     // the sub-row as the consumer sees it, and where its pieces sit inside the global row
     uint32_t sub_row, npieces, piece_len, piece_off[2] = {0, 0};
     if (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0) {
@@ -138,15 +141,13 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     a.src_row_bytes = w0.row_bytes; a.npieces = npieces; a.piece_len = piece_len;
     a.piece_off[0] = piece_off[0]; a.piece_off[1] = piece_off[1];
     if (a.x) a.x += col_lo;
-    if (a.x_ll) a.x_ll += col_lo;
     const uint32_t ge = (w0.fmt == WF_Q2_0 || w0.fmt == WF_SPARSE_TERNARY) ? 64u : 128u;   // elements per 16 weight bytes
     const uint32_t ngroups = (col_n + ge - 1) / ge;
     const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
-    const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
     for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
         const uint32_t budget = per_sm == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1;
-        if (HDR_BYTES + table_bytes + xn_bytes >= budget) continue;
-        const uint32_t avail = budget - HDR_BYTES - table_bytes - xn_bytes;
+        if (HDR_BYTES + table_bytes >= budget) continue;
+        const uint32_t avail = budget - HDR_BYTES - table_bytes;
         const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
         uint32_t best = 0;
         for (uint32_t slots = NCW; slots >= 1; slots /= 2) {
@@ -173,11 +174,10 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
             a.groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
         }
         a.seg_g0[op.nw] = a.groups;
-        a.q8_off = HDR_BYTES + nst * stage;
-        a.xn_off = a.q8_off + table_bytes;
+        a.tab_off = HDR_BYTES + nst * stage;
         pl.grid = std::min(ctas, a.groups);
-        pl.smem = HDR_BYTES + nst * (size_t)stage + table_bytes + xn_bytes;
-        pl.kl = 1; pl.swiglu = sw; pl.stage = stage; pl.q8_bytes = table_bytes; pl.xn_bytes = xn_bytes;
+        pl.smem = HDR_BYTES + nst * (size_t)stage + table_bytes;
+        pl.kl = 1; pl.swiglu = sw; pl.stage = stage;
         pl.mma = true; pl.ctas_per_sm = per_sm;
         pl.args = a;
         return ALICE_OK;
@@ -198,7 +198,7 @@ int plan_mma_split(const GemvOp& op, const LaunchCfg& cfg, const StreamArgs& a, 
     const WeightDesc& w0 = *op.w[0];
     if (plan_mma(op, cfg, a, 0, w0.cols, pl) == ALICE_OK) { pl.ksplit = 1; return ALICE_OK; }
     const uint32_t unit = (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0) ? 1024u : 128u;
-    if (w0.cols % unit || op.norm_w || op.up) return ALICE_E_SHAPE;
+    if (w0.cols % unit || op.up) return ALICE_E_SHAPE;
     for (uint32_t ks = 2; ks <= 4; ks++) {
         bool ok = true;
         for (uint32_t c = 0; c < ks && ok; c++) {
@@ -215,24 +215,12 @@ int plan_mma_split(const GemvOp& op, const LaunchCfg& cfg, const StreamArgs& a, 
 
 template <class M, bool SW, int CTAS, bool PEER>
 int launch_mma_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    static bool attr_set = false;  // per template instance
+    static bool attr_done[64] = {};  // per template instance
     auto kern = stream_gemv_mma_kernel<M, SW, CTAS, PEER>;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CTAS == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1)) != cudaSuccess)
-            return ALICE_E_CUDA;
-        attr_set = true;
-    }
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(grid);
-    lc.blockDim = dim3(STREAM_THREADS);
-    lc.dynamicSmemBytes = smem;
-    lc.stream = cfg.stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = at;
-    lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
+    if (attr_needed(attr_done) &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CTAS == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1)) != cudaSuccess)
+        return ALICE_E_CUDA;
+    return launch_kernel(kern, a, grid, smem, cfg);
 }
 
 template <class M, bool PEER>
@@ -246,20 +234,13 @@ int launch_mma_p(const StreamPlan& pl, const LaunchCfg& cfg) {
 template <class M>
 int launch_mma(const StreamPlan& pl, const LaunchCfg& cfg) {
     const StreamArgs& a = pl.args;
-    const bool peer = a.npeers || a.wait_flag || a.x_ll || a.y_ll || a.resid_ll;
+    const bool peer = a.npeers || a.pub.npeers;
     return peer ? launch_mma_p<M, true>(pl, cfg) : launch_mma_p<M, false>(pl, cfg);
 }
 
 }  // namespace
 
-int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
-                       const LaunchCfg& cfg) {
-    GemvOp op;
-    op.w[0] = &w0; op.up = w1; op.q8 = q8; op.x = x; op.y = y;
-    return launch_stream_gemv_op(op, cfg);
-}
-
-int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* lim, StreamPlan& pl) {
+int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     if (op.nw < 1 || op.nw > 3 || !op.w[0] || !op.y) return ALICE_E_INVALID;
     const WeightDesc& w0 = *op.w[0];
     const WeightDesc* w1 = op.up;
@@ -278,15 +259,16 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
         if (wi->fmt != w0.fmt || wi->cols != w0.cols || wi->row_bytes != w0.row_bytes) return ALICE_E_SHAPE;
         total_rows += wi->rows;
     }
+    // the input arrives prepared: Q8_K blocks for the K-quants, the f32 vector for everything else
     if (format_uses_q8k(w0.fmt)) {
-        // K-quants take either pre-quantized Q8_K blocks or the f32 vector (quantized in the prologue)
-        if (q8 ? q8->nb * 256u != w0.cols : (x == nullptr && !op.x_ll)) return q8 ? ALICE_E_SHAPE : ALICE_E_INVALID;
-    } else if (!x && !op.x_ll) {
+        if (!q8 || !q8->qs) return ALICE_E_INVALID;
+        if (q8->nb * 256u != w0.cols) return ALICE_E_SHAPE;
+    } else if (!x) {
         return ALICE_E_INVALID;
     }
-    if (op.norm_w && ((!x && !op.x_ll) || q8)) return ALICE_E_INVALID;  // the norm needs the f32 vector
     const uint32_t units = units_per_row(w0.fmt, w0.cols);
     if (units == 0) return ALICE_E_UNSUPPORTED;
+    if (op.pub && op.pub->mode == PUB_BLOCKS && (op.nw != 1 || total_rows % QK_K != 0 || op.pub->n != total_rows)) return ALICE_E_SHAPE;
 
     StreamArgs a = {};
     a.w0 = w0.data; a.w1 = sw ? w1->data : nullptr;
@@ -294,18 +276,15 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     a.x = x; a.aux0 = w0.scales; a.aux1 = sw ? w1->scales : nullptr;
     a.y = op.y; a.status = cfg.status;
     a.rows = total_rows; a.cols = w0.cols; a.row_bytes = w0.row_bytes; a.units = units;
-    a.norm_w = op.norm_w; a.norm_eps = op.norm_eps; a.resid = op.resid; a.argmax_key = op.argmax_key;
-    a.q8k_roundtrip = (op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
-    if (op.push) {
-        a.npeers = std::min<uint32_t>(op.push->npeers, MAX_PEERS);
-        for (uint32_t p = 0; p < a.npeers; p++) { a.peer_y[p] = op.push->y[p]; a.peer_flag[p] = op.push->flag[p]; a.peer_y_ll[p] = op.push->y_ll[p]; }
-    }
-    a.x_ll = op.x_ll; a.x_seq = op.x_seq; a.x_n = op.x_n; a.y_ll = op.y_ll; a.y_seq = op.y_seq; a.y_n = op.y_n; a.resid_ll = op.resid_ll;
-    if (op.x_ll && !op.norm_w && w0.fmt == WF_Q8_0)
-        return ALICE_E_UNSUPPORTED;   // the per-lane f32 formats read x directly; only the prologues understand tagged vectors
-    a.wait_flag = op.wait_flag; a.wait_mult = op.wait_mult; a.epoch = op.epoch;
-    a.row_stride = a.row_bytes;   // contiguous staging unless the bit-plane planner says otherwise
-    if (!lim && (w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 && !mma_disabled() && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
+    a.batch = 1; a.y_stride = op.y_stride ? op.y_stride : total_rows;
+    a.resid = op.resid; a.argmax_key = op.argmax_key;
+    a.npeers = std::min<uint32_t>(op.npeers, MAX_PEERS);
+    for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p] = op.peer_y[p];
+    a.wait_limit = op.wait_limit;
+    if (op.pub) a.pub = *op.pub;
+    a.row_stride = a.row_bytes;   // contiguous staging unless the tensor-core planner says otherwise
+    if ((w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 &&
+        ((uintptr_t)x & 15) == 0 && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
         return ALICE_OK;
 
     // warps per row: just enough lanes for one unit each, at most all eight
@@ -318,16 +297,10 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
 
     const uint32_t nmat = sw ? 2 : 1;
     const uint32_t per_sm = kl <= 2 ? 2 : 1;
-    // in-kernel Q8_K area: qs[cols] + bsums[nb][16] i16 + d[nb] f32; normalised input: f32[cols]
-    const uint32_t q8_bytes = (format_uses_q8k(w0.fmt) && !q8) ? ((w0.cols / 256u) * 292u + 127u) & ~127u : 0u;
-    const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
     const uint32_t full_budget = kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1;
-    if (!lim && HDR_BYTES + q8_bytes + xn_bytes + 4096 > full_budget) return ALICE_E_SHAPE;
     uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
-    if (lim) nst = lim->nstages;
-    // bytes the ring may use: the CTA's budget, or nstages * the fixed stage stride of a multi-matvec kernel
-    const uint32_t budget = lim ? lim->nstages * lim->stage_stride : full_budget - HDR_BYTES - q8_bytes - xn_bytes;
-    const uint32_t ctas = lim ? lim->ctas : (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
+    const uint32_t budget = full_budget - HDR_BYTES;
+    const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
     // rows per warp set per stage: as many as the ring allows (per-stage costs are amortised over
     // them) while every CTA still gets about two stages of work. Measured on 4096 x 4096 Q4_K in a chain of
     // dependent launches: 7.1 us with four stages per CTA, 5.8 with two, 5.1 with one; the whole decode step
@@ -343,7 +316,7 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
         stage = cap * nmat;
         if (stage * nst <= budget) break;
         if (rps > 1) { rps--; continue; }
-        if (nst > 2 && !lim) { nst--; continue; }
+        if (nst > 2) { nst--; continue; }
         return ALICE_E_SHAPE;  // a single row does not fit twice into shared memory
     }
     a.rps = rps; a.cap = cap; a.nstages = nst;
@@ -356,54 +329,38 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, const PlanLimits* l
     }
     a.seg_g0[op.nw] = a.groups;
     pl.grid = std::min(ctas, a.groups);
-    a.q8_off = HDR_BYTES + nst * stage;
-    a.xn_off = a.q8_off + q8_bytes;
-    pl.smem = HDR_BYTES + (size_t)nst * stage + q8_bytes + xn_bytes;
-    pl.kl = kl; pl.swiglu = sw; pl.stage = stage; pl.q8_bytes = q8_bytes; pl.xn_bytes = xn_bytes;
+    a.tab_off = HDR_BYTES + nst * stage;
+    pl.smem = HDR_BYTES + (size_t)nst * stage;
+    pl.kl = kl; pl.swiglu = sw; pl.stage = stage;
+    pl.mma = false; pl.ksplit = 1; pl.ctas_per_sm = per_sm;
     pl.args = a;
     return ALICE_OK;
 }
 
-// CTAs of the launch that stores the final rows of `op` (the last column chunk when the matvec runs as several):
-// the number of arrivals a tensor-parallel peer must expect from this GPU for this matvec.
-int stream_gemv_final_grid(const GemvOp& op, const LaunchCfg& cfg, uint32_t* grid) {
-    StreamPlan pl;
-    int rc = plan_stream_gemv(op, cfg, nullptr, pl);
-    if (rc) return rc;
-    if (pl.mma && pl.ksplit > 1) {
-        uint32_t lo, n;
-        mma_chunk(*op.w[0], pl.ksplit, pl.ksplit - 1, lo, n);
-        StreamArgs base = pl.args;
-        base.x = op.x; base.x_ll = op.x_ll; base.cols = op.w[0]->cols; base.row_bytes = op.w[0]->row_bytes;
-        StreamPlan pc;
-        rc = plan_mma(op, cfg, base, lo, n, pc);
-        if (rc) return rc;
-        pl.grid = pc.grid;
-    }
-    *grid = pl.grid;
-    return ALICE_OK;
-}
+namespace {
 
-int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
+// One launch (or, for a bit-plane matvec whose rows are too wide for shared memory, one launch per column chunk)
+// for ONE input vector.
+int launch_single(const GemvOp& op, const LaunchCfg& cfg) {
     StreamPlan pl;
-    const int prc = plan_stream_gemv(op, cfg, nullptr, pl);
+    const int prc = plan_stream_gemv(op, cfg, pl);
     if (prc) return prc;
     const StreamArgs& a = pl.args;
     const WeightDesc& w0 = *op.w[0];
     if (pl.mma) {
         // one launch per column chunk; a later chunk adds to what the earlier ones left in y, and only the last one
-        // sees the final values (greedy-argmax epilogue)
+        // sees the final values (argmax epilogue, rows pushed to peers, hand-over to the next op)
         for (uint32_t c = 0; c < pl.ksplit; c++) {
             StreamPlan pc = pl;
             if (pl.ksplit > 1) {
                 uint32_t lo, n;
                 mma_chunk(w0, pl.ksplit, c, lo, n);
                 StreamArgs base = pl.args;
-                base.x = op.x; base.x_ll = op.x_ll; base.cols = w0.cols; base.row_bytes = w0.row_bytes;
+                base.x = op.x; base.cols = w0.cols; base.row_bytes = w0.row_bytes;
                 const int rc = plan_mma(op, cfg, base, lo, n, pc);
                 if (rc) return rc;
-                if (c > 0) { pc.args.resid = op.y; pc.args.resid_ll = nullptr; }   // partial sums travel through the plain y
-                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.y_ll = nullptr; }   // only the last chunk holds final rows
+                if (c > 0) pc.args.resid = op.y;
+                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.pub = Publish{}; }
             }
             const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : w0.fmt == WF_Q2_0 ? launch_mma<MmaQ2_0>(pc, cfg)
                          : w0.fmt == WF_TERNARY ? launch_mma<MmaTernary>(pc, cfg) : launch_mma<MmaSparseTernary>(pc, cfg);
@@ -414,7 +371,6 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     const uint32_t kl = pl.kl, grid = pl.grid;
     const bool sw = pl.swiglu;
     const size_t smem = pl.smem;
-
     switch (w0.fmt) {
         case WF_Q4_K: return launch_fmt<FmtQ4K>(a, kl, sw, grid, smem, cfg);
         case WF_Q5_K: return launch_fmt<FmtQ5K>(a, kl, sw, grid, smem, cfg);
@@ -426,6 +382,76 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         case WF_SPARSE_TERNARY: return launch_fmt<FmtSparseTernary>(a, kl, sw, grid, smem, cfg);
         default: return ALICE_E_UNSUPPORTED;
     }
+}
+
+}  // namespace
+
+int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
+    if (op.batch == 0 || op.batch > (uint32_t)MAX_BATCH) return ALICE_E_SHAPE;
+    if (op.batch == 1) return launch_single(op, cfg);
+    if (op.argmax_key) return ALICE_E_INVALID;
+    // Formats without a batch kernel: one launch per input vector (the weights stream once per vector). A whole-vector
+    // hand-over rides on the last launch (every earlier one has completed by then: same stream), a per-block one on
+    // each launch for its own vector.
+    if (!op.w[0]) return ALICE_E_INVALID;
+    uint32_t total_rows = 0;
+    for (uint32_t i = 0; i < op.nw && i < 3; i++) if (op.w[i]) total_rows += op.w[i]->rows;
+    const uint32_t ys = op.y_stride ? op.y_stride : total_rows;
+    const uint32_t cols = op.w[0]->cols, nb = cols / QK_K;
+    for (uint32_t k = 0; k < op.batch; k++) {
+        GemvOp o = op;
+        o.batch = 1;
+        Q8KView v;
+        if (op.q8) { v = *op.q8; v.qs += (size_t)k * cols; v.d += (size_t)k * nb; v.bsums += (size_t)k * nb * 16; o.q8 = &v; }
+        if (op.x) o.x = op.x + (size_t)k * cols;
+        o.y = op.y + (size_t)k * ys;
+        if (op.resid) o.resid = op.resid + (size_t)k * ys;
+        for (uint32_t p = 0; p < op.npeers && p < MAX_PEERS; p++) o.peer_y[p] = op.peer_y[p] + (size_t)k * ys;
+        Publish pk;
+        if (op.pub && op.pub->mode == PUB_VECTOR) {
+            o.pub = k + 1 == op.batch ? op.pub : nullptr;
+        } else if (op.pub && op.pub->mode == PUB_BLOCKS) {
+            pk = *op.pub;
+            pk.batch = 1;
+            pk.src += (size_t)k * pk.n;
+            const uint32_t pnb = pk.n / QK_K;
+            if (pk.dst.qs) { pk.dst.qs += (size_t)k * pk.n; pk.dst.d += (size_t)k * pnb; pk.dst.bsums += (size_t)k * pnb * 16; }
+            if (pk.dst.xn) pk.dst.xn += (size_t)k * pk.n;
+            o.pub = &pk;
+        }
+        const int rc = launch_single(o, cfg);
+        if (rc) return rc;
+    }
+    return ALICE_OK;
+}
+
+// ---- stand-alone hand-over kernel ----------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) publish_vector_kernel(const Publish p, int* status) {
+    __shared__ double red[8];
+    __shared__ int ok;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (p.npeers) {
+        if (threadIdx.x == 0) ok = publish_peer_gate(p, status) ? 1 : 0;
+        __syncthreads();
+        if (!ok) return;
+    }
+    if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<8, 1>(p, red);
+}
+}  // namespace
+
+cudaError_t launch_publish_vector(const Publish& p, int* status, cudaStream_t stream, bool pdl) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(1);
+    lc.blockDim = dim3(256);
+    lc.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, publish_vector_kernel, p, status);
 }
 
 }  // namespace alice

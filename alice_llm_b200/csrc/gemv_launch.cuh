@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "publish.cuh"
 #include "q8k.cuh"
 
 namespace alice {
@@ -37,50 +38,34 @@ struct LaunchCfg {
     int force_stages; // 0 = automatic
 };
 
-// One launch of the streaming matvec with its optional fused stages.
-// Where a matvec's rows also go on the other GPUs of a tensor-parallel group (see StreamArgs::peer_y).
-struct PeerPush {
-    uint32_t npeers = 0;
-    float* y[7] = {};             // the same vector as GemvOp::y in each peer's memory
-    unsigned int* flag[7] = {};   // arrival counter of this matvec on each peer
-    uint2* y_ll[7] = {};          // tagged form (GemvOp::y_ll) of the vector in each peer's memory
-};
-
+// One streaming matvec with its optional fused stages. The input is always in prepared form: Q8_K blocks for the
+// K-quant formats (q8), the f32 vector for the others (x); see csrc/publish.cuh.
 struct GemvOp {
     const WeightDesc* w[3] = {nullptr, nullptr, nullptr};  // 1..3 matrices of one format and width sharing the input
     uint32_t nw = 1;
     uint32_t y_off[3] = {0, 0, 0};                         // output offset (floats) of each matrix inside y
     const WeightDesc* up = nullptr;                        // fused SwiGLU: w[0] = gate, up = up (nw must be 1)
-    const Q8KView* q8 = nullptr;                           // pre-quantized input (K-quants), else x
-    const float* x = nullptr;                              // f32 input vector
-    const float* norm_w = nullptr;                         // fused RMSNorm of x with these weights
-    float norm_eps = 0.0f;
-    bool q8k_roundtrip = false;                            // with norm_w, f32-activation formats: see StreamArgs
-    const float* resid = nullptr;                          // y = resid + result
-    unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs
+    const Q8KView* q8 = nullptr;                           // K-quants: input vector 0 as Q8_K; vector k follows at qs + k*cols, d + k*nb, bsums + k*nb*16
+    const float* x = nullptr;                              // other formats: input, x[k*cols + c]
+    uint32_t batch = 1;                                    // input vectors
+    uint32_t y_stride = 0;                                 // floats between the outputs of consecutive vectors (0: the rows of this op)
+    const float* resid = nullptr;                          // y = resid + result (same layout as y)
+    unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs (batch 1 only)
     float* y = nullptr;
-    const PeerPush* push = nullptr;                        // tensor parallel: also store every row result on the peers
-    const unsigned int* wait_flag = nullptr;               // tensor parallel: x is complete when *wait_flag >= (*epoch + 1) * wait_mult
-    uint32_t wait_mult = 0;
-    const unsigned int* epoch = nullptr;
-    // tagged vectors (StreamArgs::x_ll ...): input, output (with push->y_ll on the peers) and residual
-    const uint2* x_ll = nullptr;
-    uint32_t x_seq = 0, x_n = 0;
-    uint2* y_ll = nullptr;
-    uint32_t y_seq = 0, y_n = 0;
-    const uint2* resid_ll = nullptr;
+    const Publish* pub = nullptr;                          // what to leave prepared for the next op
+    uint32_t npeers = 0;                                   // tensor parallel: also store every row result on these GPUs
+    float* peer_y[MAX_PEERS] = {};
+    long long wait_limit = 0;                              // SM cycles a wait inside the kernel may take (0 = about a second)
 };
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
-// CTAs of the launch that stores the final rows of `op` (what a tensor-parallel peer counts as arrivals).
-int stream_gemv_final_grid(const GemvOp& op, const LaunchCfg& cfg, uint32_t* grid);
 
-// y[r] = W[r,:] . x  (or silu(W0 x) * (W1 x) when w1 != null). K-quant formats read `q8`,
-// the others read the f32 vector `x`. Returns 0 or a negative ALICE_E_* code.
-int launch_stream_gemv(const WeightDesc& w0, const WeightDesc* w1, const Q8KView* q8, const float* x, float* y,
-                       const LaunchCfg& cfg);
 
 // out[r*cols + c] = dequantized weight, bit-exact with the reference dequantizers.
 int launch_dequantize(const WeightDesc& w, float* out, cudaStream_t stream);
+
+// The stand-alone form of csrc/publish.cuh: one CTA prepares `p.batch` vectors (optional rms_norm, then Q8_K and / or
+// f32) - used where no producing kernel can do it (the embedding, NCCL-gathered vectors).
+cudaError_t launch_publish_vector(const Publish& p, int* status, cudaStream_t stream, bool pdl);
 
 // out[i] = d[i/256] * q[i] for i < total (the Q8_K -> f32 step of quantized_matvec_preq for
 // Q1_0/Q2_0, src/gguf.rs:4593-4605); total = batch * cols.

@@ -73,8 +73,8 @@ __device__ __forceinline__ void mma_store_digits(uint8_t* w, int f) {
     w[0] = (uint8_t)f; w[64] = (uint8_t)d1; w[128] = (uint8_t)d2; w[192] = (uint8_t)d3;
 }
 
-template <bool LL, int CODE>
-static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc xs, int* status, uint32_t cols, uint8_t* table,
+template <int CODE>
+static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float* x, uint32_t cols, uint8_t* table,
                                                      float* tsum, uint32_t tsum_blocks) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t nvec = cols / 4;
@@ -90,7 +90,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
 #pragma unroll
         for (int k = 0; k < TB_V; k++) {
             const uint32_t i = base + k * NCW * 32 + tid;
-            v[k] = i < nvec ? x_load4<LL>(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[k] = i < nvec ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int k = 0; k < TB_V; k++)
@@ -118,7 +118,7 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const XSrc 
 #pragma unroll
             for (int k = 0; k < TB_V; k++) {
                 const uint32_t i = base + k * NCW * 32 + tid;
-                v[k] = i < nvec ? x_load4<LL>(xs, i, sm, status) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[k] = i < nvec ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -397,30 +397,18 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;   // rps == 16
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const bool cg = cx.acts_cg || (PEER && a.wait_flag != nullptr);
-    if (PEER && !stream_wait_input(a, sm)) return false;   // rows other GPUs push into x
 
-    const bool norm = a.norm_w != nullptr;
-    XSrc xs;
-    if (PEER) xs = xsrc_of(a, cg); else { xs.x = a.x; xs.ll = nullptr; xs.tag = 0; xs.cg = cg; }
-    if (norm) {
-        stream_prologue(sm, smem_raw, xs, a.status, a.norm_w, a.norm_eps, a.cols, a.xn_off, a.q8_off, false, a.q8k_roundtrip != 0);
-        xs.x = reinterpret_cast<const float*>(smem_raw + a.xn_off); xs.ll = nullptr; xs.cg = false;   // the normalised vector, in shared memory
-    }
-    const uint32_t y_tag = (PEER && a.y_ll != nullptr) ? ld_acquire_sys_u32(a.epoch) * a.y_n + a.y_seq + 1u : 0u;
     constexpr uint32_t GE = mma_group_elems<M::CODE>();
     const uint32_t ngroups = (a.cols + GE - 1) / GE;
     MmaTable tb;
-    uint8_t* table = smem_raw + a.q8_off;
+    uint8_t* table = smem_raw + a.tab_off;
     float* tsum = reinterpret_cast<float*>(table + ((mma_table_bytes(ngroups) + 15u) & ~15u));
     tb.words = smem_u32(table);
     tb.half = ngroups * 256u;
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
     const uint32_t tsum_blocks = M::HAS_TSUM ? a.cols / 128 : 0u;
-    tb.kappa = (PEER && xs.ll) ? mma_build_table<true, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks)
-                     : mma_build_table<false, M::CODE>(sm, xs, a.status, a.cols, table, tsum, tsum_blocks);
-    if (cx.prof && threadIdx.x == 0) cx.prof[1] = clock64();
+    tb.kappa = mma_build_table<M::CODE>(sm, a.x, a.cols, table, tsum, tsum_blocks);
     // the warps of a row set split the groups in whole SPLIT_UNITs (a Q2_0 block is two groups)
     const uint32_t nunits = (ngroups + M::SPLIT_UNIT - 1) / M::SPLIT_UNIT;
     const uint32_t g_lo = nunits * part / P * M::SPLIT_UNIT, g_hi = min(ngroups, nunits * (part + 1) / P * M::SPLIT_UNIT);
@@ -439,12 +427,8 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
         const uint32_t set0 = slot * rps;
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
         float res = 0.0f;
-        if (part == 0 && lane < nrow) {
-            if (PEER && a.resid_ll != nullptr) res = ll_value(a.resid_ll + a.seg_y[sg] + r0 + set0 + lane);
-            else if (a.resid != nullptr) res = ld_act(a.resid + a.seg_y[sg] + r0 + set0 + lane, cg);
-        }
-        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL + (cx.op << 8))) return false;
-        if (cx.prof && threadIdx.x == 0 && g == g0) cx.prof[2] = clock64();
+        if (a.resid != nullptr && part == 0 && lane < nrow) res = __ldcg(a.resid + a.seg_y[sg] + r0 + set0 + lane);
+        if (!wait_or_abort(smem_u32(&sm->full[s]), ph, abort_flag, a.status, KERR_WAIT_FULL, cx.limit)) return false;
         const uint32_t sb = cx.ring + s * cx.stage_stride + pad + set0 * a.row_stride;
         if (nrow > 0) {
             // rows past nrow of a short last tile read whatever the stage holds; their results are never used
@@ -474,7 +458,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
             if (part != 0) {
                 if (lane == 0) mbar_arrive_n(smem_u32(&sm->red[s][slot]), RED_COUNT / (P - 1));
             } else {
-                if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status, KERR_WAIT_PARTIALS + (cx.op << 8))) return false;
+                if (P > 1 && !wait_or_abort(smem_u32(&sm->red[s][slot]), ph, abort_flag, a.status, KERR_WAIT_PARTIALS, cx.limit)) return false;
                 unsigned long long key = 0ull;
                 float v0 = 0.0f, v1 = 0.0f;
                 if (lane < nrow) {
@@ -491,34 +475,15 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
                     const uint32_t row = r0 + set0 + lane;
                     float r = M::finish(v0, a, a.seg_aux[sg], row);
                     if (SWIGLU) r = silu_ref(r) * M::finish(v1, a, a.aux1, row);
-                    const uint32_t yi = a.seg_y[sg] + row;
-                    if (a.resid != nullptr || (PEER && a.resid_ll != nullptr)) r = __fadd_rn(res, r);
-                    if (PEER && a.y_ll != nullptr) {   // tagged vector: this GPU's copy and the peers'
-                        ll_store(a.y_ll + yi, r, y_tag);
-                        for (uint32_t p = 0; p < a.npeers; p++) ll_store(a.peer_y_ll[p] + yi, r, y_tag);
-                    } else {
-                        a.y[yi] = r;
-                        if (PEER) for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p][yi] = r;
-                    }
-                    const uint32_t b = __float_as_uint(r);
-                    const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-                    if (r == r) key = ((unsigned long long)ordered << 32) | (0xFFFFFFFFu - yi);
+                    key = stream_store_row<PEER>(a, r, res, a.resid != nullptr, a.seg_y[sg] + row);
                 }
-                if (a.argmax_key != nullptr) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
-                        key = other > key ? other : key;
-                    }
-                    if (lane == 0) atomicMax(a.argmax_key, key);
-                }
+                if (a.argmax_key != nullptr) stream_argmax(a.argmax_key, key, lane);
                 continue;   // this warp has already released the stage
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->empty[s]));
     }
-    if (PEER && a.y_ll == nullptr) stream_signal_peers(a, sm, part == 0);
     return true;
 }
 
@@ -530,7 +495,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
     constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
     StreamCtx cx;
     cx.sm = sm; cx.smem_raw = smem_raw; cx.ring = smem_u32(smem_raw) + HDR;
-    cx.stage_stride = a.cap * (SWIGLU ? 2u : 1u); cx.nstages = a.nstages; cx.cc = 0; cx.op = 0; cx.acts_cg = false;
+    cx.stage_stride = a.cap * (SWIGLU ? 2u : 1u); cx.nstages = a.nstages; cx.cc = 0;
+    cx.limit = a.wait_limit > 0 ? a.wait_limit : WAIT_CYCLE_LIMIT;
     if (threadIdx.x == 0) stream_init_ring(sm, a.nstages);
     __syncthreads();
     pdl_launch_dependents();
@@ -546,6 +512,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
     }
     pdl_wait();
     stream_consume_mma<M, SWIGLU, PEER>(a, cx);
+    if (a.pub.mode != PUB_NONE) stream_publish<PEER>(a, sm);
 }
 
 }  // namespace alice

@@ -2,6 +2,7 @@
 // include/alice_cuda.h): the GpuModel of ALICE-LLM src/gpu.rs:2348 with the arithmetic of the CPU
 // forward (src/llama3.rs:13632-13687, 14167-14613).
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -10,7 +11,6 @@
 #include "abi_internal.cuh"
 #include "attn_body.cuh"
 #include "glue.cuh"
-#include "step_kernel.cuh"
 #include "tp.cuh"
 
 using namespace alice;
@@ -26,16 +26,17 @@ struct alice_model {
     std::vector<Layer> layers;
     WeightDesc emb{}, out{};
     float* out_norm = nullptr;
-    // activations
+    // activations, each for up to MAX_BATCH tokens: [k][dim]
     float *hidden = nullptr, *qkv = nullptr, *attn_out = nullptr, *ffn_h = nullptr, *logits = nullptr;
     float *kcache = nullptr, *vcache = nullptr;  // [layer][max_seq][kv_dim]
     float* attn_part = nullptr;
-    float* rope_tab = nullptr;   // (sin, cos) per rotation pair at the current position, rewritten every step
-    // Q8_K copy of the attention output, written by the attention kernel for K-quant output projections (single GPU)
-    uint8_t* attn_q8 = nullptr;
-    Q8KLayout attn_q8_lay{};
-    bool attn_q8_ok = false;
-    unsigned int* attn_tickets = nullptr;
+    float* rope_freq = nullptr;  // 1 / theta^(2j / head_dim), j < 64, computed on the host (libm powf, as the CPU path)
+    float* rope_tab = nullptr;   // [k][(sin, cos) per rotation pair] at the current positions, rewritten every step
+    // Prepared forms of the vectors the matvecs read (csrc/publish.cuh), written once by the kernel that produced the
+    // vector: Q8_K blocks for K-quant consumers, f32 (normalised) for the others
+    uint8_t *hid_q8 = nullptr, *attn_q8 = nullptr, *ffn_q8 = nullptr;
+    float* hid_xn = nullptr;
+    unsigned int *tk_vec = nullptr, *tk_blocks = nullptr, *tk_attn = nullptr, *attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
     // tensor parallel (engine's group): every projection holds rows [r*R/n, (r+1)*R/n); l* are the local sizes
@@ -45,25 +46,17 @@ struct alice_model {
     // so one IPC handle maps all of it into the peers. peer_base[p] = that region of the p-th other rank.
     uint8_t* xchg = nullptr;
     size_t xchg_bytes = 0;
-    unsigned int* flags = nullptr;      // arrival counters, one per op that has an exchanged output (4 per layer + head + keys)
+    unsigned int* flags = nullptr;      // arrival counters, one per op with an exchanged output (4 per layer + head)
     unsigned int* epoch = nullptr;      // decode steps completed
-    uint2 *hidden_ll = nullptr, *attn_ll = nullptr, *ffn_ll = nullptr;   // tagged forms of the per-layer vectors (peer mode)
     bool peer_mode = false;             // peers connected: rows are pushed by the kernels, no collective calls
     uint32_t npeers = 0;
     uint32_t peer_rank[7] = {};
     uint8_t* peer_base[7] = {};
-    // device-side state: position, current token, tokens chosen per position
+    // device-side state: position, current tokens, tokens chosen per position
     int *d_pos = nullptr, *d_token = nullptr, *d_trace = nullptr;
     uint32_t pos = 0;  // host mirror of *d_pos
     cudaGraphExec_t graph_greedy = nullptr;
     bool graph_tried = false;
-    // whole-step kernel (csrc/step_kernel.cu): op table on the device, its launch geometry
-    bool use_step_kernel = false, step_ready = false, step_tried = false;
-    StepOp* d_ops = nullptr;
-    uint32_t step_nops = 0, step_grid = 0, step_stride = 0, step_aux_off = 0;
-    size_t step_smem = 0;
-    std::vector<uint32_t> step_types;   // StepOpType per op (host copy, for the debug profile)
-    unsigned int* d_barrier = nullptr;
     std::vector<void*> owned;
 };
 
@@ -92,7 +85,8 @@ int upload_norm(alice_model* m, float** dst, const float* host, size_t n) {
     return ALICE_OK;
 }
 
-int gemv(alice_model* m, const GemvOp& op, const char* what) {
+int gemv(alice_model* m, GemvOp& op, const char* what) {
+    op.wait_limit = m->e->wait_limit;
     const int rc = launch_stream_gemv_op(op, alice_cfg_of(m->e));
     if (rc == ALICE_OK) return rc;
     return alice_fail(rc, "alice_model: %s matvec failed (%d): %s", what, rc, cudaGetErrorString(cudaGetLastError()));
@@ -103,280 +97,224 @@ int gemv(alice_model* m, const GemvOp& op, const char* what) {
 // projections see the vector rounded to the Q8_K grid.
 bool preq_roundtrip(const WeightDesc& w) { return w.fmt == WF_Q1_0 || w.fmt == WF_Q2_0; }
 
-// In-place all-gather of a row-sharded activation vector (no-op for a single GPU).
-int gather(alice_model* m, float* base, uint32_t floats_per_rank) {
-    return tp_all_gather(m->e, base, (size_t)floats_per_rank * sizeof(float));
+Q8KView q8_view(uint8_t* base, uint32_t n) {
+    const Q8KLayout l = Q8KLayout::make(n / 256, MAX_BATCH);
+    Q8KView v;
+    v.qs = reinterpret_cast<const int8_t*>(base + l.qs_off);
+    v.d = reinterpret_cast<const float*>(base + l.d_off);
+    v.bsums = reinterpret_cast<const int16_t*>(base + l.bsums_off);
+    v.nb = n / 256;
+    return v;
 }
 
-// Queues one decode step on the engine's stream. The token is read from *d_token.
-// With a tensor-parallel group every matvec computes this rank's rows into its slice of the full vector
-// and an all-gather completes it on every rank; attention runs on the rank's own KV heads (its q, k, v
-// rows), so only its output needs gathering (it is the input of the output projection).
-int enqueue_step(alice_model* m, bool greedy_feed) {
+// Which prepared forms of a vector its consumers need.
+struct Need { bool q8 = false, xn = false, roundtrip = false; };
+void need_of(Need& nd, const WeightDesc& w, bool via_preq) {
+    if (format_uses_q8k(w.fmt)) nd.q8 = true;
+    else { nd.xn = true; if (via_preq && preq_roundtrip(w)) nd.roundtrip = true; }
+}
+void fill_dst(PublishDst& d, const Need& nd, uint8_t* q8_base, float* xn, uint32_t n) {
+    d = PublishDst{};
+    if (nd.q8) {
+        const Q8KView v = q8_view(q8_base, n);
+        d.qs = const_cast<int8_t*>(v.qs); d.d = const_cast<float*>(v.d); d.bsums = const_cast<int16_t*>(v.bsums);
+    }
+    if (nd.xn) { d.xn = xn; d.roundtrip = nd.roundtrip ? 1u : 0u; }
+}
+
+// Queues one decode step for `batch` consecutive tokens (read from d_token[0 .. batch)) on the engine's stream.
+// With a tensor-parallel group every matvec computes this rank's rows into its slice of the full vector; the slices
+// reach the other ranks either by an NCCL all-gather after the kernel, or (peer mode) by the kernel itself storing its
+// rows into every peer's copy, with one flag per vector that the kernel's last CTA raises on the peers and waits for
+// here before it prepares the vector for the next op. Attention runs on the rank's own KV heads (its q, k, v rows), so
+// only its output needs exchanging (it is the input of the output projection).
+int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     const alice_model_config& c = m->cfg;
     cudaStream_t st = m->e->stream;
     const bool pdl = m->e->pdl;
-    const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r, L_n = c.num_layers;
-    const AttnShape shape{c.num_heads / m->tp_n, c.num_kv_heads / m->tp_n, c.head_dim};
-    const bool peer = m->peer_mode;
-    // Peer mode. The per-layer vectors (hidden, attention output, SwiGLU output) travel as tagged vectors: the kernel
-    // that produces rows stores (value, tag) into this GPU's copy and every peer's, the kernel that consumes the vector
-    // polls for the tag of the version it wants - no fence, no counter. hidden is rewritten 2 L + 1 times per step
-    // (embedding, then o and down of every layer), the other two L times. The logits and the argmax keys (once per
-    // step) use plain stores + an arrival counter instead.
-    // Why nobody overwrites a version that is still being read: a peer's next write into vector V is the epilogue of a
-    // matvec whose input needs rows this GPU produces only AFTER all its CTAs have read V (hidden -> peers' down needs
-    // this GPU's complete SwiGLU slice, whose CTAs read hidden in their prologue; attention output -> peers' next
-    // attention needs this GPU's o / SwiGLU / down rows; SwiGLU output -> peers' next SwiGLU needs this GPU's down rows).
-    const uint32_t hid_n = 2 * L_n + 1;
+    const uint32_t lq = m->lq, lkv = m->lkv, r = m->tp_r, L_n = c.num_layers, n = m->tp_n;
+    const uint32_t H = c.hidden_dim, F = c.intermediate_dim, q_dim = c.num_heads * c.head_dim, V = c.vocab_size;
+    const AttnShape shape{c.num_heads / n, c.num_kv_heads / n, c.head_dim};
+    const bool peer = m->peer_mode, nccl = n > 1 && !peer;
+    if (n > 1 && batch > 1) return alice_fail(ALICE_E_UNSUPPORTED, "alice_model: batches of tokens are single-GPU only");
     auto on_peer = [&](uint32_t p, const void* local) { return m->peer_base[p] + (reinterpret_cast<const uint8_t*>(local) - m->xchg); };
-    auto push_ll = [&](GemvOp& op, PeerPush& pp, uint2* vec, uint32_t seq, uint32_t n) {
-        pp.npeers = m->npeers;
-        for (uint32_t p = 0; p < m->npeers; p++) pp.y_ll[p] = reinterpret_cast<uint2*>(on_peer(p, vec));
-        op.push = &pp; op.y_ll = vec; op.y_seq = seq; op.y_n = n; op.epoch = m->epoch;
-    };
-    auto read_ll = [&](GemvOp& op, const uint2* vec, uint32_t seq, uint32_t n) { op.x_ll = vec; op.x_seq = seq; op.x_n = n; op.epoch = m->epoch; };
-    const uint32_t f_logits = 4 * L_n, f_keys = f_logits + 1;
     int rc;
-    EmbedTag et;
-    if (peer) { et.hidden_ll = m->hidden_ll; et.epoch = m->epoch; et.tag_n = hid_n; }
-    MCU(launch_embed_q8_0(m->emb.data, m->d_token, c.hidden_dim, c.vocab_size, m->hidden, m->d_pos, c.rope_theta, m->rope_tab, et, st, pdl));
+
+    // A whole-vector hand-over: what `consumers` need of vector `src` (length len), after rms_norm with norm_w (or none).
+    // Single GPU and peer mode: returned as the producing kernel's Publish. NCCL mode: the producing kernel publishes
+    // nothing; after the all-gather a one-CTA kernel prepares the vector.
+    auto vector_pub = [&](Publish& p, const float* src, uint32_t len, const float* norm_w, const Need& nd, uint8_t* q8_base, float* xn,
+                          uint32_t flag_idx) {
+        p = Publish{};
+        p.mode = PUB_VECTOR; p.n = len; p.batch = batch; p.src = src; p.tickets = m->tk_vec; p.norm_w = norm_w; p.eps = c.eps;
+        fill_dst(p.dst, nd, q8_base, xn, len);
+        p.wait_limit = m->e->wait_limit;
+        if (peer) {
+            p.npeers = m->npeers; p.wait_flag = m->flags + flag_idx; p.epoch = m->epoch;
+            for (uint32_t q = 0; q < m->npeers; q++) p.peer_flag[q] = reinterpret_cast<unsigned int*>(on_peer(q, m->flags + flag_idx));
+        }
+    };
+    // after the kernel: NCCL gather + stand-alone preparation
+    auto gather_then_publish = [&](float* vec, uint32_t floats_per_rank, Publish& p) -> int {
+        if (!nccl) return ALICE_OK;
+        int g = tp_all_gather(m->e, vec, (size_t)floats_per_rank * sizeof(float));
+        if (g) return g;
+        if (p.dst.qs || p.dst.xn) MCU(launch_publish_vector(p, m->e->status, st, pdl));
+        return ALICE_OK;
+    };
+    auto push_rows = [&](GemvOp& op, float* vec) {
+        if (!peer) return;
+        op.npeers = m->npeers;
+        for (uint32_t q = 0; q < m->npeers; q++) op.peer_y[q] = reinterpret_cast<float*>(on_peer(q, vec));
+    };
+    // input of a matvec over `w`: the prepared form of the vector
+    auto set_input = [&](GemvOp& op, const WeightDesc& w, uint8_t* q8_base, Q8KView& view, const float* xf, uint32_t len) {
+        if (format_uses_q8k(w.fmt)) { view = q8_view(q8_base, len); op.q8 = &view; } else op.x = xf;
+        op.batch = batch;
+    };
+
+    // embedding + rotation table + hidden prepared for layer 0
+    Need nd0;
+    {
+        const alice_model::Layer& L = m->layers[0];
+        need_of(nd0, L.q, true); need_of(nd0, L.k, true); need_of(nd0, L.v, true);
+    }
+    EmbedArgs ea{};
+    ea.table = m->emb.data; ea.tokens = m->d_token; ea.cols = H; ea.vocab = V; ea.batch = batch; ea.hidden = m->hidden;
+    ea.pos = m->d_pos; ea.rope_freq = m->rope_freq; ea.rope_tab = m->rope_tab; ea.status = m->e->status;
+    {
+        Publish p;
+        vector_pub(p, m->hidden, H, m->layers[0].attn_norm, nd0, m->hid_q8, m->hid_xn, 0);
+        p.npeers = 0;     // every rank computes the whole embedding row itself
+        ea.pub = p;
+    }
+    MCU(launch_embed_q8_0(ea, st, pdl));
+
     for (uint32_t l = 0; l < L_n; l++) {
         const alice_model::Layer& L = m->layers[l];
         float* kc = m->kcache + (size_t)l * c.max_seq_len * lkv;
         float* vc = m->vcache + (size_t)l * c.max_seq_len * lkv;
+        const uint32_t qkv_stride = lq + 2 * lkv;
+        // attention norm (already applied: hid_q8 / hid_xn) + q, k, v projections (src/llama3.rs:14178-14217)
         if (L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt) {
-            // attention norm + q, k, v projections in one launch (src/llama3.rs:14178-14217)
-            GemvOp op;
+            GemvOp op; Q8KView view;
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
-            op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps; op.y = m->qkv;
-            op.q8k_roundtrip = preq_roundtrip(L.q);
-            if (peer) read_ll(op, m->hidden_ll, 2 * l, hid_n);
+            set_input(op, L.q, m->hid_q8, view, m->hid_xn, H);
+            op.y = m->qkv; op.y_stride = qkv_stride;
             if ((rc = gemv(m, op, "qkv"))) return rc;
-        } else {   // mixed formats (e.g. V kept at higher precision): one launch each, same norm prologue
+        } else {   // mixed formats (e.g. V kept at higher precision): one launch each
             const WeightDesc* ws[3] = {&L.q, &L.k, &L.v};
             const uint32_t offs[3] = {0, lq, lq + lkv};
             for (int i = 0; i < 3; i++) {
-                GemvOp op;
-                op.w[0] = ws[i]; op.x = m->hidden; op.norm_w = L.attn_norm; op.norm_eps = c.eps;
-                op.q8k_roundtrip = preq_roundtrip(*ws[i]);
-                op.y = m->qkv + offs[i];
-                if (peer) read_ll(op, m->hidden_ll, 2 * l, hid_n);
+                GemvOp op; Q8KView view;
+                op.w[0] = ws[i];
+                set_input(op, *ws[i], m->hid_q8, view, m->hid_xn, H);
+                op.y = m->qkv + offs[i]; op.y_stride = qkv_stride;
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
         }
         // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
-        AttnPeers ap;
+        Need nd_o; need_of(nd_o, L.o, false);
+        const uint32_t group = shape.num_heads / shape.num_kv_heads;
+        AttnArgs aa{};
+        aa.qkv = m->qkv; aa.kcache = kc; aa.vcache = vc; aa.pos = m->d_pos; aa.shape = shape; aa.rope_tab = m->rope_tab;
+        aa.neox = (int)c.neox_rope; aa.nsplit = m->nsplit; aa.part = m->attn_part; aa.tickets = m->attn_tickets;
+        aa.attn_out = m->attn_out + (size_t)r * lq; aa.out_stride = q_dim; aa.status = m->e->status;
+        Publish attn_pub{};
+        const bool per_head_q8 = nd_o.q8 && n == 1 && group % 2 == 0;
+        if (per_head_q8) {
+            const Q8KView v = q8_view(m->attn_q8, q_dim);
+            aa.q8.qs = const_cast<int8_t*>(v.qs); aa.q8.d = const_cast<float*>(v.d); aa.q8.bsums = const_cast<int16_t*>(v.bsums);
+        } else if (nd_o.q8 || n > 1) {
+            Need nq; nq.q8 = nd_o.q8;
+            vector_pub(attn_pub, m->attn_out, q_dim, nullptr, nq, m->attn_q8, nullptr, 4 * l + 0);
+            attn_pub.tickets = m->tk_attn;
+            if (!nccl) aa.pub = attn_pub;
+        }
         if (peer) {
-            ap.npeers = m->npeers;
-            ap.out_ll = m->attn_ll + (size_t)r * lq; ap.epoch = m->epoch; ap.tag_seq = l; ap.tag_n = L_n;
-            for (uint32_t p = 0; p < m->npeers; p++) ap.peer_ll[p] = reinterpret_cast<uint2*>(on_peer(p, m->attn_ll)) + (size_t)r * lq;
+            aa.npeers = m->npeers;
+            for (uint32_t q = 0; q < m->npeers; q++) aa.peer_out[q] = reinterpret_cast<float*>(on_peer(q, m->attn_out)) + (size_t)r * lq;
         }
-        // a K-quant output projection takes the attention output already in Q8_K (written by the attention kernel)
-        const bool o_preq = m->attn_q8_ok && !peer && (L.o.fmt == WF_Q4_K || L.o.fmt == WF_Q5_K || L.o.fmt == WF_Q6_K);
-        AttnQ8Out aq;
-        Q8KView o_view{};
-        if (o_preq) {
-            aq.qs = reinterpret_cast<int8_t*>(m->attn_q8 + m->attn_q8_lay.qs_off);
-            aq.d = reinterpret_cast<float*>(m->attn_q8 + m->attn_q8_lay.d_off);
-            aq.bsums = reinterpret_cast<int16_t*>(m->attn_q8 + m->attn_q8_lay.bsums_off);
-            o_view.qs = aq.qs; o_view.d = aq.d; o_view.bsums = aq.bsums; o_view.nb = (c.num_heads * c.head_dim) / 256;
-        }
-        MCU(launch_attention(m->qkv, kc, vc, m->d_pos, shape, m->rope_tab, (int)c.neox_rope, m->nsplit, m->attn_part,
-                             m->attn_tickets, m->attn_out + (size_t)r * lq, ap, aq, st, pdl));
-        if (!peer && (rc = gather(m, m->attn_out, lq))) return rc;
-        {   // output projection + residual (src/llama3.rs:14423, 14468)
-            GemvOp op; PeerPush pp;
-            op.w[0] = &L.o; op.x = m->attn_out; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
-            if (o_preq) { op.q8 = &o_view; op.x = nullptr; }
-            if (peer) { read_ll(op, m->attn_ll, l, L_n); op.resid_ll = m->hidden_ll; push_ll(op, pp, m->hidden_ll, 2 * l + 1, hid_n); }
+        MCU(launch_attention(aa, batch, st, pdl));
+        if ((rc = gather_then_publish(m->attn_out, lq, attn_pub))) return rc;
+        {   // output projection + residual (src/llama3.rs:14423, 14468); leaves hidden prepared for gate / up
+            GemvOp op; Q8KView view; Publish p;
+            op.w[0] = &L.o;
+            set_input(op, L.o, m->attn_q8, view, m->attn_out, q_dim);
+            op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
+            Need nd; need_of(nd, L.gate, true);
+            vector_pub(p, m->hidden, H, L.ffn_norm, nd, m->hid_q8, m->hid_xn, 4 * l + 1);
+            if (!nccl) op.pub = &p;
+            push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "o_proj"))) return rc;
-            if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
+            if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
         }
-        {   // FFN norm + fused SwiGLU gate/up (src/llama3.rs:14497-14534)
-            GemvOp op; PeerPush pp;
-            op.w[0] = &L.gate; op.up = &L.up; op.x = m->hidden; op.norm_w = L.ffn_norm; op.norm_eps = c.eps;
-            op.q8k_roundtrip = preq_roundtrip(L.gate);
-            op.y = m->ffn_h; op.y_off[0] = r * m->lF;
-            if (peer) { read_ll(op, m->hidden_ll, 2 * l + 1, hid_n); push_ll(op, pp, m->ffn_ll, l, L_n); }
+        {   // fused SwiGLU gate/up (src/llama3.rs:14497-14534); leaves its output prepared for the down projection
+            GemvOp op; Q8KView view; Publish p;
+            op.w[0] = &L.gate; op.up = &L.up;
+            set_input(op, L.gate, m->hid_q8, view, m->hid_xn, H);
+            op.y = m->ffn_h; op.y_off[0] = r * m->lF; op.y_stride = F;
+            Need nd; need_of(nd, L.down, false);
+            nd.xn = false;      // an f32 down projection reads ffn_h itself
+            if (n == 1) {
+                p = Publish{};
+                if (nd.q8) {
+                    p.mode = PUB_BLOCKS; p.n = F; p.batch = batch; p.src = m->ffn_h; p.tickets = m->tk_blocks;
+                    fill_dst(p.dst, nd, m->ffn_q8, nullptr, F);
+                    op.pub = &p;
+                }
+            } else {
+                vector_pub(p, m->ffn_h, F, nullptr, nd, m->ffn_q8, nullptr, 4 * l + 2);
+                if (!nccl) op.pub = &p;
+            }
+            push_rows(op, m->ffn_h);
             if ((rc = gemv(m, op, "gate/up"))) return rc;
-            if (!peer && (rc = gather(m, m->ffn_h, m->lF))) return rc;
+            if (n > 1 && (rc = gather_then_publish(m->ffn_h, m->lF, p))) return rc;
         }
-        {   // down projection + residual (src/llama3.rs:14536-14555)
-            GemvOp op; PeerPush pp;
-            op.w[0] = &L.down; op.x = m->ffn_h; op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH;
-            if (peer) { read_ll(op, m->ffn_ll, l, L_n); op.resid_ll = m->hidden_ll; push_ll(op, pp, m->hidden_ll, 2 * l + 2, hid_n); }
+        {   // down projection + residual (src/llama3.rs:14536-14555); leaves hidden prepared for the next layer / the head
+            GemvOp op; Q8KView view; Publish p;
+            op.w[0] = &L.down;
+            set_input(op, L.down, m->ffn_q8, view, m->ffn_h, F);
+            op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
+            Need nd;
+            const float* norm_w;
+            if (l + 1 < L_n) {
+                const alice_model::Layer& N = m->layers[l + 1];
+                need_of(nd, N.q, true); need_of(nd, N.k, true); need_of(nd, N.v, true);
+                norm_w = N.attn_norm;
+            } else {
+                need_of(nd, m->out, false);
+                norm_w = m->out_norm;
+            }
+            vector_pub(p, m->hidden, H, norm_w, nd, m->hid_q8, m->hid_xn, 4 * l + 3);
+            if (!nccl) op.pub = &p;
+            push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "down_proj"))) return rc;
-            if (!peer && (rc = gather(m, m->hidden, m->lH))) return rc;
+            if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
         }
     }
-    StepPeers sp;
-    {   // output norm + head (src/llama3.rs:14590-14604)
-        GemvOp op; PeerPush pp;
-        op.w[0] = &m->out; op.x = m->hidden; op.norm_w = m->out_norm; op.norm_eps = c.eps; op.y = m->logits;
-        op.y_off[0] = r * m->lV;
-        op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
-        uint32_t head_grid = 0;
+    {   // output head on the prepared (normalised) hidden (src/llama3.rs:14590-14604)
+        GemvOp op; Q8KView view; Publish p;
+        op.w[0] = &m->out;
+        set_input(op, m->out, m->hid_q8, view, m->hid_xn, H);
+        op.y = m->logits; op.y_off[0] = r * m->lV; op.y_stride = V;
+        if (batch == 1) op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
         if (peer) {
-            read_ll(op, m->hidden_ll, 2 * L_n, hid_n);
-            pp.npeers = m->npeers;
-            for (uint32_t p = 0; p < m->npeers; p++) {
-                pp.y[p] = reinterpret_cast<float*>(on_peer(p, m->logits));
-                pp.flag[p] = reinterpret_cast<unsigned int*>(on_peer(p, m->flags + f_logits));
-            }
-            op.push = &pp;
-            const int prc = stream_gemv_final_grid(op, alice_cfg_of(m->e), &head_grid);
-            if (prc) return alice_fail(prc, "alice_model: planning the output head failed (%d)", prc);
+            Need none;
+            vector_pub(p, m->logits, V, nullptr, none, nullptr, nullptr, 4 * L_n);
+            p.key_src = m->argmax_key;
+            for (uint32_t q = 0; q < m->npeers; q++) p.peer_key[q] = reinterpret_cast<unsigned long long*>(on_peer(q, m->argmax_keys)) + r;
+            op.pub = &p;
+            push_rows(op, m->logits);
         }
         if ((rc = gemv(m, op, "output head"))) return rc;
-        if (!peer) {
-            if ((rc = gather(m, m->logits, m->lV))) return rc;
+        if (nccl) {
+            if ((rc = tp_all_gather(m->e, m->logits, (size_t)m->lV * sizeof(float)))) return rc;
             if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
-        } else {
-            sp.npeers = m->npeers; sp.rank = r;
-            for (uint32_t p = 0; p < m->npeers; p++) {
-                sp.keys[p] = reinterpret_cast<unsigned long long*>(on_peer(p, m->argmax_keys));
-                sp.key_flag[p] = reinterpret_cast<unsigned int*>(on_peer(p, m->flags + f_keys));
-            }
-            sp.my_key_flag = m->flags + f_keys; sp.my_logits_flag = m->flags + f_logits; sp.logits_mult = m->npeers * head_grid;
-            sp.epoch = m->epoch; sp.status = m->e->status;
         }
     }
-    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, sp, st, pdl));
-    return ALICE_OK;
-}
-
-// The same ops as enqueue_step, as a device-resident list for the whole-step kernel. Leaves
-// step_ready false (and the model on the one-launch-per-op path) when an op has no instance there.
-static int step_skip(int why) {
-    if (getenv("ALICE_DEBUG")) fprintf(stderr, "[alice] whole-step kernel not used (reason %d)\n", why);
-    return ALICE_OK;
-}
-
-int build_step_ops(alice_model* m) {
-    const alice_model_config& c = m->cfg;
-    const uint32_t q_dim = c.num_heads * c.head_dim, kv_dim = c.num_kv_heads * c.head_dim;
-    const AttnShape shape{c.num_heads, c.num_kv_heads, c.head_dim};
-    const uint32_t group = c.num_heads / c.num_kv_heads;
-    if (group != 1 && group != 2 && group != 4) return step_skip(1);
-    if (m->tp_n > 1) return step_skip(9);   // the whole-step kernel has no collective stage
-    std::vector<GemvOp> gops;
-    std::vector<int> kind;   // -1 embed, -2 attention(layer), >= 0 index into gops
-    std::vector<uint32_t> attn_layer;
-    kind.push_back(-1);
-    for (uint32_t l = 0; l < c.num_layers; l++) {
-        const alice_model::Layer& L = m->layers[l];
-        if (!(L.q.fmt == L.k.fmt && L.q.fmt == L.v.fmt)) return step_skip(2);
-        GemvOp qkv; qkv.w[0] = &L.q; qkv.w[1] = &L.k; qkv.w[2] = &L.v; qkv.nw = 3;
-        qkv.y_off[1] = q_dim; qkv.y_off[2] = q_dim + kv_dim;
-        qkv.x = m->hidden; qkv.norm_w = L.attn_norm; qkv.norm_eps = c.eps; qkv.y = m->qkv;
-        kind.push_back((int)gops.size()); gops.push_back(qkv);
-        kind.push_back(-2); attn_layer.push_back(l);
-        GemvOp o; o.w[0] = &L.o; o.x = m->attn_out; o.resid = m->hidden; o.y = m->hidden;
-        kind.push_back((int)gops.size()); gops.push_back(o);
-        GemvOp gu; gu.w[0] = &L.gate; gu.up = &L.up; gu.x = m->hidden; gu.norm_w = L.ffn_norm; gu.norm_eps = c.eps; gu.y = m->ffn_h;
-        kind.push_back((int)gops.size()); gops.push_back(gu);
-        GemvOp dn; dn.w[0] = &L.down; dn.x = m->ffn_h; dn.resid = m->hidden; dn.y = m->hidden;
-        kind.push_back((int)gops.size()); gops.push_back(dn);
-    }
-    GemvOp head; head.w[0] = &m->out; head.x = m->hidden; head.norm_w = m->out_norm; head.norm_eps = c.eps;
-    head.y = m->logits; head.argmax_key = m->argmax_key;
-    kind.push_back((int)gops.size()); gops.push_back(head);
-
-    const LaunchCfg cfg = alice_cfg_of(m->e);
-    const uint32_t grid = 2u * (uint32_t)m->e->num_sms;
-    // first pass: the auxiliary area (normalised input + in-kernel Q8_K, or the attention scratch)
-    uint32_t aux = (uint32_t)((group == 4 ? sizeof(AttnSmem<4>) : group == 2 ? sizeof(AttnSmem<2>) : sizeof(AttnSmem<1>)) + 127) & ~127u;
-    PlanLimits probe{2, 48 * 1024, grid};
-    for (const GemvOp& g : gops) {
-        StreamPlan pl;
-        if (plan_stream_gemv(g, cfg, &probe, pl)) return step_skip(3);
-        if (pl.kl > 2) return step_skip(4);
-        aux = std::max(aux, pl.q8_bytes + pl.xn_bytes);
-    }
-    const uint32_t ops_bytes = 2 * (uint32_t)sizeof(StepOp);   // the consumers' descriptor double buffer, after the auxiliary area
-    const uint32_t stride = ((STEP_SMEM_BUDGET - STREAM_HDR_BYTES - aux - ops_bytes) / 2) & ~127u;
-    PlanLimits lim{2, stride, grid};
-    const uint32_t aux_off = STREAM_HDR_BYTES + 2 * stride;
-    std::vector<StepOp> ops;
-    size_t ai = 0;
-    for (int k : kind) {
-        StepOp op{};
-        if (k == -1) {
-            op.type = SOP_EMBED; op.table = m->emb.data; op.hidden = m->hidden; op.cols = c.hidden_dim; op.vocab = c.vocab_size; op.theta = c.rope_theta; op.rope_tab = m->rope_tab;
-        } else if (k == -2) {
-            const uint32_t l = attn_layer[ai++];
-            op.type = SOP_ATTN; op.qkv = m->qkv;
-            op.kc = m->kcache + (size_t)l * c.max_seq_len * kv_dim; op.vc = m->vcache + (size_t)l * c.max_seq_len * kv_dim;
-            op.part = m->attn_part; op.tickets = m->attn_tickets; op.attn_out = m->attn_out;
-            op.shape = shape; op.rope_tab = m->rope_tab; op.neox = (int)c.neox_rope; op.nsplit = m->nsplit;
-        } else {
-            StreamPlan pl;
-            if (plan_stream_gemv(gops[k], cfg, &lim, pl)) return step_skip(5);
-            const int v = step_variant(gops[k].w[0]->fmt, pl.kl, pl.swiglu);
-            if (v < 0) return step_skip(6);
-            op.type = SOP_GEMV; op.variant = v; op.g = pl.args;
-            op.g.xn_off = aux_off; op.g.q8_off = aux_off + pl.xn_bytes;
-        }
-        ops.push_back(op);
-    }
-    int per_sm = 0;
-    const size_t smem = aux_off + aux + ops_bytes;
-    if (decode_step_max_ctas_per_sm(smem, &per_sm) != cudaSuccess || per_sm < 2) { cudaGetLastError(); return step_skip(7); }
-    int coop = 0;
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->e->device);
-    if (!coop) return step_skip(8);
-    int rc = dev_alloc(m, &m->d_ops, ops.size());
-    if (!rc) rc = dev_alloc(m, &m->d_barrier, 1);
-    if (rc) return rc;
-    MCU(cudaMemcpy(m->d_ops, ops.data(), ops.size() * sizeof(StepOp), cudaMemcpyHostToDevice));
-    m->step_types.clear();
-    for (const StepOp& o : ops) m->step_types.push_back(o.type);
-    m->step_nops = (uint32_t)ops.size(); m->step_grid = grid; m->step_stride = stride; m->step_aux_off = aux_off;
-    m->step_smem = smem; m->step_ready = true;
-    return ALICE_OK;
-}
-
-// n decode steps in one cooperative launch of the whole-step kernel.
-int run_step_kernel(alice_model* m, uint32_t n, bool greedy_feed) {
-    cudaStream_t st = m->e->stream;
-    MCU(cudaMemsetAsync(m->d_barrier, 0, sizeof(unsigned int), st));
-    StepArgs sa{};
-    sa.ops = m->d_ops; sa.nops = m->step_nops; sa.nsteps = n;
-    sa.pos = m->d_pos; sa.token = m->d_token; sa.trace = m->d_trace; sa.key = m->argmax_key;
-    sa.barrier = m->d_barrier; sa.status = m->e->status; sa.write_token = greedy_feed ? 1 : 0;
-    sa.nstages = 2; sa.stage_stride = m->step_stride; sa.aux_off = m->step_aux_off;
-    sa.ops_off = (uint32_t)(m->step_smem - 2 * sizeof(StepOp));
-    // ALICE_STEP_PROF=1: per-op clock stamps of one CTA during the last step, printed after the launch (debug aid)
-    long long* prof = nullptr;
-    if (getenv("ALICE_STEP_PROF")) {
-        MCU(cudaMalloc(&prof, (size_t)m->step_nops * 16 * sizeof(long long)));
-        MCU(cudaMemset(prof, 0, (size_t)m->step_nops * 16 * sizeof(long long)));
-    }
-    sa.prof = prof;
-    MCU(launch_decode_steps(sa, m->step_grid, m->step_smem, st));
-    if (prof) {
-        std::vector<long long> h((size_t)m->step_nops * 16);
-        MCU(cudaStreamSynchronize(st));
-        MCU(cudaMemcpy(h.data(), prof, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
-        cudaFree(prof);
-        fprintf(stderr, "[alice] step profile of one CTA, SM clock cycles\n");
-        for (uint32_t i = 0; i < m->step_nops; i++) {
-            const long long* p = &h[(size_t)i * 16];
-            if (m->step_types[i] == SOP_GEMV) {
-                fprintf(stderr, "[alice] %3u matvec    prologue %6lld  first stage %6lld  rows %7lld  grid barrier %6lld  total %7lld  | stages:", i,
-                        p[1] - p[0], p[2] - p[1], p[3] - p[2], p[5] - p[4], p[5] - p[0]);
-                for (int c = 0; c < 8 && p[8 + c]; c++) fprintf(stderr, " %lld", p[8 + c] - (c ? p[7 + c] : p[2]));
-                fprintf(stderr, "\n");
-            } else if (m->step_types[i] == SOP_ATTN) {
-                fprintf(stderr, "[alice] %3u attention q+rope %6lld  positions %6lld  cta combine %6lld  ticket %6lld  fold %6lld  grid barrier %6lld  total %7lld\n", i,
-                        p[1] - p[0], p[2] - p[1], p[3] - p[2], p[6] - p[3], p[4] - p[6], p[5] - p[4], p[5] - p[0]);
-            } else {
-                fprintf(stderr, "[alice] %3u embedding %6lld  grid barrier %6lld\n", i, p[4] - p[0], p[5] - p[4]);
-            }
-        }
-    }
+    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, batch, m->epoch, st, pdl));
     return ALICE_OK;
 }
 
@@ -420,6 +358,7 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     MCU(cudaSetDevice(e->device));
     auto* m = new alice_model();
     m->e = e; m->cfg = c; m->emb = embedding->d; m->out = output->d;
+    alice_engine_retain(e);
     m->tp_n = n; m->tp_r = e->tp_rank; m->lq = lq; m->lkv = lkv; m->lH = lH; m->lF = lF; m->lV = lV;
     int rc = ALICE_OK;
     for (uint32_t l = 0; l < c.num_layers && !rc; l++) {
@@ -444,13 +383,13 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     m->nsplit = std::max<uint32_t>(1, std::min<uint32_t>(64, (2 * (uint32_t)e->num_sms) / (c.num_kv_heads / n)));
     const size_t kv_elems = (size_t)c.num_layers * c.max_seq_len * lkv;
     if (!rc) rc = upload_norm(m, &m->out_norm, output_norm, c.hidden_dim);
+    constexpr uint32_t B = MAX_BATCH;
     {   // the vectors other ranks need, the argmax keys and the hand-over counters share one allocation
         auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-        const size_t o_hidden = 0, o_attn = o_hidden + up((size_t)c.hidden_dim * 4), o_ffn = o_attn + up((size_t)q_dim * 4),
-                     o_logits = o_ffn + up((size_t)c.intermediate_dim * 4), o_keys = o_logits + up((size_t)c.vocab_size * 4),
-                     o_flags = o_keys + up(8 * 8), o_epoch = o_flags + up(((size_t)4 * c.num_layers + 2) * 4),
-                     o_hll = o_epoch + 256, o_all = o_hll + up((size_t)c.hidden_dim * 8), o_fll = o_all + up((size_t)q_dim * 8);
-        m->xchg_bytes = o_fll + up((size_t)c.intermediate_dim * 8);
+        const size_t o_hidden = 0, o_attn = o_hidden + up((size_t)B * c.hidden_dim * 4), o_ffn = o_attn + up((size_t)B * q_dim * 4),
+                     o_logits = o_ffn + up((size_t)B * c.intermediate_dim * 4), o_keys = o_logits + up((size_t)B * c.vocab_size * 4),
+                     o_flags = o_keys + up(8 * 8), o_epoch = o_flags + up(((size_t)4 * c.num_layers + 2) * 4);
+        m->xchg_bytes = o_epoch + 256;
         if (!rc) rc = dev_alloc(m, &m->xchg, m->xchg_bytes);
         if (!rc) {
             const cudaError_t zerr = cudaMemset(m->xchg, 0, m->xchg_bytes);
@@ -463,29 +402,39 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
             m->argmax_key = m->argmax_keys + m->tp_r;
             m->flags = reinterpret_cast<unsigned int*>(m->xchg + o_flags);
             m->epoch = reinterpret_cast<unsigned int*>(m->xchg + o_epoch);
-            m->hidden_ll = reinterpret_cast<uint2*>(m->xchg + o_hll);
-            m->attn_ll = reinterpret_cast<uint2*>(m->xchg + o_all);
-            m->ffn_ll = reinterpret_cast<uint2*>(m->xchg + o_fll);
         }
     }
-    if (!rc) rc = dev_alloc(m, &m->qkv, lq + 2 * lkv);
+    const uint32_t tk_blocks_n = (c.intermediate_dim + 255) / 256 + 1;
+    if (!rc) rc = dev_alloc(m, &m->qkv, (size_t)B * (lq + 2 * lkv));
     if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
-    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
-    if (!rc) rc = dev_alloc(m, &m->attn_tickets, c.num_kv_heads / n);
-    if (!rc) rc = dev_alloc(m, &m->rope_tab, 128);
-    m->attn_q8_lay = Q8KLayout::make(q_dim / 256, 1);
-    m->attn_q8_ok = n == 1 && (group % 2) == 0 && q_dim % 256 == 0 && !getenv("ALICE_NO_ATTN_Q8");
-    if (!rc && m->attn_q8_ok) rc = dev_alloc(m, &m->attn_q8, m->attn_q8_lay.total);
+    if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)B * m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
+    if (!rc) rc = dev_alloc(m, &m->attn_tickets, (size_t)B * (c.num_kv_heads / n));
+    if (!rc) rc = dev_alloc(m, &m->tk_vec, 1);
+    if (!rc) rc = dev_alloc(m, &m->tk_attn, 1);
+    if (!rc) rc = dev_alloc(m, &m->tk_blocks, tk_blocks_n);
+    if (!rc) rc = dev_alloc(m, &m->rope_tab, (size_t)B * 128);
+    if (!rc) rc = dev_alloc(m, &m->rope_freq, 64);
+    if (!rc) rc = dev_alloc(m, &m->hid_q8, Q8KLayout::make((c.hidden_dim + 255) / 256, B).total);
+    if (!rc) rc = dev_alloc(m, &m->attn_q8, Q8KLayout::make((q_dim + 255) / 256, B).total);
+    if (!rc) rc = dev_alloc(m, &m->ffn_q8, Q8KLayout::make((c.intermediate_dim + 255) / 256, B).total);
+    if (!rc) rc = dev_alloc(m, &m->hid_xn, (size_t)B * c.hidden_dim);
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
-    if (!rc) rc = dev_alloc(m, &m->d_token, 1);
+    if (!rc) rc = dev_alloc(m, &m->d_token, B);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
     if (!rc) {
-        cudaError_t err = cudaMemsetAsync(m->kcache, 0, kv_elems * 4, e->stream);
+        // apply_rope's frequencies (src/llama3.rs:5323-5333): 1 / theta^(i / head_dim) for even i, in f32 with the host's powf
+        float freq[64];
+        for (int j = 0; j < 64; j++) freq[j] = 1.0f / std::pow(c.rope_theta, (float)(2 * j) / (float)c.head_dim);
+        cudaError_t err = cudaMemcpy(m->rope_freq, freq, sizeof freq, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->kcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)(c.num_kv_heads / n) * 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)B * (c.num_kv_heads / n) * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_vec, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_attn, 0, 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_blocks, 0, (size_t)tk_blocks_n * 4, e->stream);
+        if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4 * B, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
         if (err != cudaSuccess) rc = alice_cuda_fail(err, "alice_model_create: clearing state");
@@ -498,30 +447,56 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
 int32_t alice_model_destroy(alice_model* m) {
     if (!m) return ALICE_OK;
     cudaSetDevice(m->e->device);
-    cudaStreamSynchronize(m->e->stream);
+    if (!m->e->dead) cudaStreamSynchronize(m->e->stream);
     if (m->graph_greedy) cudaGraphExecDestroy(m->graph_greedy);
     for (uint32_t p = 0; p < m->npeers; p++) cudaIpcCloseMemHandle(m->peer_base[p]);
     for (void* p : m->owned) cudaFree(p);
+    alice_engine_release(m->e);
     delete m;
     return ALICE_OK;
 }
 
-static int set_token(alice_model* m, uint32_t token) {
-    if (token >= m->cfg.vocab_size) return alice_fail(ALICE_E_INVALID, "alice_model: token %u >= vocab %u", token, m->cfg.vocab_size);
-    const int t = (int)token;
-    MCU(cudaMemcpyAsync(m->d_token, &t, 4, cudaMemcpyHostToDevice, m->e->stream));
+static int set_tokens(alice_model* m, const uint32_t* tokens, uint32_t n) {
+    int t[MAX_BATCH];
+    for (uint32_t k = 0; k < n; k++) {
+        if (tokens[k] >= m->cfg.vocab_size) return alice_fail(ALICE_E_INVALID, "alice_model: token %u >= vocab %u", tokens[k], m->cfg.vocab_size);
+        t[k] = (int)tokens[k];
+    }
+    MCU(cudaMemcpyAsync(m->d_token, t, 4 * n, cudaMemcpyHostToDevice, m->e->stream));
     MCU(cudaStreamSynchronize(m->e->stream));  // `t` lives on this stack frame
     return ALICE_OK;
 }
+static int set_token(alice_model* m, uint32_t token) { return set_tokens(m, &token, 1); }
 
 int32_t alice_model_forward(alice_model* m, uint32_t token) {
     if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_forward: null model");
     MCU(cudaSetDevice(m->e->device));
     int rc = check_room(m, 1, "alice_model_forward");
     if (!rc) rc = set_token(m, token);
-    if (!rc) rc = enqueue_step(m, false);
+    if (!rc) rc = enqueue_step(m, 1, false);
     if (!rc) m->pos += 1;
     return rc;
+}
+
+int32_t alice_model_forward_batch(alice_model* m, const uint32_t* tokens, uint32_t n) {
+    const char* who = "alice_model_forward_batch";
+    if (!m || !tokens) return alice_fail(ALICE_E_INVALID, "%s: null argument", who);
+    if (n == 0 || n > (uint32_t)MAX_BATCH) return alice_fail(ALICE_E_SHAPE, "%s: %u tokens outside 1..%d", who, n, MAX_BATCH);
+    MCU(cudaSetDevice(m->e->device));
+    int rc = check_room(m, n, who);
+    if (!rc) rc = set_tokens(m, tokens, n);
+    if (!rc) rc = enqueue_step(m, n, false);
+    if (!rc) m->pos += n;
+    return rc;
+}
+
+int32_t alice_model_forward_batch_read(alice_model* m, const uint32_t* tokens, uint32_t n, float* logits) {
+    if (!logits) return alice_fail(ALICE_E_INVALID, "alice_model_forward_batch_read: null argument");
+    int rc = alice_model_forward_batch(m, tokens, n);
+    if (rc) return rc;
+    MCU(cudaMemcpyAsync(logits, m->logits, (size_t)n * m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, m->e->stream));
+    MCU(cudaStreamSynchronize(m->e->stream));
+    return alice_sync(m->e);
 }
 
 int32_t alice_model_read_logits(alice_model* m, float* logits) {
@@ -547,28 +522,15 @@ int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t
     if (rc) return rc;
     cudaStream_t st = m->e->stream;
     const uint32_t pos0 = m->pos;
-    if (m->use_step_kernel && !m->step_tried) {
-        m->step_tried = true;
-        rc = build_step_ops(m);
-        if (rc) return rc;
-    }
-    if (m->use_step_kernel && m->step_ready) {
-        rc = run_step_kernel(m, n, true);
-        if (rc) return rc;
-        m->pos += n;
-        MCU(cudaMemcpyAsync(out_tokens, m->d_trace + pos0, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
-        MCU(cudaStreamSynchronize(st));
-        return alice_sync(m->e);
-    }
     if (!m->graph_tried) {
         // Capture one step (every kernel reads position and token from device memory) and replay it.
         m->graph_tried = true;
-        rc = enqueue_step(m, true);   // eager first step: also sets per-kernel attributes outside capture
+        rc = enqueue_step(m, 1, true);   // eager first step: also sets per-kernel attributes outside capture
         if (rc) return rc;
         m->pos += 1;
         cudaGraph_t g = nullptr;
         if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-            const int crc = enqueue_step(m, true);
+            const int crc = enqueue_step(m, 1, true);
             cudaError_t err = cudaStreamEndCapture(st, &g);
             if (crc == ALICE_OK && err == cudaSuccess && g) {
                 if (cudaGraphInstantiate(&m->graph_greedy, g, 0) != cudaSuccess) m->graph_greedy = nullptr;
@@ -581,7 +543,7 @@ int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t
         if (m->graph_greedy) {
             MCU(cudaGraphLaunch(m->graph_greedy, st));
         } else {
-            rc = enqueue_step(m, true);
+            rc = enqueue_step(m, 1, true);
             if (rc) return rc;
         }
         m->pos += 1;
@@ -608,11 +570,6 @@ int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes
     if (bytes_per_handle < sizeof(cudaIpcMemHandle_t)) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: handles of %zu bytes, need %zu", bytes_per_handle, sizeof(cudaIpcMemHandle_t));
     if (m->peer_mode) return alice_fail(ALICE_E_INVALID, "alice_model_tp_connect: already connected");
     if (m->tp_n <= 1) return ALICE_OK;
-    for (const alice_model::Layer& L : m->layers)
-        for (const WeightDesc* w : {&L.o, &L.down})
-            if (w->fmt == WF_Q8_0 || w->fmt == WF_Q2_0 || w->fmt == WF_SPARSE_TERNARY)
-                return alice_fail(ALICE_E_UNSUPPORTED, "alice_model_tp_connect: o / down projections in Q8_0, Q2_0 or sparse ternary read their input "
-                                                       "directly and cannot take pushed vectors; the model keeps using NCCL all-gathers");
     MCU(cudaSetDevice(m->e->device));
     MCU(cudaStreamSynchronize(m->e->stream));
     uint32_t k = 0;
@@ -637,12 +594,6 @@ int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes
     return ALICE_OK;
 }
 
-int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled) {
-    if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_use_step_kernel: null model");
-    m->use_step_kernel = enabled != 0;
-    return ALICE_OK;
-}
-
 int32_t alice_model_position(const alice_model* m, uint32_t* pos) {
     if (!m || !pos) return alice_fail(ALICE_E_INVALID, "alice_model_position: null argument");
     *pos = m->pos;
@@ -659,6 +610,7 @@ int32_t alice_model_set_position(alice_model* m, uint32_t pos) {
     if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_set_position: null model");
     if (pos > m->cfg.max_seq_len) return alice_fail(ALICE_E_SHAPE, "alice_model_set_position: %u > max_seq_len %u", pos, m->cfg.max_seq_len);
     const int p = (int)pos;
+    MCU(cudaSetDevice(m->e->device));
     MCU(cudaMemcpyAsync(m->d_pos, &p, 4, cudaMemcpyHostToDevice, m->e->stream));
     MCU(cudaStreamSynchronize(m->e->stream));
     m->pos = pos;
@@ -674,6 +626,7 @@ int32_t alice_model_rollback_to(alice_model* m, uint32_t pos) {
 int32_t alice_model_reset(alice_model* m) {
     if (!m) return alice_fail(ALICE_E_INVALID, "alice_model_reset: null model");
     const size_t kv_bytes = (size_t)m->cfg.num_layers * m->cfg.max_seq_len * m->lkv * 4;
+    MCU(cudaSetDevice(m->e->device));
     MCU(cudaMemsetAsync(m->kcache, 0, kv_bytes, m->e->stream));
     MCU(cudaMemsetAsync(m->vcache, 0, kv_bytes, m->e->stream));
     return alice_model_set_position(m, 0);
@@ -686,6 +639,7 @@ static int kv_copy(alice_model* m, uint32_t layer, uint32_t pos0, uint32_t npos,
     const size_t kv_dim = m->lkv;   // this rank's KV heads
     const size_t off = ((size_t)layer * c.max_seq_len + pos0) * kv_dim, bytes = (size_t)npos * kv_dim * 4;
     cudaStream_t st = m->e->stream;
+    MCU(cudaSetDevice(m->e->device));
     if (to_device) {
         MCU(cudaMemcpyAsync(m->kcache + off, k, bytes, cudaMemcpyHostToDevice, st));
         MCU(cudaMemcpyAsync(m->vcache + off, v, bytes, cudaMemcpyHostToDevice, st));

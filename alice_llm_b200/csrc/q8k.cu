@@ -1,6 +1,6 @@
 // Stand-alone Q8_K activation quantizer (quantize_row_q8_k, ALICE-LLM src/gguf.rs:1323-1374):
 // one warp per 256-element block; the per-block routine lives in q8k.cuh and is shared with the
-// matvec kernels, which quantize their f32 input in their own prologue.
+// kernels that leave their output prepared for the next op (csrc/publish.cuh).
 #include "common.cuh"
 #include "q8k.cuh"
 
@@ -15,19 +15,27 @@ __global__ void __launch_bounds__(128) quantize_q8k_kernel(const float* __restri
     const uint32_t blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (blk >= nblocks) return;
 
-    q8k_quantize_block_warp(q8k_load_lane(x + (size_t)blk * QK_K, lane), lane, qs + (size_t)blk * QK_K, d + blk, bsums + (size_t)blk * 16);
+    q8k_quantize_block_warp(q8k_load_lane(x + (size_t)blk * QK_K, lane, true), lane, qs + (size_t)blk * QK_K, d + blk, bsums + (size_t)blk * 16);
 }
 
-void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* base, cudaStream_t stream) {
+void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* base, cudaStream_t stream, bool pdl) {
     const uint32_t nb = cols / QK_K;
     const Q8KLayout l = Q8KLayout::make(nb, batch);
     const uint32_t nblocks = nb * batch;
     if (nblocks == 0) return;
     auto* p = static_cast<uint8_t*>(base);
     const uint32_t warps = 4;
-    quantize_q8k_kernel<<<(nblocks + warps - 1) / warps, warps * 32, 0, stream>>>(
-        x, nblocks, reinterpret_cast<int8_t*>(p + l.qs_off), reinterpret_cast<float*>(p + l.d_off),
-        reinterpret_cast<int16_t*>(p + l.bsums_off));
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((nblocks + warps - 1) / warps);
+    lc.blockDim = dim3(warps * 32);
+    lc.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = pdl ? 1 : 0;
+    cudaLaunchKernelEx(&lc, quantize_q8k_kernel, x, nblocks, reinterpret_cast<int8_t*>(p + l.qs_off), reinterpret_cast<float*>(p + l.d_off),
+                       reinterpret_cast<int16_t*>(p + l.bsums_off));
 }
 
 }  // namespace alice

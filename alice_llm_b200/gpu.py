@@ -139,6 +139,10 @@ class GpuEngine:
     def set_tuning(self, rows_per_set: int = 0, stages: int = 0):
         check(self._lib.alice_engine_set_tuning(self._h, rows_per_set, stages))
 
+    def set_wait_limit(self, sm_cycles: int = 0):
+        """Cycle budget of every bounded wait inside the kernels (0 = about one second)."""
+        check(self._lib.alice_engine_set_wait_limit(self._h, sm_cycles))
+
     # -- tensor parallel: one engine (one process) per GPU, rows of every projection sharded over the group --
     TP_ID_BYTES = 128
 
@@ -279,6 +283,14 @@ class GpuEngine:
 
     def dequantize_dev(self, w: GpuWeightBuffer, out: GpuBuffer):
         check(self._lib.alice_dequantize(self._h, w._h, out._h))
+
+    def plan_query(self, w: GpuWeightBuffer, swiglu: bool = False, preq: bool = False) -> dict:
+        """Launch geometry the planner picks for a matvec over `w` (diagnostic; no reference counterpart)."""
+        out = (C.c_uint32 * 10)()
+        check(self._lib.alice_plan_query(self._h, w._h, int(swiglu), int(preq), out, 10))
+        keys = ("grid", "warps_per_row", "row_sets", "rows_per_set", "groups", "stages", "units_per_lane", "mma", "col_chunks",
+                "ctas_per_sm")
+        return dict(zip(keys, (int(v) for v in out)))
 
     # -- one-shot helpers (src/gpu.rs:838, 962) --
     def matvec(self, weights: GpuWeightBuffer, input_) -> np.ndarray:
@@ -498,10 +510,17 @@ class GpuModel:
         buf = C.create_string_buffer(blob, len(blob))
         check(self.engine._lib.alice_model_tp_connect(self._h, buf, self.TP_HANDLE_BYTES))
 
-    def use_step_kernel(self, enabled: bool):
-        """decode_greedy as one launch per op replayed from a CUDA graph (default) or, when enabled, inside one
-        cooperative whole-step kernel (same tokens; opt-in)."""
-        check(self.engine._lib.alice_model_use_step_kernel(self._h, int(enabled)))
+    # -- src/gpu.rs:6020-6094 --
+    def forward_batch(self, token_ids):
+        t = _np(token_ids, np.uint32).reshape(-1)
+        check(self.engine._lib.alice_model_forward_batch(self._h, _ptr(t), t.size))
+
+    def forward_batch_and_read(self, token_ids) -> np.ndarray:
+        """-> logits[k * vocab + v] of the len(token_ids) consecutive tokens (src/gpu.rs:6057)."""
+        t = _np(token_ids, np.uint32).reshape(-1)
+        out = np.empty(t.size * self._config.vocab_size, np.float32)
+        check(self.engine._lib.alice_model_forward_batch_read(self._h, _ptr(t), t.size, _ptr(out)))
+        return out
 
     def decode_greedy(self, first_token: int, n: int) -> np.ndarray:
         out = np.empty(n, np.uint32)
@@ -524,13 +543,20 @@ class GpuModel:
         check(self.engine._lib.alice_model_reset(self._h))
 
     # -- pre-filled context (no reference counterpart: the benchmark starts from a filled KV cache) --
+    def _local_kv_dim(self) -> int:
+        """Floats per cached position on this rank: the KV heads are sharded over a tensor-parallel group."""
+        return self._config.num_kv_heads * self._config.head_dim // self.engine.tp_info()[1]
+
     def kv_write(self, layer: int, pos0: int, k, v):
+        """k, v: [npos, kv_dim / world] rows of this rank's KV heads."""
         k, v = _np(k, np.float32), _np(v, np.float32)
-        kv_dim = self._config.num_kv_heads * self._config.head_dim
+        kv_dim = self._local_kv_dim()
+        if k.size != v.size or k.size % kv_dim:
+            raise AliceError(_lib.E_SHAPE, f"kv_write: {k.size} / {v.size} floats are not whole rows of {kv_dim}")
         check(self.engine._lib.alice_model_kv_write(self._h, layer, pos0, k.size // kv_dim, _ptr(k), _ptr(v)))
 
     def kv_read(self, layer: int, pos0: int, npos: int):
-        kv_dim = self._config.num_kv_heads * self._config.head_dim
+        kv_dim = self._local_kv_dim()
         k, v = np.empty((npos, kv_dim), np.float32), np.empty((npos, kv_dim), np.float32)
         check(self.engine._lib.alice_model_kv_read(self._h, layer, pos0, npos, _ptr(k), _ptr(v)))
         return k, v

@@ -70,6 +70,10 @@ int32_t alice_sync(alice_engine* e);
 int32_t alice_engine_set_pdl(alice_engine* e, int32_t enabled);
 /* Tuning overrides for the streaming matvec: rows per warp set per stage and ring depth; 0 = automatic. */
 int32_t alice_engine_set_tuning(alice_engine* e, int32_t rows_per_set, int32_t stages);
+/* Cycle budget (SM clock cycles) of every bounded wait inside the kernels launched from now on; 0 = the default of
+ * about one second. A wait that runs out records its code in the engine's status word and the kernel returns;
+ * alice_sync then reports ALICE_E_KERNEL and clears the word (the engine stays usable). No reference counterpart. */
+int32_t alice_engine_set_wait_limit(alice_engine* e, uint64_t sm_cycles);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 /* GpuEngine::upload_weights / _q5k / _q6k / _q8_0 / _q1_0 (src/gpu.rs:698-798): raw GGUF blocks,
@@ -135,6 +139,13 @@ int32_t alice_swiglu_preq(alice_engine* e, const alice_weights* gate, const alic
 /* dequantize_weight_row / GgufFile::tensor_to_f32 (src/gguf.rs:6168, 574): out[r*cols + c], bit-exact. */
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out);
 
+/* Launch geometry the planner chooses for one matvec over `w` (fused SwiGLU of two such matrices when swiglu != 0;
+ * pre-quantized Q8_K input when preq != 0): out[0..9] = CTAs, warps per row (or per 16-row tile), row sets per CTA,
+ * rows per set per stage, stage-sized row groups in total, ring stages, activation units per lane, 1 if the bit-plane
+ * tensor-core kernel is used, column chunks, CTAs per SM. A CTA handles about groups / CTAs stages, so a test can
+ * assert that a shape really re-uses the ring. No reference counterpart (diagnostic). */
+int32_t alice_plan_query(alice_engine* e, const alice_weights* w, int32_t swiglu, int32_t preq, uint32_t* out, uint32_t n_out);
+
 /* ---- tensor parallel ------------------------------------------------------------------------ */
 /* One engine (one process) per GPU; output rows of every projection are sharded over the group and the
  * full vector is rebuilt on every rank by an NCCL all-gather queued on the engine's stream (the row
@@ -153,8 +164,9 @@ int32_t alice_engine_tp_info(const alice_engine* e, uint32_t* rank, uint32_t* wo
  * of Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613): per layer
  * rms_norm -> q/k/v matvec -> RoPE -> KV append -> GQA attention -> o matvec + residual ->
  * rms_norm -> fused SwiGLU gate/up -> down matvec + residual; then output norm and head.
- * One decode step is ~7 kernels per layer replayed from a CUDA graph; position and token live on
- * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations).
+ * One decode step is 5 kernels per layer replayed from a CUDA graph; position and token live on
+ * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations). Every kernel leaves
+ * its output in the form the next one reads (normalised, Q8_K-quantized), prepared once by its last CTA.
  * On an engine that is rank r of a tensor-parallel group of n, the config stays the whole model's and the
  * weight handles are row shards: rows [r*R/n, (r+1)*R/n) of q, k, v, o, gate, up, down and the output
  * head (R = that matrix's row count; contiguous byte ranges of the raw blocks); the embedding table is
@@ -180,25 +192,27 @@ int32_t alice_model_destroy(alice_model* m);
 /* GpuModel::forward / forward_and_read (src/gpu.rs:5010, 5033): one token at the current position. */
 int32_t alice_model_forward(alice_model* m, uint32_t token);
 int32_t alice_model_forward_read(alice_model* m, uint32_t token, float* logits);
+/* GpuModel::forward_batch / forward_batch_and_read (src/gpu.rs:6020, 6057): n consecutive tokens (1..8; the reference
+ * takes exactly 4) in one pass over the weights, token k at position + k attending position + k + 1 rows (causal,
+ * src/shaders/attention.wgsl:45); the position advances by n. logits[k * vocab + v]. Together with
+ * alice_model_rollback_to this is the verify step of speculative decoding (examples/speculative_dual_gpu.rs:230-322).
+ * Single GPU only. */
+int32_t alice_model_forward_batch(alice_model* m, const uint32_t* tokens, uint32_t n);
+int32_t alice_model_forward_batch_read(alice_model* m, const uint32_t* tokens, uint32_t n, float* logits);
 /* Greedy decode loop (Llama3Model::generate's decode loop, src/llama3.rs:16084, with argmax sampling):
  * feeds first_token, then n-1 times the argmax of the previous logits; out_tokens[i] = argmax after
  * step i. No host round trip between steps. */
 int32_t alice_model_decode_greedy(alice_model* m, uint32_t first_token, uint32_t n, uint32_t* out_tokens);
 int32_t alice_model_read_logits(alice_model* m, float* logits);
-/* alice_model_decode_greedy replays one launch per op from a CUDA graph (default, enabled = 0). enabled = 1
- * selects the whole-step kernel instead: all steps inside one cooperative launch (every matvec, the
- * attention and the token hand-over; weights of the next matvec are prefetched across op boundaries), used
- * when every op of the model has an instance there. Same tokens either way; the graph path is the faster
- * one at present, so the whole-step kernel is opt-in. */
-int32_t alice_model_use_step_kernel(alice_model* m, int32_t enabled);
 /* Tensor parallel without collective calls: after every rank has created its model, each exports a handle to its
  * exchange region (ALICE_TP_HANDLE_BYTES; CUDA IPC, same node), the host gathers the handles of all ranks in rank
  * order and every rank connects. From then on the kernel that produces a sharded vector stores its rows straight
- * into every peer's copy over NVLink. The per-layer vectors travel as 8-byte (value, tag) elements written with one
- * store each, and the consuming kernel polls (bounded, ALICE_E_KERNEL on expiry) for the tag of the version it wants:
- * no fence, no counter, no extra launch. The logits and the argmax keys (once per step) use plain stores and an
- * arrival counter. Refused (ALICE_E_UNSUPPORTED, the model keeps using NCCL) when an o / down projection is Q8_0,
- * Q2_0 or sparse ternary. No reference counterpart (the reference is single device). */
+ * into every peer's copy over NVLink; its last CTA raises one counter per vector on every peer (release) and waits,
+ * bounded (ALICE_E_KERNEL on expiry), until all peers have raised the same counter here, then prepares the complete
+ * vector for the next op. The consuming kernels read local memory only. The connect result must be the same on every
+ * rank (all-reduce the status on the host and rebuild the models if any rank failed: a rank left on NCCL would block
+ * in its next all-gather), and the ranks must meet in a host barrier before alice_model_destroy (a peer may still be
+ * storing into the region). No reference counterpart (the reference is single device). */
 #define ALICE_TP_HANDLE_BYTES 64
 int32_t alice_model_tp_export(alice_model* m, void* out, size_t nbytes);
 int32_t alice_model_tp_connect(alice_model* m, const void* handles, size_t bytes_per_handle);

@@ -123,34 +123,37 @@ def test_rollback_reset_and_limits(eng, oracle):
     gm.free()
 
 
-# the second shape makes several warps share a row (hidden 2304 -> 36 Q4_K units) and gives the down
-# projection two activation positions per lane (ffn 8704 -> 272 Q6_K units over 8 warps)
-@pytest.mark.parametrize("shape", [dict(), dict(hidden_dim=2304, intermediate_dim=8704, vocab_size=700)])
-def test_step_kernel_equals_per_op_launches(eng, oracle, shape):
-    """decode_greedy inside the one cooperative whole-step kernel must give the tokens, the logits and
-    the KV rows of the one-launch-per-op path (same arithmetic, different scheduling)."""
+@pytest.mark.parametrize("mix,heads", [(None, (4, 2)), ("smooth", (8, 2)), (Q1_MIX, (10, 2)),
+                                       ({n: synth.TERNARY for n in ("q", "k", "v", "o", "gate", "up", "down", "output")}, (8, 2))])
+@pytest.mark.parametrize("nbatch", [4, 8])
+def test_forward_batch_matches_token_by_token_oracle(eng, oracle, mix, heads, nbatch):
+    """forward_batch_and_read (src/gpu.rs:6057): token k of the batch sits at position + k and attends position + k + 1
+    rows, so its logits equal those of feeding the tokens one by one; then rollback_to and a second, different batch
+    (the accept / reject loop of examples/speculative_dual_gpu.rs:230-322)."""
     from alice_llm_b200.gpu import GpuModel
-    rng = np.random.default_rng(8)
-    cfg = dict(CFG, num_layers=3, **shape)
-    model = synth.make_llama(rng, cfg)
-    kv_dim = cfg["num_kv_heads"] * cfg["head_dim"]
-    pre = [(rng.standard_normal((50, kv_dim), dtype=np.float32), rng.standard_normal((50, kv_dim), dtype=np.float32))
-           for _ in range(cfg["num_layers"])]
-    outs = []
-    for step_kernel in (True, False):
-        gm = GpuModel.load(eng, model)
-        gm.use_step_kernel(step_kernel)
-        for l, (k, v) in enumerate(pre):
-            gm.kv_write(l, 0, k, v)
-        gm.set_position(50)
-        toks = gm.decode_greedy(3, 10)
-        logits = gm.read_logits()
-        toks2 = gm.decode_greedy(int(toks[-1]), 5)       # second launch continues from device state
-        kv = gm.kv_read(cfg["num_layers"] - 1, 50, 15)
-        outs.append((toks, logits, toks2, kv))
-        assert gm.position() == 65
-        gm.free()
-    a, b = outs
-    assert np.array_equal(a[0], b[0]) and np.array_equal(a[2], b[2])
-    assert np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
-    assert np.array_equal(a[3][0], b[3][0]) and np.array_equal(a[3][1], b[3][1])
+    from softmodel import SMOOTH_MIX, soft_model, steps_pass
+    cfg = dict(CFG, num_heads=heads[0], num_kv_heads=heads[1])
+    rng = np.random.default_rng(21)
+    smooth = mix == "smooth"
+    mix = SMOOTH_MIX if smooth else mix
+    model = soft_model(rng, cfg, mix) if (mix is None or smooth) else synth.make_llama(rng, cfg, mix)
+    gm = GpuModel.load(eng, model)
+    orc = oracle.LlamaOracle(model)
+    prefill(rng, cfg, gm, orc, 29)
+    toks = [int(t) for t in rng.integers(0, cfg["vocab_size"], nbatch)]
+    got = gm.forward_batch_and_read(toks).reshape(nbatch, -1)
+    assert gm.position() == 29 + nbatch
+    res = [close(got[k], orc.forward(t)) for k, t in enumerate(toks)]
+    errs, l2s = [r[0] for r in res], [r[1] for r in res]
+    assert (max(errs) <= 1e-3 and max(l2s) <= 1e-3) if smooth else steps_pass(errs, l2s), (errs, l2s)
+    k_dev, v_dev = gm.kv_read(1, 29, nbatch)
+    assert close(k_dev, orc.kcache[1, 29:29 + nbatch])[0] <= 1e-3 and close(v_dev, orc.vcache[1, 29:29 + nbatch])[0] <= 1e-3
+    # reject everything after the second token, verify another continuation from there
+    gm.rollback_to(31)
+    orc.pos = 31
+    toks2 = [int(t) for t in rng.integers(0, cfg["vocab_size"], 4)]
+    got2 = gm.forward_batch_and_read(toks2).reshape(4, -1)
+    res = [close(got2[k], orc.forward(t)) for k, t in enumerate(toks2)]
+    errs, l2s = [r[0] for r in res], [r[1] for r in res]
+    assert (max(errs) <= 1e-3 and max(l2s) <= 1e-3) if smooth else steps_pass(errs, l2s), ("after rollback", errs, l2s)
+    gm.free()

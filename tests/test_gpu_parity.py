@@ -224,3 +224,41 @@ def test_errors_instead_of_panics(eng):
         eng.matvec_dev(w, eng.alloc_f32(100), eng.alloc_f32(1), 1)
     with pytest.raises(AliceError):   # batch outside 1..8
         eng.matvec_dev(w, eng.alloc_f32(256 * 9), eng.alloc_f32(9), 9)
+
+
+def test_handles_may_outlive_their_engine():
+    """A binding whose drop order frees the engine first must not crash: handles keep what they need alive."""
+    from alice_llm_b200 import _lib
+    from alice_llm_b200.gpu import GpuEngine, GpuQuantType
+    e = GpuEngine(0)
+    rng = np.random.default_rng(3)
+    w = e.upload_weights_typed(synth.make_q4k(rng, 8, 256), 8, 256, GpuQuantType.Q4K)
+    b = e.alloc_f32(256)
+    q = e.alloc_q8k(256, 1)
+    lib = _lib.load()
+    h, e._h = e._h, None          # destroy the engine behind the wrappers' back, children still alive
+    assert lib.alice_engine_destroy(h) == 0
+    w.free(); b.free(); q.free()
+
+
+def test_host_pointer_entry_points_match_oracle(oracle):
+    """alice_matvec_host / alice_dequantize_host are what a gguf.rs-level binding of quantized_matvec and
+    dequantize_weight_row calls (host slices in, host slices out)."""
+    import ctypes as C
+    from alice_llm_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(12)
+    for qtype, rows, cols in [(Q4_K, 300, 4096), (Q6_K, 64, 1024), (Q8_0, 33, 512), (Q1_0, 17, 1024)]:
+        data = synth.make_weights(qtype, rng, rows, cols)
+        x = synth.make_x(rng, cols)
+        y = np.empty(rows, np.float32)
+        rc = lib.alice_matvec_host(qtype, C.c_void_p(data.ctypes.data), data.size, rows, cols, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data))
+        assert rc == 0, lib.alice_last_error()
+        assert_close(y, oracle.matvec(qtype, x, data, rows, cols), f"host matvec {synth.TYPE_NAMES[qtype]}")
+        rb = synth.row_bytes(qtype, cols)
+        out = np.empty(cols, np.float32)
+        rc = lib.alice_dequantize_host(qtype, C.c_void_p(data.ctypes.data), rb, C.c_void_p(out.ctypes.data), cols)
+        assert rc == 0, lib.alice_last_error()
+        # (dequantize_weight_row itself returns zeros for Q1_0 / Q2_0, src/gguf.rs:6168-6195; the library dequantizes them)
+        assert np.array_equal(bits(out), bits(oracle.dequantize(qtype, data[:rb])))
+    assert lib.alice_matvec_host(2, C.c_void_p(data.ctypes.data), data.size, rows, cols, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)) != 0

@@ -12,6 +12,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def main():
@@ -25,6 +26,12 @@ def main():
                vocab_size=1000, max_seq_len=96, rope_theta=500000.0, eps=1e-5)
     rng = np.random.default_rng(11)
     model = synth.make_llama(rng, cfg)
+    # q / k / v scaled down so that the softmax spreads over the pre-filled rows (a dropped or misplaced part of
+    # the sharded KV cache then shows up in the logits)
+    from softmodel import scale_blocks
+    for L in model["layers"]:
+        for n in ("q", "k", "v"):
+            L[n] = scale_blocks(L[n], 0.3 / float(np.sqrt(cfg["hidden_dim"])))
     kv_dim = cfg["num_kv_heads"] * cfg["head_dim"]
     npos = 21
     pre = [(rng.standard_normal((npos, kv_dim), dtype=np.float32), rng.standard_normal((npos, kv_dim), dtype=np.float32))
