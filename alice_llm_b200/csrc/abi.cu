@@ -496,7 +496,7 @@ static int ensure_shadow(alice_engine* e, size_t bytes) {
 
 // f32 input of a matvec. K-quant weights want it as Q8_K blocks (q4k_matvec = quantize_row_q8_k + q4k_matvec_preq,
 // src/gguf.rs:3600-3603): either the blocks the kernel that produced x left behind (the fused SwiGLU does that for its
-// output, which only ever feeds a down projection), or a small quantizer kernel into engine scratch, ahead of the matvec.
+// output, which only ever feeds a down projection), or the matvec kernel quantizes the vector in its own prologue.
 static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_buf* x,
                          alice_buf* y, uint32_t batch, const char* who) {
     if (!e || !w0 || !x || !y) return fail(ALICE_E_INVALID, "%s: null argument", who);
@@ -510,16 +510,9 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
     const bool kq = format_uses_q8k(d.fmt);
     if (kq) {
         const uint32_t nb = d.cols / 256;
-        if (e->shadow_of == x && e->shadow_cols == d.cols && e->shadow_batch == batch) {
-            v = view_at(e->shadow, nb, batch);
-        } else {
-            int rc = ensure_scratch(e, Q8KLayout::make(nb, batch).total);
-            if (rc) return rc;
-            launch_quantize_q8k(x->p, d.cols, batch, e->scratch, e->stream, e->pdl);
-            CU(cudaGetLastError());
-            v = view_at(e->scratch, nb, batch);
-        }
+        if (e->shadow_of == x && e->shadow_cols == d.cols && e->shadow_batch == batch) v = view_at(e->shadow, nb, batch);
     }
+    const bool have_q8 = kq && v.qs != nullptr;
     if (e->shadow_of == y) e->shadow_of = nullptr;   // y is about to be rewritten
     Publish pub{};
     const bool leave_q8 = w1 && kq && y->owned && d.rows % 256 == 0 && d.rows / 256 <= ALICE_ENGINE_TICKETS && y->len == (size_t)batch * d.rows;
@@ -530,7 +523,7 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
         pub.mode = PUB_BLOCKS; pub.n = d.rows; pub.batch = batch; pub.src = y->p; pub.tickets = e->tickets;
         pub.dst.qs = const_cast<int8_t*>(sv.qs); pub.dst.d = const_cast<float*>(sv.d); pub.dst.bsums = const_cast<int16_t*>(sv.bsums);
     }
-    int rc = run_gemv(e, w0, w1, kq ? &v : nullptr, kq ? nullptr : x->p, y->p, batch, leave_q8 ? &pub : nullptr, who);
+    int rc = run_gemv(e, w0, w1, have_q8 ? &v : nullptr, have_q8 ? nullptr : x->p, y->p, batch, leave_q8 ? &pub : nullptr, who);
     if (!rc && leave_q8) { e->shadow_of = y; e->shadow_cols = d.rows; e->shadow_batch = batch; }
     return rc;
 }

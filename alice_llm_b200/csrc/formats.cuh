@@ -29,15 +29,16 @@ struct ActGroup64 {
     float d8;              // Q8_K block scale
 };
 
-// The Q8_K blocks live in global memory, written by an earlier kernel (possibly on another SM): L2 loads.
+// The Q8_K blocks sit in shared memory (fetched once per CTA) or, for shapes where that copy is not possible, in
+// global memory written by an earlier kernel: generic loads serve both (a kernel boundary lies in between).
 __device__ __forceinline__ void load_act_group64(ActGroup64& r, const Q8KView& v, uint32_t u, bool valid) {
     if (!valid) { r = ActGroup64{}; return; }
     const uint4* q = reinterpret_cast<const uint4*>(v.qs + (size_t)u * 64);
-    r.p0 = __ldcg(q); r.p1 = __ldcg(q + 1); r.p2 = __ldcg(q + 2); r.p3 = __ldcg(q + 3);
-    const uint2 b = __ldcg(reinterpret_cast<const uint2*>(v.bsums + (size_t)u * 4));
+    r.p0 = q[0]; r.p1 = q[1]; r.p2 = q[2]; r.p3 = q[3];
+    const uint2 b = *reinterpret_cast<const uint2*>(v.bsums + (size_t)u * 4);
     r.bs0 = (int)(short)(b.x & 0xffff) + (int)(short)(b.x >> 16);
     r.bs1 = (int)(short)(b.y & 0xffff) + (int)(short)(b.y >> 16);
-    r.d8 = __ldcg(v.d + (u >> 2));
+    r.d8 = v.d[u >> 2];
 }
 
 // ── Q4_K: 144-byte block = d f16, dmin f16, 12 B scales, 128 B nibbles (src/gguf.rs:903-939).
@@ -47,7 +48,7 @@ struct FmtQ4K {
     static constexpr uint32_t BLOCK_BYTES = 144, UNITS_PER_BLOCK = 4;
     using Act = ActGroup64;
     static constexpr bool USES_Q8K = true;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act_group64(r, a.q8, u, valid); }
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& q8, const float*, bool, uint32_t u, bool valid) { load_act_group64(r, q8, u, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t g = u & 3u;
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
@@ -80,7 +81,7 @@ struct FmtQ5K {
     static constexpr uint32_t BLOCK_BYTES = 176, UNITS_PER_BLOCK = 4;
     using Act = ActGroup64;
     static constexpr bool USES_Q8K = true;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act_group64(r, a.q8, u, valid); }
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& q8, const float*, bool, uint32_t u, bool valid) { load_act_group64(r, q8, u, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t g = u & 3u;
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
@@ -121,17 +122,16 @@ struct FmtQ6K {
         float d8;
     };
     static constexpr bool USES_Q8K = true;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView& v, const float*, bool, uint32_t u, bool valid) {
         if (!valid) { r = Act{}; return; }
-        const Q8KView& v = a.q8;
         const uint32_t b = u >> 3, n = (u >> 2) & 1u, l0 = (u & 3u) * 8u;
         const int8_t* q = v.qs + (size_t)b * 256 + n * 128 + l0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            r.p[j] = __ldcg(reinterpret_cast<const uint2*>(q + 32 * j));
+            r.p[j] = *reinterpret_cast<const uint2*>(q + 32 * j);
             r.s[j] = dp4a_ss(0x01010101u, r.p[j].x, dp4a_ss(0x01010101u, r.p[j].y, 0));
         }
-        r.d8 = __ldcg(v.d + b);
+        r.d8 = v.d[b];
     }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t n = (u >> 2) & 1u, l0 = (u & 3u) * 8u;
@@ -178,14 +178,14 @@ struct FmtQ8_0 {
     static constexpr uint32_t BLOCK_BYTES = 34, UNITS_PER_BLOCK = 2;
     struct Act { float x[16]; };
     static constexpr bool USES_Q8K = false;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView&, const float* x, bool cg, uint32_t u, bool valid) {
 #pragma unroll
         for (int i = 0; i < 16; i++) r.x[i] = 0.0f;
         if (!valid) return;
-        const float4* p = reinterpret_cast<const float4*>(a.x + (size_t)u * 16);
+        const float4* p = reinterpret_cast<const float4*>(x + (size_t)u * 16);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float4 v = __ldcg(p + i);
+            const float4 v = cg ? __ldcg(p + i) : p[i];
             r.x[4 * i] = v.x; r.x[4 * i + 1] = v.y; r.x[4 * i + 2] = v.z; r.x[4 * i + 3] = v.w;
         }
     }
@@ -223,12 +223,12 @@ __device__ __forceinline__ float masked_sum32(uint32_t m, const float* x) {
 }
 
 struct Act32 { float x[32]; float sum; };
-__device__ __forceinline__ void load_act32(Act32& r, const float* x, uint32_t u, uint32_t cols, bool valid) {
+__device__ __forceinline__ void load_act32(Act32& r, const float* x, bool cg, uint32_t u, uint32_t cols, bool valid) {
     r.sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 32; i++) {
         const uint32_t c = u * 32 + i;
-        r.x[i] = (valid && c < cols) ? __ldcg(x + c) : 0.0f;
+        r.x[i] = (valid && c < cols) ? (cg ? __ldcg(x + c) : x[c]) : 0.0f;
         r.sum += r.x[i];
     }
 }
@@ -239,7 +239,7 @@ struct FmtQ1_0 {
     static constexpr uint32_t BLOCK_BYTES = 18, UNITS_PER_BLOCK = 4;
     using Act = Act32;
     static constexpr bool USES_Q8K = false;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, const float* x, bool cg, uint32_t u, bool valid) { load_act32(r, x, cg, u, a.cols, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t blk = rb + (u >> 2) * BLOCK_BYTES;
         const uint32_t bits = lds32_u2(blk + 2 + (u & 3u) * 4);
@@ -254,11 +254,11 @@ struct FmtQ2_0 {
     static constexpr uint32_t BLOCK_BYTES = 34, UNITS_PER_BLOCK = 8;
     struct Act { float x[16]; float sum; };
     static constexpr bool USES_Q8K = false;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) {
+    __device__ static void load_act(Act& r, const StreamArgs&, const Q8KView&, const float* x, bool cg, uint32_t u, bool valid) {
         r.sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            r.x[i] = valid ? __ldcg(a.x + (size_t)u * 16 + i) : 0.0f;
+            r.x[i] = valid ? (cg ? __ldcg(x + (size_t)u * 16 + i) : x[(size_t)u * 16 + i]) : 0.0f;
             r.sum += r.x[i];
         }
     }
@@ -280,7 +280,7 @@ struct FmtTernary {
     static constexpr uint32_t UNIT_COLS = 32;
     using Act = Act32;
     static constexpr bool USES_Q8K = false;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, const float* x, bool cg, uint32_t u, bool valid) { load_act32(r, x, cg, u, a.cols, valid); }
     __device__ static float unit(uint32_t rb, uint32_t u, const Act& x, const StreamArgs& a) {
         const uint32_t pm = lds32(rb + 4 * u), nm = lds32(rb + (a.row_bytes >> 1) + 4 * u);
         return masked_sum32(pm, x.x) - masked_sum32(nm, x.x);
@@ -295,7 +295,7 @@ struct FmtSparseTernary {
     static constexpr uint32_t UNIT_COLS = 32;
     using Act = Act32;
     static constexpr bool USES_Q8K = false;
-    __device__ static void load_act(Act& r, const StreamArgs& a, uint32_t u, bool valid) { load_act32(r, a.x, u, a.cols, valid); }
+    __device__ static void load_act(Act& r, const StreamArgs& a, const Q8KView&, const float* x, bool cg, uint32_t u, bool valid) { load_act32(r, x, cg, u, a.cols, valid); }
     __device__ static float half(uint32_t w, const float* x) {
         const uint32_t act = w & 0x55555555u, neg = (w >> 1) & act;
         float s = 0.0f;

@@ -261,8 +261,9 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     }
     // the input arrives prepared: Q8_K blocks for the K-quants, the f32 vector for everything else
     if (format_uses_q8k(w0.fmt)) {
-        if (!q8 || !q8->qs) return ALICE_E_INVALID;
-        if (q8->nb * 256u != w0.cols) return ALICE_E_SHAPE;
+        if (q8 ? q8->qs == nullptr : x == nullptr) return ALICE_E_INVALID;
+        if (q8 && q8->nb * 256u != w0.cols) return ALICE_E_SHAPE;
+        if (q8 && op.norm_w) return ALICE_E_INVALID;   // the norm needs the f32 vector
     } else if (!x) {
         return ALICE_E_INVALID;
     }
@@ -284,7 +285,7 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     if (op.pub) a.pub = *op.pub;
     a.row_stride = a.row_bytes;   // contiguous staging unless the tensor-core planner says otherwise
     if ((w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 &&
-        ((uintptr_t)x & 15) == 0 && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
+        ((uintptr_t)x & 15) == 0 && !op.norm_w && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
         return ALICE_OK;
 
     // warps per row: just enough lanes for one unit each, at most all eight
@@ -299,7 +300,38 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     const uint32_t per_sm = kl <= 2 ? 2 : 1;
     const uint32_t full_budget = kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1;
     uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
-    const uint32_t budget = full_budget - HDR_BYTES;
+    // activation area: the input, fetched once per CTA (bulk copies when addresses and sizes are multiples of 16)
+    uint32_t act_bytes = 0;
+    const bool kq = format_uses_q8k(w0.fmt);
+    const uint32_t nb = w0.cols / 256u;
+    const uint32_t q8_area = (nb * 288u + ((nb * 4u + 15u) & ~15u) + 127u) & ~127u;
+    if (kq && q8) {
+        a.act_n = 3;
+        a.act_bulk = (!((uintptr_t)q8->qs & 15) && !((uintptr_t)q8->bsums & 15) && !((uintptr_t)q8->d & 15)) ? 1u : 0u;
+        a.act_src[0] = q8->qs; a.act_bytes[0] = nb * 256u; a.act_off[0] = 0;
+        a.act_src[1] = q8->bsums; a.act_bytes[1] = nb * 32u; a.act_off[1] = nb * 256u;
+        // with bulk copies the d piece is rounded up to 16 bytes (the array is padded in memory)
+        a.act_src[2] = q8->d; a.act_bytes[2] = a.act_bulk ? (nb * 4u + 15u) & ~15u : nb * 4u; a.act_off[2] = nb * 288u;
+        act_bytes = q8_area;
+    } else if (kq || op.norm_w) {
+        // raw f32 vector (+ norm weights): every CTA prepares its own copy (stream_prologue)
+        if (((uintptr_t)x & 3) || (op.norm_w && ((uintptr_t)op.norm_w & 3))) return ALICE_E_INVALID;
+        const uint32_t vec = (w0.cols * 4u + 127u) & ~127u;
+        a.pro_mode = 1; a.pro_norm_w = op.norm_w; a.pro_eps = op.norm_eps;
+        a.pro_roundtrip = (!kq && op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
+        a.act_n = 1;
+        a.act_bulk = (w0.cols % 4 == 0 && !((uintptr_t)x & 15)) ? 1u : 0u;
+        a.act_src[0] = x; a.act_bytes[0] = w0.cols * 4u; a.act_off[0] = 0;
+        a.pro_q8_off = vec;
+        act_bytes = vec + (kq ? q8_area : 0u);
+    } else if (w0.cols * 4u <= 64u * 1024u && !((uintptr_t)x & 3)) {
+        a.act_n = 1;
+        a.act_bulk = (w0.cols % 4 == 0 && !((uintptr_t)x & 15)) ? 1u : 0u;
+        a.act_src[0] = x; a.act_bytes[0] = w0.cols * 4u; a.act_off[0] = 0;
+        act_bytes = (w0.cols * 4u + 127u) & ~127u;
+    }
+    if (HDR_BYTES + act_bytes + 8192 > full_budget) return ALICE_E_SHAPE;
+    const uint32_t budget = full_budget - HDR_BYTES - act_bytes;
     const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
     // rows per warp set per stage: as many as the ring allows (per-stage costs are amortised over
     // them) while every CTA still gets about two stages of work. Measured on 4096 x 4096 Q4_K in a chain of
@@ -330,7 +362,7 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     a.seg_g0[op.nw] = a.groups;
     pl.grid = std::min(ctas, a.groups);
     a.tab_off = HDR_BYTES + nst * stage;
-    pl.smem = HDR_BYTES + (size_t)nst * stage;
+    pl.smem = HDR_BYTES + (size_t)nst * stage + act_bytes;
     pl.kl = kl; pl.swiglu = sw; pl.stage = stage;
     pl.mma = false; pl.ksplit = 1; pl.ctas_per_sm = per_sm;
     pl.args = a;
@@ -427,17 +459,17 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
 
 // ---- stand-alone hand-over kernel ----------------------------------------------------------------------------
 namespace {
-__global__ void __launch_bounds__(256) publish_vector_kernel(const Publish p, int* status) {
+__global__ void __launch_bounds__(256) publish_vector_kernel(const __grid_constant__ Publish p, int* status) {
     __shared__ double red[8];
     __shared__ int ok;
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     if (p.npeers) {
         if (threadIdx.x == 0) ok = publish_peer_gate(p, status) ? 1 : 0;
         __syncthreads();
         if (!ok) return;
     }
-    if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<8, 1>(p, red);
+    if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<8, 1>(p, red, true);
 }
 }  // namespace
 

@@ -38,15 +38,19 @@ struct LaunchCfg {
     int force_stages; // 0 = automatic
 };
 
-// One streaming matvec with its optional fused stages. The input is always in prepared form: Q8_K blocks for the
-// K-quant formats (q8), the f32 vector for the others (x); see csrc/publish.cuh.
+// One streaming matvec with its optional fused stages. The input is either already prepared (Q8_K blocks for the
+// K-quant formats, the final f32 vector for the others; see csrc/publish.cuh) or the raw f32 vector, which every CTA
+// then prepares for itself in shared memory (rms_norm, Q8_K quantization).
 struct GemvOp {
     const WeightDesc* w[3] = {nullptr, nullptr, nullptr};  // 1..3 matrices of one format and width sharing the input
     uint32_t nw = 1;
     uint32_t y_off[3] = {0, 0, 0};                         // output offset (floats) of each matrix inside y
     const WeightDesc* up = nullptr;                        // fused SwiGLU: w[0] = gate, up = up (nw must be 1)
     const Q8KView* q8 = nullptr;                           // K-quants: input vector 0 as Q8_K; vector k follows at qs + k*cols, d + k*nb, bsums + k*nb*16
-    const float* x = nullptr;                              // other formats: input, x[k*cols + c]
+    const float* x = nullptr;                              // f32 input, x[k*cols + c]; K-quants without q8 quantize it per CTA
+    const float* norm_w = nullptr;                         // rms_norm of x with these weights first, in every CTA (per-lane kernels only)
+    float norm_eps = 0.0f;
+    bool q8k_roundtrip = false;                            // with norm_w, f32-activation formats: round the vector to the Q8_K grid
     uint32_t batch = 1;                                    // input vectors
     uint32_t y_stride = 0;                                 // floats between the outputs of consecutive vectors (0: the rows of this op)
     const float* resid = nullptr;                          // y = resid + result (same layout as y)

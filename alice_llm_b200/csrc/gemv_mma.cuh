@@ -489,7 +489,7 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
 
 // One matvec per launch, bit-plane tensor-core form. CTAS: resident CTAs per SM the launch is planned for.
 template <class M, bool SWIGLU, int CTAS, bool PEER>
-__global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
     constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
     cx.sm = sm; cx.smem_raw = smem_raw; cx.ring = smem_u32(smem_raw) + HDR;
     cx.stage_stride = a.cap * (SWIGLU ? 2u : 1u); cx.nstages = a.nstages; cx.cc = 0;
     cx.limit = a.wait_limit > 0 ? a.wait_limit : WAIT_CYCLE_LIMIT;
-    if (threadIdx.x == 0) stream_init_ring(sm, a.nstages);
+    stream_init_ring(sm, a.nstages);
     __syncthreads();
     pdl_launch_dependents();
     if ((threadIdx.x >> 5) == NCW) {

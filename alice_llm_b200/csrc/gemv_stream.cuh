@@ -45,7 +45,27 @@ struct StreamArgs {
     uint32_t cap;        // bytes reserved per matrix per stage (multiple of 128)
     uint32_t batch;      // input vectors sharing one pass over the weights (batch kernels), else 1
     uint32_t y_stride;   // floats between the outputs of consecutive input vectors
-    uint32_t tab_off;    // shared-memory offset of the activation area (bit-plane digit table / batch Q8_K blocks)
+    uint32_t tab_off;    // shared-memory offset of the activation area (Q8_K blocks / f32 vector / bit-plane digit table)
+    // The prepared input is fetched ONCE per CTA into shared memory with bulk copies (up to three pieces: Q8_K qs, bsums,
+    // d; or the f32 vector), not by every warp from global memory: all CTAs of a launch want the same few KB, and
+    // per-warp loads of the same lines queue up at their L2 slices (measured: 1-5 us per CTA for 4.6 KB).
+    // act_bulk == 0: addresses or sizes do not allow bulk copies; the consumer threads copy the pieces with L2 loads.
+    // act_n == 0 (f32 vector too long for shared memory): the lanes read their columns from global memory.
+    uint32_t act_n;
+    uint32_t act_bulk;
+    // pro_mode != 0: the piece is the raw f32 vector (at offset 0 of the area); every CTA prepares its own copy
+    // (stream_prologue): rms_norm with the weights pro_norm_w (global memory, constants: pulled into L1 while the CTA
+    // waits for the previous kernel), then Q8_K blocks at pro_q8_off (K-quant formats) or the normalised f32 vector in
+    // place (pro_roundtrip: rounded to the Q8_K grid). Redundant across CTAs, but parallel: a single CTA doing it once
+    // for everybody costs a serial chain of ~10 us (ticket, loads, reduction, quantization, each a dependent round trip)
+    // at the end of the producing kernel.
+    uint32_t pro_mode, pro_roundtrip;
+    uint32_t pro_q8_off;
+    const float* pro_norm_w;
+    float pro_eps;
+    const void* act_src[3];
+    uint32_t act_bytes[3];   // multiples of 16
+    uint32_t act_off[3];     // offsets inside the activation area, multiples of 16
     // Optional residual epilogue: y[row] = resid[row] + result (resid may alias y)
     const float* resid;
     // Optional greedy-argmax epilogue: atomicMax of (order-preserving bits of y[i]) << 32 | ~i, so the
@@ -150,17 +170,20 @@ __device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t n) {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(n) : "memory");
 }
 
+// Called by every thread of the CTA (one barrier per thread: a single thread initialising all of them costs ~0.6 us
+// on the critical path of a small matvec); the caller follows with __syncthreads().
 __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstages) {
-    for (uint32_t s = 0; s < nstages; s++) {
-        mbar_init(smem_u32(&sm->full[s]), 1);
-        mbar_init(smem_u32(&sm->empty[s]), NCW);
-        for (uint32_t q = 0; q < NCW; q++) mbar_init(smem_u32(&sm->red[s][q]), RED_COUNT);
+    const uint32_t t = threadIdx.x;
+    if (t < nstages) mbar_init(smem_u32(&sm->full[t]), 1);
+    else if (t < 2 * nstages) mbar_init(smem_u32(&sm->empty[t - nstages]), NCW);
+    else if (t < (2 + NCW) * nstages) mbar_init(smem_u32(&sm->red[(t - 2 * nstages) / NCW][(t - 2 * nstages) % NCW]), RED_COUNT);
+    else if (t == (2 + NCW) * nstages) {
+        mbar_init(smem_u32(&sm->act_bar), 1);
+        sm->abort_flag = 0;
+        sm->pub_last = 0;
+        sm->pub_mask = 0;
     }
-    mbar_init(smem_u32(&sm->act_bar), 1);
-    sm->abort_flag = 0;
-    sm->pub_last = 0;
-    sm->pub_mask = 0;
-    mbar_fence_init();
+    if (t <= (2 + NCW) * nstages) mbar_fence_init();
 }
 
 // Producer side of one matvec: streams this CTA's row groups of `a` through the ring. One thread.
@@ -272,7 +295,7 @@ static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSm
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         if (!sm->pub_last) return;
-        if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<NCW, 1>(p, sm->norm_part);
+        if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<NCW, 1>(p, sm->norm_part, true);
         return;
     }
     // PUB_BLOCKS: rows [ra, rb) of the single matrix are this CTA's; a 256-row block is prepared by the CTA whose
@@ -312,9 +335,74 @@ static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSm
     }
 }
 
+// Per-CTA input preparation (pro_mode), run by the NCW consumer warps on the f32 vector that bulk copies have just
+// put into shared memory. Warp w owns the 256-element blocks w, w + NCW, ...; a lane owns 8 consecutive elements.
+//   wn != null: rms_norm (src/llama3.rs:5244-5256) with the weights wn (global): f64 sum of squares, f32 mean / sqrt / divide, (x * scale) * w;
+//   q8 != null: Q8_K blocks (quantize_row_q8_k, src/gguf.rs:1323-1374) into qs | bsums | d at q8 (cols % 256 == 0);
+//   else the normalised vector goes back to xn in place (roundtrip: as d * q of its Q8_K quantisation, which is what
+//   quantized_matvec_preq hands a Q1_0 / Q2_0 matvec, src/gguf.rs:4593-4605).
+// One compact out-of-line copy with rolled loops: it runs once per launch, so every instruction is an instruction-cache miss.
+static __device__ __noinline__ void stream_prologue(StreamSmem* sm, float* xn, const float* wn, float eps, uint32_t cols, uint8_t* q8,
+                                                    bool roundtrip) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nblk = (cols + QK_K - 1) / QK_K, nb = cols / QK_K;
+    auto load8 = [&](const float* p, uint32_t i0) {
+        Q8KLaneInput r;
+        if (i0 + 8 <= cols && (reinterpret_cast<uintptr_t>(p + i0) & 15) == 0) {
+            r.a = *reinterpret_cast<const float4*>(p + i0);
+            r.b = *reinterpret_cast<const float4*>(p + i0 + 4);
+        } else {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = i0 + j < cols ? p[i0 + j] : 0.0f;
+            r.a = make_float4(v[0], v[1], v[2], v[3]);
+            r.b = make_float4(v[4], v[5], v[6], v[7]);
+        }
+        return r;
+    };
+    float scale = 1.0f;
+    if (wn != nullptr) {
+        double ss = 0.0;
+#pragma unroll 1
+        for (uint32_t b = warp; b < nblk; b += NCW) ss += pub_sumsq(load8(xn, b * QK_K + lane * 8));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sm->norm_part[warp] = ss;
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        double tot = 0.0;
+#pragma unroll
+        for (int w = 0; w < NCW; w++) tot += sm->norm_part[w];
+        const float mean = (float)(tot / (double)cols);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    }
+    int8_t* qs_s = reinterpret_cast<int8_t*>(q8);
+    int16_t* bs_s = reinterpret_cast<int16_t*>(q8 + (size_t)nb * 256);
+    float* d_s = reinterpret_cast<float*>(q8 + (size_t)nb * 288);
+#pragma unroll 1
+    for (uint32_t b = warp; b < nblk; b += NCW) {
+        const uint32_t i0 = b * QK_K + lane * 8;
+        Q8KLaneInput v = load8(xn, i0);
+        if (wn != nullptr) v = pub_scale(v, scale, load8(wn, i0));
+        if (q8 != nullptr) {
+            q8k_quantize_block_warp(v, lane, qs_s + (size_t)b * QK_K, d_s + b, bs_s + (size_t)b * 16);
+        } else if (roundtrip) {
+            q8k_quantize_block_warp<true>(v, lane, nullptr, nullptr, nullptr, xn + (size_t)b * QK_K);
+        } else if (wn != nullptr) {
+            if (i0 + 8 <= cols) {
+                *reinterpret_cast<float4*>(xn + i0) = v.a;
+                *reinterpret_cast<float4*>(xn + i0 + 4) = v.b;
+            } else {
+                const float e[8] = {v.a.x, v.a.y, v.a.z, v.a.w, v.b.x, v.b.y, v.b.z, v.b.w};
+                for (uint32_t j = 0; j < 8 && i0 + j < cols; j++) xn[i0 + j] = e[j];
+            }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+}
+
 // F supplies:
 //   struct Act;                                            per-position activation registers
-//   static void load_act(Act&, const StreamArgs&, uint32_t u, bool valid)
+//   static void load_act(Act&, const StreamArgs&, const Q8KView&, const float* x, bool x_global, uint32_t u, bool valid)
 //   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
 //   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
 // Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1). Returns false after an abort.
@@ -330,11 +418,55 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     unsigned long long* const argmax_key = a.argmax_key;
     const uint32_t nseg = a.nseg;
 
+    // the prepared input: one fetch per CTA into shared memory, then every lane takes its own columns into registers
+    Q8KView q8 = a.q8;
+    const float* xin = a.x;
+    if (a.act_n) {
+        uint8_t* area = cx.smem_raw + a.tab_off;
+        if (a.act_bulk) {
+            const uint32_t ab = smem_u32(&sm->act_bar);
+            if (threadIdx.x == 0) {
+                uint32_t total = 0;
+                for (uint32_t i = 0; i < a.act_n; i++) total += a.act_bytes[i];
+                mbar_arrive_expect_tx(ab, total);
+                for (uint32_t i = 0; i < a.act_n; i++)
+                    bulk_g2s(smem_u32(area + a.act_off[i]), a.act_src[i], a.act_bytes[i], ab);
+            }
+            if (!wait_or_abort(ab, 0, abort_flag, a.status, KERR_WAIT_FULL, cx.limit)) return false;
+        } else {
+            for (uint32_t i = 0; i < a.act_n; i++) {   // pieces are whole 32-bit words, 4-byte aligned
+                const uint32_t* src = static_cast<const uint32_t*>(a.act_src[i]);
+                uint32_t* dst = reinterpret_cast<uint32_t*>(area + a.act_off[i]);
+                for (uint32_t w = threadIdx.x; w < a.act_bytes[i] / 4; w += NCW * 32) dst[w] = __ldcg(src + w);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        }
+        if (a.pro_mode) {
+            float* xn = reinterpret_cast<float*>(area);
+            uint8_t* q8a = F::USES_Q8K ? area + a.pro_q8_off : nullptr;
+            stream_prologue(sm, xn, a.pro_norm_w, a.pro_eps, a.cols, q8a, a.pro_roundtrip != 0);
+            if (F::USES_Q8K) {
+                const uint32_t nb = a.cols / QK_K;
+                q8.qs = reinterpret_cast<const int8_t*>(q8a);
+                q8.bsums = reinterpret_cast<const int16_t*>(q8a + (size_t)nb * 256);
+                q8.d = reinterpret_cast<const float*>(q8a + (size_t)nb * 288);
+                q8.nb = nb;
+            } else {
+                xin = xn;
+            }
+        } else if (F::USES_Q8K) {
+            q8.qs = reinterpret_cast<const int8_t*>(area + a.act_off[0]);
+            q8.bsums = reinterpret_cast<const int16_t*>(area + a.act_off[1]);
+            q8.d = reinterpret_cast<const float*>(area + a.act_off[2]);
+        } else {
+            xin = reinterpret_cast<const float*>(area + a.act_off[0]);
+        }
+    }
     typename F::Act act[KL];
 #pragma unroll
     for (int k = 0; k < KL; k++) {
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-        F::load_act(act[k], a, u, u < a.units);
+        F::load_act(act[k], a, q8, xin, a.act_n == 0, u, u < a.units);
     }
 
     // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
@@ -424,7 +556,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
 
 // One matvec per launch.
 template <class F, int KL, bool SWIGLU, bool PEER>
-__global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const StreamArgs a) {
+__global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
     constexpr uint32_t HDR = (sizeof(StreamSmem) + 127) & ~127u;
@@ -432,7 +564,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     cx.sm = sm; cx.smem_raw = smem_raw; cx.ring = smem_u32(smem_raw) + HDR;
     cx.stage_stride = a.cap * (SWIGLU ? 2u : 1u); cx.nstages = a.nstages; cx.cc = 0;
     cx.limit = a.wait_limit > 0 ? a.wait_limit : WAIT_CYCLE_LIMIT;
-    if (threadIdx.x == 0) stream_init_ring(sm, a.nstages);
+    stream_init_ring(sm, a.nstages);
     __syncthreads();
     pdl_launch_dependents();
     if ((threadIdx.x >> 5) == NCW) {

@@ -12,26 +12,35 @@ namespace alice {
 
 // hidden[c] = d * q of row `token` of a Q8_0 table (dequantize_q8_0, src/gguf.rs:990-1004); the
 // CPU model dequantizes the whole table at load (src/llama3.rs:12890) and copies a row per token.
-__global__ void __launch_bounds__(256) embed_q8_0_kernel(const EmbedArgs a) {
+__global__ void __launch_bounds__(256) embed_q8_0_kernel(const __grid_constant__ EmbedArgs a) {
     __shared__ double red[8];
+    pdl_launch_dependents();   // the next kernel may become resident (and prefetch its weights) while this one waits
     pdl_wait();
-    pdl_launch_dependents();
     const uint32_t pos0 = (uint32_t)*a.pos;
     for (uint32_t i = threadIdx.x; i < 64 * a.batch; i += blockDim.x) rope_table_entry(a.rope_tab + (size_t)(i >> 6) * 128, i & 63, pos0 + (i >> 6), a.rope_freq);
-    for (uint32_t k = 0; k < a.batch; k++) {
+    // one thread per 34-byte block (f16 scale + 32 int8): 17 independent 16-bit loads, so the row costs one memory
+    // round trip instead of one per element
+    const uint32_t nblk = a.cols / 32;
+    for (uint32_t i = threadIdx.x; i < nblk * a.batch; i += blockDim.x) {
+        const uint32_t k = i / nblk, b = i % nblk;
         uint32_t t = (uint32_t)a.tokens[k];
         if (t >= a.vocab) t = 0;
-        const uint8_t* row = a.table + (size_t)t * (a.cols / 32) * 34;
-        for (uint32_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
-            const uint8_t* b = row + (c >> 5) * 34;
-            const float d = f16_bits_to_f32((uint32_t)b[0] | ((uint32_t)b[1] << 8));
-            a.hidden[(size_t)k * a.cols + c] = __fmul_rn(d, (float)(int8_t)b[2 + (c & 31)]);
+        const unsigned short* src = reinterpret_cast<const unsigned short*>(a.table + (size_t)t * nblk * 34 + (size_t)b * 34);
+        unsigned short h[17];
+#pragma unroll
+        for (int j = 0; j < 17; j++) h[j] = __ldg(src + j);
+        const float d = f16_bits_to_f32(h[0]);
+        float* out = a.hidden + (size_t)k * a.cols + (size_t)b * 32;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            out[2 * j] = __fmul_rn(d, (float)(int8_t)(h[1 + j] & 0xff));
+            out[2 * j + 1] = __fmul_rn(d, (float)(int8_t)(h[1 + j] >> 8));
         }
     }
     if (a.pub.mode == PUB_VECTOR && (a.pub.dst.qs != nullptr || a.pub.dst.xn != nullptr)) {
         __threadfence();
         __syncthreads();
-        publish_vector<8, 0>(a.pub, red);
+        publish_vector<8, 0>(a.pub, red, true);
     }
 }
 
@@ -39,10 +48,10 @@ __global__ void __launch_bounds__(256) embed_q8_0_kernel(const EmbedArgs a) {
 // for NeoX, freq = 1 / theta^(i_even / d), angle = pos * freq; a lane owns dims 4*lane .. 4*lane+3 of a
 // head vector (head_dim = 128, so a NeoX partner sits in lane ^ 16).
 template <int GROUP>
-__global__ void __launch_bounds__(256, GROUP <= 5 ? 2 : 1) attn_fused_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256, GROUP <= 5 ? 2 : 1) attn_fused_kernel(const __grid_constant__ AttnArgs a) {
     __shared__ AttnSmem<GROUP> sh;
+    pdl_launch_dependents();   // the next kernel may become resident (and prefetch its weights) while this one waits
     pdl_wait();
-    pdl_launch_dependents();
     attn_fused_body<GROUP>(a, (uint32_t)*a.pos, blockIdx.x, blockIdx.y, blockIdx.z, &sh);
 }
 
@@ -52,8 +61,8 @@ __global__ void __launch_bounds__(256, GROUP <= 5 ? 2 : 1) attn_fused_kernel(con
 __global__ void finish_step_kernel(unsigned long long* __restrict__ keys, uint32_t nkeys, int* __restrict__ token,
                                    int* __restrict__ pos, int* __restrict__ trace, int write_token, uint32_t advance,
                                    unsigned int* __restrict__ epoch) {
+    pdl_launch_dependents();   // the next kernel may become resident (and prefetch its weights) while this one waits
     pdl_wait();
-    pdl_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         unsigned long long k = 0ull;
         for (uint32_t i = 0; i < nkeys; i++) {

@@ -107,11 +107,17 @@ Q8KView q8_view(uint8_t* base, uint32_t n) {
     return v;
 }
 
-// Which prepared forms of a vector its consumers need.
+// The bit-plane tensor-core kernels (Q1_0, Q2_0, ternary formats) take their input as a finished f32 vector in global
+// memory; every other kernel prepares the raw vector per CTA (rms_norm, Q8_K) in its own prologue.
+bool wants_prepared(const WeightDesc& w) {
+    return (w.fmt == WF_Q1_0 || w.fmt == WF_Q2_0 || w.fmt == WF_TERNARY || w.fmt == WF_SPARSE_TERNARY) && w.cols % 4 == 0;
+}
+// Which prepared forms of a vector its consumers need from the kernel that produces it.
 struct Need { bool q8 = false, xn = false, roundtrip = false; };
 void need_of(Need& nd, const WeightDesc& w, bool via_preq) {
-    if (format_uses_q8k(w.fmt)) nd.q8 = true;
-    else { nd.xn = true; if (via_preq && preq_roundtrip(w)) nd.roundtrip = true; }
+    if (!wants_prepared(w)) return;
+    nd.xn = true;
+    if (via_preq && preq_roundtrip(w)) nd.roundtrip = true;
 }
 void fill_dst(PublishDst& d, const Need& nd, uint8_t* q8_base, float* xn, uint32_t n) {
     d = PublishDst{};
@@ -159,7 +165,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         if (!nccl) return ALICE_OK;
         int g = tp_all_gather(m->e, vec, (size_t)floats_per_rank * sizeof(float));
         if (g) return g;
-        if (p.dst.qs || p.dst.xn) MCU(launch_publish_vector(p, m->e->status, st, pdl));
+        if (p.dst.qs || p.dst.xn) { p.mode = PUB_VECTOR; MCU(launch_publish_vector(p, m->e->status, st, pdl)); }
         return ALICE_OK;
     };
     auto push_rows = [&](GemvOp& op, float* vec) {
@@ -167,9 +173,11 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         op.npeers = m->npeers;
         for (uint32_t q = 0; q < m->npeers; q++) op.peer_y[q] = reinterpret_cast<float*>(on_peer(q, vec));
     };
-    // input of a matvec over `w`: the prepared form of the vector
-    auto set_input = [&](GemvOp& op, const WeightDesc& w, uint8_t* q8_base, Q8KView& view, const float* xf, uint32_t len) {
-        if (format_uses_q8k(w.fmt)) { view = q8_view(q8_base, len); op.q8 = &view; } else op.x = xf;
+    // input of a matvec over `w` that reads the (normalised) hidden state: the prepared f32 vector for the tensor-core
+    // kernels, else the raw vector plus the norm weights (prepared per CTA)
+    auto hidden_input = [&](GemvOp& op, const WeightDesc& w, const float* norm_w, bool via_preq) {
+        if (wants_prepared(w)) op.x = m->hid_xn;
+        else { op.x = m->hidden; op.norm_w = norm_w; op.norm_eps = c.eps; op.q8k_roundtrip = via_preq && preq_roundtrip(w); }
         op.batch = batch;
     };
 
@@ -186,7 +194,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         Publish p;
         vector_pub(p, m->hidden, H, m->layers[0].attn_norm, nd0, m->hid_q8, m->hid_xn, 0);
         p.npeers = 0;     // every rank computes the whole embedding row itself
-        ea.pub = p;
+        if (nd0.xn) ea.pub = p;
     }
     MCU(launch_embed_q8_0(ea, st, pdl));
 
@@ -200,7 +208,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             GemvOp op; Q8KView view;
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
-            set_input(op, L.q, m->hid_q8, view, m->hid_xn, H);
+            hidden_input(op, L.q, L.attn_norm, true);
             op.y = m->qkv; op.y_stride = qkv_stride;
             if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each
@@ -209,26 +217,28 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             for (int i = 0; i < 3; i++) {
                 GemvOp op; Q8KView view;
                 op.w[0] = ws[i];
-                set_input(op, *ws[i], m->hid_q8, view, m->hid_xn, H);
+                hidden_input(op, *ws[i], L.attn_norm, true);
                 op.y = m->qkv + offs[i]; op.y_stride = qkv_stride;
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
         }
         // RoPE, KV append, GQA attention and the split combine in one launch (src/llama3.rs:14307-14362)
-        Need nd_o; need_of(nd_o, L.o, false);
         const uint32_t group = shape.num_heads / shape.num_kv_heads;
         AttnArgs aa{};
         aa.qkv = m->qkv; aa.kcache = kc; aa.vcache = vc; aa.pos = m->d_pos; aa.shape = shape; aa.rope_tab = m->rope_tab;
         aa.neox = (int)c.neox_rope; aa.nsplit = m->nsplit; aa.part = m->attn_part; aa.tickets = m->attn_tickets;
         aa.attn_out = m->attn_out + (size_t)r * lq; aa.out_stride = q_dim; aa.status = m->e->status;
         Publish attn_pub{};
-        const bool per_head_q8 = nd_o.q8 && n == 1 && group % 2 == 0;
+        // a K-quant output projection takes the attention output as Q8_K: written by the attention kernel itself when a
+        // KV head's outputs are whole blocks, else quantized in the projection's own prologue
+        const bool per_head_q8 = format_uses_q8k(L.o.fmt) && n == 1 && group % 2 == 0 && q_dim % 256 == 0;
         if (per_head_q8) {
             const Q8KView v = q8_view(m->attn_q8, q_dim);
             aa.q8.qs = const_cast<int8_t*>(v.qs); aa.q8.d = const_cast<float*>(v.d); aa.q8.bsums = const_cast<int16_t*>(v.bsums);
-        } else if (nd_o.q8 || n > 1) {
-            Need nq; nq.q8 = nd_o.q8;
-            vector_pub(attn_pub, m->attn_out, q_dim, nullptr, nq, m->attn_q8, nullptr, 4 * l + 0);
+        }
+        if (n > 1) {   // tensor parallel: the hand-over of the pushed rows
+            Need none;
+            vector_pub(attn_pub, m->attn_out, q_dim, nullptr, none, nullptr, nullptr, 4 * l + 0);
             attn_pub.tickets = m->tk_attn;
             if (!nccl) aa.pub = attn_pub;
         }
@@ -241,11 +251,12 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         {   // output projection + residual (src/llama3.rs:14423, 14468); leaves hidden prepared for gate / up
             GemvOp op; Q8KView view; Publish p;
             op.w[0] = &L.o;
-            set_input(op, L.o, m->attn_q8, view, m->attn_out, q_dim);
+            if (per_head_q8) { view = q8_view(m->attn_q8, q_dim); op.q8 = &view; } else op.x = m->attn_out;
+            op.batch = batch;
             op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
             Need nd; need_of(nd, L.gate, true);
             vector_pub(p, m->hidden, H, L.ffn_norm, nd, m->hid_q8, m->hid_xn, 4 * l + 1);
-            if (!nccl) op.pub = &p;
+            if (!nccl && (nd.xn || n > 1)) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -253,10 +264,10 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         {   // fused SwiGLU gate/up (src/llama3.rs:14497-14534); leaves its output prepared for the down projection
             GemvOp op; Q8KView view; Publish p;
             op.w[0] = &L.gate; op.up = &L.up;
-            set_input(op, L.gate, m->hid_q8, view, m->hid_xn, H);
+            hidden_input(op, L.gate, L.ffn_norm, true);
             op.y = m->ffn_h; op.y_off[0] = r * m->lF; op.y_stride = F;
-            Need nd; need_of(nd, L.down, false);
-            nd.xn = false;      // an f32 down projection reads ffn_h itself
+            Need nd;
+            nd.q8 = n == 1 && format_uses_q8k(L.down.fmt);   // else the down projection reads ffn_h itself
             if (n == 1) {
                 p = Publish{};
                 if (nd.q8) {
@@ -275,7 +286,8 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         {   // down projection + residual (src/llama3.rs:14536-14555); leaves hidden prepared for the next layer / the head
             GemvOp op; Q8KView view; Publish p;
             op.w[0] = &L.down;
-            set_input(op, L.down, m->ffn_q8, view, m->ffn_h, F);
+            if (n == 1 && format_uses_q8k(L.down.fmt)) { view = q8_view(m->ffn_q8, F); op.q8 = &view; } else op.x = m->ffn_h;
+            op.batch = batch;
             op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
             Need nd;
             const float* norm_w;
@@ -288,7 +300,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
                 norm_w = m->out_norm;
             }
             vector_pub(p, m->hidden, H, norm_w, nd, m->hid_q8, m->hid_xn, 4 * l + 3);
-            if (!nccl) op.pub = &p;
+            if (!nccl && (nd.xn || n > 1)) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "down_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -297,7 +309,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     {   // output head on the prepared (normalised) hidden (src/llama3.rs:14590-14604)
         GemvOp op; Q8KView view; Publish p;
         op.w[0] = &m->out;
-        set_input(op, m->out, m->hid_q8, view, m->hid_xn, H);
+        hidden_input(op, m->out, m->out_norm, false);
         op.y = m->logits; op.y_off[0] = r * m->lV; op.y_stride = V;
         if (batch == 1) op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
         if (peer) {

@@ -92,15 +92,16 @@ __device__ __forceinline__ Q8KLaneInput pub_scale(const Q8KLaneInput& v, float s
 }
 
 // One prepared 256-element block leaves the warp: Q8_K fields and / or f32.
-__device__ __forceinline__ void pub_emit_block(const PublishDst& dst, const Q8KLaneInput& v, uint32_t lane, uint32_t vec, uint32_t blk, uint32_t n) {
+__device__ __forceinline__ void pub_emit_block(const PublishDst& dst, const Q8KLaneInput& v, uint32_t lane, uint32_t vec, uint32_t blk, uint32_t n,
+                                               bool store = true) {
     const uint32_t nb = n / QK_K;
     const size_t bi = (size_t)vec * nb + blk;
-    if (dst.qs != nullptr) q8k_quantize_block_warp(v, lane, dst.qs + bi * QK_K, dst.d + bi, dst.bsums + bi * 16);
+    if (dst.qs != nullptr) q8k_quantize_block_warp(v, lane, dst.qs + bi * QK_K, dst.d + bi, dst.bsums + bi * 16, nullptr, store);
     if (dst.xn != nullptr) {
         float* out = dst.xn + (size_t)vec * n + (size_t)blk * QK_K;
         if (dst.roundtrip) {
-            q8k_quantize_block_warp<true>(v, lane, nullptr, nullptr, nullptr, out);
-        } else {
+            q8k_quantize_block_warp<true>(v, lane, nullptr, nullptr, nullptr, out, store);
+        } else if (store) {
             const uint32_t i0 = blk * QK_K + lane * 8;
             if (i0 + 8 <= n) {
                 reinterpret_cast<float4*>(out + lane * 8)[0] = v.a;
@@ -117,13 +118,19 @@ __device__ __forceinline__ void pub_emit_block(const PublishDst& dst, const Q8KL
 // Warp w owns the 256-element blocks w, w + NW, ...; a lane owns 8 consecutive elements of each. Up to PUB_REG_BLOCKS
 // blocks per warp stay in registers between the sum of squares and the second pass (one trip to L2 for vectors of up to
 // NW * PUB_REG_BLOCKS * 256 elements), longer vectors are read twice. `red` = NW doubles of shared memory.
-constexpr int PUB_REG_BLOCKS = 4;
+//
+// Only ONE CTA of a launch runs this, once: its instructions are then in nobody's instruction cache, and a cold walk
+// through a few hundred instructions costs on the order of 10 us (measured 14 us) - far more than the arithmetic.
+// So every CTA of the launch first calls it with store == false while it waits for the previous kernel anyway: same
+// instructions, results discarded, and the real call finds them in the SM's cache.
+constexpr int PUB_REG_BLOCKS = 2;
 template <int NW, int BAR>
-static __device__ __noinline__ void publish_vector(const Publish p, double* red) {
+static __device__ __noinline__ void publish_vector(const Publish& p, double* red, bool store) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n = p.n, nblk = (n + QK_K - 1) / QK_K;
     const bool in_regs = nblk <= (uint32_t)(NW * PUB_REG_BLOCKS);
-    for (uint32_t k = 0; k < p.batch; k++) {
+    const uint32_t nvec = store ? p.batch : 1u;
+    for (uint32_t k = 0; k < nvec; k++) {
         const float* x = p.src + (size_t)k * n;
         Q8KLaneInput xv[PUB_REG_BLOCKS], wv[PUB_REG_BLOCKS];
         float scale = 1.0f;
@@ -161,13 +168,13 @@ static __device__ __noinline__ void publish_vector(const Publish p, double* red)
 #pragma unroll
             for (int i = 0; i < PUB_REG_BLOCKS; i++) {
                 const uint32_t b = warp + (uint32_t)i * NW;
-                if (b < nblk) pub_emit_block(p.dst, p.norm_w != nullptr ? pub_scale(xv[i], scale, wv[i]) : xv[i], lane, k, b, n);
+                if (b < nblk) pub_emit_block(p.dst, p.norm_w != nullptr ? pub_scale(xv[i], scale, wv[i]) : xv[i], lane, k, b, n, store);
             }
         } else {
             for (uint32_t b = warp; b < nblk; b += NW) {
                 const Q8KLaneInput v = pub_load8(x, b * QK_K + lane * 8, n);
-                if (p.norm_w != nullptr) pub_emit_block(p.dst, pub_scale(v, scale, pub_load8_w(p.norm_w, b * QK_K + lane * 8, n)), lane, k, b, n);
-                else pub_emit_block(p.dst, v, lane, k, b, n);
+                if (p.norm_w != nullptr) pub_emit_block(p.dst, pub_scale(v, scale, pub_load8_w(p.norm_w, b * QK_K + lane * 8, n)), lane, k, b, n, store);
+                else pub_emit_block(p.dst, v, lane, k, b, n, store);
             }
         }
     }

@@ -9,8 +9,8 @@ namespace alice {
 __global__ void __launch_bounds__(128) quantize_q8k_kernel(const float* __restrict__ x, uint32_t nblocks,
                                                            int8_t* __restrict__ qs, float* __restrict__ d,
                                                            int16_t* __restrict__ bsums) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (blk >= nblocks) return;

@@ -48,9 +48,11 @@ __device__ __forceinline__ Q8KLaneInput q8k_load_lane(const float* xb, uint32_t 
 }
 // ROUNDTRIP: instead of storing the block, write d * q back as f32 to `rt` (256 floats) - the vector as a
 // kernel sees it after quantized_matvec_preq turned the Q8_K blocks back into f32 (src/gguf.rs:4593-4605).
+// store == false: everything is computed and nothing is written (used to pull the routine's instructions into the
+// SM's instruction cache ahead of time).
 template <bool ROUNDTRIP = false>
 __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, uint32_t lane, int8_t* qs, float* d,
-                                                        int16_t* bsums, float* rt = nullptr) {
+                                                        int16_t* bsums, float* rt = nullptr, bool store = true) {
     const float4 a = in.a, b = in.b;
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     // local first-maximum, then a warp max over (|x| bits, reversed index) keys
@@ -88,13 +90,15 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, u
         dval = __fdiv_rn(1.0f, iscale);
     }
     if (ROUNDTRIP) {
+        if (!store) return;
         float4* out = reinterpret_cast<float4*>(rt + lane * 8);
         out[0] = make_float4(__fmul_rn(dval, (float)q[0]), __fmul_rn(dval, (float)q[1]), __fmul_rn(dval, (float)q[2]), __fmul_rn(dval, (float)q[3]));
         out[1] = make_float4(__fmul_rn(dval, (float)q[4]), __fmul_rn(dval, (float)q[5]), __fmul_rn(dval, (float)q[6]), __fmul_rn(dval, (float)q[7]));
         return;
     }
-    reinterpret_cast<uint2*>(qs)[lane] = make_uint2(w0, w1);
     const int pair = lsum + __shfl_xor_sync(0xffffffffu, lsum, 1);
+    if (!store) return;
+    reinterpret_cast<uint2*>(qs)[lane] = make_uint2(w0, w1);
     if ((lane & 1) == 0) bsums[lane >> 1] = (int16_t)pair;
     if (lane == 0) *d = dval;
 }

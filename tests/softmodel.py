@@ -8,8 +8,11 @@ _F16_FIELDS = {synth.Q4_K: (0, 2), synth.Q5_K: (0, 2), synth.Q6_K: (208,), synth
 
 
 def scale_blocks(entry, factor):
-    """(type, raw blocks) with every f16 block scale multiplied by `factor`."""
+    """(type, raw blocks) with every f16 block scale multiplied by `factor` (ternary planes: the per-row scales)."""
     t, data = entry
+    if t == synth.TERNARY:
+        pos, neg, sc = data
+        return t, (pos, neg, (sc * np.float32(factor)).astype(np.float32))
     blk = data.reshape(-1, synth.BLOCK_BYTES[t]).copy()
     for off in _F16_FIELDS[t]:
         v = blk[:, off:off + 2].copy().view(np.float16).astype(np.float32) * np.float32(factor)
@@ -19,22 +22,29 @@ def scale_blocks(entry, factor):
 
 def soft_model(rng, cfg, mix=None, factor=None):
     """make_llama with the block scales of q / k / v multiplied by `factor` (default 0.3 / sqrt(hidden): the synthetic
-    weights have a positive mean, so an unscaled q . k grows with hidden_dim and the softmax turns one-hot)."""
-    if factor is None:
-        factor = 0.3 / float(np.sqrt(cfg["hidden_dim"]))
+    K-quant weights have a positive mean, so an unscaled q . k grows with hidden_dim and the softmax turns one-hot).
+    For the all-ternary SMOOTH_MIX (zero-mean weights of scale ~0.01) the opposite holds: q, k and o are scaled UP so
+    that the scores spread over a few hundred rows and the attention output is felt in the residual stream."""
     model = synth.make_llama(rng, cfg, mix)
+    if mix is SMOOTH_MIX:
+        factors = {"q": 20.0, "k": 20.0, "v": 8.0, "o": 20.0} if factor is None else {n: factor for n in ("q", "k", "v")}
+    else:
+        if factor is None:
+            factor = 0.3 / float(np.sqrt(cfg["hidden_dim"]))
+        factors = {n: factor for n in ("q", "k", "v")}
     for L in model["layers"]:
-        for n in ("q", "k", "v"):
-            L[n] = scale_blocks(L[n], factor)
+        for n, f in factors.items():
+            L[n] = scale_blocks(L[n], f)
     return model
 
 
-# every projection in Q8_0: activations stay f32 all the way, so the forward is a smooth function of its inputs.
+# every projection in ternary bit planes: the CPU forward (forward_ternary, src/llama3.rs:16951-17064) keeps activations
+# in f32 all the way, so the forward is a smooth function of its inputs.
 # (With K-quant weights the activations are quantized to Q8_K, whose scale is 128 / the SIGNED largest-magnitude
 # element of a block: when two elements of opposite sign tie for the largest magnitude, a 1e-6 perturbation flips the
 # choice and moves that block by ~1 %. Two correct implementations that differ only in f32 summation order then
 # disagree at the 1e-2 level at such a step, so element-wise gates on K-quant MODEL outputs allow for a rare step.)
-SMOOTH_MIX = {n: synth.Q8_0 for n in ("q", "k", "v", "o", "gate", "up", "down", "output")}
+SMOOTH_MIX = {n: synth.TERNARY for n in ("q", "k", "v", "o", "gate", "up", "down", "output")}
 
 
 def steps_pass(errs, l2s, tol=1e-3, rare=1, rare_l2=3e-2):

