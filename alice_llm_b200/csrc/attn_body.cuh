@@ -98,7 +98,7 @@ __device__ __forceinline__ void attn_fused_body(const AttnArgs& a, uint32_t pos0
     // KB positions per warp round: their 2*KB row loads are issued before the first is used, so a round costs one
     // memory round trip instead of KB (positions are still folded in ascending order). The first round is requested
     // before q and the rotation table are looked at: none of these loads depends on another.
-    constexpr int KB = GROUP <= 4 ? 8 : 4;   // k, v of a round: 8 * KB registers
+    constexpr int KB = 4;
     float4 k[KB], v[KB];
     auto load_round = [&](uint32_t tb) {
 #pragma unroll

@@ -78,10 +78,10 @@ int launch_kernel(K kern, const StreamArgs& a, uint32_t grid, size_t smem, const
     return cudaLaunchKernelEx(&lc, kern, a) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
 }
 
-template <class F, int KL, bool SW, bool PEER>
+template <class F, int KL, bool SW, bool PEER, bool PLAIN>
 int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     static bool attr_done[64] = {};  // per template instance
-    auto kern = stream_gemv_kernel<F, KL, SW, PEER>;
+    auto kern = stream_gemv_kernel<F, KL, SW, PEER, PLAIN>;
     if (attr_needed(attr_done) &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(KL <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1)) != cudaSuccess)
         return ALICE_E_CUDA;
@@ -92,7 +92,9 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
     const bool peer = a.npeers || a.pub.npeers;
-    return peer ? launch_one_v<F, KL, SW, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false>(a, grid, smem, cfg);
+    if (peer) return launch_one_v<F, KL, SW, true, false>(a, grid, smem, cfg);
+    const bool plain = !a.resid && !a.argmax_key && a.nseg == 1 && a.pub.mode == PUB_NONE;
+    return plain ? launch_one_v<F, KL, SW, false, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false, false>(a, grid, smem, cfg);
 }
 
 template <class F>
@@ -300,35 +302,18 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     const uint32_t per_sm = kl <= 2 ? 2 : 1;
     const uint32_t full_budget = kl <= 2 ? SMEM_BUDGET_2 : SMEM_BUDGET_1;
     uint32_t nst = cfg.force_stages >= 2 ? std::min<uint32_t>(cfg.force_stages, MAX_STAGES) : DEFAULT_STAGES;
-    // activation area: the input, fetched once per CTA (bulk copies when addresses and sizes are multiples of 16)
+    // activation area: only when the kernel prepares the raw f32 vector itself (normalised f32 copy and / or Q8_K blocks)
     uint32_t act_bytes = 0;
     const bool kq = format_uses_q8k(w0.fmt);
-    const uint32_t nb = w0.cols / 256u;
-    const uint32_t q8_area = (nb * 288u + ((nb * 4u + 15u) & ~15u) + 127u) & ~127u;
-    if (kq && q8) {
-        a.act_n = 3;
-        a.act_bulk = (!((uintptr_t)q8->qs & 15) && !((uintptr_t)q8->bsums & 15) && !((uintptr_t)q8->d & 15)) ? 1u : 0u;
-        a.act_src[0] = q8->qs; a.act_bytes[0] = nb * 256u; a.act_off[0] = 0;
-        a.act_src[1] = q8->bsums; a.act_bytes[1] = nb * 32u; a.act_off[1] = nb * 256u;
-        // with bulk copies the d piece is rounded up to 16 bytes (the array is padded in memory)
-        a.act_src[2] = q8->d; a.act_bytes[2] = a.act_bulk ? (nb * 4u + 15u) & ~15u : nb * 4u; a.act_off[2] = nb * 288u;
-        act_bytes = q8_area;
-    } else if (kq || op.norm_w) {
-        // raw f32 vector (+ norm weights): every CTA prepares its own copy (stream_prologue)
-        if (((uintptr_t)x & 3) || (op.norm_w && ((uintptr_t)op.norm_w & 3))) return ALICE_E_INVALID;
-        const uint32_t vec = (w0.cols * 4u + 127u) & ~127u;
+    if ((kq && !q8) || op.norm_w) {
+        if (((uintptr_t)x & 15) || (op.norm_w && (((uintptr_t)op.norm_w & 15) || w0.cols % 4))) return ALICE_E_INVALID;
+        const uint32_t nb = w0.cols / 256u;
+        const uint32_t xn_bytes = op.norm_w ? (w0.cols * 4u + 127u) & ~127u : 0u;
+        const uint32_t q8_bytes = kq ? (nb * 292u + 127u) & ~127u : 0u;
         a.pro_mode = 1; a.pro_norm_w = op.norm_w; a.pro_eps = op.norm_eps;
         a.pro_roundtrip = (!kq && op.q8k_roundtrip && op.norm_w && w0.cols % QK_K == 0) ? 1u : 0u;
-        a.act_n = 1;
-        a.act_bulk = (w0.cols % 4 == 0 && !((uintptr_t)x & 15)) ? 1u : 0u;
-        a.act_src[0] = x; a.act_bytes[0] = w0.cols * 4u; a.act_off[0] = 0;
-        a.pro_q8_off = vec;
-        act_bytes = vec + (kq ? q8_area : 0u);
-    } else if (w0.cols * 4u <= 64u * 1024u && !((uintptr_t)x & 3)) {
-        a.act_n = 1;
-        a.act_bulk = (w0.cols % 4 == 0 && !((uintptr_t)x & 15)) ? 1u : 0u;
-        a.act_src[0] = x; a.act_bytes[0] = w0.cols * 4u; a.act_off[0] = 0;
-        act_bytes = (w0.cols * 4u + 127u) & ~127u;
+        a.pro_q8_off = xn_bytes;
+        act_bytes = xn_bytes + q8_bytes;
     }
     if (HDR_BYTES + act_bytes + 8192 > full_budget) return ALICE_E_SHAPE;
     const uint32_t budget = full_budget - HDR_BYTES - act_bytes;

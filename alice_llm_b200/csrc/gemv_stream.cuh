@@ -46,19 +46,10 @@ struct StreamArgs {
     uint32_t batch;      // input vectors sharing one pass over the weights (batch kernels), else 1
     uint32_t y_stride;   // floats between the outputs of consecutive input vectors
     uint32_t tab_off;    // shared-memory offset of the activation area (Q8_K blocks / f32 vector / bit-plane digit table)
-    // The prepared input is fetched ONCE per CTA into shared memory with bulk copies (up to three pieces: Q8_K qs, bsums,
-    // d; or the f32 vector), not by every warp from global memory: all CTAs of a launch want the same few KB, and
-    // per-warp loads of the same lines queue up at their L2 slices (measured: 1-5 us per CTA for 4.6 KB).
-    // act_bulk == 0: addresses or sizes do not allow bulk copies; the consumer threads copy the pieces with L2 loads.
-    // act_n == 0 (f32 vector too long for shared memory): the lanes read their columns from global memory.
-    uint32_t act_n;
-    uint32_t act_bulk;
-    // pro_mode != 0: the piece is the raw f32 vector (at offset 0 of the area); every CTA prepares its own copy
-    // (stream_prologue): rms_norm with the weights pro_norm_w (global memory, constants: pulled into L1 while the CTA
-    // waits for the previous kernel), then Q8_K blocks at pro_q8_off (K-quant formats) or the normalised f32 vector in
-    // place (pro_roundtrip: rounded to the Q8_K grid). Redundant across CTAs, but parallel: a single CTA doing it once
-    // for everybody costs a serial chain of ~10 us (ticket, loads, reduction, quantization, each a dependent round trip)
-    // at the end of the producing kernel.
+    // pro_mode != 0: x is the raw f32 vector and every CTA prepares its own copy in the activation area
+    // (stream_prologue): rms_norm with the weights pro_norm_w into the f32 area at offset 0, then Q8_K blocks at
+    // pro_q8_off (K-quant formats); f32-activation formats read the normalised vector (pro_roundtrip: rounded to the
+    // Q8_K grid).
     uint32_t pro_mode, pro_roundtrip;
     uint32_t pro_q8_off;
     const float* pro_norm_w;
@@ -335,36 +326,51 @@ static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSm
     }
 }
 
-// Per-CTA input preparation (pro_mode), run by the NCW consumer warps on the f32 vector that bulk copies have just
-// put into shared memory. Warp w owns the 256-element blocks w, w + NCW, ...; a lane owns 8 consecutive elements.
-//   wn != null: rms_norm (src/llama3.rs:5244-5256) with the weights wn (global): f64 sum of squares, f32 mean / sqrt / divide, (x * scale) * w;
-//   q8 != null: Q8_K blocks (quantize_row_q8_k, src/gguf.rs:1323-1374) into qs | bsums | d at q8 (cols % 256 == 0);
-//   else the normalised vector goes back to xn in place (roundtrip: as d * q of its Q8_K quantisation, which is what
-//   quantized_matvec_preq hands a Q1_0 / Q2_0 matvec, src/gguf.rs:4593-4605).
-// One compact out-of-line copy with rolled loops: it runs once per launch, so every instruction is an instruction-cache miss.
-static __device__ __noinline__ void stream_prologue(StreamSmem* sm, float* xn, const float* wn, float eps, uint32_t cols, uint8_t* q8,
-                                                    bool roundtrip) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t nblk = (cols + QK_K - 1) / QK_K, nb = cols / QK_K;
-    auto load8 = [&](const float* p, uint32_t i0) {
-        Q8KLaneInput r;
-        if (i0 + 8 <= cols && (reinterpret_cast<uintptr_t>(p + i0) & 15) == 0) {
-            r.a = *reinterpret_cast<const float4*>(p + i0);
-            r.b = *reinterpret_cast<const float4*>(p + i0 + 4);
-        } else {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = i0 + j < cols ? p[i0 + j] : 0.0f;
-            r.a = make_float4(v[0], v[1], v[2], v[3]);
-            r.b = make_float4(v[4], v[5], v[6], v[7]);
-        }
-        return r;
-    };
-    float scale = 1.0f;
-    if (wn != nullptr) {
+// Per-CTA input preparation (pro_mode), run by the NCW consumer warps on the raw f32 vector in global memory.
+//   norm_w != null: rms_norm (src/llama3.rs:5244-5256) - f64 sum of squares, mean and scale in f32, then
+//                   (x * scale) * w - into the f32 area xn (shared memory);
+//   q8 != null:     the (normalised) vector -> Q8_K in shared memory at q8 (qs | bsums | d), one warp per
+//                   256-element block, exactly the stand-alone quantizer (cols % 256 == 0);
+//   roundtrip:      (with norm_w) the normalised vector is replaced by d * q of its Q8_K quantization, which is what
+//                   quantized_matvec_preq hands a Q1_0 / Q2_0 matvec (src/gguf.rs:4593-4605).
+// Loads travel in rounds (several per thread in flight), so a pass over x costs a few memory round trips.
+// Redundant across CTAs, but parallel: a single CTA doing it once for everybody costs a serial chain of ~10 us
+// (ticket, loads, reduction, quantization, each a dependent round trip) at the end of the producing kernel.
+static __device__ __forceinline__ void stream_prologue(StreamSmem* sm, const float* x, const float* norm_w, float norm_eps, uint32_t cols,
+                                                       float* xn, uint8_t* q8, bool roundtrip) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const float* src = x;
+    bool src_global = true;
+    if (norm_w != nullptr) {
+        // a thread's share of x stays in registers between the two passes when it fits in NORM_V float4
+        // (cols <= NCW*32*4*NORM_V); the norm weights ride the same memory round trip as x
+        constexpr int NORM_V = 4;
+        const uint32_t nvec = cols / 4;
+        const float4* xg = reinterpret_cast<const float4*>(x);
+        const float4* wg = reinterpret_cast<const float4*>(norm_w);
+        const bool one_round = nvec <= NCW * 32 * NORM_V;
+        float4 xv[NORM_V], wv[NORM_V];
         double ss = 0.0;
 #pragma unroll 1
-        for (uint32_t b = warp; b < nblk; b += NCW) ss += pub_sumsq(load8(xn, b * QK_K + lane * 8));
+        for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++) {
+                const uint32_t i = base + k * NCW * 32 + tid;
+                xv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < nvec) xv[k] = xg[i];
+            }
+            if (one_round) {
+#pragma unroll
+                for (int k = 0; k < NORM_V; k++) {
+                    const uint32_t i = k * NCW * 32 + tid;
+                    if (i < nvec) wv[k] = __ldg(wg + i);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++)
+                ss += (double)xv[k].x * (double)xv[k].x + (double)xv[k].y * (double)xv[k].y +
+                      (double)xv[k].z * (double)xv[k].z + (double)xv[k].w * (double)xv[k].w;
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) sm->norm_part[warp] = ss;
@@ -373,31 +379,57 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, float* xn, c
 #pragma unroll
         for (int w = 0; w < NCW; w++) tot += sm->norm_part[w];
         const float mean = (float)(tot / (double)cols);
-        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    }
-    int8_t* qs_s = reinterpret_cast<int8_t*>(q8);
-    int16_t* bs_s = reinterpret_cast<int16_t*>(q8 + (size_t)nb * 256);
-    float* d_s = reinterpret_cast<float*>(q8 + (size_t)nb * 288);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, norm_eps)));
 #pragma unroll 1
-    for (uint32_t b = warp; b < nblk; b += NCW) {
-        const uint32_t i0 = b * QK_K + lane * 8;
-        Q8KLaneInput v = load8(xn, i0);
-        if (wn != nullptr) v = pub_scale(v, scale, load8(wn, i0));
-        if (q8 != nullptr) {
-            q8k_quantize_block_warp(v, lane, qs_s + (size_t)b * QK_K, d_s + b, bs_s + (size_t)b * 16);
-        } else if (roundtrip) {
-            q8k_quantize_block_warp<true>(v, lane, nullptr, nullptr, nullptr, xn + (size_t)b * QK_K);
-        } else if (wn != nullptr) {
-            if (i0 + 8 <= cols) {
-                *reinterpret_cast<float4*>(xn + i0) = v.a;
-                *reinterpret_cast<float4*>(xn + i0 + 4) = v.b;
-            } else {
-                const float e[8] = {v.a.x, v.a.y, v.a.z, v.a.w, v.b.x, v.b.y, v.b.z, v.b.w};
-                for (uint32_t j = 0; j < 8 && i0 + j < cols; j++) xn[i0 + j] = e[j];
+        for (uint32_t base = 0; base < nvec; base += NCW * 32 * NORM_V) {
+#pragma unroll
+            for (int k = 0; k < NORM_V; k++) {
+                const uint32_t i = base + k * NCW * 32 + tid;
+                if (i < nvec) {
+                    const float4 v = one_round ? xv[k] : xg[i];
+                    const float4 w = one_round ? wv[k] : __ldg(wg + i);
+                    reinterpret_cast<float4*>(xn)[i] = make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
+                                                                   __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
+                }
             }
         }
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");  // xn complete
+        src = xn;
+        src_global = false;
+        if (roundtrip) {   // xn <- d * q of its own Q8_K quantization, block by block, in place
+#pragma unroll 1
+            for (uint32_t b = warp; b < cols / QK_K; b += NCW) {
+                const Q8KLaneInput in = q8k_load_lane(xn + (size_t)b * QK_K, lane, false);
+                q8k_quantize_block_warp<true>(in, lane, nullptr, nullptr, nullptr, xn + (size_t)b * QK_K);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+    if (q8 != nullptr) {
+        const uint32_t nb = cols / QK_K;
+        int8_t* qs_s = reinterpret_cast<int8_t*>(q8);
+        int16_t* bs_s = reinterpret_cast<int16_t*>(q8 + (size_t)nb * 256);  // 8-byte aligned for any nb
+        float* d_s = reinterpret_cast<float*>(q8 + (size_t)nb * 288);
+        // QB blocks per warp per round: their loads travel together (one memory round trip per round when
+        // the source is global memory) and their reduction chains interleave
+        constexpr int QB = 4;
+#pragma unroll 1
+        for (uint32_t b0 = warp; b0 < nb; b0 += QB * NCW) {
+            Q8KLaneInput in[QB];
+#pragma unroll
+            for (int i = 0; i < QB; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) in[i] = q8k_load_lane(src + (size_t)blk * QK_K, lane, false);
+            }
+#pragma unroll
+            for (int i = 0; i < QB; i++) {
+                const uint32_t blk = b0 + i * NCW;
+                if (blk < nb) q8k_quantize_block_warp(in[i], lane, qs_s + (size_t)blk * QK_K, d_s + blk, bs_s + (size_t)blk * 16);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+    }
+    (void)src_global;
 }
 
 // F supplies:
@@ -406,7 +438,9 @@ static __device__ __noinline__ void stream_prologue(StreamSmem* sm, float* xn, c
 //   static float unit(uint32_t row_smem_addr, uint32_t u, const Act&, const StreamArgs&)   partial dot of unit u
 //   static float finish(float v, const StreamArgs&, const float* aux, uint32_t row)   per-row epilogue
 // Consumer side of one matvec (the NCW consumer warps of the CTA, threads 0 .. NCW*32-1). Returns false after an abort.
-template <class F, int KL, bool SWIGLU, bool PEER>
+// PLAIN: the matvec is known to use none of the fused extras (residual / argmax epilogue, q/k/v segments, hand-over to
+// the next op, peers), so their code is compiled out - the stand-alone matvec entry points run this leaner instance.
+template <class F, int KL, bool SWIGLU, bool PEER, bool PLAIN>
 __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
     volatile int* abort_flag = &sm->abort_flag;
@@ -414,59 +448,34 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     const uint32_t P = a.P, slots = a.slots, rps = a.rps;
     const uint32_t rows_per_group = slots * rps;
     const uint32_t slot = warp / P, part = warp % P;
-    const float* const resid = a.resid;
-    unsigned long long* const argmax_key = a.argmax_key;
-    const uint32_t nseg = a.nseg;
+    const float* const resid = PLAIN ? nullptr : a.resid;
+    unsigned long long* const argmax_key = PLAIN ? nullptr : a.argmax_key;
+    const uint32_t nseg = PLAIN ? 1u : a.nseg;
 
-    // the prepared input: one fetch per CTA into shared memory, then every lane takes its own columns into registers
+    // the input: already prepared in global memory (every lane takes its own columns straight into registers; the
+    // loads are L1-cached, so the warp sets of a CTA share one trip to L2), or the raw f32 vector, prepared per CTA
     Q8KView q8 = a.q8;
     const float* xin = a.x;
-    if (a.act_n) {
+    if (a.pro_mode) {
         uint8_t* area = cx.smem_raw + a.tab_off;
-        if (a.act_bulk) {
-            const uint32_t ab = smem_u32(&sm->act_bar);
-            if (threadIdx.x == 0) {
-                uint32_t total = 0;
-                for (uint32_t i = 0; i < a.act_n; i++) total += a.act_bytes[i];
-                mbar_arrive_expect_tx(ab, total);
-                for (uint32_t i = 0; i < a.act_n; i++)
-                    bulk_g2s(smem_u32(area + a.act_off[i]), a.act_src[i], a.act_bytes[i], ab);
-            }
-            if (!wait_or_abort(ab, 0, abort_flag, a.status, KERR_WAIT_FULL, cx.limit)) return false;
+        float* xn = reinterpret_cast<float*>(area);
+        uint8_t* q8a = F::USES_Q8K ? area + a.pro_q8_off : nullptr;
+        stream_prologue(sm, a.x, a.pro_norm_w, a.pro_eps, a.cols, xn, q8a, a.pro_roundtrip != 0);
+        if (F::USES_Q8K) {
+            const uint32_t nb = a.cols / QK_K;
+            q8.qs = reinterpret_cast<const int8_t*>(q8a);
+            q8.bsums = reinterpret_cast<const int16_t*>(q8a + (size_t)nb * 256);
+            q8.d = reinterpret_cast<const float*>(q8a + (size_t)nb * 288);
+            q8.nb = nb;
         } else {
-            for (uint32_t i = 0; i < a.act_n; i++) {   // pieces are whole 32-bit words, 4-byte aligned
-                const uint32_t* src = static_cast<const uint32_t*>(a.act_src[i]);
-                uint32_t* dst = reinterpret_cast<uint32_t*>(area + a.act_off[i]);
-                for (uint32_t w = threadIdx.x; w < a.act_bytes[i] / 4; w += NCW * 32) dst[w] = __ldcg(src + w);
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        }
-        if (a.pro_mode) {
-            float* xn = reinterpret_cast<float*>(area);
-            uint8_t* q8a = F::USES_Q8K ? area + a.pro_q8_off : nullptr;
-            stream_prologue(sm, xn, a.pro_norm_w, a.pro_eps, a.cols, q8a, a.pro_roundtrip != 0);
-            if (F::USES_Q8K) {
-                const uint32_t nb = a.cols / QK_K;
-                q8.qs = reinterpret_cast<const int8_t*>(q8a);
-                q8.bsums = reinterpret_cast<const int16_t*>(q8a + (size_t)nb * 256);
-                q8.d = reinterpret_cast<const float*>(q8a + (size_t)nb * 288);
-                q8.nb = nb;
-            } else {
-                xin = xn;
-            }
-        } else if (F::USES_Q8K) {
-            q8.qs = reinterpret_cast<const int8_t*>(area + a.act_off[0]);
-            q8.bsums = reinterpret_cast<const int16_t*>(area + a.act_off[1]);
-            q8.d = reinterpret_cast<const float*>(area + a.act_off[2]);
-        } else {
-            xin = reinterpret_cast<const float*>(area + a.act_off[0]);
+            xin = xn;
         }
     }
     typename F::Act act[KL];
 #pragma unroll
     for (int k = 0; k < KL; k++) {
         const uint32_t u = ((uint32_t)k * P + part) * 32 + lane;
-        F::load_act(act[k], a, q8, xin, a.act_n == 0, u, u < a.units);
+        F::load_act(act[k], a, q8, xin, false, u, u < a.units);
     }
 
     // Rows are walked RB at a time so that RB*M independent unit decodes are in flight per lane
@@ -555,7 +564,7 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
 }
 
 // One matvec per launch.
-template <class F, int KL, bool SWIGLU, bool PEER>
+template <class F, int KL, bool SWIGLU, bool PEER, bool PLAIN>
 __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_kernel(const __grid_constant__ StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     StreamSmem* sm = reinterpret_cast<StreamSmem*>(smem_raw);
@@ -576,8 +585,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
         return;
     }
     pdl_wait();  // activations come from the previous kernel
-    stream_consume<F, KL, SWIGLU, PEER>(a, cx);
-    if (a.pub.mode != PUB_NONE) stream_publish<PEER>(a, sm);
+    stream_consume<F, KL, SWIGLU, PEER, PLAIN>(a, cx);
+    if (!PLAIN && a.pub.mode != PUB_NONE) stream_publish<PEER>(a, sm);
 }
 
 }  // namespace alice
