@@ -54,9 +54,6 @@ struct StreamArgs {
     uint32_t pro_q8_off;
     const float* pro_norm_w;
     float pro_eps;
-    const void* act_src[3];
-    uint32_t act_bytes[3];   // multiples of 16
-    uint32_t act_off[3];     // offsets inside the activation area, multiples of 16
     // Optional residual epilogue: y[row] = resid[row] + result (resid may alias y)
     const float* resid;
     // Optional greedy-argmax epilogue: atomicMax of (order-preserving bits of y[i]) << 32 | ~i, so the
