@@ -53,6 +53,7 @@ SIGNATURES = {
     "alice_swiglu_preq": (C.c_int32, [_vp, _vp, _vp, _vp, _vp]),
     "alice_dequantize": (C.c_int32, [_vp, _vp, _vp]),
     "alice_plan_query": (C.c_int32, [_vp, _vp, C.c_int32, C.c_int32, _vp, C.c_uint32]),
+    "alice_batch_plan": (C.c_int32, [_vp, _vp, C.c_int32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "alice_model_create": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _pp]),
     "alice_model_destroy": (C.c_int32, [_vp]),
     "alice_model_forward": (C.c_int32, [_vp, C.c_uint32]),

@@ -512,6 +512,15 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
         const uint32_t nb = d.cols / 256;
         if (e->shadow_of == x && e->shadow_cols == d.cols && e->shadow_batch == batch) v = view_at(e->shadow, nb, batch);
     }
+    if (kq && batch > 1 && v.qs == nullptr) {
+        // the batch kernel shares one copy of the Q8_K blocks of all vectors: quantize them once, ahead of it
+        const uint32_t nb = d.cols / 256;
+        int rc = ensure_scratch(e, Q8KLayout::make(nb, batch).total);
+        if (rc) return rc;
+        launch_quantize_q8k(x->p, d.cols, batch, e->scratch, e->stream, e->pdl);
+        CU(cudaGetLastError());
+        v = view_at(e->scratch, nb, batch);
+    }
     const bool have_q8 = kq && v.qs != nullptr;
     if (e->shadow_of == y) e->shadow_of = nullptr;   // y is about to be rewritten
     Publish pub{};
@@ -591,6 +600,20 @@ int32_t alice_plan_query(alice_engine* e, const alice_weights* w, int32_t swiglu
     out[0] = pl.grid; out[1] = a.P; out[2] = a.slots; out[3] = a.rps; out[4] = a.groups; out[5] = a.nstages;
     out[6] = pl.kl; out[7] = pl.mma ? 1u : 0u; out[8] = pl.ksplit; out[9] = pl.ctas_per_sm;
     return ALICE_OK;
+}
+
+int32_t alice_batch_plan(alice_engine* e, const alice_weights* w, int32_t swiglu, uint32_t batch, uint32_t* launches, uint32_t* weight_passes) {
+    if (!e || !w || !launches || !weight_passes) return fail(ALICE_E_INVALID, "alice_batch_plan: null argument");
+    if (batch == 0 || batch > 8) return fail(ALICE_E_SHAPE, "alice_batch_plan: batch %u outside 1..8", batch);
+    GemvOp op;
+    op.w[0] = &w->d;
+    if (swiglu) op.up = &w->d;
+    alignas(16) static float dummy[4];
+    Q8KView v{};
+    if (format_uses_q8k(w->d.fmt)) { v.qs = reinterpret_cast<const int8_t*>(dummy); v.d = dummy; v.bsums = reinterpret_cast<const int16_t*>(dummy); v.nb = w->d.cols / 256; op.q8 = &v; }
+    else op.x = dummy;
+    op.y = dummy; op.batch = batch;
+    return launch_rc(batch_plan(op, cfg_of(e), launches, weight_passes), "alice_batch_plan");
 }
 
 int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out) {

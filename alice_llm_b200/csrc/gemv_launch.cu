@@ -6,6 +6,7 @@
 #include "../../include/alice_cuda.h"
 #include "formats.cuh"
 #include "gemv_mma.cuh"
+#include "gemv_kq_mma.cuh"
 #include "gemv_launch.cuh"
 #include "gemv_plan.cuh"
 
@@ -242,6 +243,123 @@ int launch_mma(const StreamPlan& pl, const LaunchCfg& cfg) {
 
 }  // namespace
 
+// ---- batched K-quant matvec on the int8 tensor cores (csrc/gemv_kq_mma.cuh) --------------------------------------
+namespace {
+constexpr uint32_t KQ_PART_BYTES = (sizeof(KqPartials) + 127) & ~127u;
+
+uint32_t kq_block_bytes(WeightFormat f) { return f == WF_Q4_K ? 144u : f == WF_Q5_K ? 176u : 210u; }
+
+// Column chunk [col_lo, col_lo + col_n) of the matrix (whole 256-blocks); the whole row when col_n == cols.
+int plan_kq(const GemvOp& op, const LaunchCfg& cfg, uint32_t col_lo, uint32_t col_n, StreamPlan& pl) {
+    const WeightDesc& w0 = *op.w[0];
+    const bool sw = op.up != nullptr;
+    const uint32_t nmat = sw ? 2 : 1, bb = kq_block_bytes(w0.fmt), nbc = col_n / 256u;
+    if (w0.row_bytes % 16 || col_lo % 256 || col_n % 256 || nbc == 0) return ALICE_E_SHAPE;
+    const uint32_t off = col_lo / 256u * bb, pad = off & 15u;
+    const uint32_t piece_len = (pad + nbc * bb + 15u) & ~15u;
+    uint32_t row_stride = (piece_len + 31u) & ~31u;
+    while (row_stride % 128u != 32u && row_stride % 128u != 96u) row_stride += 32u;
+    const uint32_t acts = kq_acts_bytes(col_n);
+    StreamArgs a = {};
+    a.w0 = w0.data; a.w1 = sw ? op.up->data : nullptr;
+    a.q8 = *op.q8;
+    a.q8.qs += col_lo; a.q8.d += col_lo / 256u; a.q8.bsums += (size_t)(col_lo / 256u) * 16;
+    a.y = op.y; a.status = cfg.status;
+    a.cols = col_n; a.row_bytes = nbc * bb; a.row_stride = row_stride; a.row_mode = 1; a.src_row_bytes = w0.row_bytes;
+    a.npieces = 1; a.piece_len = piece_len; a.piece_off[0] = off - pad; a.row_pad = pad;
+    a.batch = op.batch; a.x_stride = w0.cols;
+    a.resid = op.resid; a.wait_limit = op.wait_limit;
+    if (op.pub) a.pub = *op.pub;
+    uint32_t total_rows = 0;
+    for (uint32_t i = 0; i < op.nw; i++) total_rows += op.w[i]->rows;
+    a.rows = total_rows; a.y_stride = op.y_stride ? op.y_stride : total_rows;
+    for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
+        const uint32_t budget = per_sm == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1;
+        if (HDR_BYTES + KQ_PART_BYTES + acts >= budget) continue;
+        const uint32_t avail = budget - HDR_BYTES - KQ_PART_BYTES - acts;
+        const uint32_t ctas = (uint32_t)std::max(cfg.num_sms, 1) * per_sm;
+        uint32_t best = 0;
+        for (uint32_t slots = NCW; slots >= 1; slots /= 2) {
+            const uint32_t cap = (slots * 16 * row_stride + 127) & ~127u;
+            if ((uint64_t)cap * nmat * 2 > avail || NCW / slots > nbc) continue;
+            best = slots;                                      // fits; keep shrinking while the CTAs are short of stages
+            uint32_t groups = 0;
+            for (uint32_t i = 0; i < op.nw; i++) groups += (op.w[i]->rows + slots * 16 - 1) / (slots * 16);
+            if (groups >= 2 * ctas) break;
+        }
+        if (best == 0) continue;
+        a.slots = best; a.P = NCW / best; a.rps = 16;
+        a.cap = (best * 16 * row_stride + 127) & ~127u;
+        a.nstages = 2;       // the partial-sum area is double buffered by stage
+        a.nseg = op.nw;
+        a.groups = 0;
+        for (uint32_t i = 0; i < op.nw; i++) {
+            a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i]; a.seg_aux[i] = nullptr;
+            a.seg_g0[i] = a.groups;
+            a.groups += (op.w[i]->rows + best * 16 - 1) / (best * 16);
+        }
+        a.seg_g0[op.nw] = a.groups;
+        a.tab_off = HDR_BYTES + KQ_PART_BYTES + 2 * a.cap * nmat;
+        pl.grid = std::min(ctas, a.groups);
+        pl.smem = (size_t)a.tab_off + acts;
+        pl.kl = 1; pl.swiglu = sw; pl.stage = a.cap * nmat; pl.mma = true; pl.ctas_per_sm = per_sm; pl.ksplit = 1;
+        pl.args = a;
+        return ALICE_OK;
+    }
+    return ALICE_E_SHAPE;
+}
+
+template <class T, bool SW, int CTAS>
+int launch_kq_one(const StreamPlan& pl, const LaunchCfg& cfg) {
+    static bool attr_done[64] = {};
+    auto kern = stream_gemv_kq_kernel<T, SW, CTAS>;
+    if (attr_needed(attr_done) &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CTAS == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1)) != cudaSuccess)
+        return ALICE_E_CUDA;
+    return launch_kernel(kern, pl.args, pl.grid, pl.smem, cfg);
+}
+template <class T>
+int launch_kq_fmt(const StreamPlan& pl, const LaunchCfg& cfg) {
+    if (pl.swiglu) return pl.ctas_per_sm == 2 ? launch_kq_one<T, true, 2>(pl, cfg) : launch_kq_one<T, true, 1>(pl, cfg);
+    return pl.ctas_per_sm == 2 ? launch_kq_one<T, false, 2>(pl, cfg) : launch_kq_one<T, false, 1>(pl, cfg);
+}
+
+// The whole batch in one pass over the weights: one launch, or one per column chunk when 16 rows of the matrix do not
+// fit a stage (a later chunk adds to what the earlier ones left in y). ALICE_E_SHAPE: no such plan (the caller falls
+// back to one launch per vector).
+int launch_kq_batch(const GemvOp& op, const LaunchCfg& cfg, bool dry, uint32_t* nlaunch) {
+    const WeightDesc& w0 = *op.w[0];
+    if (!format_uses_q8k(w0.fmt) || !op.q8 || op.argmax_key || op.npeers || op.norm_w) return ALICE_E_SHAPE;
+    if (((uintptr_t)op.q8->qs & 15) || w0.cols % 256) return ALICE_E_SHAPE;
+    for (uint32_t i = 0; i < op.nw; i++)
+        if (op.w[i]->fmt != w0.fmt || op.w[i]->cols != w0.cols || ((uintptr_t)op.w[i]->data & 15)) return ALICE_E_SHAPE;
+    if (op.up && (op.nw != 1 || op.up->fmt != w0.fmt || op.up->rows != w0.rows || op.up->cols != w0.cols)) return ALICE_E_SHAPE;
+    const uint32_t nbt = w0.cols / 256u;
+    for (uint32_t ks = 1; ks <= 8; ks++) {
+        if (ks > 1 && op.up) break;          // the fused SwiGLU needs whole rows (silu of the complete gate)
+        if (nbt % ks) continue;
+        const uint32_t nbc = nbt / ks;
+        if ((nbc * 256u) % 16u) continue;
+        StreamPlan probe;
+        if (plan_kq(op, cfg, 0, nbc * 256u, probe) != ALICE_OK) continue;
+        if (nlaunch) *nlaunch = ks;
+        if (dry) return ALICE_OK;
+        for (uint32_t c = 0; c < ks; c++) {
+            StreamPlan pc;
+            const int rc = plan_kq(op, cfg, c * nbc * 256u, nbc * 256u, pc);
+            if (rc) return rc;
+            if (c > 0) pc.args.resid = op.y;
+            if (c + 1 < ks) pc.args.pub = Publish{};
+            const int lrc = w0.fmt == WF_Q4_K ? launch_kq_fmt<KqK4<false>>(pc, cfg) : w0.fmt == WF_Q5_K ? launch_kq_fmt<KqK4<true>>(pc, cfg)
+                                                                                                        : launch_kq_fmt<KqQ6K>(pc, cfg);
+            if (lrc) return lrc;
+        }
+        return ALICE_OK;
+    }
+    return ALICE_E_SHAPE;
+}
+}  // namespace
+
 int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     if (op.nw < 1 || op.nw > 3 || !op.w[0] || !op.y) return ALICE_E_INVALID;
     const WeightDesc& w0 = *op.w[0];
@@ -407,6 +525,10 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
     if (op.batch == 0 || op.batch > (uint32_t)MAX_BATCH) return ALICE_E_SHAPE;
     if (op.batch == 1) return launch_single(op, cfg);
     if (op.argmax_key) return ALICE_E_INVALID;
+    {   // K-quants with prepared Q8_K input: the int8 tensor-core kernel serves the whole batch in one pass over the weights
+        const int brc = launch_kq_batch(op, cfg, false, nullptr);
+        if (brc != ALICE_E_SHAPE) return brc;
+    }
     // Formats without a batch kernel: one launch per input vector (the weights stream once per vector). A whole-vector
     // hand-over rides on the last launch (every earlier one has completed by then: same stream), a per-block one on
     // each launch for its own vector.
@@ -439,6 +561,17 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         const int rc = launch_single(o, cfg);
         if (rc) return rc;
     }
+    return ALICE_OK;
+}
+
+int batch_plan(const GemvOp& op, const LaunchCfg& cfg, uint32_t* launches, uint32_t* weight_passes) {
+    uint32_t n = 0;
+    if (op.batch > 1 && launch_kq_batch(op, cfg, true, &n) == ALICE_OK) { *launches = n; *weight_passes = 1; return ALICE_OK; }
+    GemvOp one = op; one.batch = 1;
+    StreamPlan pl;
+    const int rc = plan_stream_gemv(one, cfg, pl);
+    if (rc) return rc;
+    *launches = op.batch * pl.ksplit; *weight_passes = op.batch;
     return ALICE_OK;
 }
 

@@ -62,6 +62,8 @@ struct GemvOp {
     long long wait_limit = 0;                              // SM cycles a wait inside the kernel may take (0 = about a second)
 };
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
+// How a batch of op.batch vectors would run: kernel launches, and how many times the weight bytes stream from HBM.
+int batch_plan(const GemvOp& op, const LaunchCfg& cfg, uint32_t* launches, uint32_t* weight_passes);
 
 
 // out[r*cols + c] = dequantized weight, bit-exact with the reference dequantizers.

@@ -78,6 +78,8 @@ struct StreamArgs {
     uint32_t npieces;
     uint32_t piece_off[2];
     uint32_t piece_len;
+    uint32_t row_pad;    // bytes in front of the first wanted byte of a staged row (piece start rounded down to 16)
+    uint32_t x_stride;   // elements between consecutive input vectors (the matrix's full column count)
     // Tensor parallel: every row result is also stored at the same index of the vector of each of npeers other GPUs
     // (peer-mapped memory); the hand-over that tells the peers lives in `pub` (Publish::peer_flag).
     uint32_t npeers;

@@ -175,10 +175,26 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     };
     // input of a matvec over `w` that reads the (normalised) hidden state: the prepared f32 vector for the tensor-core
     // kernels, else the raw vector plus the norm weights (prepared per CTA)
-    auto hidden_input = [&](GemvOp& op, const WeightDesc& w, const float* norm_w, bool via_preq) {
-        if (wants_prepared(w)) op.x = m->hid_xn;
-        else { op.x = m->hidden; op.norm_w = norm_w; op.norm_eps = c.eps; op.q8k_roundtrip = via_preq && preq_roundtrip(w); }
+    // Batches: the tensor-core batch kernel of the K-quants wants ONE shared copy of the Q8_K blocks of all vectors, so
+    // a one-CTA kernel prepares them (norm + Q8_K of every vector) ahead of the matvec; `fresh` = the hidden state has
+    // changed since the last such preparation.
+    Q8KView hid_view = q8_view(m->hid_q8, H);
+    auto hidden_input = [&](GemvOp& op, const WeightDesc& w, const float* norm_w, bool via_preq, bool fresh) -> int {
         op.batch = batch;
+        if (wants_prepared(w)) { op.x = m->hid_xn; return ALICE_OK; }
+        if (batch > 1 && format_uses_q8k(w.fmt)) {
+            if (fresh) {
+                Publish p{};
+                p.mode = PUB_VECTOR; p.n = H; p.batch = batch; p.src = m->hidden; p.norm_w = norm_w; p.eps = c.eps;
+                Need nd; nd.q8 = true;
+                fill_dst(p.dst, nd, m->hid_q8, nullptr, H);
+                MCU(launch_publish_vector(p, m->e->status, st, pdl));
+            }
+            op.q8 = &hid_view;
+            return ALICE_OK;
+        }
+        op.x = m->hidden; op.norm_w = norm_w; op.norm_eps = c.eps; op.q8k_roundtrip = via_preq && preq_roundtrip(w);
+        return ALICE_OK;
     };
 
     // embedding + rotation table + hidden prepared for layer 0
@@ -208,7 +224,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             GemvOp op; Q8KView view;
             op.w[0] = &L.q; op.w[1] = &L.k; op.w[2] = &L.v; op.nw = 3;
             op.y_off[0] = 0; op.y_off[1] = lq; op.y_off[2] = lq + lkv;
-            hidden_input(op, L.q, L.attn_norm, true);
+            if ((rc = hidden_input(op, L.q, L.attn_norm, true, true))) return rc;
             op.y = m->qkv; op.y_stride = qkv_stride;
             if ((rc = gemv(m, op, "qkv"))) return rc;
         } else {   // mixed formats (e.g. V kept at higher precision): one launch each
@@ -217,7 +233,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             for (int i = 0; i < 3; i++) {
                 GemvOp op; Q8KView view;
                 op.w[0] = ws[i];
-                hidden_input(op, *ws[i], L.attn_norm, true);
+                if ((rc = hidden_input(op, *ws[i], L.attn_norm, true, i == 0))) return rc;
                 op.y = m->qkv + offs[i]; op.y_stride = qkv_stride;
                 if ((rc = gemv(m, op, "q/k/v"))) return rc;
             }
@@ -264,7 +280,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         {   // fused SwiGLU gate/up (src/llama3.rs:14497-14534); leaves its output prepared for the down projection
             GemvOp op; Q8KView view; Publish p;
             op.w[0] = &L.gate; op.up = &L.up;
-            hidden_input(op, L.gate, L.ffn_norm, true);
+            if ((rc = hidden_input(op, L.gate, L.ffn_norm, true, true))) return rc;
             op.y = m->ffn_h; op.y_off[0] = r * m->lF; op.y_stride = F;
             Need nd;
             nd.q8 = n == 1 && format_uses_q8k(L.down.fmt);   // else the down projection reads ffn_h itself
@@ -309,7 +325,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     {   // output head on the prepared (normalised) hidden (src/llama3.rs:14590-14604)
         GemvOp op; Q8KView view; Publish p;
         op.w[0] = &m->out;
-        hidden_input(op, m->out, m->out_norm, false);
+        if ((rc = hidden_input(op, m->out, m->out_norm, false, true))) return rc;
         op.y = m->logits; op.y_off[0] = r * m->lV; op.y_stride = V;
         if (batch == 1) op.argmax_key = m->argmax_key;   // greedy sampling: the head kernel leaves the packed maximum of its rows
         if (peer) {

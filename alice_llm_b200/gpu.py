@@ -292,6 +292,12 @@ class GpuEngine:
                 "ctas_per_sm")
         return dict(zip(keys, (int(v) for v in out)))
 
+    def batch_plan(self, w: GpuWeightBuffer, batch: int, swiglu: bool = False):
+        """-> (kernel launches, passes over the weight bytes) of a batch of `batch` vectors (diagnostic)."""
+        a, b = C.c_uint32(), C.c_uint32()
+        check(self._lib.alice_batch_plan(self._h, w._h, int(swiglu), batch, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     # -- one-shot helpers (src/gpu.rs:838, 962) --
     def matvec(self, weights: GpuWeightBuffer, input_) -> np.ndarray:
         """GpuEngine::matvec (src/gpu.rs:838): upload input, run, read back."""

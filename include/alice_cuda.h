@@ -146,6 +146,11 @@ int32_t alice_dequantize(alice_engine* e, const alice_weights* w, alice_buf* out
  * assert that a shape really re-uses the ring. No reference counterpart (diagnostic). */
 int32_t alice_plan_query(alice_engine* e, const alice_weights* w, int32_t swiglu, int32_t preq, uint32_t* out, uint32_t n_out);
 
+/* How alice_matvec / alice_swiglu run `batch` input vectors over `w`: the number of kernel launches and how many times
+ * the weight bytes stream from HBM (1 = the batch kernel decodes every weight once for all vectors, as the reference's
+ * *_batch4 shaders do, src/gpu.rs:4759; `batch` = one pass per vector). No reference counterpart (diagnostic). */
+int32_t alice_batch_plan(alice_engine* e, const alice_weights* w, int32_t swiglu, uint32_t batch, uint32_t* launches, uint32_t* weight_passes);
+
 /* ---- tensor parallel ------------------------------------------------------------------------ */
 /* One engine (one process) per GPU; output rows of every projection are sharded over the group and the
  * full vector is rebuilt on every rank by an NCCL all-gather queued on the engine's stream (the row

@@ -147,10 +147,11 @@ def test_swiglu_matches_oracle(eng, oracle, qtype, rows, cols):
     assert_close(got, oracle.swiglu(qtype, x, gate, up, rows, cols), synth.TYPE_NAMES[qtype])
 
 
-@pytest.mark.parametrize("qtype,batch", [(Q4_K, 4), (Q6_K, 4), (Q1_0, 8), (Q8_0, 2)])
-def test_batched_matvec_matches_oracle(eng, oracle, qtype, batch):
+@pytest.mark.parametrize("qtype,batch,rows,cols", [(Q4_K, 4, 130, 4096), (Q6_K, 4, 130, 4096), (Q1_0, 8, 130, 5120), (Q8_0, 2, 130, 5120),
+                                                   (Q4_K, 8, 1000, 4096), (Q5_K, 3, 77, 2048), (Q6_K, 8, 300, 14336), (Q4_K, 2, 33, 256),
+                                                   (Q4_K, 5, 4096, 14336), (Q6_K, 7, 16, 1024)])
+def test_batched_matvec_matches_oracle(eng, oracle, qtype, batch, rows, cols):
     rng = np.random.default_rng(500 + qtype)
-    rows, cols = 130, 5120 if qtype in (Q1_0, Q8_0) else 4096
     data = synth.make_weights(qtype, rng, rows, cols)
     x = synth.make_x(rng, cols, batch)
     w = eng.upload_weights_typed(data, rows, cols, quant(qtype))
@@ -160,6 +161,28 @@ def test_batched_matvec_matches_oracle(eng, oracle, qtype, batch):
     eng.sync()
     for k in range(batch):   # layout x[k*cols + c] -> y[k*rows + r] (src/gpu.rs:1141-1143)
         assert_close(got[k], oracle.matvec(qtype, x[k * cols:(k + 1) * cols], data, rows, cols), f"batch {k}")
+    launches, passes = eng.batch_plan(w, batch)
+    if qtype in (Q4_K, Q5_K, Q6_K) and synth.row_bytes(qtype, cols) % 16 == 0:
+        # the weights stream once for the whole batch; one launch unless 16 rows do not fit a shared-memory stage
+        # (rows that are not a multiple of 16 bytes cannot be staged row by row and fall back to one pass per vector)
+        assert passes == 1 and launches == (1 if cols <= 4096 else launches), (launches, passes)
+        assert launches <= 8
+
+
+@pytest.mark.parametrize("batch", [4, 8])
+def test_batched_swiglu_one_pass_over_the_weights(eng, oracle, batch):
+    rng = np.random.default_rng(77)
+    rows, cols = 600, 4096
+    gate, up = synth.make_q4k(rng, rows, cols), synth.make_q4k(rng, rows, cols)
+    x = synth.make_x(rng, cols, batch)
+    g, u = eng.upload_weights(gate, rows, cols), eng.upload_weights(up, rows, cols)
+    y = eng.alloc_f32(rows * batch)
+    eng.swiglu_dev(g, u, eng.upload_f32(x), y, batch)
+    got = eng.read_f32(y).reshape(batch, rows)
+    eng.sync()
+    for k in range(batch):
+        assert_close(got[k], oracle.swiglu(Q4_K, x[k * cols:(k + 1) * cols], gate, up, rows, cols), f"swiglu batch {k}")
+    assert eng.batch_plan(g, batch, swiglu=True) == (1, 1)
 
 
 @pytest.mark.parametrize("rows,cols", [(5, 128), (3, 100), (70, 8192), (12, 28672), (9, 1000), (600, 8192), (33, 14336 + 128)])
