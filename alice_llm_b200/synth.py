@@ -133,6 +133,34 @@ def ternary_to_sparse(pos: np.ndarray, neg: np.ndarray, cols: int):
     return active, sign
 
 
+_F16_FIELDS = {Q4_K: (0, 2), Q5_K: (0, 2), Q6_K: (208,), Q8_0: (0,), Q1_0: (0,), Q2_0: (0,)}
+
+
+def scale_blocks(entry, factor):
+    """(type, raw blocks) with every f16 block scale multiplied by `factor` (ternary planes: the per-row scales)."""
+    t, data = entry
+    if t == TERNARY:
+        pos, neg, sc = data
+        return t, (pos, neg, (sc * np.float32(factor)).astype(np.float32))
+    blk = data.reshape(-1, BLOCK_BYTES[t]).copy()
+    for off in _F16_FIELDS[t]:
+        v = blk[:, off:off + 2].copy().view(np.float16).astype(np.float32) * np.float32(factor)
+        blk[:, off:off + 2] = v.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    return t, blk.reshape(-1)
+
+
+def soften_attention(model: dict, factor: float | None = None) -> dict:
+    """Scales the q / k / v projections of a make_llama model (default 0.3 / sqrt(hidden)) so that the softmax spreads
+    over the context instead of collapsing onto the newest row: the synthetic K-quant weights have a positive mean, so
+    an unscaled q . k grows with hidden_dim. Returns the model (modified in place)."""
+    if factor is None:
+        factor = 0.3 / float(np.sqrt(model["config"]["hidden_dim"]))
+    for L in model["layers"]:
+        for n in ("q", "k", "v"):
+            L[n] = scale_blocks(L[n], factor)
+    return model
+
+
 def make_x(rng, n: int, batch: int = 1) -> np.ndarray:
     """Activations ~ N(0,1), f32, layout x[k*n + c]."""
     return rng.standard_normal(batch * n, dtype=np.float32)

@@ -1,28 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-matvec decode path on B200.
 
-Workload ("ffn_q4k_q6k_b1"): the mixed-quant SwiGLU FFN block at Llama-3-8B shapes, batch 1:
+Headline workload ("ffn_q4k_q6k_b1"): the mixed-quant SwiGLU FFN block at Llama-3-8B shapes, batch 1:
 gate/up 14336x4096 Q4_K, down 4096x14336 Q6_K, x f32[4096] ~ N(0,1); out = down(silu(gate x) * (up x)).
-One step = one pass of the block = 2 kernels (fused SwiGLU gate/up matvec, down matvec; each quantizes
-its f32 input to Q8_K in its prologue, bit-exactly as the reference does) over 114,229,248 weight bytes.  Weights are synthetic (seed 0, the distributions of
-alice_llm_b200/synth.py); 8 distinct copies of the block (914 MB, far above the 126 MB L2) are
-cycled so every step streams its weights from HBM.
+One step = one pass of the block = 2 kernels (fused SwiGLU gate/up matvec, which quantizes x to Q8_K in its prologue and
+leaves its output as Q8_K blocks too; down matvec) over 114,229,248 weight bytes. Weights are synthetic (seed 0, the
+distributions of alice_llm_b200/synth.py); 8 distinct copies of the block (914 MB, far above the 126 MB L2) are cycled
+so every step streams its weights from HBM. The result of the first step is compared with the CPU oracle before
+anything is timed (`parity`).
 
-  metric  weight_stream_gbs = algorithmic weight bytes per step / step time (whole job)
-  e2e     same metric through the C ABI with host buffers: x copied from pinned host memory and
-          y read back to the host inside every timed step
-  roofline  the fused SwiGLU Q4_K kernel alone (66,060,288 bytes per launch) against the measured
-          HBM copy bandwidth of MEASURED_PEAKS.json
-  cpu_baseline  the C++ restatement of the reference CPU path on the host cores (the reference
-          itself is Rust and cannot be built here)
+  metric     weight_stream_gbs = algorithmic weight bytes per step / step time (whole job)
+  e2e        same metric through the C ABI with host buffers: x copied from pinned host memory and y read back to the
+             host inside every timed step
+  roofline   the slower of the step's two kernels, timed alone with CUDA events, against the measured HBM copy bandwidth
+  cpu_baseline  the C++ restatement of the reference CPU path on the host cores (the reference is Rust; no toolchain here)
+  formats    every weight format on a matrix of >= 64 MB (several copies cycled): GB/s and fraction of the measured peak
+  configs    the other single-GPU configurations of the benchmark definition: the Q4_K 4096x4096 GEMV alone, the FFN block
+             at batch 4 (weights streamed once for the four inputs), the 70B shapes in the packed 2-bit ternary form
+  decode     greedy decode of the synthetic whole-model configurations (128 tokens after a prefilled context): the 8B
+             Q4_K_M mix, the 27B Q1_0 model and the 70B ternary model on one GPU; with --gpus N > 1 the 27B and 70B
+             models row-sharded over the N GPUs, both exchange mechanisms, with the same seeded weights at every N,
+             plus a small seed-shared model checked against the CPU oracle on rank 0 (tp_parity).
 
-  decode  greedy decode of the synthetic whole-model configurations (128 tokens after a prefilled context):
-          the 8B Q4_K_M mix, the 27B Q1_0 model and the 70B ternary model on one GPU; with --gpus N > 1 the
-          27B and 70B models row-sharded over the N GPUs (one process per GPU, NCCL all-gather of every
-          projection output inside the library). tok/s, ms/token and the ratio to the pure weight-streaming
-          time at the measured HBM bandwidth. `--decode none` skips it.
-
-`--impl reference` times that CPU path alone, with all host threads, on the same block.
+`--impl reference` times the CPU path alone, with all host threads, on the same block.
 """
 from __future__ import annotations
 
@@ -47,6 +47,8 @@ DOWN_BYTES = HIDDEN * (FFN // 256) * 210      # 48,168,960
 STEP_BYTES = 2 * GU_BYTES + DOWN_BYTES        # 114,229,248
 NCOPIES = 8
 KERNELS_PER_STEP = 2
+CONFIG = {"workload": "ffn_q4k_q6k_b1", "hidden": HIDDEN, "ffn": FFN, "gate_up": "Q4_K", "down": "Q6_K", "batch": 1,
+          "weight_bytes_per_step": STEP_BYTES}
 
 
 def make_block(seed=0):
@@ -107,6 +109,11 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+CPU_SAMPLE = ("full FFN-block passes; C++ restatement of the reference CPU path (scalar block kernels of src/gguf.rs, "
+              "auto-vectorised with -O3 -march=native, rows split over a persistent thread pool standing in for rayon); "
+              "the reference itself is Rust and cannot be built on the box")
+
+
 def cpu_ffn_rate(block, threads, min_seconds, max_passes):
     """FFN passes on the host cores until min_seconds have elapsed -> (GB/s, passes, seconds)."""
     from oracle import oracle as orc
@@ -141,50 +148,159 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "weight_stream_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-        "config": {"workload": "ffn_q4k_q6k_b1", "hidden": HIDDEN, "ffn": FFN, "gate_up": "Q4_K", "down": "Q6_K",
-                   "batch": 1, "weight_bytes_per_step": STEP_BYTES},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": f"{args.steps} full FFN-block passes; C++ restatement of the reference CPU path "
-                                   "(reference is Rust, no toolchain on the box)"},
+        "config": dict(CONFIG),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": f"{args.steps} {CPU_SAMPLE}"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def run_decode(eng, name, tokens, stream, world, dist, dev, peak):
-    """Greedy decode of one whole-model configuration; returns its report entry (device-timed, max over ranks)."""
+# ---------------------------------------------------------------------------------------------------------------------
+# synthetic tensors drawn on the device (timing runs of 5-17 GB models need bytes of the right layout and value ranges,
+# not host copies); every tensor has its own seed, the same on every rank, and a rank keeps only its row shard
+# ---------------------------------------------------------------------------------------------------------------------
+DECODE_CONFIGS = {
+    # Llama-3-8B shapes, Q4_K_M mix: q/k/v/o/gate/up Q4_K, down and head Q6_K, embedding Q8_0; context 2048
+    "c3_8b_q4km": dict(num_layers=32, hidden_dim=4096, intermediate_dim=14336, num_heads=32, num_kv_heads=8, head_dim=128,
+                       vocab_size=128256, rope_theta=500000.0, eps=1e-5, context=2048,
+                       mix=dict(q=12, k=12, v=12, o=12, gate=12, up=12, down=14, output=14)),
+    # 27B-class dense model in Q1_0 binary weights, Q8_0 head; context 4096
+    "c4_27b_q1_0": dict(num_layers=64, hidden_dim=5120, intermediate_dim=25600, num_heads=40, num_kv_heads=8, head_dim=128,
+                        vocab_size=151936, rope_theta=1000000.0, eps=1e-6, context=4096,
+                        mix=dict(q=41, k=41, v=41, o=41, gate=41, up=41, down=41, output=8)),
+    # Llama-2-70B shapes in ternary bit planes; context 2048
+    "c5_70b_ternary": dict(num_layers=80, hidden_dim=8192, intermediate_dim=28672, num_heads=64, num_kv_heads=8, head_dim=128,
+                           vocab_size=32000, rope_theta=10000.0, eps=1e-5, context=2048,
+                           mix={n: 1000 for n in ("q", "k", "v", "o", "gate", "up", "down", "output")}),
+}
+# byte offset of the f16 scale fields inside a block, and their sigma (|N(0,1)| * sigma)
+_SCALES = {12: ((0, 0.01), (2, 0.005)), 13: ((0, 0.01), (2, 0.005)), 14: ((208, 0.01),), 8: ((0, 0.01),), 41: ((0, 0.02),), 42: ((0, 0.02),)}
+
+
+def dev_ggml_tensor(gen, dev, qtype, rows, cols):
     import torch
-    from alice_llm_b200.synth_device import build_model
+    from alice_llm_b200 import synth
+    bb, be = synth.BLOCK_BYTES[qtype], synth.BLOCK_ELEMS[qtype]
+    nblk = rows * (cols // be)
+    t = torch.randint(0, 256, (nblk, bb), dtype=torch.uint8, device=dev, generator=gen)
+    for off, sigma in _SCALES[qtype]:
+        d = (torch.randn(nblk, device=dev, generator=gen).abs() * sigma).to(torch.float16)
+        t[:, off:off + 2] = d.view(torch.uint8).reshape(nblk, 2)
+    if qtype == 14:   # int8 sub-block scales uniform -32..31
+        t[:, 192:208] = torch.randint(-32, 32, (nblk, 16), dtype=torch.int8, device=dev, generator=gen).view(torch.uint8)
+    if qtype == 42:   # 2-bit slots over the three codes the encoder emits
+        s = torch.randint(0, 3, (nblk, 32, 4), dtype=torch.uint8, device=dev, generator=gen)
+        t[:, 2:] = s[..., 0] | (s[..., 1] << 2) | (s[..., 2] << 4) | (s[..., 3] << 6)
+    return t.reshape(-1)
+
+
+def dev_ternary_tensor(gen, dev, rows, cols):
+    """Device layout of the library: row = [pos plane | neg plane]; P(+1) = P(-1) = 0.25, P(0) = 0.5."""
+    import torch
+    pb = (cols + 31) // 32 * 4
+    a = torch.randint(0, 256, (rows, pb), dtype=torch.uint8, device=dev, generator=gen)
+    b = torch.randint(0, 256, (rows, pb), dtype=torch.uint8, device=dev, generator=gen)
+    planes = torch.stack([a & b, ~a & b], dim=1).reshape(rows, 2 * pb)   # disjoint, each bit set with probability 1/4
+    scales = (torch.randn(rows, device=dev, generator=gen).abs() * 0.01).float()
+    return planes, scales
+
+
+def build_model(engine, name, seed=0, extra_positions=160, force_world=None):
+    """Configuration `name` on the engine's device: this rank's row shards when the engine belongs to a tensor-parallel
+    group. The WHOLE tensor is drawn from its own seed on every rank and the rank keeps its rows, so the model is the
+    same at every group size. Returns (GpuModel, info)."""
+    import torch
+    from alice_llm_b200 import synth
+    from alice_llm_b200.gpu import GpuModel, GpuModelConfig, GpuQuantType
+    c = DECODE_CONFIGS[name]
+    rank, world = engine.tp_info()
+    dev = torch.device("cuda", engine.device)
+    H, F, V = c["hidden_dim"], c["intermediate_dim"], c["vocab_size"]
+    q_dim, kv_dim = c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
+    shapes = {"q": (q_dim, H), "k": (kv_dim, H), "v": (kv_dim, H), "o": (H, q_dim), "gate": (F, H), "up": (F, H), "down": (H, F)}
+    keep, total_bytes, counter = [], 0, [0]
+
+    def tensor(role, rows, cols, shard=True):
+        nonlocal total_bytes
+        counter[0] += 1
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed * 100003 + counter[0])
+        qt = c["mix"][role] if role != "embedding" else synth.Q8_0
+        lo, n = (rank * (rows // world), rows // world) if shard else (0, rows)
+        if qt == synth.TERNARY:
+            planes, scales = dev_ternary_tensor(gen, dev, rows, cols)
+            planes, scales = planes[lo:lo + n].contiguous().reshape(-1), scales[lo:lo + n].contiguous()
+            keep.extend([planes, scales])
+            total_bytes += rows * ((cols + 7) // 8 * 2 + 4)
+            return engine.ternary_from_device(planes.data_ptr(), scales.data_ptr(), n, cols)
+        rb = synth.row_bytes(qt, cols)
+        t = dev_ggml_tensor(gen, dev, qt, rows, cols)
+        if n != rows:
+            t = t[lo * rb:(lo + n) * rb].clone()
+        keep.append(t)
+        if role != "embedding":
+            total_bytes += rb * rows
+        return engine.weights_from_device(t.data_ptr(), t.numel(), n, cols, GpuQuantType(qt))
+
+    def norm():
+        return (1.0 + 0.02 * np.random.default_rng(seed).standard_normal(H)).astype(np.float32)
+
+    layers = [dict({r: tensor(r, *shapes[r]) for r in shapes}, attn_norm=norm(), ffn_norm=norm()) for _ in range(c["num_layers"])]
+    model = {"layers": layers, "embedding": tensor("embedding", V, H, shard=False), "output_norm": norm(), "output": tensor("output", V, H)}
+    cfg = GpuModelConfig(c["num_layers"], H, F, c["num_heads"], c["num_kv_heads"], c["head_dim"], c["rope_theta"], c["eps"],
+                         c["context"] + extra_positions, V)
+    gm = GpuModel.load(engine, model, cfg)
+    gm._keep.append(keep)
+    # KV cache prefilled with N(0,1) to the context length: one [context, kv_dim] block reused for every layer
+    rng = np.random.default_rng(seed + 1)
+    k = rng.standard_normal((c["context"], kv_dim), dtype=np.float32)
+    v = rng.standard_normal((c["context"], kv_dim), dtype=np.float32)
+    lkv = kv_dim // world
+    k, v = np.ascontiguousarray(k[:, rank * lkv:(rank + 1) * lkv]), np.ascontiguousarray(v[:, rank * lkv:(rank + 1) * lkv])
+    for l in range(c["num_layers"]):
+        gm.kv_write(l, 0, k, v)
+    gm.set_position(c["context"])
+    info = dict(name=name, weight_bytes_per_token=total_bytes + (H // 32) * 34, context=c["context"],
+                kv_bytes_per_token=2 * c["context"] * kv_dim * 4 * c["num_layers"])
+    return gm, info
+
+
+def timed_decode(gm, ctx, tokens, stream, world, dist, dev):
+    import torch
+    gm.decode_greedy(1, 8)          # warm-up; also captures the step graph
+    gm.set_position(ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    toks = gm.decode_greedy(1, tokens)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, toks
+
+
+def run_decode(eng, name, tokens, stream, world, dist, dev, peak, n1):
+    """Greedy decode of one whole-model configuration; returns its report entry (device-timed, max over ranks).
+    n1: {config: ms per token of the single-GPU model}, measured by the caller on rank 0's GPU when world > 1."""
+    import torch
     gm, info = build_model(eng, name)
     ctx = info["context"]
-    def timed_decode():
-        gm.decode_greedy(1, 8)          # warm-up; also captures the step graph
-        gm.set_position(ctx)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0.record(stream)
-        toks = gm.decode_greedy(1, tokens)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, toks
-
     nccl_ms = None
     if world > 1:
         # first with NCCL all-gathers (the baseline), then with the kernels pushing their rows into the peers' memory
-        nccl_ms, _ = timed_decode()
+        nccl_ms, nccl_toks = timed_decode(gm, ctx, tokens, stream, world, dist, dev)
         handles = [None] * world
         dist.all_gather_object(handles, gm.tp_export())
         gm.tp_connect(handles)
         gm.set_position(ctx)
-    ms, toks = timed_decode()
+    ms, toks = timed_decode(gm, ctx, tokens, stream, world, dist, dev)
     if world > 1:
         dist.barrier()              # no rank frees memory its peers may still be writing into
     gm.free()
@@ -194,20 +310,165 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak):
     bound_ms = wb / world / (peak * 1e9) * 1e3
     entry = {"config": name, "tokens": tokens, "context": ctx, "weight_bytes_per_token": wb,
              "kv_bytes_per_token_at_context": info["kv_bytes_per_token"], "stream_bound_ms_per_token": bound_ms,
-             "first_tokens": [int(t) for t in toks[:4]]}
+             "first_tokens": [int(t) for t in toks[:8]]}
     if world == 1:
         entry["parallelism"] = "single GPU"
     else:
-        # both exchange mechanisms were timed; the entry's headline is the faster one, both are listed
         entry["parallelism"] = f"tp{world}: rows of every projection sharded"
         entry["pushed_rows_ms_per_token"] = ms / tokens
         entry["nccl_all_gather_ms_per_token"] = nccl_ms / tokens
-        entry["exchange"] = "rows pushed into the peers' vectors by the producing kernels (NVLink stores, tagged elements)" \
+        entry["nccl_first_tokens"] = [int(t) for t in nccl_toks[:8]]
+        entry["exchange"] = "rows pushed into the peers' vectors by the producing kernels (NVLink stores, one flag per vector)" \
             if ms <= nccl_ms else "NCCL all-gather issued by the library"
         ms = min(ms, nccl_ms)
+        if n1 and name in n1:
+            entry["ms_per_token_n1"] = n1[name]["ms_per_token"]
+            entry["first_tokens_n1"] = n1[name]["first_tokens"]
+            entry["tp_speedup"] = n1[name]["ms_per_token"] / (ms / tokens)
     entry.update({"tok_s": tokens / (ms * 1e-3), "ms_per_token": ms / tokens, "weight_gbs": wb * tokens / (ms * 1e-3) / 1e9,
                   "x_of_stream_bound": (ms / tokens) / bound_ms})
     return entry
+
+
+def tp_parity(eng, world, rank, dist):
+    """A small seed-shared model (same weights on every rank, shards cut from it), 8 greedy tokens in both exchange
+    modes; rank 0 compares token ids and the last logits with the CPU oracle of the whole model."""
+    from alice_llm_b200 import synth
+    from alice_llm_b200.gpu import GpuModel
+    cfg = dict(num_layers=2, hidden_dim=1024, intermediate_dim=2048, num_heads=16, num_kv_heads=8, head_dim=128,
+               vocab_size=2048, max_seq_len=96, rope_theta=500000.0, eps=1e-5)
+    rng = np.random.default_rng(11)
+    model = synth.soften_attention(synth.make_llama(rng, cfg))
+    kv_dim = cfg["num_kv_heads"] * cfg["head_dim"]
+    npos = 33
+    pre = [(rng.standard_normal((npos, kv_dim), dtype=np.float32), rng.standard_normal((npos, kv_dim), dtype=np.float32))
+           for _ in range(cfg["num_layers"])]
+    lkv = kv_dim // world
+    out = {}
+    ref_toks = ref_logits = None
+    if rank == 0:
+        from oracle import oracle as orc
+        orc.build()
+        o = orc.LlamaOracle(model, threads=orc.hw_threads())
+        for l, (k, v) in enumerate(pre):
+            o.kcache[l, :npos] = k
+            o.vcache[l, :npos] = v
+        o.pos = npos
+        ref_toks, tok = [], 5
+        for _ in range(8):
+            ref_logits = o.forward(tok)
+            tok = int(np.argmax(ref_logits))
+            ref_toks.append(tok)
+    for mode in ("nccl", "pushed_rows"):
+        gm = GpuModel.load(eng, model)
+        if mode == "pushed_rows":
+            handles = [None] * world
+            dist.all_gather_object(handles, gm.tp_export())
+            gm.tp_connect(handles)
+        for l, (k, v) in enumerate(pre):
+            gm.kv_write(l, 0, np.ascontiguousarray(k[:, rank * lkv:(rank + 1) * lkv]), np.ascontiguousarray(v[:, rank * lkv:(rank + 1) * lkv]))
+        gm.set_position(npos)
+        toks = [int(t) for t in gm.decode_greedy(5, 8)]
+        logits = gm.read_logits()
+        if rank == 0:
+            err = float((np.abs(logits.astype(np.float64) - ref_logits) / np.maximum(np.abs(ref_logits), 1.0)).max())
+            out[mode] = {"tokens_match_oracle": toks == ref_toks, "last_logits_max_rel_err": err}
+        dist.barrier()
+        gm.free()
+    return out
+
+
+def extras(eng, dev, stream, peak, steps, block_handles, xd4, hd4, yd4, only):
+    """formats / configs keys (single GPU, rank 0): CUDA events around `n` launches that cycle distinct weight copies."""
+    import torch
+    from alice_llm_b200 import synth
+    from alice_llm_b200.gpu import GpuQuantType
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+
+    def timed(fn, n):
+        for i in range(5):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3     # us per call
+
+    n = max(20, min(steps, 100))
+    out_formats, out_configs = {}, {}
+    cases = [("Q4_K", 12, 32768, 4096), ("Q5_K", 13, 32768, 4096), ("Q6_K", 14, 32768, 4096), ("Q8_0", 8, 32768, 4096),
+             ("Q1_0", 41, 102400, 5120), ("Q2_0", 42, 51200, 5120), ("ternary", 1000, 28672, 8192), ("sparse_ternary_packed_2bit", 1001, 28672, 8192)]
+    for name, qt, rows, cols in cases:
+        if only and name not in only:
+            continue
+        try:
+            if qt == 1000:
+                per = rows * ((cols + 31) // 32 * 8)
+            elif qt == 1001:
+                per = rows * ((cols + 15) // 16 * 4)
+            else:
+                per = rows * synth.row_bytes(qt, cols)
+            ncopy = max(2, int(300e6 // per) + 1)
+            keep, ws = [], []
+            for _ in range(ncopy):
+                if qt == 1000:
+                    planes, sc = dev_ternary_tensor(gen, dev, rows, cols)
+                    keep += [planes, sc]
+                    ws.append(eng.ternary_from_device(planes.data_ptr(), sc.data_ptr(), rows, cols))
+                elif qt == 1001:
+                    # packed 2-bit codes 00 / 01 / 11 with P(0) = 0.5, P(+1) = P(-1) = 0.25; uploaded through the host API
+                    a = torch.randint(0, 256, (per,), dtype=torch.uint8, device=dev, generator=gen) & 0x55
+                    b = torch.randint(0, 256, (per,), dtype=torch.uint8, device=dev, generator=gen) & 0x55
+                    packed = (a | ((a & b) << 1)).cpu().numpy()
+                    sc = (np.abs(np.random.default_rng(3).standard_normal(rows)) * 0.01).astype(np.float32)
+                    ws.append(eng.upload_sparse_ternary(packed, sc, rows, cols))
+                else:
+                    t = dev_ggml_tensor(gen, dev, qt, rows, cols)
+                    keep.append(t)
+                    ws.append(eng.weights_from_device(t.data_ptr(), t.numel(), rows, cols, GpuQuantType(qt)))
+            x = eng.upload_f32(np.random.default_rng(1).standard_normal(cols).astype(np.float32))
+            y = eng.alloc_f32(rows)
+            us = timed(lambda i: eng.matvec_dev(ws[i % ncopy], x, y, 1), n)
+            gbs = per / us / 1e3
+            out_formats[name] = {"rows": rows, "cols": cols, "bytes_per_launch": per, "us_per_launch": us, "gbs": gbs, "frac_of_peak": gbs / peak}
+            for w in ws:
+                w.free()
+            x.free(); y.free()
+            del keep, ws
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            out_formats[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    # configuration 1 alone: Q4_K 4096 x 4096, 32 copies (302 MB) cycled
+    try:
+        per = 4096 * 16 * 144
+        ts = [dev_ggml_tensor(gen, dev, 12, 4096, 4096) for _ in range(32)]
+        ws = [eng.weights_from_device(t.data_ptr(), t.numel(), 4096, 4096, GpuQuantType.Q4K) for t in ts]
+        x = eng.upload_f32(np.random.default_rng(0).standard_normal(4096).astype(np.float32))
+        y = eng.alloc_f32(4096)
+        us = timed(lambda i: eng.matvec_dev(ws[i % 32], x, y, 1), n)
+        out_configs["c1_q4k_4096x4096_b1"] = {"bytes_per_launch": per, "us_per_launch": us, "gbs": per / us / 1e3, "frac_of_peak": per / us / 1e3 / peak}
+        del ts, ws
+    except Exception as exc:
+        out_configs["c1_q4k_4096x4096_b1"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    # configuration 2 at batch 4: the weights stream once for the four inputs
+    try:
+        def step4(i):
+            g, u, d = block_handles[i % NCOPIES]
+            eng.swiglu_dev(g, u, xd4, hd4, 4)
+            eng.matvec_dev(d, hd4, yd4, 4)
+        us = timed(step4, n)
+        g, u, d = block_handles[0]
+        plan = [eng.batch_plan(g, 4, swiglu=True), eng.batch_plan(d, 4)]
+        out_configs["c2_ffn_q4k_q6k_b4"] = {"weight_bytes_per_step": STEP_BYTES, "us_per_step": us, "gbs": STEP_BYTES / us / 1e3,
+                                            "frac_of_peak": STEP_BYTES / us / 1e3 / peak, "tokens_per_step": 4,
+                                            "launches_and_weight_passes": {"swiglu": plan[0], "down": plan[1]}}
+    except Exception as exc:
+        out_configs["c2_ffn_q4k_q6k_b4"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    return out_formats, out_configs
 
 
 def run_ours(args, rank, world, local_rank):
@@ -243,6 +504,8 @@ def run_ours(args, rank, world, local_rank):
     xd = eng.upload_f32(x)
     hd = eng.alloc_f32(FFN)
     yd = eng.alloc_f32(HIDDEN)
+    x4 = np.concatenate([x, np.random.default_rng(5).standard_normal(3 * HIDDEN).astype(np.float32)])
+    xd4, hd4, yd4 = eng.upload_f32(x4), eng.alloc_f32(4 * FFN), eng.alloc_f32(4 * HIDDEN)
     x_pin = torch.from_numpy(x).pin_memory()
     y_pin = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
     import ctypes as C
@@ -259,6 +522,19 @@ def run_ours(args, rank, world, local_rank):
         eng.swiglu_dev(g, u, xd, hd, 1)
         eng.matvec_dev(d, hd, yd, 1)
         lib.alice_buf_read_f32(eng._h, yd._h, C.c_void_p(y_pin.data_ptr()), HIDDEN)
+
+    # parity of the timed code path, untimed: one step against the CPU oracle (rank 0)
+    parity = None
+    if rank == 0 and not args.no_cpu:
+        from oracle import oracle as orc
+        orc.build()
+        step(0)
+        got = eng.read_f32(yd).astype(np.float64)
+        eng.sync()
+        ref = orc.base_ffn(Q4_K, gate, up, Q6_K, down, HIDDEN, FFN, x, orc.hw_threads()).astype(np.float64)
+        parity = {"ffn_block_rel_l2": float(np.linalg.norm(got - ref) / np.linalg.norm(ref)),
+                  "ffn_block_max_rel_err": float((np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)).max()),
+                  "against": "CPU oracle (oracle/), same seeded inputs"}
 
     def barrier():
         if world > 1:
@@ -280,7 +556,8 @@ def run_ours(args, rank, world, local_rank):
             ms = float(t.item())
         return ms
 
-    for i in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for i in range(warm):
         step(i)
         step_e2e(i)
     eng.sync()
@@ -290,14 +567,19 @@ def run_ours(args, rank, world, local_rank):
         sampler.start()
     ms = timed(step, args.steps)
     ms_e2e = timed(step_e2e, args.steps)
-    # dominant kernel alone: the fused SwiGLU Q4_K matvec, one launch per weight copy
-    ms_k = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps)
+    # each kernel of the step alone, one launch per weight copy (the down projection takes the Q8_K blocks the last
+    # SwiGLU launch left, exactly as inside the step)
+    ms_sw = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps)
     ms_down = timed(lambda i: eng.matvec_dev(copies[i % NCOPIES][2], hd, yd, 1), args.steps)
     clocks = sampler.stop() if rank == 0 else None
     eng.sync()
 
     peak, peak_src = measured_peak()
-    decode = []
+    formats, configs = {}, {}
+    if rank == 0 and not args.no_extras:
+        formats, configs = extras(eng, dev, stream, peak, args.steps, copies, xd4, hd4, yd4,
+                                  set(args.formats.split(",")) if args.formats else None)
+    decode, n1, tp_par = [], {}, None
     if args.decode != "none":
         names = (["c3_8b_q4km", "c4_27b_q1_0", "c5_70b_ternary"] if world == 1 else ["c4_27b_q1_0", "c5_70b_ternary"]) \
             if args.decode == "auto" else args.decode.split(",")
@@ -306,12 +588,30 @@ def run_ours(args, rank, world, local_rank):
         del copies, base
         torch.cuda.empty_cache()
         if world > 1:
+            # the single-GPU figure of every sharded model, on rank 0's GPU, before the group is formed
+            if rank == 0:
+                for name in names:
+                    try:
+                        gm1, info1 = build_model(eng, name)
+                        ms1, toks1 = timed_decode(gm1, info1["context"], args.decode_tokens, stream, 1, None, dev)
+                        n1[name] = {"ms_per_token": ms1 / args.decode_tokens, "first_tokens": [int(t) for t in toks1[:8]]}
+                        gm1.free()
+                        del gm1
+                        torch.cuda.empty_cache()
+                    except Exception as exc:
+                        n1[name] = None
+            dist.barrier()
             ids = [eng.tp_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             eng.tp_init(rank, world, ids[0])
+            try:
+                tp_par = tp_parity(eng, world, rank, dist)
+            except Exception as exc:
+                tp_par = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            n1 = {k: v for k, v in n1.items() if v}
         for name in names:
             try:
-                decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak))
+                decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak, n1))
             except Exception as exc:   # the headline line must still be printed; every wait in the library is bounded
                 decode.append({"config": name, "error": f"{type(exc).__name__}: {exc}"[:300]})
                 break
@@ -322,41 +622,53 @@ def run_ours(args, rank, world, local_rank):
         return
     value = STEP_BYTES * world * args.steps / (ms * 1e-3) / 1e9
     e2e = STEP_BYTES * world * args.steps / (ms_e2e * 1e-3) / 1e9
-    k_gbs = 2 * GU_BYTES / (ms_k / args.steps * 1e-3) / 1e9
-    traffic = None
+    sw_gbs = 2 * GU_BYTES / (ms_sw / args.steps * 1e-3) / 1e9
+    down_gbs = DOWN_BYTES / (ms_down / args.steps * 1e-3) / 1e9
+    traffic = {}
     try:
         with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as f:
-            traffic = json.load(f).get("swiglu_q4k_bytes_per_launch")
+            traffic = json.load(f)
     except Exception:
         pass
+    kernels = {
+        "swiglu_q4k": {"kernel": "stream_gemv_kernel<FmtQ4K, fused SwiGLU>", "achieved": sw_gbs, "frac": sw_gbs / peak,
+                       "bytes_per_launch": 2 * GU_BYTES, "us_per_launch": ms_sw / args.steps * 1e3,
+                       "traffic": traffic.get("swiglu_q4k_bytes_per_launch")},
+        "down_q6k": {"kernel": "stream_gemv_kernel<FmtQ6K>", "achieved": down_gbs, "frac": down_gbs / peak,
+                     "bytes_per_launch": DOWN_BYTES, "us_per_launch": ms_down / args.steps * 1e3,
+                     "traffic": traffic.get("down_q6k_bytes_per_launch")},
+    }
+    slow = min(kernels.values(), key=lambda k: k["frac"])      # the roofline names the slower kernel of the step
     line = {
         "metric": "weight_stream_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-        "config": {"workload": "ffn_q4k_q6k_b1", "hidden": HIDDEN, "ffn": FFN, "gate_up": "Q4_K", "down": "Q6_K",
-                   "batch": 1, "weight_bytes_per_step": STEP_BYTES,
-                   "l2": f"{NCOPIES} distinct weight copies cycled ({NCOPIES * STEP_BYTES >> 20} MiB > 126 MB L2)",
-                   "parallelism": f"replicas x{world}" if world > 1 else "single"},
-        "roofline": {"bound": "hbm", "kernel": "stream_gemv_kernel<FmtQ4K, swiglu>", "achieved": k_gbs, "peak": peak,
-                     "unit": "GB/s", "frac": k_gbs / peak, "peak_source": f"{peak_src} (of {peak_src})",
-                     "bytes_per_launch": 2 * GU_BYTES, "us_per_launch": ms_k / args.steps * 1e3, "traffic": traffic,
-                     "frac_of_8000_nominal": k_gbs / 8000.0,
-                     "down_q6k": {"achieved": DOWN_BYTES / (ms_down / args.steps * 1e-3) / 1e9,
-                                  "us_per_launch": ms_down / args.steps * 1e3, "bytes_per_launch": DOWN_BYTES}},
+        "config": dict(CONFIG),
+        "l2": f"{NCOPIES} distinct weight copies cycled ({NCOPIES * STEP_BYTES >> 20} MiB > 126 MB L2)",
+        "parallelism": f"replicas x{world} (the FFN block does not shard; sharded work is under `decode`)" if world > 1 else "single",
+        "roofline": {"bound": "hbm", "kernel": slow["kernel"], "achieved": slow["achieved"], "peak": peak, "unit": "GB/s",
+                     "frac": slow["frac"], "peak_source": f"{peak_src} (of {peak_src})", "bytes_per_launch": slow["bytes_per_launch"],
+                     "us_per_launch": slow["us_per_launch"], "traffic": slow["traffic"],
+                     "frac_of_8000_nominal": slow["achieved"] / 8000.0, "whole_step_frac": value / world / peak,
+                     "kernels": kernels},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": KERNELS_PER_STEP * args.steps,
         "clocks": clocks,
+        "parity": parity,
+        "formats": formats,
+        "configs": configs,
         "decode": decode,
     }
+    if tp_par is not None:
+        line["tp_parity"] = tp_par
     if world == 1 and not args.no_cpu:
         from oracle import oracle as orc
         orc.build()
         threads = orc.hw_threads()
         v, n, dt = cpu_ffn_rate(block, threads, args.cpu_seconds, 2000)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
-                                "sample": f"{n} full FFN-block passes in {dt:.1f} s; C++ restatement of the "
-                                          "reference CPU path, row-parallel threads"}
+                                "sample": f"{n} {CPU_SAMPLE}; {dt:.1f} s"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -370,6 +682,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-format and per-configuration tables")
+    ap.add_argument("--formats", default="", help="comma list restricting the per-format table (default: all eight)")
     ap.add_argument("--decode", default="auto", help="auto | none | comma list of c3_8b_q4km,c4_27b_q1_0,c5_70b_ternary")
     ap.add_argument("--decode-tokens", type=int, default=128)
     args = ap.parse_args()

@@ -1,27 +1,83 @@
 // Timed CPU baseline: the oracle's restatement of the reference CPU path, compiled
 // -O3 -march=native (the reference builds with -C target-cpu=native, .cargo/config.toml) and
-// run row-parallel on worker threads, standing in for rayon's par_iter_mut over output rows
+// run row-parallel on a persistent pool of worker threads, standing in for rayon's par_iter_mut over output rows
 // (ALICE-LLM src/gguf.rs:3661-3675). TEST / BENCHMARK INFRASTRUCTURE ONLY: it is what the GPU
 // numbers are placed next to, never something the product calls.
 //
 // The per-block kernels are the same functions as in alice_oracle.cpp (included below), i.e. the
 // scalar bodies the reference's own "avx512" Q4_K kernel consists of (src/gguf.rs:2681-2695);
 // the compiler vectorizes them for the host.
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <mutex>
 #include <thread>
 
 #include "alice_oracle.cpp"
 
 namespace {
 
+// A persistent pool (rayon keeps its workers alive between par_iter calls too): the workers sleep on a condition
+// variable, a call hands every worker one contiguous row range and waits for all of them.
+class Pool {
+public:
+    explicit Pool(int n) : n_(n) {
+        for (int t = 0; t < n; t++) th_.emplace_back([this, t] { work(t); });
+    }
+    ~Pool() {
+        { std::lock_guard<std::mutex> lk(mu_); stop_ = true; gen_++; }
+        cv_.notify_all();
+        for (auto& t : th_) t.join();
+    }
+    int size() const { return n_; }
+    void run(size_t rows, const std::function<void(size_t, size_t)>& fn) {
+        std::unique_lock<std::mutex> lk(mu_);
+        fn_ = &fn; rows_ = rows; pending_ = n_; gen_++;
+        cv_.notify_all();
+        done_.wait(lk, [this] { return pending_ == 0; });
+    }
+private:
+    void work(int t) {
+        unsigned seen = 0;
+        for (;;) {
+            const std::function<void(size_t, size_t)>* fn;
+            size_t rows;
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return gen_ != seen; });
+                seen = gen_;
+                if (stop_) return;
+                fn = fn_; rows = rows_;
+            }
+            const size_t r0 = rows * t / n_, r1 = rows * (t + 1) / n_;
+            if (r1 > r0) (*fn)(r0, r1);
+            { std::lock_guard<std::mutex> lk(mu_); if (--pending_ == 0) done_.notify_one(); }
+        }
+    }
+    int n_;
+    std::vector<std::thread> th_;
+    std::mutex mu_;
+    std::condition_variable cv_, done_;
+    const std::function<void(size_t, size_t)>* fn_ = nullptr;
+    size_t rows_ = 0;
+    int pending_ = 0;
+    unsigned gen_ = 0;
+    bool stop_ = false;
+};
+
+Pool* pool_for(int nthreads) {
+    static std::mutex mu;
+    static Pool* pool = nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!pool || pool->size() != nthreads) { delete pool; pool = new Pool(nthreads); }
+    return pool;
+}
+
 template <class Fn>
 void par_rows(size_t rows, int nthreads, Fn fn) {
     if (nthreads <= 1) { fn(0, rows); return; }
-    std::vector<std::thread> th;
-    for (int t = 0; t < nthreads; t++) {
-        size_t r0 = rows * t / nthreads, r1 = rows * (t + 1) / nthreads;
-        if (r1 > r0) th.emplace_back([=] { fn(r0, r1); });
-    }
-    for (auto& t : th) t.join();
+    std::function<void(size_t, size_t)> f = fn;
+    pool_for(nthreads)->run(rows, f);
 }
 
 }  // namespace

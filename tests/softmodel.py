@@ -4,20 +4,7 @@ import numpy as np
 
 from alice_llm_b200 import synth
 
-_F16_FIELDS = {synth.Q4_K: (0, 2), synth.Q5_K: (0, 2), synth.Q6_K: (208,), synth.Q8_0: (0,), synth.Q1_0: (0,), synth.Q2_0: (0,)}
-
-
-def scale_blocks(entry, factor):
-    """(type, raw blocks) with every f16 block scale multiplied by `factor` (ternary planes: the per-row scales)."""
-    t, data = entry
-    if t == synth.TERNARY:
-        pos, neg, sc = data
-        return t, (pos, neg, (sc * np.float32(factor)).astype(np.float32))
-    blk = data.reshape(-1, synth.BLOCK_BYTES[t]).copy()
-    for off in _F16_FIELDS[t]:
-        v = blk[:, off:off + 2].copy().view(np.float16).astype(np.float32) * np.float32(factor)
-        blk[:, off:off + 2] = v.astype(np.float16).view(np.uint8).reshape(-1, 2)
-    return t, blk.reshape(-1)
+scale_blocks = synth.scale_blocks
 
 
 def soft_model(rng, cfg, mix=None, factor=None):
