@@ -6,6 +6,7 @@ GPU (nvcc cross-compiles). Output: alice_llm_b200/libalice_cuda.so, kept in-tree
 from __future__ import annotations
 
 import os
+from concurrent.futures import ThreadPoolExecutor
 import subprocess
 import sys
 
@@ -36,15 +37,18 @@ def _stale() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
-    objs = []
-    for src in SOURCES:
+    def compile_one(src):
         obj = os.path.join(CSRC, src.replace(".cu", ".o"))
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
         subprocess.check_call(cmd)
-        objs.append(obj)
+        return obj
+
+    # the translation units are independent: compile them side by side
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
     subprocess.check_call([_nvcc(), "-shared", "-o", LIB, *objs, "-lcudart", "-ldl"])
     return LIB
 

@@ -17,13 +17,6 @@ struct alice_engine {
     int* status = nullptr;        // device status word
     void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
     size_t scratch_bytes = 0;
-    // Q8_K blocks of the most recent fused-SwiGLU output, left there by the kernel itself; valid while shadow_of is
-    // the buffer that output went to and nobody has rewritten it since
-    void* shadow = nullptr;
-    size_t shadow_bytes = 0;
-    const struct alice_buf* shadow_of = nullptr;
-    uint32_t shadow_cols = 0, shadow_batch = 0;
-    unsigned int* tickets = nullptr;   // ALICE_ENGINE_TICKETS zeroed counters for the stand-alone entry points
     long long wait_limit = 0;          // SM cycles a kernel wait may take (0 = about one second)
     // handles created on the engine keep the struct alive after alice_engine_destroy (which releases everything else)
     int refs = 1;
@@ -60,4 +53,3 @@ int alice_cuda_fail(cudaError_t err, const char* what);
 alice::LaunchCfg alice_cfg_of(const alice_engine* e);
 void alice_engine_retain(alice_engine* e);
 void alice_engine_release(alice_engine* e);
-constexpr uint32_t ALICE_ENGINE_TICKETS = 1024;

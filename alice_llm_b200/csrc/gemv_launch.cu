@@ -389,7 +389,6 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     }
     const uint32_t units = units_per_row(w0.fmt, w0.cols);
     if (units == 0) return ALICE_E_UNSUPPORTED;
-    if (op.pub && op.pub->mode == PUB_BLOCKS && (op.nw != 1 || total_rows % QK_K != 0 || op.pub->n != total_rows)) return ALICE_E_SHAPE;
 
     StreamArgs a = {};
     a.w0 = w0.data; a.w1 = sw ? w1->data : nullptr;
@@ -456,14 +455,27 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     }
     a.rps = rps; a.cap = cap; a.nstages = nst;
     a.nseg = op.nw;
-    a.groups = 0;
+    // the rows are dealt out in "set rows" of `slots` rows (RowWalk, csrc/gemv_stream.cuh)
+    uint32_t total_sets = 0;
     for (uint32_t i = 0; i < op.nw; i++) {
         a.seg_w[i] = op.w[i]->data; a.seg_rows[i] = op.w[i]->rows; a.seg_y[i] = op.y_off[i]; a.seg_aux[i] = op.w[i]->scales;
-        a.seg_g0[i] = a.groups;
-        a.groups += (op.w[i]->rows + a.slots * rps - 1) / (a.slots * rps);
+        a.seg_t0[i] = total_sets;
+        total_sets += (op.w[i]->rows + a.slots - 1) / a.slots;
     }
-    a.seg_g0[op.nw] = a.groups;
-    pl.grid = std::min(ctas, a.groups);
+    for (uint32_t i = op.nw; i < 4; i++) a.seg_t0[i] = total_sets;
+    pl.grid = std::min(ctas, total_sets);
+    // the number of stages the walk produces, over all CTAs (what alice_plan_query reports)
+    a.groups = 0;
+    for (uint32_t cta = 0; cta < pl.grid; cta++) {
+        uint32_t t = (uint32_t)((uint64_t)total_sets * cta / pl.grid);
+        const uint32_t t_end = (uint32_t)((uint64_t)total_sets * (cta + 1) / pl.grid);
+        for (uint32_t sg = 0; t < t_end;) {
+            while (sg + 1 < op.nw && t >= a.seg_t0[sg + 1]) sg++;
+            const uint32_t T = std::min(t_end, a.seg_t0[sg + 1]) - t;
+            a.groups += (T + rps - 1) / rps;
+            t += T;
+        }
+    }
     a.tab_off = HDR_BYTES + nst * stage;
     pl.smem = HDR_BYTES + (size_t)nst * stage + act_bytes;
     pl.kl = kl; pl.swiglu = sw; pl.stage = stage;
@@ -529,9 +541,8 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         const int brc = launch_kq_batch(op, cfg, false, nullptr);
         if (brc != ALICE_E_SHAPE) return brc;
     }
-    // Formats without a batch kernel: one launch per input vector (the weights stream once per vector). A whole-vector
-    // hand-over rides on the last launch (every earlier one has completed by then: same stream), a per-block one on
-    // each launch for its own vector.
+    // Formats without a batch kernel: one launch per input vector (the weights stream once per vector). A hand-over
+    // to the next op rides on the last launch (every earlier one has completed by then: same stream).
     if (!op.w[0]) return ALICE_E_INVALID;
     uint32_t total_rows = 0;
     for (uint32_t i = 0; i < op.nw && i < 3; i++) if (op.w[i]) total_rows += op.w[i]->rows;
@@ -546,18 +557,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         o.y = op.y + (size_t)k * ys;
         if (op.resid) o.resid = op.resid + (size_t)k * ys;
         for (uint32_t p = 0; p < op.npeers && p < MAX_PEERS; p++) o.peer_y[p] = op.peer_y[p] + (size_t)k * ys;
-        Publish pk;
-        if (op.pub && op.pub->mode == PUB_VECTOR) {
-            o.pub = k + 1 == op.batch ? op.pub : nullptr;
-        } else if (op.pub && op.pub->mode == PUB_BLOCKS) {
-            pk = *op.pub;
-            pk.batch = 1;
-            pk.src += (size_t)k * pk.n;
-            const uint32_t pnb = pk.n / QK_K;
-            if (pk.dst.qs) { pk.dst.qs += (size_t)k * pk.n; pk.dst.d += (size_t)k * pnb; pk.dst.bsums += (size_t)k * pnb * 16; }
-            if (pk.dst.xn) pk.dst.xn += (size_t)k * pk.n;
-            o.pub = &pk;
-        }
+        if (op.pub) o.pub = k + 1 == op.batch ? op.pub : nullptr;
         const int rc = launch_single(o, cfg);
         if (rc) return rc;
     }

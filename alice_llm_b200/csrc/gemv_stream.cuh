@@ -2,8 +2,9 @@
 //
 // Two CTAs per SM stream the raw weight rows they own, in order, through a ring of shared-memory stages filled by
 // untiled TMA bulk copies (cp.async.bulk + mbarrier complete_tx), so the number of bytes in flight does not depend on
-// registers. A stage holds slots*rps whole consecutive rows (and, for the fused SwiGLU variant, the same rows of the
-// second matrix). Eight consumer warps decode from shared memory: P = 8/slots warps share a row, each warp set walks
+// registers. A stage holds up to slots*rps whole consecutive rows (and, for the fused SwiGLU variant, the same rows of
+// the second matrix); the rows are dealt to the CTAs in equal shares (to within one row per warp set), each CTA cuts
+// its share into stages of nearly equal size (RowWalk). Eight consumer warps decode from shared memory: P = 8/slots warps share a row, each warp set walks
 // rps rows per stage, and every lane owns the same KL "unit" positions (column ranges) of every row it ever sees, so
 // the activations of those columns are loaded ONCE into registers and no activation traffic touches shared memory
 // inside the loop. A ninth warp is the copy producer.
@@ -39,8 +40,8 @@ struct StreamArgs {
     uint32_t units;      // units per row (format specific)
     uint32_t P;          // consumer warps per row: 1, 2, 4 or 8
     uint32_t slots;      // warp sets per CTA = NCW / P
-    uint32_t rps;        // rows each warp set handles per stage (<= MAX_RPS)
-    uint32_t groups;     // ceil(rows / (slots * rps)) = number of stage-sized row groups
+    uint32_t rps;        // rows each warp set handles per stage, at most (<= MAX_RPS)
+    uint32_t groups;     // number of stage-sized row groups over all CTAs
     uint32_t nstages;
     uint32_t cap;        // bytes reserved per matrix per stage (multiple of 128)
     uint32_t batch;      // input vectors sharing one pass over the weights (batch kernels), else 1
@@ -65,6 +66,7 @@ struct StreamArgs {
     const uint8_t* seg_w[3];
     uint32_t seg_rows[3];
     uint32_t seg_g0[4];
+    uint32_t seg_t0[4];  // per-lane kernel: prefix sums of ceil(seg_rows / slots), the "set rows" RowWalk deals out
     uint32_t seg_y[3];
     const float* seg_aux[3];   // per-row scales of each segment's matrix (formats that have them), else null
     // Row-wise staging (tensor-core kernels): instead of one contiguous copy per stage every row is
@@ -176,6 +178,40 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
     if (t <= (2 + NCW) * nstages) mbar_fence_init();
 }
 
+// The row groups (stages) of one CTA of the per-lane kernel, in order; producer and consumers walk them in step.
+// A "set row" is `slots` consecutive rows (one per warp set when a stage holds one row per set); segment s owns set
+// rows [seg_t0[s], seg_t0[s+1]). CTA c owns the set rows [total*c/grid, total*(c+1)/grid) - shares differ by at most
+// one - and cuts the part inside each segment into ceil(T / rps) groups of floor or ceil(T / groups) set rows, so its
+// stages are of nearly equal size and no CTA streams a whole stage more than another (with fixed-size groups dealt
+// out whole, 1195 groups on 296 CTAs give some CTAs five and most four; measured on the 8B FFN block: 32.2 us per
+// block with the even shares, 32.9 us without).
+struct RowWalk {
+    uint32_t t, t_end, sg, left, base, extra;
+    __device__ __forceinline__ void init(const StreamArgs& a) {
+        const uint32_t total = a.seg_t0[a.nseg];
+        t = (uint32_t)(((uint64_t)total * blockIdx.x) / gridDim.x);
+        t_end = (uint32_t)(((uint64_t)total * (blockIdx.x + 1)) / gridDim.x);
+        sg = 0; left = 0; base = 0; extra = 0;
+
+    }
+    // Next group: segment, first row inside it, rows per warp set. false when the CTA's share is done.
+    __device__ __forceinline__ bool next(const StreamArgs& a, uint32_t& seg, uint32_t& r0, uint32_t& rps_g) {
+        if (left == 0) {
+            if (t >= t_end) return false;
+            while (sg + 1 < a.nseg && t >= a.seg_t0[sg + 1]) sg++;
+            const uint32_t T = min(t_end, a.seg_t0[sg + 1]) - t;
+            const uint32_t G = (T + a.rps - 1) / a.rps;
+            base = T / G; extra = T % G; left = G;
+        }
+        rps_g = base + (extra > 0 ? 1u : 0u);
+        if (extra > 0) extra--;
+        left--;
+        seg = sg; r0 = (t - a.seg_t0[sg]) * a.slots;
+        t += rps_g;
+        return true;
+    }
+};
+
 // Producer side of one matvec: streams this CTA's row groups of `a` through the ring. One thread.
 __device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& cx) {
     StreamSmem* sm = cx.sm;
@@ -191,6 +227,29 @@ __device__ __forceinline__ void stream_produce(const StreamArgs& a, StreamCtx& c
         while (sg + 1 < a.nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
         const uint32_t nrow = min(rows_per_group, a.seg_rows[sg] - r0);
+        const uint64_t off = (uint64_t)r0 * a.row_bytes;
+        const uint64_t a0 = off & ~uint64_t(15);
+        const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
+        const uint32_t fb = smem_u32(&sm->full[s]);
+        mbar_arrive_expect_tx(fb, two ? 2 * cb : cb);
+        bulk_g2s(cx.ring + s * cx.stage_stride, a.seg_w[sg] + a0, cb, fb);
+        if (two) bulk_g2s(cx.ring + s * cx.stage_stride + a.cap, a.w1 + a0, cb, fb);
+        cx.cc++;
+    }
+}
+
+// Producer side of the per-lane kernel: the CTA's share of the rows, group by group (RowWalk). One thread.
+__device__ __forceinline__ void stream_produce_walk(const StreamArgs& a, StreamCtx& cx) {
+    StreamSmem* sm = cx.sm;
+    volatile int* abort_flag = &sm->abort_flag;
+    const bool two = a.w1 != nullptr;
+    RowWalk walk;
+    walk.init(a);
+    uint32_t sg, r0, rps_g;
+    while (walk.next(a, sg, r0, rps_g)) {
+        const uint32_t s = cx.cc % cx.nstages, use = cx.cc / cx.nstages;
+        if (use > 0 && !wait_or_abort(smem_u32(&sm->empty[s]), (use - 1) & 1, abort_flag, a.status, KERR_WAIT_EMPTY, 2 * cx.limit)) return;
+        const uint32_t nrow = min(a.slots * rps_g, a.seg_rows[sg] - r0);
         const uint64_t off = (uint64_t)r0 * a.row_bytes;
         const uint64_t a0 = off & ~uint64_t(15);
         const uint32_t cb = (uint32_t)((off - a0) + (uint64_t)nrow * a.row_bytes + 15) & ~15u;
@@ -268,11 +327,11 @@ __device__ __forceinline__ void stream_argmax(unsigned long long* argmax_key, un
 template <bool PEER>
 static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSmem* sm) {
     const Publish& p = a.pub;
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tid = threadIdx.x;
     if (PEER && a.npeers) __threadfence_system(); else __threadfence();   // this thread's row stores come before the ticket
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
     if (sm->abort_flag) return;
-    if (p.mode == PUB_VECTOR) {
+    {
         if (tid == 0) {
             const unsigned int t = atomicAdd(p.tickets, 1u);
             int last = t == gridDim.x - 1 ? 1 : 0;
@@ -286,42 +345,6 @@ static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSm
         asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
         if (!sm->pub_last) return;
         if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<NCW, 1>(p, sm->norm_part, true);
-        return;
-    }
-    // PUB_BLOCKS: rows [ra, rb) of the single matrix are this CTA's; a 256-row block is prepared by the CTA whose
-    // rows complete it
-    const uint32_t rpg = a.slots * a.rps;
-    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
-    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t ra = min(a.rows, g0 * rpg), rb = min(a.rows, g1 * rpg);
-    if (ra >= rb) return;
-    const uint32_t b_lo = ra / QK_K, b_hi = (rb - 1) / QK_K;
-    for (uint32_t bb = b_lo; bb <= b_hi; bb += 32) {
-        if (warp == 0) {
-            const uint32_t b = bb + lane;
-            bool done = false;
-            if (b <= b_hi) {
-                const uint32_t lo = max(ra, b * QK_K), hi = min(rb, (b + 1) * QK_K);
-                const uint32_t full = min((uint32_t)QK_K, a.rows - b * QK_K);
-                const unsigned int old = atomicAdd(p.tickets + b, hi - lo);
-                done = old + (hi - lo) == full;
-                if (done) p.tickets[b] = 0;
-            }
-            const uint32_t mask = __ballot_sync(0xffffffffu, done);
-            if (lane == 0) sm->pub_mask = mask;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        const uint32_t mask = sm->pub_mask;
-        if (mask) {
-            __threadfence();
-            const uint32_t nset = __popc(mask);
-            for (uint32_t item = warp; item < nset * p.batch; item += NCW) {
-                const uint32_t k = item / nset;
-                const uint32_t b = bb + (uint32_t)__fns(mask, 0, (item % nset) + 1);
-                pub_emit_block(p.dst, pub_load8(p.src + (size_t)k * p.n, b * QK_K + lane * 8, p.n), lane, k, b, p.n);
-            }
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");   // pub_mask is rewritten in the next round
     }
 }
 
@@ -444,12 +467,10 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     StreamSmem* sm = cx.sm;
     volatile int* abort_flag = &sm->abort_flag;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t P = a.P, slots = a.slots, rps = a.rps;
-    const uint32_t rows_per_group = slots * rps;
+    const uint32_t P = a.P, slots = a.slots;
     const uint32_t slot = warp / P, part = warp % P;
     const float* const resid = PLAIN ? nullptr : a.resid;
     unsigned long long* const argmax_key = PLAIN ? nullptr : a.argmax_key;
-    const uint32_t nseg = PLAIN ? 1u : a.nseg;
 
     // the input: already prepared in global memory (every lane takes its own columns straight into registers; the
     // loads are L1-cached, so the warp sets of a CTA share one trip to L2), or the raw f32 vector, prepared per CTA
@@ -484,15 +505,13 @@ __device__ __forceinline__ bool stream_consume(const StreamArgs& a, StreamCtx& c
     constexpr int NV = RB * M;
     constexpr uint32_t LANES_PER_VALUE = 32 / NV;
 
-    const uint32_t g0 = (uint32_t)(((uint64_t)a.groups * blockIdx.x) / gridDim.x);
-    const uint32_t g1 = (uint32_t)(((uint64_t)a.groups * (blockIdx.x + 1)) / gridDim.x);
-    for (uint32_t g = g0; g < g1; g++) {
+    RowWalk walk;
+    walk.init(a);
+    uint32_t sg, r0, rps;
+    while (walk.next(a, sg, r0, rps)) {
         const uint32_t s = cx.cc % cx.nstages, ph = (cx.cc / cx.nstages) & 1;
         cx.cc++;
-        uint32_t sg = 0;
-        while (sg + 1 < nseg && g >= a.seg_g0[sg + 1]) sg++;
         const uint32_t seg_rows = a.seg_rows[sg];
-        const uint32_t r0 = (g - a.seg_g0[sg]) * rows_per_group;
         const uint32_t pad = (uint32_t)(((uint64_t)r0 * a.row_bytes) & 15);
         const uint32_t set0 = slot * rps;                 // first row (within the stage) of this warp set
         const uint32_t nrow = r0 + set0 < seg_rows ? min(rps, seg_rows - r0 - set0) : 0;
@@ -578,14 +597,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     if ((threadIdx.x >> 5) == NCW) {
         // producer: weights do not depend on the previous kernel, so copies start at once
         if ((threadIdx.x & 31) == 0) {
-            stream_produce(a, cx);
+            stream_produce_walk(a, cx);
             if (sm->abort_flag) stream_drain(cx);
         }
         return;
     }
     pdl_wait();  // activations come from the previous kernel
     stream_consume<F, KL, SWIGLU, PEER, PLAIN>(a, cx);
-    if (!PLAIN && a.pub.mode != PUB_NONE) stream_publish<PEER>(a, sm);
+    if (!PLAIN && a.pub.mode == PUB_VECTOR) stream_publish<PEER>(a, sm);
 }
 
 }  // namespace alice

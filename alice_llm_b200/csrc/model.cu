@@ -36,7 +36,7 @@ struct alice_model {
     // vector: Q8_K blocks for K-quant consumers, f32 (normalised) for the others
     uint8_t *hid_q8 = nullptr, *attn_q8 = nullptr, *ffn_q8 = nullptr;
     float* hid_xn = nullptr;
-    unsigned int *tk_vec = nullptr, *tk_blocks = nullptr, *tk_attn = nullptr, *attn_tickets = nullptr;
+    unsigned int *tk_vec = nullptr, *tk_attn = nullptr, *attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
     // tensor parallel (engine's group): every projection holds rows [r*R/n, (r+1)*R/n); l* are the local sizes
@@ -108,7 +108,8 @@ Q8KView q8_view(uint8_t* base, uint32_t n) {
 }
 
 // The bit-plane tensor-core kernels (Q1_0, Q2_0, ternary formats) take their input as a finished f32 vector in global
-// memory; every other kernel prepares the raw vector per CTA (rms_norm, Q8_K) in its own prologue.
+// memory, left there by the kernel that produced the vector; the K-quant kernels take Q8_K blocks that a one-CTA kernel
+// prepares between producer and consumer; the rest (Q8_0) prepare the raw vector per CTA in their own prologue.
 bool wants_prepared(const WeightDesc& w) {
     return (w.fmt == WF_Q1_0 || w.fmt == WF_Q2_0 || w.fmt == WF_TERNARY || w.fmt == WF_SPARSE_TERNARY) && w.cols % 4 == 0;
 }
@@ -173,16 +174,17 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         op.npeers = m->npeers;
         for (uint32_t q = 0; q < m->npeers; q++) op.peer_y[q] = reinterpret_cast<float*>(on_peer(q, vec));
     };
-    // input of a matvec over `w` that reads the (normalised) hidden state: the prepared f32 vector for the tensor-core
-    // kernels, else the raw vector plus the norm weights (prepared per CTA)
-    // Batches: the tensor-core batch kernel of the K-quants wants ONE shared copy of the Q8_K blocks of all vectors, so
-    // a one-CTA kernel prepares them (norm + Q8_K of every vector) ahead of the matvec; `fresh` = the hidden state has
-    // changed since the last such preparation.
+    // input of a matvec over `w` that reads the (normalised) hidden state: the prepared f32 vector for the bit-plane
+    // tensor-core kernels; for the K-quants ONE shared copy of the Q8_K blocks (of all vectors of a batch), which a
+    // one-CTA kernel prepares (norm + Q8_K) ahead of the matvec - the matvec is its programmatic dependent, so its CTAs
+    // are resident and streaming weights meanwhile (measured on the 8B decode step: 2.23 ms per token this way, 2.28
+    // with every CTA of the matvec normalising and quantizing the vector itself); else the raw vector plus the norm
+    // weights, prepared per CTA. `fresh` = the hidden state has changed since the last such preparation.
     Q8KView hid_view = q8_view(m->hid_q8, H);
     auto hidden_input = [&](GemvOp& op, const WeightDesc& w, const float* norm_w, bool via_preq, bool fresh) -> int {
         op.batch = batch;
         if (wants_prepared(w)) { op.x = m->hid_xn; return ALICE_OK; }
-        if (batch > 1 && format_uses_q8k(w.fmt)) {
+        if (format_uses_q8k(w.fmt)) {
             if (fresh) {
                 Publish p{};
                 p.mode = PUB_VECTOR; p.n = H; p.batch = batch; p.src = m->hidden; p.norm_w = norm_w; p.eps = c.eps;
@@ -277,26 +279,22 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
         }
-        {   // fused SwiGLU gate/up (src/llama3.rs:14497-14534); leaves its output prepared for the down projection
-            GemvOp op; Q8KView view; Publish p;
+        {   // fused SwiGLU gate/up (src/llama3.rs:14497-14534)
+            GemvOp op; Publish p;
             op.w[0] = &L.gate; op.up = &L.up;
             if ((rc = hidden_input(op, L.gate, L.ffn_norm, true, true))) return rc;
             op.y = m->ffn_h; op.y_off[0] = r * m->lF; op.y_stride = F;
-            Need nd;
-            nd.q8 = n == 1 && format_uses_q8k(L.down.fmt);   // else the down projection reads ffn_h itself
-            if (n == 1) {
-                p = Publish{};
-                if (nd.q8) {
-                    p.mode = PUB_BLOCKS; p.n = F; p.batch = batch; p.src = m->ffn_h; p.tickets = m->tk_blocks;
-                    fill_dst(p.dst, nd, m->ffn_q8, nullptr, F);
-                    op.pub = &p;
-                }
-            } else {
-                vector_pub(p, m->ffn_h, F, nullptr, nd, m->ffn_q8, nullptr, 4 * l + 2);
+            // a K-quant down projection takes the SwiGLU output as Q8_K: a small quantizer kernel follows (single GPU;
+            // with a tensor-parallel group the down projection prepares the gathered vector in its own prologue)
+            const bool down_q8 = n == 1 && format_uses_q8k(L.down.fmt);
+            if (n > 1) {
+                Need none;
+                vector_pub(p, m->ffn_h, F, nullptr, none, nullptr, nullptr, 4 * l + 2);
                 if (!nccl) op.pub = &p;
             }
             push_rows(op, m->ffn_h);
             if ((rc = gemv(m, op, "gate/up"))) return rc;
+            if (down_q8) { launch_quantize_q8k(m->ffn_h, F, batch, m->ffn_q8, st, pdl, MAX_BATCH); MCU(cudaGetLastError()); }
             if (n > 1 && (rc = gather_then_publish(m->ffn_h, m->lF, p))) return rc;
         }
         {   // down projection + residual (src/llama3.rs:14536-14555); leaves hidden prepared for the next layer / the head
@@ -432,7 +430,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
             m->epoch = reinterpret_cast<unsigned int*>(m->xchg + o_epoch);
         }
     }
-    const uint32_t tk_blocks_n = (c.intermediate_dim + 255) / 256 + 1;
     if (!rc) rc = dev_alloc(m, &m->qkv, (size_t)B * (lq + 2 * lkv));
     if (!rc) rc = dev_alloc(m, &m->kcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
@@ -440,7 +437,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->attn_tickets, (size_t)B * (c.num_kv_heads / n));
     if (!rc) rc = dev_alloc(m, &m->tk_vec, 1);
     if (!rc) rc = dev_alloc(m, &m->tk_attn, 1);
-    if (!rc) rc = dev_alloc(m, &m->tk_blocks, tk_blocks_n);
     if (!rc) rc = dev_alloc(m, &m->rope_tab, (size_t)B * 128);
     if (!rc) rc = dev_alloc(m, &m->rope_freq, 64);
     if (!rc) rc = dev_alloc(m, &m->hid_q8, Q8KLayout::make((c.hidden_dim + 255) / 256, B).total);
@@ -461,7 +457,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)B * (c.num_kv_heads / n) * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_vec, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_attn, 0, 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_blocks, 0, (size_t)tk_blocks_n * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4 * B, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);

@@ -2,9 +2,9 @@
 //
 // Every CTA of a matvec needs its whole input in the form its inner loop reads: Q8_K blocks for the K-quant
 // formats, the RMS-normalised f32 vector for the others. That form is the same in every CTA, so it is computed
-// once - by the last CTA of the PRODUCING kernel to finish (a ticket counter), or, where the output needs no
-// whole-vector reduction (no norm), block by block by whichever CTA completes a 256-element block - and left in
-// global memory; the consumer's CTAs fetch it straight into registers. Arithmetic: rms_norm (src/llama3.rs:5244-5256:
+// once - by the last CTA of the PRODUCING kernel to finish (a ticket counter), or by a small stand-alone kernel
+// launched between producer and consumer (csrc/q8k.cu, publish_vector_kernel) - and left in global memory; the
+// consumer's CTAs fetch it straight into registers. Arithmetic: rms_norm (src/llama3.rs:5244-5256:
 // f64 sum of squares, f32 mean / sqrt / divide, (x * scale) * w) and quantize_row_q8_k (src/gguf.rs:1323-1374).
 #pragma once
 #include "common.cuh"
@@ -13,7 +13,6 @@
 namespace alice {
 
 constexpr uint32_t PUB_NONE = 0;
-constexpr uint32_t PUB_BLOCKS = 1;   // Q8_K of the output, per 256 rows, by the CTA that completes the block (no norm)
 constexpr uint32_t PUB_VECTOR = 2;   // whole vector, by the last CTA of the grid: optional rms_norm, then Q8_K and / or f32
 
 constexpr uint32_t MAX_PEERS = 7;
@@ -30,10 +29,10 @@ struct PublishDst {
 
 struct Publish {
     uint32_t mode;
-    uint32_t n;              // elements per vector (PUB_BLOCKS: the matvec's own rows)
+    uint32_t n;              // elements per vector
     uint32_t batch;          // vectors, src[k * n + i]
     const float* src;        // the f32 vector(s) this matvec writes rows of
-    unsigned int* tickets;   // PUB_BLOCKS: one counter per (vector, 256-row block); PUB_VECTOR: one counter. Zero between launches.
+    unsigned int* tickets;   // one counter, zero between launches
     const float* norm_w;     // PUB_VECTOR: rms_norm weights, or null
     float eps;
     PublishDst dst;

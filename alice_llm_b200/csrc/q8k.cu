@@ -18,9 +18,9 @@ __global__ void __launch_bounds__(128) quantize_q8k_kernel(const float* __restri
     q8k_quantize_block_warp(q8k_load_lane(x + (size_t)blk * QK_K, lane, true), lane, qs + (size_t)blk * QK_K, d + blk, bsums + (size_t)blk * 16);
 }
 
-void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* base, cudaStream_t stream, bool pdl) {
+void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* base, cudaStream_t stream, bool pdl, uint32_t layout_batch) {
     const uint32_t nb = cols / QK_K;
-    const Q8KLayout l = Q8KLayout::make(nb, batch);
+    const Q8KLayout l = Q8KLayout::make(nb, layout_batch ? layout_batch : batch);
     const uint32_t nblocks = nb * batch;
     if (nblocks == 0) return;
     auto* p = static_cast<uint8_t*>(base);

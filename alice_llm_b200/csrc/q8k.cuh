@@ -106,6 +106,6 @@ __device__ __forceinline__ void q8k_quantize_block_warp(const Q8KLaneInput in, u
 
 // Quantizes `batch` vectors of `cols` floats (x[k*cols + c]) into the layout above.
 // Bit-exact with quantize_row_q8_k (src/gguf.rs:1323-1374).
-void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* q8k_base, cudaStream_t stream, bool pdl = false);
+void launch_quantize_q8k(const float* x, uint32_t cols, uint32_t batch, void* q8k_base, cudaStream_t stream, bool pdl = false, uint32_t layout_batch = 0);
 
 }  // namespace alice
