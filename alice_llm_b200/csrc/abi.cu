@@ -100,6 +100,16 @@ int ensure_scratch(alice_engine* e, size_t bytes) {
     return ALICE_OK;
 }
 
+int ensure_prep(alice_engine* e, size_t bytes) {
+    if (bytes <= e->prep_bytes) return ALICE_OK;
+    CU(cudaStreamSynchronize(e->stream));
+    if (e->prep) CU(cudaFree(e->prep));
+    e->prep = nullptr; e->prep_bytes = 0;
+    CU(cudaMalloc(&e->prep, bytes));
+    e->prep_bytes = bytes;
+    return ALICE_OK;
+}
+
 int launch_rc(int rc, const char* what) {
     if (rc == ALICE_OK) return rc;
     if (rc == ALICE_E_CUDA) return fail(rc, "%s: launch failed: %s", what, cudaGetErrorString(cudaGetLastError()));
@@ -155,9 +165,10 @@ int32_t alice_engine_destroy(alice_engine* e) {
     cudaStreamSynchronize(e->stream);
     alice::tp_release(e);
     if (e->scratch) cudaFree(e->scratch);
+    if (e->prep) cudaFree(e->prep);
     if (e->status) cudaFree(e->status);
     if (e->own_stream) cudaStreamDestroy(e->stream);
-    e->scratch = nullptr; e->status = nullptr; e->stream = nullptr;
+    e->scratch = e->prep = nullptr; e->status = nullptr; e->stream = nullptr;
     e->dead = true;               // handles created on this engine may outlive it: they only free their own memory
     alice_engine_release(e);
     return ALICE_OK;
@@ -463,8 +474,14 @@ Q8KView view_at(void* base, uint32_t nb, uint32_t batch) {
 
 // One matvec / fused SwiGLU over `batch` prepared input vectors.
 static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const Q8KView* q8, const float* xf,
-                    float* y, uint32_t batch, const Publish* pub, const char* who) {
+                    float* y, uint32_t batch, const Publish* pub, const char* who, bool may_alloc = true) {
     GemvOp op;
+    const WeightFormat f = w0->d.fmt;
+    if (f == WF_Q1_0 || f == WF_Q2_0 || f == WF_TERNARY || f == WF_SPARSE_TERNARY) {
+        // room for the activation digit table, prepared once ahead of the matvec (csrc/gemv_mma.cuh)
+        if (may_alloc) { const int rc = ensure_prep(e, mma_prep_bytes(w0->d.cols)); if (rc) return rc; }
+        op.prep = e->prep; op.prep_bytes = e->prep_bytes;
+    }
     op.w[0] = &w0->d; op.up = w1 ? &w1->d : nullptr;
     op.q8 = q8; op.x = xf; op.y = y; op.batch = batch; op.pub = pub;
     op.wait_limit = e->wait_limit;
@@ -697,7 +714,7 @@ int32_t alice_matvec_preq_noalloc(alice_engine* e, const alice_weights* w, const
     const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 8);
     q8k_to_f32_noalloc_kernel<<<blocks, 256, 0, e->stream>>>(view_of(q, 0), (uint32_t)total);
     CU(cudaGetLastError());
-    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, nullptr, who);
+    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, nullptr, who, false);   // never allocates
 }
 
 }  // extern "C"

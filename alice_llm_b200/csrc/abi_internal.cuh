@@ -17,6 +17,8 @@ struct alice_engine {
     int* status = nullptr;        // device status word
     void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
     size_t scratch_bytes = 0;
+    void* prep = nullptr;         // engine-owned scratch of the bit-plane kernels: the activation digit table of the current input
+    size_t prep_bytes = 0;
     long long wait_limit = 0;          // SM cycles a kernel wait may take (0 = about one second)
     // handles created on the engine keep the struct alive after alice_engine_destroy (which releases everything else)
     int refs = 1;

@@ -146,7 +146,7 @@ int plan_mma(const GemvOp& op, const LaunchCfg& cfg, StreamArgs a, uint32_t col_
     if (a.x) a.x += col_lo;
     const uint32_t ge = (w0.fmt == WF_Q2_0 || w0.fmt == WF_SPARSE_TERNARY) ? 64u : 128u;   // elements per 16 weight bytes
     const uint32_t ngroups = (col_n + ge - 1) / ge;
-    const uint32_t table_bytes = (((mma_table_bytes(ngroups) + 15u) & ~15u) + ngroups * 4u + 127u) & ~127u;   // digit table, then per-block sums
+    const uint32_t table_bytes = (mma_blob_bytes(ngroups) + 127u) & ~127u;   // digit table, per-block sums, fixed-point unit
     for (uint32_t per_sm = 2; per_sm >= 1; per_sm--) {
         const uint32_t budget = per_sm == 2 ? MMA_BUDGET_2 : MMA_BUDGET_1;
         if (HDR_BYTES + table_bytes >= budget) continue;
@@ -486,6 +486,28 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
 
 namespace {
 
+template <int CODE>
+int launch_mma_table_code(const float* x, uint32_t cols, uint8_t* blob, uint32_t tsum_blocks, const LaunchCfg& cfg) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((cols + MMA_PREP_ELEMS - 1) / MMA_PREP_ELEMS);
+    lc.blockDim = dim3(NCW * 32);
+    lc.stream = cfg.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = cfg.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, mma_table_kernel<CODE>, x, cols, blob, tsum_blocks) == cudaSuccess ? ALICE_OK : ALICE_E_CUDA;
+}
+int launch_mma_table(WeightFormat f, const float* x, uint32_t cols, uint8_t* blob, const LaunchCfg& cfg) {
+    switch (f) {
+        case WF_Q1_0: return launch_mma_table_code<0>(x, cols, blob, cols / 128, cfg);
+        case WF_TERNARY: return launch_mma_table_code<0>(x, cols, blob, 0, cfg);
+        case WF_Q2_0: return launch_mma_table_code<1>(x, cols, blob, cols / 128, cfg);
+        default: return launch_mma_table_code<2>(x, cols, blob, 0, cfg);
+    }
+}
+
 // One launch (or, for a bit-plane matvec whose rows are too wide for shared memory, one launch per column chunk)
 // for ONE input vector.
 int launch_single(const GemvOp& op, const LaunchCfg& cfg) {
@@ -497,6 +519,7 @@ int launch_single(const GemvOp& op, const LaunchCfg& cfg) {
     if (pl.mma) {
         // one launch per column chunk; a later chunk adds to what the earlier ones left in y, and only the last one
         // sees the final values (argmax epilogue, rows pushed to peers, hand-over to the next op)
+        size_t prep_off = 0;
         for (uint32_t c = 0; c < pl.ksplit; c++) {
             StreamPlan pc = pl;
             if (pl.ksplit > 1) {
@@ -508,6 +531,16 @@ int launch_single(const GemvOp& op, const LaunchCfg& cfg) {
                 if (rc) return rc;
                 if (c > 0) pc.args.resid = op.y;
                 if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.pub = Publish{}; }
+            }
+            // the activation digit table of this (chunk of the) vector, prepared once ahead of the matvec
+            const uint32_t ge = (w0.fmt == WF_Q2_0 || w0.fmt == WF_SPARSE_TERNARY) ? 64u : 128u;
+            const uint32_t blob = (mma_blob_bytes((pc.args.cols + ge - 1) / ge) + 127u) & ~127u;
+            if (op.prep && prep_off + blob <= op.prep_bytes && ((uintptr_t)op.prep & 15) == 0) {
+                uint8_t* dst = static_cast<uint8_t*>(op.prep) + prep_off;
+                prep_off += blob;
+                const int trc = launch_mma_table(w0.fmt, pc.args.x, pc.args.cols, dst, cfg);
+                if (trc) return trc;
+                pc.args.tab_global = dst;
             }
             const int rc = w0.fmt == WF_Q1_0 ? launch_mma<MmaQ1_0>(pc, cfg) : w0.fmt == WF_Q2_0 ? launch_mma<MmaQ2_0>(pc, cfg)
                          : w0.fmt == WF_TERNARY ? launch_mma<MmaTernary>(pc, cfg) : launch_mma<MmaSparseTernary>(pc, cfg);
@@ -562,6 +595,12 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         if (rc) return rc;
     }
     return ALICE_OK;
+}
+
+size_t mma_prep_bytes(uint32_t cols) {
+    // the finest grouping (64 elements per group) and the slack of up to four column chunks, each with its own
+    // zero record, sums and unit, rounded to 128 bytes
+    return ((size_t)mma_blob_bytes((cols + 63) / 64) + 1024 + 255) & ~size_t(255);
 }
 
 int batch_plan(const GemvOp& op, const LaunchCfg& cfg, uint32_t* launches, uint32_t* weight_passes) {

@@ -60,7 +60,13 @@ struct GemvOp {
     uint32_t npeers = 0;                                   // tensor parallel: also store every row result on these GPUs
     float* peer_y[MAX_PEERS] = {};
     long long wait_limit = 0;                              // SM cycles a wait inside the kernel may take (0 = about a second)
+    // Bit-plane tensor-core kernels: device scratch for the activation digit table, prepared once by a small kernel
+    // ahead of the matvec; without it (or when it is too small) every CTA of the matvec builds the table itself.
+    void* prep = nullptr;
+    size_t prep_bytes = 0;
 };
+// Scratch bytes GemvOp::prep needs for a bit-plane matvec over `cols` columns (any such format, any column split).
+size_t mma_prep_bytes(uint32_t cols);
 int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg);
 // How a batch of op.batch vectors would run: kernel launches, and how many times the weight bytes stream from HBM.
 int batch_plan(const GemvOp& op, const LaunchCfg& cfg, uint32_t* launches, uint32_t* weight_passes);

@@ -73,20 +73,20 @@ __device__ __forceinline__ void mma_store_digits(uint8_t* w, int f) {
     w[0] = (uint8_t)f; w[64] = (uint8_t)d1; w[128] = (uint8_t)d2; w[192] = (uint8_t)d3;
 }
 
-template <int CODE>
-static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float* x, uint32_t cols, uint8_t* table,
-                                                     float* tsum, uint32_t tsum_blocks) {
+// Bytes of the prepared activation blob of a vector of `groups` groups: digit table (two halves + zero record),
+// per-128-element sums (one float per group at most), the fixed-point unit kappa. The same layout in shared memory
+// (built per CTA) and in global memory (built once by mma_table_kernel and bulk-copied in). A multiple of 16.
+__host__ __device__ constexpr uint32_t mma_blob_tsum_off(uint32_t groups) { return (mma_table_bytes(groups) + 15u) & ~15u; }
+__host__ __device__ constexpr uint32_t mma_blob_kappa_off(uint32_t groups) { return mma_blob_tsum_off(groups) + ((groups * 4u + 15u) & ~15u); }
+__host__ __device__ constexpr uint32_t mma_blob_bytes(uint32_t groups) { return mma_blob_kappa_off(groups) + 16u; }
+
+// max |x| over the whole vector; all NCW*32 threads take part (red = NCW floats of shared memory).
+static __device__ __forceinline__ float mma_vec_amax(float* red, const float* x, uint32_t nvec) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t nvec = cols / 4;
-    const bool one_round = nvec <= NCW * 32 * TB_V;   // then the registers of the first pass serve the second
-    constexpr uint32_t GE = mma_group_elems<CODE>();
-    const uint32_t groups = (cols + GE - 1) / GE;
-    const uint32_t half_bytes = groups * 256;
-    float4 v[TB_V];
-    // 1. power-of-two scale above max |x|
     float amax = 0.0f;
 #pragma unroll 1
     for (uint32_t base = 0; base < nvec; base += NCW * 32 * TB_V) {
+        float4 v[TB_V];
 #pragma unroll
         for (int k = 0; k < TB_V; k++) {
             const uint32_t i = base + k * NCW * 32 + tid;
@@ -98,39 +98,39 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    float* red = reinterpret_cast<float*>(sm->norm_part);
     if (lane == 0) red[warp] = amax;
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
     amax = 0.0f;
 #pragma unroll
     for (int w = 0; w < NCW; w++) amax = fmaxf(amax, red[w]);
-    // scale = 2^(exponent(amax) + 1) > amax; inf / nan inputs fall back to scale 1 (their products are garbage
-    // in the reference too)
-    const uint32_t ebits = (__float_as_uint(amax) >> 23) & 0xffu;
-    const int e = (ebits == 0u || ebits == 0xffu) ? 0 : (int)ebits - 126;
-    const float to_fixed = ldexpf(1.0f, MMA_FIX_BITS - e);
-    const float kappa = ldexpf(1.0f, e - MMA_FIX_BITS);
-    // 2. digits. Record of (group G, digit d, quad lane t) at ((G*4 + d)*4 + t)*16 in the half of its bit position;
-    //    word j & 3 of the record, byte `byte & 3` of the word.
+    return amax;
+}
+
+// Digits of the float4s [v_lo, v_hi) of x (v_lo a multiple of NCW*32, so that a warp's 32 float4 of one round are
+// one 128-element block) into `table` (record of group G at G*256 in each half, the halves half_bytes apart; a caller
+// that builds a slice passes a pointer moved back by the slice's first group) and their block sums into tsum[block].
+template <int CODE>
+static __device__ __forceinline__ void mma_build_digits(const float* x, uint32_t v_lo, uint32_t v_hi, uint8_t* table, uint32_t half_bytes,
+                                                        float* tsum, uint32_t tsum_blocks, float to_fixed) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31;
 #pragma unroll 1
-    for (uint32_t base = 0; base < nvec; base += NCW * 32 * TB_V) {
-        if (!one_round) {
+    for (uint32_t base = v_lo; base < v_hi; base += NCW * 32 * TB_V) {
+        float4 v[TB_V];
 #pragma unroll
-            for (int k = 0; k < TB_V; k++) {
-                const uint32_t i = base + k * NCW * 32 + tid;
-                v[k] = i < nvec ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+        for (int k = 0; k < TB_V; k++) {
+            const uint32_t i = base + k * NCW * 32 + tid;
+            v[k] = i < v_hi ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int k = 0; k < TB_V; k++) {
             const uint32_t i = base + k * NCW * 32 + tid;
-            if (base + k * NCW * 32 < nvec) {     // warp-uniform: the whole warp takes part in the block sum
+            if (base + k * NCW * 32 < v_hi) {     // warp-uniform: the whole warp takes part in the block sum
                 float ts = (v[k].x + v[k].y) + (v[k].z + v[k].w);
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
                 if (lane == 0 && (i >> 5) < tsum_blocks) tsum[i >> 5] = ts;
             }
-            if (i < nvec) {
+            if (i < v_hi) {
                 const float xq[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
                 if (CODE == 0) {
                     // this float4 is bits 4h .. 4h+3 (h = i & 1) of one weight byte
@@ -158,9 +158,14 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float
             }
         }
     }
-    // zero the part of the last group past `cols` (only a ragged ternary row has one; its weight bits there are zero,
-    // so the table content only has to be finite)
-    for (uint32_t idx = cols + tid; idx < groups * GE; idx += NCW * 32) {
+}
+
+// Zeroes the part of the last group past `cols` (only a ragged ternary row has one; its weight bits there are zero,
+// so the table content only has to be finite). Group indices as in mma_build_digits.
+template <int CODE>
+static __device__ __forceinline__ void mma_zero_tail(uint32_t cols, uint32_t groups, uint8_t* table, uint32_t half_bytes) {
+    constexpr uint32_t GE = mma_group_elems<CODE>();
+    for (uint32_t idx = cols + threadIdx.x; idx < groups * GE; idx += NCW * 32) {
         const uint32_t byte = CODE == 0 ? idx >> 3 : idx >> 2, G = byte >> 4, t = (byte >> 2) & 3u, bi = byte & 3u;
         uint8_t* rec = table + ((size_t)(G * 4) * 4 + t) * 16 + bi;
         if (CODE == 0) {
@@ -173,9 +178,70 @@ static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float
             mma_store_digits(w + 4, 0);
         }
     }
-    if (tid < 4) reinterpret_cast<uint32_t*>(table + 2 * (size_t)half_bytes)[tid] = 0u;   // the zero record
+}
+
+// scale = 2^(exponent(amax) + 1) > amax; inf / nan inputs fall back to scale 1 (their products are garbage in the
+// reference too). to_fixed turns x into 26-bit fixed point, kappa is the value of one unit.
+__device__ __forceinline__ void mma_fixed_scale(float amax, float& to_fixed, float& kappa) {
+    const uint32_t ebits = (__float_as_uint(amax) >> 23) & 0xffu;
+    const int e = (ebits == 0u || ebits == 0xffu) ? 0 : (int)ebits - 126;
+    to_fixed = ldexpf(1.0f, MMA_FIX_BITS - e);
+    kappa = ldexpf(1.0f, e - MMA_FIX_BITS);
+}
+
+// The whole table, built by the NCW consumer warps of a matvec CTA in its own shared memory (the path for callers
+// that give the matvec no room for a prepared copy).
+template <int CODE>
+static __device__ __noinline__ float mma_build_table(StreamSmem* sm, const float* x, uint32_t cols, uint8_t* table,
+                                                     float* tsum, uint32_t tsum_blocks) {
+    const uint32_t nvec = cols / 4;
+    constexpr uint32_t GE = mma_group_elems<CODE>();
+    const uint32_t groups = (cols + GE - 1) / GE;
+    const uint32_t half_bytes = groups * 256;
+    float to_fixed, kappa;
+    mma_fixed_scale(mma_vec_amax(reinterpret_cast<float*>(sm->norm_part), x, nvec), to_fixed, kappa);
+    mma_build_digits<CODE>(x, 0, nvec, table, half_bytes, tsum, tsum_blocks, to_fixed);
+    mma_zero_tail<CODE>(cols, groups, table, half_bytes);
+    if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(table + 2 * (size_t)half_bytes)[threadIdx.x] = 0u;   // the zero record
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
     return kappa;
+}
+
+// The same table built ONCE per vector, ahead of the matvec, by a small grid: CTA b (NCW*32 threads) turns the
+// elements [b * MMA_PREP_ELEMS, (b + 1) * MMA_PREP_ELEMS) into digits in shared memory and copies its slice of both
+// halves (and of the block sums) to the blob in global memory with 16-byte stores; every CTA finds max |x| of the
+// whole vector for itself (the vector is a few tens of KB in L2). The matvec's CTAs then fetch the blob with one bulk
+// copy instead of each building the table (5120 columns: 20 KB of scattered byte stores per CTA, ~5 us on the critical
+// path of every launch).
+constexpr uint32_t MMA_PREP_ELEMS = 4096;   // a multiple of NCW*32*4 elements and of both group sizes
+template <int CODE>
+__global__ void __launch_bounds__(NCW * 32) mma_table_kernel(const float* x, uint32_t cols, uint8_t* blob, uint32_t tsum_blocks) {
+    __shared__ float red[NCW];
+    __shared__ __align__(16) uint8_t stage[2 * (MMA_PREP_ELEMS / mma_group_elems<CODE>()) * 256];
+    __shared__ float ts[MMA_PREP_ELEMS / 128];
+    pdl_launch_dependents();
+    pdl_wait();   // x comes from the previous kernel; the blob may still be read by the matvec before it
+    constexpr uint32_t GE = mma_group_elems<CODE>();
+    const uint32_t nvec = cols / 4, groups = (cols + GE - 1) / GE, half_bytes = groups * 256;
+    float to_fixed, kappa;
+    mma_fixed_scale(mma_vec_amax(red, x, nvec), to_fixed, kappa);
+    const uint32_t e_lo = blockIdx.x * MMA_PREP_ELEMS, e_hi = min(cols, e_lo + MMA_PREP_ELEMS);
+    const uint32_t G_lo = e_lo / GE, G_hi = (e_hi + GE - 1) / GE, ng = G_hi - G_lo;   // this CTA's groups
+    const uint32_t local_half = ng * 256;
+    uint8_t* local = stage - (size_t)G_lo * 256;          // record of group G lands at stage + (G - G_lo) * 256
+    float* local_ts = ts - e_lo / 128;
+    mma_build_digits<CODE>(x, e_lo / 4, e_hi / 4, local, local_half, local_ts, tsum_blocks, to_fixed);
+    if (e_hi == cols) mma_zero_tail<CODE>(cols, groups, local, local_half);
+    __syncthreads();
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t i = tid; i < ng * 16; i += NCW * 32) {   // 16-byte units of each half
+        reinterpret_cast<uint4*>(blob + (size_t)G_lo * 256)[i] = reinterpret_cast<const uint4*>(stage)[i];
+        reinterpret_cast<uint4*>(blob + half_bytes + (size_t)G_lo * 256)[i] = reinterpret_cast<const uint4*>(stage + local_half)[i];
+    }
+    float* tsum_g = reinterpret_cast<float*>(blob + mma_blob_tsum_off(groups));
+    for (uint32_t b = e_lo / 128 + tid; b < min(tsum_blocks, (e_hi + 127) / 128); b += NCW * 32) tsum_g[b] = ts[b - e_lo / 128];
+    if (blockIdx.x == 0 && tid < 4) reinterpret_cast<uint32_t*>(blob + 2 * (size_t)half_bytes)[tid] = 0u;   // the zero record
+    if (blockIdx.x == 0 && tid == 4) *reinterpret_cast<float*>(blob + mma_blob_kappa_off(groups)) = kappa;
 }
 
 // f32 value of the four digit accumulators a thread holds for one row: quad lane 0 has digits 0, 1
@@ -408,7 +474,18 @@ __device__ __forceinline__ bool stream_consume_mma(const StreamArgs& a, StreamCt
     tb.zero = tb.words + 2 * tb.half;
     tb.tsum = smem_u32(tsum);
     const uint32_t tsum_blocks = M::HAS_TSUM ? a.cols / 128 : 0u;
-    tb.kappa = mma_build_table<M::CODE>(sm, a.x, a.cols, table, tsum, tsum_blocks);
+    if (a.tab_global != nullptr) {
+        // prepared once by mma_table_kernel: one bulk copy per CTA, same layout as the table built in place
+        const uint32_t bar = smem_u32(&sm->act_bar), bytes = mma_blob_bytes(ngroups);
+        if (threadIdx.x == 0) {
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_g2s(tb.words, a.tab_global, bytes, bar);
+        }
+        if (!wait_or_abort(bar, 0, abort_flag, a.status, KERR_WAIT_FULL, cx.limit)) return false;
+        tb.kappa = *reinterpret_cast<const float*>(table + mma_blob_kappa_off(ngroups));
+    } else {
+        tb.kappa = mma_build_table<M::CODE>(sm, a.x, a.cols, table, tsum, tsum_blocks);
+    }
     // the warps of a row set split the groups in whole SPLIT_UNITs (a Q2_0 block is two groups)
     const uint32_t nunits = (ngroups + M::SPLIT_UNIT - 1) / M::SPLIT_UNIT;
     const uint32_t g_lo = nunits * part / P * M::SPLIT_UNIT, g_hi = min(ngroups, nunits * (part + 1) / P * M::SPLIT_UNIT);

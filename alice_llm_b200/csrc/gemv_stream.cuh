@@ -47,6 +47,7 @@ struct StreamArgs {
     uint32_t batch;      // input vectors sharing one pass over the weights (batch kernels), else 1
     uint32_t y_stride;   // floats between the outputs of consecutive input vectors
     uint32_t tab_off;    // shared-memory offset of the activation area (Q8_K blocks / f32 vector / bit-plane digit table)
+    const uint8_t* tab_global;  // bit-plane kernels: the digit table prepared in global memory (mma_table_kernel), or null
     // pro_mode != 0: x is the raw f32 vector and every CTA prepares its own copy in the activation area
     // (stream_prologue): rms_norm with the weights pro_norm_w into the f32 area at offset 0, then Q8_K blocks at
     // pro_q8_off (K-quant formats); f32-activation formats read the normalised vector (pro_roundtrip: rounded to the

@@ -36,6 +36,8 @@ struct alice_model {
     // vector: Q8_K blocks for K-quant consumers, f32 (normalised) for the others
     uint8_t *hid_q8 = nullptr, *attn_q8 = nullptr, *ffn_q8 = nullptr;
     float* hid_xn = nullptr;
+    uint8_t* prep = nullptr;            // scratch of the bit-plane kernels: the activation digit table of the current input
+    size_t prep_bytes = 0;
     unsigned int *tk_vec = nullptr, *tk_attn = nullptr, *attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
@@ -87,6 +89,7 @@ int upload_norm(alice_model* m, float** dst, const float* host, size_t n) {
 
 int gemv(alice_model* m, GemvOp& op, const char* what) {
     op.wait_limit = m->e->wait_limit;
+    op.prep = m->prep; op.prep_bytes = m->prep_bytes;
     const int rc = launch_stream_gemv_op(op, alice_cfg_of(m->e));
     if (rc == ALICE_OK) return rc;
     return alice_fail(rc, "alice_model: %s matvec failed (%d): %s", what, rc, cudaGetErrorString(cudaGetLastError()));
@@ -148,8 +151,9 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     int rc;
 
     // A whole-vector hand-over: what `consumers` need of vector `src` (length len), after rms_norm with norm_w (or none).
-    // Single GPU and peer mode: returned as the producing kernel's Publish. NCCL mode: the producing kernel publishes
-    // nothing; after the all-gather a one-CTA kernel prepares the vector.
+    // Peer mode: the producing kernel's own Publish (its last CTA gates on the peers' rows, then prepares the vector).
+    // Single GPU and NCCL mode: the producing kernel publishes nothing; a one-CTA kernel prepares the vector after it
+    // (after the all-gather).
     auto vector_pub = [&](Publish& p, const float* src, uint32_t len, const float* norm_w, const Need& nd, uint8_t* q8_base, float* xn,
                           uint32_t flag_idx) {
         p = Publish{};
@@ -163,6 +167,12 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     };
     // after the kernel: NCCL gather + stand-alone preparation
     auto gather_then_publish = [&](float* vec, uint32_t floats_per_rank, Publish& p) -> int {
+        if (n == 1) {
+            // single GPU: a one-CTA kernel between producer and consumer (the consumer is its programmatic dependent
+            // and streams weights meanwhile) instead of the last CTA of the producer doing the same as a serial tail
+            if (p.dst.qs || p.dst.xn) { p.mode = PUB_VECTOR; MCU(launch_publish_vector(p, m->e->status, st, pdl)); }
+            return ALICE_OK;
+        }
         if (!nccl) return ALICE_OK;
         int g = tp_all_gather(m->e, vec, (size_t)floats_per_rank * sizeof(float));
         if (g) return g;
@@ -274,7 +284,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
             Need nd; need_of(nd, L.gate, true);
             vector_pub(p, m->hidden, H, L.ffn_norm, nd, m->hid_q8, m->hid_xn, 4 * l + 1);
-            if (!nccl && (nd.xn || n > 1)) op.pub = &p;
+            if (peer) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -314,7 +324,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
                 norm_w = m->out_norm;
             }
             vector_pub(p, m->hidden, H, norm_w, nd, m->hid_q8, m->hid_xn, 4 * l + 3);
-            if (!nccl && (nd.xn || n > 1)) op.pub = &p;
+            if (peer) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "down_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -443,6 +453,10 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->attn_q8, Q8KLayout::make((q_dim + 255) / 256, B).total);
     if (!rc) rc = dev_alloc(m, &m->ffn_q8, Q8KLayout::make((c.intermediate_dim + 255) / 256, B).total);
     if (!rc) rc = dev_alloc(m, &m->hid_xn, (size_t)B * c.hidden_dim);
+    if (!rc) {
+        m->prep_bytes = mma_prep_bytes(std::max({c.hidden_dim, c.intermediate_dim, q_dim}));
+        rc = dev_alloc(m, &m->prep, m->prep_bytes);
+    }
     if (!rc) rc = dev_alloc(m, &m->d_pos, 1);
     if (!rc) rc = dev_alloc(m, &m->d_token, B);
     if (!rc) rc = dev_alloc(m, &m->d_trace, c.max_seq_len);
