@@ -350,7 +350,9 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
         }
     }
-    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, batch, m->epoch, st, pdl));
+    MCU(launch_finish_step(m->argmax_keys, m->tp_n, m->d_token, m->d_pos, m->d_trace, greedy_feed ? 1 : 0, batch,
+                           peer ? m->epoch : nullptr,   // the epoch counts steps whose rows were pushed (it is what the per-vector flags are compared with)
+                           st, pdl));
     return ALICE_OK;
 }
 

@@ -492,8 +492,14 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    t_start = time.time()
+
+    def log(msg):
+        print(f"[bench rank {rank} +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
 
     block = make_block(0)
     gate, up, down, x = block
@@ -594,21 +600,102 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed(step, args.steps)
+    # replicas on several GPUs queue their steps from the host (a capture beside a live process group is avoided)
+    ms = timed(step, args.steps, graph=world == 1)
     ms_e2e = timed(step_e2e, args.steps, graph=False)   # host buffers, a blocking read per step: not capturable
     # each half of the step alone (quantizer + matvec), over the weight copies
-    ms_sw = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps)
-    ms_down = timed(lambda i: eng.matvec_dev(copies[i % NCOPIES][2], hd, yd, 1), args.steps)
+    ms_sw = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps, graph=world == 1)
+    ms_down = timed(lambda i: eng.matvec_dev(copies[i % NCOPIES][2], hd, yd, 1), args.steps, graph=world == 1)
     clocks = sampler.stop() if rank == 0 else None
     eng.sync()
 
     peak, peak_src = measured_peak()
+    log("FFN block timed")
     formats, configs = {}, {}
     if rank == 0 and not args.no_extras:
         formats, configs = extras(eng, dev, stream, peak, args.steps, copies, xd4, hd4, yd4,
                                   set(args.formats.split(",")) if args.formats else None)
+        log("format and configuration tables done")
+
+    # ---- the line, complete except for the whole-model entries ------------------------------------------------------
+    line = None
+    if rank == 0:
+        value = STEP_BYTES * world * args.steps / (ms * 1e-3) / 1e9
+        e2e = STEP_BYTES * world * args.steps / (ms_e2e * 1e-3) / 1e9
+        sw_gbs = 2 * GU_BYTES / (ms_sw / args.steps * 1e-3) / 1e9
+        down_gbs = DOWN_BYTES / (ms_down / args.steps * 1e-3) / 1e9
+        traffic = {}
+        try:
+            with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as f:
+                traffic = json.load(f)
+        except Exception:
+            pass
+        kernels = {
+            "swiglu_q4k": {"kernel": "quantize_q8k_kernel + stream_gemv_kernel<FmtQ4K, fused SwiGLU>", "achieved": sw_gbs, "frac": sw_gbs / peak,
+                           "bytes_per_launch": 2 * GU_BYTES, "us_per_launch": ms_sw / args.steps * 1e3,
+                           "traffic": traffic.get("swiglu_q4k_bytes_per_launch")},
+            "down_q6k": {"kernel": "quantize_q8k_kernel + stream_gemv_kernel<FmtQ6K>", "achieved": down_gbs, "frac": down_gbs / peak,
+                         "bytes_per_launch": DOWN_BYTES, "us_per_launch": ms_down / args.steps * 1e3,
+                         "traffic": traffic.get("down_q6k_bytes_per_launch")},
+        }
+        slow = min(kernels.values(), key=lambda k: k["frac"])      # the roofline names the slower kernel of the step
+        line = {
+            "metric": "weight_stream_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+            "config": dict(CONFIG),
+            "l2": f"{NCOPIES} distinct weight copies cycled ({NCOPIES * STEP_BYTES >> 20} MiB > 126 MB L2)",
+            "parallelism": f"replicas x{world} (the FFN block does not shard; sharded work is under `decode`)" if world > 1 else "single",
+            "roofline": {"bound": "hbm", "kernel": slow["kernel"], "achieved": slow["achieved"], "peak": peak, "unit": "GB/s",
+                         "frac": slow["frac"], "peak_source": f"{peak_src} (of {peak_src})", "bytes_per_launch": slow["bytes_per_launch"],
+                         "us_per_launch": slow["us_per_launch"], "traffic": slow["traffic"],
+                         "frac_of_8000_nominal": slow["achieved"] / 8000.0, "whole_step_frac": value / world / peak,
+                         "kernels": kernels},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": KERNELS_PER_STEP * args.steps,
+            "launch": (f"steps queued as replays of a CUDA graph of {GRAPH_STEPS} steps" if world == 1 else "one API call sequence per step from the host")
+                      + "; e2e: one API call sequence per step from the host",
+            "clocks": clocks,
+            "parity": parity,
+            "formats": formats,
+            "configs": configs,
+            "decode": [],
+        }
+        if world == 1 and not args.no_cpu:
+            from oracle import oracle as orc
+            orc.build()
+            threads = orc.hw_threads()
+            v, n, dt = cpu_ffn_rate(block, threads, args.cpu_seconds, 2000)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"{n} {CPU_SAMPLE}; {dt:.1f} s"}
+            log("CPU baseline timed")
+
+    # ---- whole-model decode entries; a time limit guards the line: when it runs out, rank 0 prints what it has and
+    # every rank leaves (a rank stuck in a collective would otherwise keep the launcher waiting) ------------------------
     decode, n1, tp_par = [], {}, None
+    printed = threading.Lock()
+
+    def finish(note=None):
+        if not printed.acquire(blocking=False):
+            return
+        if rank == 0:
+            line["decode"] = decode + ([{"error": note}] if note else [])
+            if tp_par is not None:
+                line["tp_parity"] = tp_par
+            print(json.dumps(line), flush=True)
+
+    def out_of_time():
+        log(f"whole-model section exceeded {args.decode_seconds:.0f} s: leaving")
+        finish(f"time limit of {args.decode_seconds:.0f} s for the whole-model section reached")
+        os._exit(0)
+
     if args.decode != "none":
+        guard = threading.Timer(args.decode_seconds, out_of_time)
+        guard.daemon = True
+        guard.start()
+        import faulthandler
+        faulthandler.dump_traceback_later(max(1.0, args.decode_seconds - 3.0), file=sys.stderr)   # where it was stuck
         names = (["c3_8b_q4km", "c4_27b_q1_0", "c5_70b_ternary"] if world == 1 else ["c4_27b_q1_0", "c5_70b_ternary"]) \
             if args.decode == "auto" else args.decode.split(",")
         for t in keep:      # the FFN weight copies are no longer needed
@@ -626,81 +713,36 @@ def run_ours(args, rank, world, local_rank):
                         gm1.free()
                         del gm1
                         torch.cuda.empty_cache()
+                        log(f"{name} on one GPU: {ms1 / args.decode_tokens:.3f} ms per token")
                     except Exception as exc:
-                        n1[name] = None
+                        log(f"{name} on one GPU failed: {exc}")
+            log("waiting for the other ranks")
             dist.barrier()
             ids = [eng.tp_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             eng.tp_init(rank, world, ids[0])
+            log("tensor-parallel group formed")
             try:
                 tp_par = tp_parity(eng, world, rank, dist)
             except Exception as exc:
                 tp_par = {"error": f"{type(exc).__name__}: {exc}"[:300]}
-            n1 = {k: v for k, v in n1.items() if v}
+            log(f"tensor-parallel parity check done: {tp_par}")
         for name in names:
             try:
                 decode.append(run_decode(eng, name, args.decode_tokens, stream, world, dist, dev, peak, n1))
-            except Exception as exc:   # the headline line must still be printed; every wait in the library is bounded
+                log(f"{name}: {decode[-1].get('ms_per_token')} ms per token")
+            except Exception as exc:   # the line must still be printed; every wait in the library is bounded
                 decode.append({"config": name, "error": f"{type(exc).__name__}: {exc}"[:300]})
+                log(f"{name} failed: {exc}")
                 break
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    value = STEP_BYTES * world * args.steps / (ms * 1e-3) / 1e9
-    e2e = STEP_BYTES * world * args.steps / (ms_e2e * 1e-3) / 1e9
-    sw_gbs = 2 * GU_BYTES / (ms_sw / args.steps * 1e-3) / 1e9
-    down_gbs = DOWN_BYTES / (ms_down / args.steps * 1e-3) / 1e9
-    traffic = {}
-    try:
-        with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as f:
-            traffic = json.load(f)
-    except Exception:
-        pass
-    kernels = {
-        "swiglu_q4k": {"kernel": "quantize_q8k_kernel + stream_gemv_kernel<FmtQ4K, fused SwiGLU>", "achieved": sw_gbs, "frac": sw_gbs / peak,
-                       "bytes_per_launch": 2 * GU_BYTES, "us_per_launch": ms_sw / args.steps * 1e3,
-                       "traffic": traffic.get("swiglu_q4k_bytes_per_launch")},
-        "down_q6k": {"kernel": "quantize_q8k_kernel + stream_gemv_kernel<FmtQ6K>", "achieved": down_gbs, "frac": down_gbs / peak,
-                     "bytes_per_launch": DOWN_BYTES, "us_per_launch": ms_down / args.steps * 1e3,
-                     "traffic": traffic.get("down_q6k_bytes_per_launch")},
-    }
-    slow = min(kernels.values(), key=lambda k: k["frac"])      # the roofline names the slower kernel of the step
-    line = {
-        "metric": "weight_stream_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-        "config": dict(CONFIG),
-        "l2": f"{NCOPIES} distinct weight copies cycled ({NCOPIES * STEP_BYTES >> 20} MiB > 126 MB L2)",
-        "parallelism": f"replicas x{world} (the FFN block does not shard; sharded work is under `decode`)" if world > 1 else "single",
-        "roofline": {"bound": "hbm", "kernel": slow["kernel"], "achieved": slow["achieved"], "peak": peak, "unit": "GB/s",
-                     "frac": slow["frac"], "peak_source": f"{peak_src} (of {peak_src})", "bytes_per_launch": slow["bytes_per_launch"],
-                     "us_per_launch": slow["us_per_launch"], "traffic": slow["traffic"],
-                     "frac_of_8000_nominal": slow["achieved"] / 8000.0, "whole_step_frac": value / world / peak,
-                     "kernels": kernels},
-        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
-                "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": KERNELS_PER_STEP * args.steps,
-        "launch": f"steps queued as replays of a CUDA graph of {GRAPH_STEPS} steps; e2e: one API call sequence per step from the host",
-        "clocks": clocks,
-        "parity": parity,
-        "formats": formats,
-        "configs": configs,
-        "decode": decode,
-    }
-    if tp_par is not None:
-        line["tp_parity"] = tp_par
-    if world == 1 and not args.no_cpu:
-        from oracle import oracle as orc
-        orc.build()
-        threads = orc.hw_threads()
-        v, n, dt = cpu_ffn_rate(block, threads, args.cpu_seconds, 2000)
-        line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
-                                "sample": f"{n} {CPU_SAMPLE}; {dt:.1f} s"}
-    print(json.dumps(line), flush=True)
+        guard.cancel()
+        faulthandler.cancel_dump_traceback_later()
+    finish()
     if world > 1:
-        dist.destroy_process_group()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
 def main():
@@ -715,6 +757,7 @@ def main():
     ap.add_argument("--formats", default="", help="comma list restricting the per-format table (default: all eight)")
     ap.add_argument("--decode", default="auto", help="auto | none | comma list of c3_8b_q4km,c4_27b_q1_0,c5_70b_ternary")
     ap.add_argument("--decode-tokens", type=int, default=128)
+    ap.add_argument("--decode-seconds", type=float, default=300.0, help="time limit of the whole-model section")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -19,19 +19,20 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("mix", ["kquant", "q1_0", "ternary"])
 @pytest.mark.parametrize("world", [2])
-def test_tp_decode_matches_oracle(world):
+def test_tp_decode_matches_oracle(world, mix):
     import torch
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     port = _free_port()
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), str(port)],
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), str(world), str(port), mix],
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env) for r in range(world)]
     outs = []
     try:
         for p in procs:
-            outs.append(p.communicate(timeout=240))
+            outs.append(p.communicate(timeout=120))
     finally:
         for p in procs:
             if p.poll() is None:

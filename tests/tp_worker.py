@@ -3,7 +3,7 @@
 Every rank builds the same seeded synthetic model, uploads its row shards, joins the group and decodes
 greedily; rank 0 compares logits and token ids with the CPU oracle's forward of the whole model, and all
 ranks must agree on the tokens. The group id travels through a gloo process group (host side only).
-usage: tp_worker.py RANK WORLD PORT"""
+usage: tp_worker.py RANK WORLD PORT [MIX]   (MIX: kquant (default) | q1_0 | ternary - the weight formats of the model)"""
 import json
 import os
 import sys
@@ -17,6 +17,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def main():
     rank, world, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+    mix_name = sys.argv[4] if len(sys.argv) > 4 else "kquant"
     import torch.distributed as dist
     from alice_llm_b200 import synth
     from alice_llm_b200.gpu import GpuEngine, GpuModel
@@ -25,7 +26,15 @@ def main():
     cfg = dict(num_layers=2, hidden_dim=512, intermediate_dim=1024, num_heads=8, num_kv_heads=4, head_dim=128,
                vocab_size=1000, max_seq_len=96, rope_theta=500000.0, eps=1e-5)
     rng = np.random.default_rng(11)
-    model = synth.make_llama(rng, cfg)
+    roles = ("q", "k", "v", "o", "gate", "up", "down")
+    if mix_name == "q1_0":       # the binary-weight configuration: Q1_0 projections, Q8_0 head, 5 query heads per KV head
+        cfg.update(num_heads=10, num_kv_heads=2)
+        mix = {**{n: synth.Q1_0 for n in roles}, "output": synth.Q8_0}
+    elif mix_name == "ternary":  # every projection and the head as ternary bit planes
+        mix = {n: synth.TERNARY for n in roles + ("output",)}
+    else:
+        mix = None
+    model = synth.make_llama(rng, cfg, mix)
     # q / k / v scaled down so that the softmax spreads over the pre-filled rows (a dropped or misplaced part of
     # the sharded KV cache then shows up in the logits)
     from softmodel import scale_blocks
