@@ -56,6 +56,11 @@ class _Reader:
             return self.string()
         if vtype == 9:
             atype, n = self.take("<I"), self.take("<Q")
+            # every element takes at least one byte of the file: a count beyond what is left is a corrupt header
+            if n > len(self.buf) - self.pos:
+                raise GgufError(f"GGUF: array of {n} elements in a file with {len(self.buf) - self.pos} bytes left")
+            if atype == 9:
+                raise GgufError("GGUF: nested arrays are not supported")
             return [self.value(atype) for _ in range(n)]
         raise GgufError(f"GGUF: unknown metadata value type {vtype}")
 
@@ -98,6 +103,9 @@ class GgufFile:
         if version not in (2, 3):
             raise GgufError(f"GGUF: unsupported version {version}")
         n_tensors, n_meta = r.take("<Q"), r.take("<Q")
+        # a tensor info is at least 24 bytes, a metadata entry at least 12: counts the file cannot hold are rejected up front
+        if n_tensors * 24 > len(r.buf) or n_meta * 12 > len(r.buf):
+            raise GgufError(f"GGUF: header claims {n_tensors} tensors and {n_meta} metadata entries in a file of {len(r.buf)} bytes")
         metadata = {}
         for _ in range(n_meta):
             key = r.string()
@@ -105,10 +113,15 @@ class GgufFile:
         tensors = {}
         for _ in range(n_tensors):
             name = r.string()
-            dims = [r.take("<Q") for _ in range(r.take("<I"))]
+            n_dims = r.take("<I")
+            if n_dims > 8:
+                raise GgufError(f"GGUF: tensor {name} has {n_dims} dimensions")
+            dims = [r.take("<Q") for _ in range(n_dims)]
             qtype, offset = r.take("<I"), r.take("<Q")
             tensors[name] = TensorInfo(name, dims, qtype, offset)
-        align = int(metadata.get("general.alignment", DEFAULT_ALIGNMENT))
+        align = metadata.get("general.alignment", DEFAULT_ALIGNMENT)
+        if not isinstance(align, int) or isinstance(align, bool) or align < 1 or align & (align - 1) or align > (1 << 20):
+            raise GgufError(f"GGUF: general.alignment = {align!r} (a power of two of at least 1 is expected)")
         start = (r.pos + align - 1) // align * align
         return cls(r.buf, metadata, tensors, start, keep)
 
@@ -138,6 +151,12 @@ class GgufFile:
     def model_config(self, max_seq_len=None) -> dict:
         arch = self.metadata.get("general.architecture", "llama")
         m = self.metadata
+        # The decode graph built here is the Llama branch of the reference (interleaved RoPE pairs, no biases, RMSNorm,
+        # SwiGLU). The reference dispatches on ModelArch (src/llama3.rs:74-236: NeoX RoPE for qwen2 / gemma / ...,
+        # other defaults for mistral); until those branches exist a file of another architecture is refused rather
+        # than decoded with the wrong semantics.
+        if arch != "llama":
+            raise GgufError(f"GGUF: architecture {arch!r} is not supported (only 'llama')")
 
         def need(key):
             if f"{arch}.{key}" not in m:

@@ -244,7 +244,14 @@ int32_t alice_model_set_position(alice_model* m, uint32_t pos);
  * than Q1_0 / Q2_0 with ALICE_E_UNSUPPORTED. The call itself performs no cudaMalloc / cudaFree and
  * calls no allocating library routine. The first call on a device looks up the address of that
  * device's copy of the array (cudaGetSymbolAddress); make that first call before starting any stream
- * capture. All calls share the one array and it keeps the previous call's contents (each call
+ * capture. Warm-up: with CUDA's lazy module loading the FIRST call per device and weight shape still makes the
+ * driver take device memory - the array is materialised by that first address look-up, and each kernel instance's
+ * code is loaded at its first launch (so is the opt-in shared-memory attribute). A process that hands all HBM to
+ * its own pool must therefore make one call per shape it will use BEFORE the pool takes the memory (or run with
+ * CUDA_MODULE_LOADING=EAGER); calls after that warm-up leave the device's free memory unchanged, which the test
+ * suite checks with cudaMemGetInfo. It also uses the activation digit table scratch of an earlier alice_matvec /
+ * alice_matvec_preq call on the engine when one is there and large enough, and never creates it. All calls share
+ * the one array and it keeps the previous call's contents (each call
  * rewrites every element it reads, so nothing needs clearing); two calls whose GPU work overlaps -
  * different streams or engines on one device - race on it. Results equal alice_matvec_preq's. */
 #define ALICE_NOALLOC_MAX_FLOATS 65536

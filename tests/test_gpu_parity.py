@@ -285,3 +285,31 @@ def test_host_pointer_entry_points_match_oracle(oracle):
         # (dequantize_weight_row itself returns zeros for Q1_0 / Q2_0, src/gguf.rs:6168-6195; the library dequantizes them)
         assert np.array_equal(bits(out), bits(oracle.dequantize(qtype, data[:rb])))
     assert lib.alice_matvec_host(2, C.c_void_p(data.ctypes.data), data.size, rows, cols, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)) != 0
+
+
+def test_engines_on_two_devices_in_one_process(oracle):
+    """Per-device state (the opt-in shared-memory attribute of every kernel instance, the fixed no-allocation scratch) must
+    be set up on each device an engine is created on: the same matvecs on device 0, then device 1, then device 0 again."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from alice_llm_b200.gpu import GpuEngine
+    rng = np.random.default_rng(77)
+    cases = [(Q4_K, 70, 4096), (Q6_K, 40, 14336), (Q1_0, 70, 5120), (Q8_0, 50, 5120)]
+    data = {(qt, r, c): (synth.make_weights(qt, rng, r, c), synth.make_x(rng, c)) for qt, r, c in cases}
+    engines = [GpuEngine(0), GpuEngine(1)]
+    for eng in (engines[0], engines[1], engines[0]):
+        for (qt, r, c), (w, x) in data.items():
+            got = eng.matvec(eng.upload_weights_typed(w, r, c, quant(qt)), x)
+            assert_close(got, oracle.matvec(qt, x, w, r, c), f"device {eng.device} type {qt}")
+        # the no-allocation entry point keeps one fixed array per device
+        w, x = data[(Q1_0, 70, 5120)]
+        wd = eng.upload_weights_typed(w, 70, 5120, quant(Q1_0))
+        q = eng.alloc_q8k(5120, 1)
+        eng.quantize_q8k(eng.upload_f32(x), q)
+        y1, y2 = eng.alloc_f32(70), eng.alloc_f32(70)
+        eng.matvec_preq_dev(wd, q, y1)
+        eng.matvec_preq_noalloc_dev(wd, q, y2)
+        assert np.array_equal(eng.read_f32(y1).view(np.uint32), eng.read_f32(y2).view(np.uint32))
+    for eng in engines:
+        eng.close()
