@@ -47,6 +47,10 @@ SIGNATURES = {
     "alice_q8k_read": (C.c_int32, [_vp, _vp, _vp, _vp, _vp]),
     "alice_q8k_upload": (C.c_int32, [_vp, _vp, _vp, _vp, C.c_uint32, C.c_uint32, _pp]),
     "alice_q8k_free": (C.c_int32, [_vp]),
+    "alice_debug_expire_wait": (C.c_int32, [_vp]),
+    "alice_ternarize": (C.c_int32, [_vp, _vp, C.c_uint32, C.c_uint32, C.c_float, _pp]),
+    "alice_sparsify": (C.c_int32, [_vp, _vp, _vp, C.c_uint32, _pp]),
+    "alice_weights_download": (C.c_int32, [_vp, _vp, _vp, C.c_size_t, _vp]),
     "alice_matvec": (C.c_int32, [_vp, _vp, _vp, _vp, C.c_uint32]),
     "alice_matvec_preq": (C.c_int32, [_vp, _vp, _vp, _vp]),
     "alice_swiglu": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, C.c_uint32]),

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libalice_cuda.so")
-SOURCES = ["abi.cu", "gemv_launch.cu", "q8k.cu", "dequant.cu", "glue.cu", "model.cu", "tp.cu"]
+SOURCES = ["abi.cu", "gemv_launch.cu", "q8k.cu", "dequant.cu", "ternarize.cu", "glue.cu", "model.cu", "tp.cu"]
 # never --use_fast_math: dequantization and the Q8_K quantizer must round like the reference
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-strict-aliasing"]

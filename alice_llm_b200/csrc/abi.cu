@@ -216,6 +216,26 @@ int32_t alice_sync(alice_engine* e) {
     return ALICE_OK;
 }
 
+int32_t alice_debug_expire_wait(alice_engine* e) {
+    if (!e) return fail(ALICE_E_INVALID, "alice_debug_expire_wait: null engine");
+    CU(cudaSetDevice(e->device));
+    // scratch: [256 floats source][epoch u32][own flag u32][peer flag u32], all zero: the gate expects
+    // (epoch + 1) * 1 = 1 at the own flag, which nothing raises
+    int rc = ensure_scratch(e, 4096);
+    if (rc) return rc;
+    CU(cudaMemsetAsync(e->scratch, 0, 4096, e->stream));
+    auto* base = static_cast<uint8_t*>(e->scratch);
+    Publish p{};
+    p.mode = PUB_VECTOR; p.n = 256; p.batch = 1; p.src = reinterpret_cast<const float*>(base);
+    p.npeers = 1;
+    p.epoch = reinterpret_cast<const unsigned int*>(base + 1024);
+    p.wait_flag = reinterpret_cast<const unsigned int*>(base + 1028);
+    p.peer_flag[0] = reinterpret_cast<unsigned int*>(base + 1032);
+    p.wait_limit = e->wait_limit;
+    CU(launch_publish_vector(p, e->status, e->stream, e->pdl));
+    return ALICE_OK;
+}
+
 // ---- weights -------------------------------------------------------------------------------
 
 static int make_ggml_desc(const char* who, size_t nbytes, uint32_t type, uint32_t rows, uint32_t cols, WeightDesc& d) {

@@ -143,6 +143,10 @@ class GpuEngine:
         """Cycle budget of every bounded wait inside the kernels (0 = about one second)."""
         check(self._lib.alice_engine_set_wait_limit(self._h, sm_cycles))
 
+    def debug_expire_wait(self):
+        """Queues a hand-over whose flag nobody raises: its bounded wait runs out (self-test of that path)."""
+        check(self._lib.alice_debug_expire_wait(self._h))
+
     # -- tensor parallel: one engine (one process) per GPU, rows of every projection sharded over the group --
     TP_ID_BYTES = 128
 
@@ -217,6 +221,31 @@ class GpuEngine:
         h = C.c_void_p()
         check(self._lib.alice_upload_sparse_ternary(self._h, _ptr(p), _ptr(s), rows, cols, C.byref(h)))
         return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.SparseTernary)
+
+    def ternarize(self, w: GpuBuffer, rows: int, cols: int, threshold_ratio: float) -> GpuWeightBuffer:
+        """TernaryRow::from_f32 of every row of the f32 matrix ``w`` (src/gguf.rs:5207-5245), on the device."""
+        h = C.c_void_p()
+        check(self._lib.alice_ternarize(self._h, w._h, rows, cols, threshold_ratio, C.byref(h)))
+        return GpuWeightBuffer(self, h, rows, cols, GpuQuantType.Ternary)
+
+    def sparsify(self, ternary: GpuWeightBuffer, w: GpuBuffer, n_keep: int) -> GpuWeightBuffer:
+        """SparseTernaryRow::from_ternary_row of every row (src/gguf.rs:5451-5507), on the device."""
+        h = C.c_void_p()
+        check(self._lib.alice_sparsify(self._h, ternary._h, w._h, n_keep, C.byref(h)))
+        return GpuWeightBuffer(self, h, ternary.rows, ternary.cols, GpuQuantType.SparseTernary)
+
+    def download_weights(self, w: GpuWeightBuffer):
+        """(device rows as uint8 [rows][row bytes], per-row scales or None) of a ternary / sparse-ternary matrix."""
+        if w.quant is GpuQuantType.Ternary:
+            rb = (w.cols + 31) // 32 * 8
+        elif w.quant is GpuQuantType.SparseTernary:
+            rb = (w.cols + 15) // 16 * 4
+        else:
+            raise AliceError(_lib.E_UNSUPPORTED, "download_weights: ternary forms only")
+        rows = np.empty((w.rows, rb), np.uint8)
+        scales = np.empty(w.rows, np.float32)
+        check(self._lib.alice_weights_download(self._h, w._h, _ptr(rows), rows.size, _ptr(scales)))
+        return rows, scales
 
     # -- f32 buffers (src/gpu.rs:667-695, 801-824) --
     def alloc_f32(self, length: int) -> GpuBuffer:
@@ -308,6 +337,29 @@ class GpuEngine:
         self.sync()
         return out
 
+    # -- pre-bound matvec helpers of the reference's benchmarks (src/gpu.rs:311-318, 848-964) --
+    def create_matvec_context(self, weights: GpuWeightBuffer) -> "MatvecContext":
+        """GpuEngine::create_matvec_context: input and output buffers bound to one weight matrix, made once."""
+        return MatvecContext(self, weights, self.alloc_f32(weights.cols), self.alloc_f32(weights.rows))
+
+    def matvec_fast(self, ctx: "MatvecContext", input_) -> np.ndarray:
+        """GpuEngine::matvec_fast: write the input, one dispatch, read the result back."""
+        self.dispatch_matvec_only(ctx, input_)
+        return self.read_f32(ctx.output)
+
+    def dispatch_matvec_only(self, ctx: "MatvecContext", input_):
+        """GpuEngine::dispatch_matvec_only: write the input and queue one dispatch; no read-back, no wait."""
+        self.write_f32(ctx.input, input_)
+        self.matvec_dev(ctx.weights, ctx.input, ctx.output, 1)
+
+    def bench_dispatch_batch(self, ctx: "MatvecContext", input_, n: int):
+        """GpuEngine::bench_dispatch_batch: the input once, then n dispatches queued back to back (the reference encodes
+        them into one command buffer and polls once); returns after the last has completed."""
+        self.write_f32(ctx.input, input_)
+        for _ in range(n):
+            self.matvec_dev(ctx.weights, ctx.input, ctx.output, 1)
+        self.sync()
+
     def dequantize(self, weights: GpuWeightBuffer) -> np.ndarray:
         out = self.alloc_f32(weights.rows * weights.cols)
         self.dequantize_dev(weights, out)
@@ -320,6 +372,13 @@ class GpuEngine:
 
     def sync(self):
         check(self._lib.alice_sync(self._h))
+
+
+class MatvecContext:
+    """MatvecContext (src/gpu.rs:311): one weight matrix with its input and output buffers."""
+
+    def __init__(self, engine: "GpuEngine", weights: GpuWeightBuffer, input_: GpuBuffer, output: GpuBuffer):
+        self.engine, self.weights, self.input, self.output, self.rows = engine, weights, input_, output, weights.rows
 
 
 class GpuPass:
@@ -432,6 +491,15 @@ class GpuModel:
                 keep.append(entry)
                 return entry
             t, data = entry
+            if GpuQuantType(t) is GpuQuantType.SparseTernary:   # (packed 2-bit codes, per-row scales), SparseTernaryMatrix
+                packed, sc = data
+                packed = _np(packed, np.uint8).reshape(rows, -1)
+                if shard and world > 1:
+                    (packed, n), (sc, _) = shard_rows(packed, rows, rank, world), shard_rows(sc, rows, rank, world)
+                    rows = n
+                w = engine.upload_sparse_ternary(packed, sc, rows, cols)
+                keep.append(w)
+                return w
             if GpuQuantType(t) is GpuQuantType.Ternary:   # (pos planes, neg planes, per-row scales)
                 pos, neg, sc = data
                 if shard and world > 1:
@@ -462,6 +530,13 @@ class GpuModel:
         check(engine._lib.alice_model_create(engine._h, C.byref(c), C.byref(layers), emb._h, _ptr(onorm), out._h,
                                              C.byref(h)))
         return cls(engine, h, cfg, keep)
+
+    @classmethod
+    def load_shared(cls, engine: GpuEngine, model: dict, config: GpuModelConfig | None = None) -> "GpuModel":
+        """GpuModel::load_shared (src/gpu.rs:2837): a model on an engine other models already use (draft and target of
+        speculative decoding share device, stream and scratch). Engines here are shared by reference, so this is
+        ``load``; the models' steps run in the order they are queued on the engine's stream."""
+        return cls.load(engine, model, config)
 
     @classmethod
     def load_gguf(cls, engine: GpuEngine, path, max_seq_len=None) -> "GpuModel":

@@ -17,6 +17,7 @@ QK_K = 256
 # GGML type ids (src/gguf.rs:101-122)
 Q8_0, Q4_K, Q5_K, Q6_K, Q1_0, Q2_0 = 8, 12, 13, 14, 41, 42
 TERNARY = 1000   # in-memory ternary bit planes (TernaryMatrix, src/gguf.rs:5198); not a GGML id
+SPARSE_TERNARY = 1001   # SparseTernaryMatrix's packed 2-bit codes + per-row scales (src/gguf.rs:5432); not a GGML id
 BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q1_0: 18, Q2_0: 34}
 BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, Q1_0: 128, Q2_0: 128}
 TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", Q1_0: "Q1_0", Q2_0: "Q2_0"}
@@ -134,6 +135,38 @@ def ternary_to_sparse(pos: np.ndarray, neg: np.ndarray, cols: int):
 
 
 _F16_FIELDS = {Q4_K: (0, 2), Q5_K: (0, 2), Q6_K: (208,), Q8_0: (0,), Q1_0: (0,), Q2_0: (0,)}
+
+
+def pack_2bit(pos: np.ndarray, neg: np.ndarray, cols: int) -> np.ndarray:
+    """SparseTernaryMatrix.packed_2bit of bit planes (src/gguf.rs:5432-5450): per weight two bits, 00 = 0, 01 = +1,
+    11 = -1, four weights per byte (lowest bits first), rows padded to whole blocks of 16 weights (4 bytes).
+    Returns uint8 [rows][ceil(cols / 16) * 4]."""
+    rows = pos.shape[0]
+    bpr = (cols + 15) // 16
+    bits_p = np.unpackbits(pos, axis=1, bitorder="little")[:, :cols]
+    bits_n = np.unpackbits(neg, axis=1, bitorder="little")[:, :cols]
+    codes = np.zeros((rows, bpr * 16), dtype=np.uint8)
+    codes[:, :cols] = bits_p | bits_n | (bits_n << 1)          # +1 -> 01, -1 -> 11
+    c = codes.reshape(rows, bpr * 4, 4)
+    return (c[..., 0] | (c[..., 1] << 2) | (c[..., 2] << 4) | (c[..., 3] << 6)).astype(np.uint8)
+
+
+def to_sparse_ternary(model: dict) -> dict:
+    """A make_llama model whose TERNARY tensors become SPARSE_TERNARY ones holding the same weights (nothing dropped):
+    the form Llama3Model::forward_sparse_ternary runs on (src/llama3.rs:17216-17330)."""
+    def conv(entry, cols):
+        t, data = entry
+        if t != TERNARY:
+            return entry
+        pos, neg, sc = data
+        return SPARSE_TERNARY, (pack_2bit(pos, neg, cols), sc)
+    cfg = model["config"]
+    H, F, q_dim = cfg["hidden_dim"], cfg["intermediate_dim"], cfg["num_heads"] * cfg["head_dim"]
+    cols = {"q": H, "k": H, "v": H, "o": q_dim, "gate": H, "up": H, "down": F}
+    out = dict(model)
+    out["layers"] = [{**L, **{n: conv(L[n], c) for n, c in cols.items()}} for L in model["layers"]]
+    out["output"] = conv(model["output"], H)
+    return out
 
 
 def scale_blocks(entry, factor):

@@ -74,6 +74,11 @@ int32_t alice_engine_set_tuning(alice_engine* e, int32_t rows_per_set, int32_t s
  * about one second. A wait that runs out records its code in the engine's status word and the kernel returns;
  * alice_sync then reports ALICE_E_KERNEL and clears the word (the engine stays usable). No reference counterpart. */
 int32_t alice_engine_set_wait_limit(alice_engine* e, uint64_t sm_cycles);
+/* Self-test of that path, nothing else: queues the tensor-parallel hand-over of a 256-element vector with one "peer"
+ * whose flag nobody ever raises (both flags live in scratch memory of this GPU), so the bounded wait runs out after
+ * the engine's cycle budget and the kernel returns with status 6 recorded. The next alice_sync reports ALICE_E_KERNEL;
+ * work queued afterwards runs normally. Set a short budget first (a few million cycles). No reference counterpart. */
+int32_t alice_debug_expire_wait(alice_engine* e);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 /* GpuEngine::upload_weights / _q5k / _q6k / _q8_0 / _q1_0 (src/gpu.rs:698-798): raw GGUF blocks,
@@ -120,6 +125,21 @@ int32_t alice_q8k_read(alice_engine* e, const alice_q8k* q, float* d, int8_t* qs
 int32_t alice_q8k_upload(alice_engine* e, const float* d, const int8_t* qs, const int16_t* bsums,
                          uint32_t cols, uint32_t batch, alice_q8k** out);
 int32_t alice_q8k_free(alice_q8k* q);
+
+/* TernaryRow::from_f32 for every row of an f32 matrix on the device (src/gguf.rs:5207-5245; w[r * cols + c]):
+ * threshold = threshold_ratio * mean |w| of the row, masks of the weights above it, scale = their mean magnitude. The
+ * masks and scales equal the reference's bit for bit (sums run in its order). *out is a ternary matrix like
+ * alice_upload_ternary's. */
+int32_t alice_ternarize(alice_engine* e, const alice_buf* w, uint32_t rows, uint32_t cols, float threshold_ratio,
+                        alice_weights** out);
+/* SparseTernaryRow::from_ternary_row for every row (src/gguf.rs:5451-5507): of the non-zero weights of each block of 16
+ * the n_keep largest |w| stay (ties: the earlier one); packed as SparseTernaryMatrix.packed_2bit, scale = mean kept
+ * magnitude (the dense scale for a row that keeps nothing). `w` is the f32 matrix `ternary` was made from. */
+int32_t alice_sparsify(alice_engine* e, const alice_weights* ternary, const alice_buf* w, uint32_t n_keep, alice_weights** out);
+/* The device rows of a weight matrix back on the host (rows * row bytes, the layout the library keeps: raw GGUF blocks;
+ * [pos plane | neg plane] per row with planes of ceil(cols / 32) * 4 bytes; packed 2-bit rows of ceil(cols / 16) * 4
+ * bytes) and, for the ternary forms, the per-row scales (scales_out may be null). No reference counterpart. */
+int32_t alice_weights_download(alice_engine* e, const alice_weights* w, uint8_t* rows_out, size_t rows_bytes, float* scales_out);
 
 /* ---- the hot path ------------------------------------------------------------------------ */
 /* quantized_matvec / q4k_matvec / q5k_matvec / q6k_matvec / q8_0_matvec / ternary_matvec /

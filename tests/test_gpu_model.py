@@ -157,3 +157,62 @@ def test_forward_batch_matches_token_by_token_oracle(eng, oracle, mix, heads, nb
     errs, l2s = [r[0] for r in res], [r[1] for r in res]
     assert (max(errs) <= 1e-3 and max(l2s) <= 1e-3) if smooth else steps_pass(errs, l2s), ("after rollback", errs, l2s)
     gm.free()
+
+
+def test_forward_sparse_ternary_matches_oracle(eng, oracle):
+    """Every projection and the head as SparseTernaryMatrix (packed 2-bit codes) through GpuModel.load: the weights are
+    those of the ternary bit-plane model, so the oracle's forward of that model is the reference
+    (Llama3Model::forward_sparse_ternary, src/llama3.rs:17216-17330, sums the same +x / -x terms)."""
+    from alice_llm_b200.gpu import GpuModel
+    cfg = dict(CFG, num_heads=8, num_kv_heads=2)
+    rng = np.random.default_rng(15)
+    tern = synth.make_llama(rng, cfg, {n: synth.TERNARY for n in ("q", "k", "v", "o", "gate", "up", "down", "output")})
+    model = synth.to_sparse_ternary(tern)
+    # the packing agrees with the oracle's restatement of the reference packer
+    pos, neg, _ = tern["layers"][0]["down"][1]
+    active, sign = synth.ternary_to_sparse(pos, neg, cfg["intermediate_dim"])
+    want = oracle.sparse_pack_2bit(active, sign, cfg["hidden_dim"], cfg["intermediate_dim"])
+    assert np.array_equal(model["layers"][0]["down"][1][0].reshape(-1), want)
+    gm = GpuModel.load(eng, model)
+    orc = oracle.LlamaOracle(tern)
+    prefill(rng, cfg, gm, orc, 29)
+    for step, tok in enumerate([2, 640, 77]):
+        e, l2 = close(gm.forward_and_read(tok), orc.forward(tok))
+        assert e <= 1e-3 and l2 <= 1e-3, (step, e, l2)
+    got = gm.decode_greedy(9, 6)
+    ref, tok = [], 9
+    for _ in range(6):
+        tok = int(np.argmax(orc.forward(tok)))
+        ref.append(tok)
+    assert [int(t) for t in got] == ref
+    gm.free()
+
+
+def test_two_models_share_one_engine(eng, oracle):
+    """GpuModel::load_shared: a draft and a target model on one engine, steps interleaved (the speculative-decoding loop
+    of examples/speculative_dual_gpu.rs: the draft proposes, the target verifies a batch, both roll back on a mismatch);
+    each must decode exactly as it does alone."""
+    from alice_llm_b200.gpu import GpuModel
+    rng = np.random.default_rng(31)
+    big_cfg = dict(CFG, num_heads=8, num_kv_heads=2)
+    small_cfg = dict(CFG, num_layers=1, intermediate_dim=512)
+    target, draft = synth.make_llama(rng, big_cfg), synth.make_llama(rng, small_cfg)
+    gt, gd = GpuModel.load_shared(eng, target), GpuModel.load_shared(eng, draft)
+    alone_t, alone_d = oracle.LlamaOracle(target), oracle.LlamaOracle(draft)
+    tok_t, tok_d = 7, 7
+    for step in range(4):
+        lt, ld = gt.forward_and_read(tok_t), gd.forward_and_read(tok_d)     # interleaved on the shared stream
+        rt, rd = alone_t.forward(tok_t), alone_d.forward(tok_d)
+        for got, ref in ((lt, rt), (ld, rd)):
+            e, l2 = close(got, ref)
+            assert e <= 1e-3 and l2 <= 1e-3, (step, e, l2)
+        tok_t, tok_d = int(np.argmax(rt)), int(np.argmax(rd))
+    # the draft runs ahead, the target verifies the proposals as one batch, then both return to the accepted prefix
+    proposals = [int(t) for t in gd.decode_greedy(tok_d, 3)]
+    pos = gt.position()
+    logits = gt.forward_batch_and_read([tok_t] + proposals[:2])
+    assert logits.shape == (3, big_cfg["vocab_size"]) and gt.position() == pos + 3
+    gt.rollback_to(pos + 1)
+    gd.rollback_to(pos + 1)
+    assert gt.position() == pos + 1 and gd.position() == pos + 1
+    gt.free(); gd.free()

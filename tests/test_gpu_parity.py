@@ -313,3 +313,66 @@ def test_engines_on_two_devices_in_one_process(oracle):
         assert np.array_equal(eng.read_f32(y1).view(np.uint32), eng.read_f32(y2).view(np.uint32))
     for eng in engines:
         eng.close()
+
+
+@pytest.mark.parametrize("rows,cols", [(70, 200), (33, 8192), (5, 16), (130, 1000)])
+def test_device_ternarizers_bit_exact(eng, oracle, rows, cols):
+    """alice_ternarize / alice_sparsify against the oracle's TernaryRow::from_f32 and SparseTernaryRow::from_ternary_row:
+    masks, packed codes and scales equal bit for bit (weights rounded to a coarse grid, so magnitudes tie often and the
+    stable-sort rule decides which weights of a block stay)."""
+    rng = np.random.default_rng(rows * 7 + cols)
+    w = np.round(rng.standard_normal((rows, cols)).astype(np.float32) * 4) / 4
+    w[0] = 0.0                                       # a row that keeps nothing
+    wd = eng.upload_f32(w)
+    src_pb, pb = (cols + 7) // 8, (cols + 31) // 32 * 4
+    for ratio in (0.7, 0.0):
+        t = eng.ternarize(wd, rows, cols, ratio)
+        got_rows, got_scales = eng.download_weights(t)
+        want = [oracle.ternarize_row(w[r], ratio) for r in range(rows)]
+        for r, (pos, neg, scale) in enumerate(want):
+            assert np.array_equal(got_rows[r, :src_pb], pos) and np.array_equal(got_rows[r, pb:pb + src_pb], neg), (ratio, r)
+            assert not got_rows[r, src_pb:pb].any() and not got_rows[r, pb + src_pb:].any()
+            assert bits(got_scales[r]) == bits(scale), (ratio, r, got_scales[r], scale)
+        # the device matrix is usable as it is
+        x = synth.make_x(rng, cols)
+        pos = np.stack([p for p, _, _ in want]); neg = np.stack([n for _, n, _ in want])
+        sc = np.array([s for _, _, s in want], np.float32)
+        y = eng.alloc_f32(rows)
+        eng.matvec_dev(t, eng.upload_f32(x), y, 1)
+        assert_close(eng.read_f32(y), oracle.ternary_matvec(pos, neg, sc, rows, cols, x), "matvec over the device-made planes")
+        for n_keep in (3, 16):
+            s = eng.sparsify(t, wd, n_keep)
+            got_packed, got_sscales = eng.download_weights(s)
+            for r, (p, n, scale) in enumerate(want):
+                active, sign, sscale = oracle.sparsify_row(p, n, scale, w[r], n_keep)
+                packed = oracle.sparse_pack_2bit(active, sign, 1, cols)
+                assert np.array_equal(got_packed[r], packed), (ratio, n_keep, r)
+                assert bits(got_sscales[r]) == bits(sscale), (ratio, n_keep, r)
+            s.free()
+        t.free()
+
+
+def test_bounded_wait_runs_out_and_engine_stays_usable(oracle):
+    """A wait inside a kernel that nothing will ever satisfy (a hand-over flag nobody raises) returns after the engine's
+    cycle budget with a status the host reads: ALICE_E_KERNEL from alice_sync, naming the wait, and work queued after it
+    is correct. Nothing here faults or hangs the GPU: the kernel gives up by itself after a few milliseconds."""
+    import time
+    from alice_llm_b200 import _lib
+    from alice_llm_b200.gpu import AliceError, GpuEngine
+    eng = GpuEngine(0)
+    rng = np.random.default_rng(5)
+    data, x = synth.make_q4k(rng, 70, 4096), synth.make_x(rng, 4096)
+    w = eng.upload_weights(data, 70, 4096)
+    ref = oracle.matvec(Q4_K, x, data, 70, 4096)
+    assert_close(eng.matvec(w, x), ref, "before")
+    eng.set_wait_limit(4_000_000)            # about 2 ms of SM cycles
+    t0 = time.perf_counter()
+    eng.debug_expire_wait()
+    with pytest.raises(AliceError) as ei:
+        eng.sync()
+    assert time.perf_counter() - t0 < 1.0
+    assert ei.value.code == _lib.E_KERNEL and "status 6" in str(ei.value) and "peer" in str(ei.value)
+    eng.sync()                               # the status word was cleared by the report
+    eng.set_wait_limit(0)
+    assert_close(eng.matvec(w, x), ref, "after")
+    eng.close()
