@@ -380,7 +380,7 @@ def tp_parity(eng, world, rank, dist):
     return out
 
 
-def extras(eng, dev, stream, peak, steps, block_handles, xd4, hd4, yd4, only):
+def extras(eng, dev, stream, peak, steps, block_handles, xd4, hd4, yd4, only, use_graph=True):
     """formats / configs keys (single GPU, rank 0): CUDA events around `n` launches that cycle distinct weight copies."""
     import torch
     from alice_llm_b200 import synth
@@ -394,6 +394,14 @@ def extras(eng, dev, stream, peak, steps, block_handles, xd4, hd4, yd4, only):
         for i in range(5):
             fn(i)
         torch.cuda.synchronize()
+        if not use_graph:        # plain launches (for a profiler): the figure then includes the host's launch overhead
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(n):
+                fn(i)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n * 1e3
         chunk = 48
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
@@ -601,11 +609,12 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         sampler.start()
     # replicas on several GPUs queue their steps from the host (a capture beside a live process group is avoided)
-    ms = timed(step, args.steps, graph=world == 1)
+    use_graph = world == 1 and not args.no_graph
+    ms = timed(step, args.steps, graph=use_graph)
     ms_e2e = timed(step_e2e, args.steps, graph=False)   # host buffers, a blocking read per step: not capturable
     # each half of the step alone (quantizer + matvec), over the weight copies
-    ms_sw = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps, graph=world == 1)
-    ms_down = timed(lambda i: eng.matvec_dev(copies[i % NCOPIES][2], hd, yd, 1), args.steps, graph=world == 1)
+    ms_sw = timed(lambda i: eng.swiglu_dev(copies[i % NCOPIES][0], copies[i % NCOPIES][1], xd, hd, 1), args.steps, graph=use_graph)
+    ms_down = timed(lambda i: eng.matvec_dev(copies[i % NCOPIES][2], hd, yd, 1), args.steps, graph=use_graph)
     clocks = sampler.stop() if rank == 0 else None
     eng.sync()
 
@@ -614,7 +623,7 @@ def run_ours(args, rank, world, local_rank):
     formats, configs = {}, {}
     if rank == 0 and not args.no_extras:
         formats, configs = extras(eng, dev, stream, peak, args.steps, copies, xd4, hd4, yd4,
-                                  set(args.formats.split(",")) if args.formats else None)
+                                  set(args.formats.split(",")) if args.formats else None, use_graph=not args.no_graph)
         log("format and configuration tables done")
 
     # ---- the line, complete except for the whole-model entries ------------------------------------------------------
@@ -654,7 +663,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": KERNELS_PER_STEP * args.steps,
-            "launch": (f"steps queued as replays of a CUDA graph of {GRAPH_STEPS} steps" if world == 1 else "one API call sequence per step from the host")
+            "launch": (f"steps queued as replays of a CUDA graph of {GRAPH_STEPS} steps" if use_graph else "one API call sequence per step from the host")
                       + "; e2e: one API call sequence per step from the host",
             "clocks": clocks,
             "parity": parity,
@@ -754,6 +763,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-format and per-configuration tables")
+    ap.add_argument("--no-graph", action="store_true", help="queue every step from the host instead of replaying CUDA graphs (for profilers)")
     ap.add_argument("--formats", default="", help="comma list restricting the per-format table (default: all eight)")
     ap.add_argument("--decode", default="auto", help="auto | none | comma list of c3_8b_q4km,c4_27b_q1_0,c5_70b_ternary")
     ap.add_argument("--decode-tokens", type=int, default=128)
