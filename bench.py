@@ -404,7 +404,7 @@ def extras(eng, dev, stream, peak, steps, block_handles, xd4, hd4, yd4, only, us
             return e0.elapsed_time(e1) / n * 1e3
         chunk = 48
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
             for i in range(chunk):
                 fn(i)
         g.replay()
@@ -501,6 +501,11 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     t_start = time.time()
+    # stdout carries the one JSON line and nothing else: libraries that print there (NCCL's version banner) are sent to
+    # stderr for the duration of the run
+    sys.stdout.flush()
+    line_fd = os.dup(1)
+    os.dup2(2, 1)
 
     def log(msg):
         print(f"[bench rank {rank} +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
@@ -576,11 +581,17 @@ def run_ours(args, rank, world, local_rank):
         step from Python would otherwise bound the loop by the host, not the device."""
         g = None
         if graph and n >= GRAPH_STEPS:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                for i in range(GRAPH_STEPS):
-                    fn(i)
-            g.replay()
+            try:
+                g = torch.cuda.CUDAGraph()
+                # thread-local capture: the process group's watchdog thread may query events meanwhile
+                with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                    for i in range(GRAPH_STEPS):
+                        fn(i)
+                g.replay()
+            except Exception as exc:       # fall back to queueing every step from the host
+                log(f"graph capture failed ({exc}); steps are queued one by one")
+                g = None
+                torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(stream)
@@ -608,8 +619,7 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # replicas on several GPUs queue their steps from the host (a capture beside a live process group is avoided)
-    use_graph = world == 1 and not args.no_graph
+    use_graph = not args.no_graph
     ms = timed(step, args.steps, graph=use_graph)
     ms_e2e = timed(step_e2e, args.steps, graph=False)   # host buffers, a blocking read per step: not capturable
     # each half of the step alone (quantizer + matvec), over the weight copies
@@ -692,7 +702,7 @@ def run_ours(args, rank, world, local_rank):
             line["decode"] = decode + ([{"error": note}] if note else [])
             if tp_par is not None:
                 line["tp_parity"] = tp_par
-            print(json.dumps(line), flush=True)
+            os.write(line_fd, (json.dumps(line) + "\n").encode())
 
     def out_of_time():
         log(f"whole-model section exceeded {args.decode_seconds:.0f} s: leaving")
