@@ -135,7 +135,7 @@ void fill_dst(PublishDst& d, const Need& nd, uint8_t* q8_base, float* xn, uint32
 // Queues one decode step for `batch` consecutive tokens (read from d_token[0 .. batch)) on the engine's stream.
 // With a tensor-parallel group every matvec computes this rank's rows into its slice of the full vector; the slices
 // reach the other ranks either by an NCCL all-gather after the kernel, or (peer mode) by the kernel itself storing its
-// rows into every peer's copy, with one flag per vector that the kernel's last CTA raises on the peers and waits for
+// rows into every peer's copy, with one flag per vector that a one-CTA kernel behind it raises on the peers and waits for
 // here before it prepares the vector for the next op. Attention runs on the rank's own KV heads (its q, k, v rows), so
 // only its output needs exchanging (it is the input of the output projection).
 int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
@@ -173,7 +173,15 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             if (p.dst.qs || p.dst.xn) { p.mode = PUB_VECTOR; MCU(launch_publish_vector(p, m->e->status, st, pdl)); }
             return ALICE_OK;
         }
-        if (!nccl) return ALICE_OK;
+        if (peer) {
+            // pushed rows: the producing kernel has stored its rows into every peer's copy; a one-CTA kernel behind it
+            // (which starts once that kernel and its stores are complete) raises this vector's counter on the peers,
+            // waits (bounded) for theirs, and then prepares the now complete vector if the consumer wants it prepared.
+            // (The same hand-over run by the producing kernel's last CTA was a serial tail of ~10 us per vector.)
+            p.mode = PUB_VECTOR;
+            MCU(launch_publish_vector(p, m->e->status, st, pdl));
+            return ALICE_OK;
+        }
         int g = tp_all_gather(m->e, vec, (size_t)floats_per_rank * sizeof(float));
         if (g) return g;
         if (p.dst.qs || p.dst.xn) { p.mode = PUB_VECTOR; MCU(launch_publish_vector(p, m->e->status, st, pdl)); }
@@ -268,7 +276,6 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             Need none;
             vector_pub(attn_pub, m->attn_out, q_dim, nullptr, none, nullptr, nullptr, 4 * l + 0);
             attn_pub.tickets = m->tk_attn;
-            if (!nccl) aa.pub = attn_pub;
         }
         if (peer) {
             aa.npeers = m->npeers;
@@ -284,7 +291,6 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             op.resid = m->hidden; op.y = m->hidden; op.y_off[0] = r * m->lH; op.y_stride = H;
             Need nd; need_of(nd, L.gate, true);
             vector_pub(p, m->hidden, H, L.ffn_norm, nd, m->hid_q8, m->hid_xn, 4 * l + 1);
-            if (peer) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "o_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -300,7 +306,6 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             if (n > 1) {
                 Need none;
                 vector_pub(p, m->ffn_h, F, nullptr, none, nullptr, nullptr, 4 * l + 2);
-                if (!nccl) op.pub = &p;
             }
             push_rows(op, m->ffn_h);
             if ((rc = gemv(m, op, "gate/up"))) return rc;
@@ -324,7 +329,6 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
                 norm_w = m->out_norm;
             }
             vector_pub(p, m->hidden, H, norm_w, nd, m->hid_q8, m->hid_xn, 4 * l + 3);
-            if (peer) op.pub = &p;
             push_rows(op, m->hidden);
             if ((rc = gemv(m, op, "down_proj"))) return rc;
             if ((rc = gather_then_publish(m->hidden, m->lH, p))) return rc;
@@ -341,10 +345,10 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
             vector_pub(p, m->logits, V, nullptr, none, nullptr, nullptr, 4 * L_n);
             p.key_src = m->argmax_key;
             for (uint32_t q = 0; q < m->npeers; q++) p.peer_key[q] = reinterpret_cast<unsigned long long*>(on_peer(q, m->argmax_keys)) + r;
-            op.pub = &p;
             push_rows(op, m->logits);
         }
         if ((rc = gemv(m, op, "output head"))) return rc;
+        if (peer) MCU(launch_publish_vector(p, m->e->status, st, pdl));   // logits rows and the argmax key have been pushed: hand over
         if (nccl) {
             if ((rc = tp_all_gather(m->e, m->logits, (size_t)m->lV * sizeof(float)))) return rc;
             if ((rc = tp_all_gather(m->e, m->argmax_keys, sizeof(unsigned long long)))) return rc;
