@@ -494,7 +494,7 @@ Q8KView view_at(void* base, uint32_t nb, uint32_t batch) {
 
 // One matvec / fused SwiGLU over `batch` prepared input vectors.
 static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const Q8KView* q8, const float* xf,
-                    float* y, uint32_t batch, const Publish* pub, const char* who, bool may_alloc = true) {
+                    float* y, uint32_t batch, const char* who, bool may_alloc = true) {
     GemvOp op;
     const WeightFormat f = w0->d.fmt;
     if (f == WF_Q1_0 || f == WF_Q2_0 || f == WF_TERNARY || f == WF_SPARSE_TERNARY) {
@@ -503,7 +503,7 @@ static int run_gemv(alice_engine* e, const alice_weights* w0, const alice_weight
         op.prep = e->prep; op.prep_bytes = e->prep_bytes;
     }
     op.w[0] = &w0->d; op.up = w1 ? &w1->d : nullptr;
-    op.q8 = q8; op.x = xf; op.y = y; op.batch = batch; op.pub = pub;
+    op.q8 = q8; op.x = xf; op.y = y; op.batch = batch;
     op.wait_limit = e->wait_limit;
     return launch_rc(launch_stream_gemv_op(op, cfg_of(e)), who);
 }
@@ -527,7 +527,7 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
     if (x->len < (size_t)batch * d.cols) return fail(ALICE_E_SHAPE, "%s: input has %zu floats, need %zu", who, x->len, (size_t)batch * d.cols);
     if (y->len < (size_t)batch * d.rows) return fail(ALICE_E_SHAPE, "%s: output has %zu floats, need %zu", who, y->len, (size_t)batch * d.rows);
     CU(cudaSetDevice(e->device));
-    if (!format_uses_q8k(d.fmt)) return run_gemv(e, w0, w1, nullptr, x->p, y->p, batch, nullptr, who);
+    if (!format_uses_q8k(d.fmt)) return run_gemv(e, w0, w1, nullptr, x->p, y->p, batch, who);
     if ((uintptr_t)x->p & 15) return fail(ALICE_E_INVALID, "%s: input vector must be 16-byte aligned", who);
     const uint32_t nb = d.cols / 256;
     int rc = ensure_scratch(e, Q8KLayout::make(nb, batch).total);
@@ -535,7 +535,7 @@ static int matvec_common(alice_engine* e, const alice_weights* w0, const alice_w
     launch_quantize_q8k(x->p, d.cols, batch, e->scratch, e->stream, e->pdl);
     CU(cudaGetLastError());
     const Q8KView v = view_at(e->scratch, nb, batch);
-    return run_gemv(e, w0, w1, &v, nullptr, y->p, batch, nullptr, who);
+    return run_gemv(e, w0, w1, &v, nullptr, y->p, batch, who);
 }
 
 static int preq_common(alice_engine* e, const alice_weights* w0, const alice_weights* w1, const alice_q8k* q,
@@ -549,14 +549,14 @@ static int preq_common(alice_engine* e, const alice_weights* w0, const alice_wei
     CU(cudaSetDevice(e->device));
     if (format_uses_q8k(d.fmt)) {
         const Q8KView v = view_of(q, 0);
-        return run_gemv(e, w0, w1, &v, nullptr, y->p, q->batch, nullptr, who);
+        return run_gemv(e, w0, w1, &v, nullptr, y->p, q->batch, who);
     }
     if (d.fmt == WF_Q1_0 || d.fmt == WF_Q2_0) {
         const size_t total = (size_t)q->batch * d.cols;
         int rc = ensure_scratch(e, total * sizeof(float));
         if (rc) return rc;
         launch_q8k_to_f32(view_of(q, 0), total, static_cast<float*>(e->scratch), e->stream);
-        return run_gemv(e, w0, w1, nullptr, static_cast<float*>(e->scratch), y->p, q->batch, nullptr, who);
+        return run_gemv(e, w0, w1, nullptr, static_cast<float*>(e->scratch), y->p, q->batch, who);
     }
     // quantized_matvec_preq panics for every other type (src/gguf.rs:4606)
     return fail(ALICE_E_UNSUPPORTED, "%s: pre-quantized input only for Q4_K/Q5_K/Q6_K/Q1_0/Q2_0", who);
@@ -734,7 +734,7 @@ int32_t alice_matvec_preq_noalloc(alice_engine* e, const alice_weights* w, const
     const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 8);
     q8k_to_f32_noalloc_kernel<<<blocks, 256, 0, e->stream>>>(view_of(q, 0), (uint32_t)total);
     CU(cudaGetLastError());
-    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, nullptr, who, false);   // never allocates
+    return run_gemv(e, w, nullptr, nullptr, scratch, y->p, q->batch, who, false);   // never allocates
 }
 
 }  // extern "C"

@@ -263,24 +263,6 @@ __device__ __forceinline__ void attn_fused_body(const AttnArgs& a, uint32_t pos0
             q8k_quantize_block_warp(in, lane, a.q8.qs + blk * QK_K, a.q8.d + blk, a.q8.bsums + blk * 16);
         }
     }
-    if (a.pub.mode == PUB_VECTOR) {
-        // the last (token, KV head) of the whole launch hands the complete output vector over (tensor-parallel gate,
-        // or a whole-vector Q8_K when the heads of a KV head do not make whole blocks)
-        if (a.npeers) __threadfence_system(); else __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned int t = atomicAdd(a.pub.tickets, 1u);
-            unsigned int last = t == gridDim.x * gridDim.z - 1 ? 1u : 0u;
-            if (last) {
-                *a.pub.tickets = 0;
-                __threadfence();
-                if (!publish_peer_gate(a.pub, a.status)) last = 0;
-            }
-            sh->last = last;
-        }
-        __syncthreads();
-        if (sh->last && (a.pub.dst.qs != nullptr || a.pub.dst.xn != nullptr)) publish_vector<8, 0>(a.pub, sh->red, true);
-    }
 }
 
 }  // namespace alice

@@ -319,7 +319,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_kq_kernel(co
     }
     pdl_wait();
     stream_consume_kq<T, SWIGLU>(a, cx, reinterpret_cast<KqPartials*>(smem_raw + HDR), smem_raw + a.tab_off);
-    if (a.pub.mode != PUB_NONE) stream_publish<false>(a, sm);
 }
 
 }  // namespace alice

@@ -92,9 +92,9 @@ int launch_one_v(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCf
 // The instance with the tensor-parallel row push only when the matvec takes part in one.
 template <class F, int KL, bool SW>
 int launch_one(const StreamArgs& a, uint32_t grid, size_t smem, const LaunchCfg& cfg) {
-    const bool peer = a.npeers || a.pub.npeers;
+    const bool peer = a.npeers != 0;
     if (peer) return launch_one_v<F, KL, SW, true, false>(a, grid, smem, cfg);
-    const bool plain = !a.resid && !a.argmax_key && a.nseg == 1 && a.pub.mode == PUB_NONE;
+    const bool plain = !a.resid && !a.argmax_key && a.nseg == 1;
     return plain ? launch_one_v<F, KL, SW, false, true>(a, grid, smem, cfg) : launch_one_v<F, KL, SW, false, false>(a, grid, smem, cfg);
 }
 
@@ -237,7 +237,7 @@ int launch_mma_p(const StreamPlan& pl, const LaunchCfg& cfg) {
 template <class M>
 int launch_mma(const StreamPlan& pl, const LaunchCfg& cfg) {
     const StreamArgs& a = pl.args;
-    const bool peer = a.npeers || a.pub.npeers;
+    const bool peer = a.npeers != 0;
     return peer ? launch_mma_p<M, true>(pl, cfg) : launch_mma_p<M, false>(pl, cfg);
 }
 
@@ -269,7 +269,6 @@ int plan_kq(const GemvOp& op, const LaunchCfg& cfg, uint32_t col_lo, uint32_t co
     a.npieces = 1; a.piece_len = piece_len; a.piece_off[0] = off - pad; a.row_pad = pad;
     a.batch = op.batch; a.x_stride = w0.cols;
     a.resid = op.resid; a.wait_limit = op.wait_limit;
-    if (op.pub) a.pub = *op.pub;
     uint32_t total_rows = 0;
     for (uint32_t i = 0; i < op.nw; i++) total_rows += op.w[i]->rows;
     a.rows = total_rows; a.y_stride = op.y_stride ? op.y_stride : total_rows;
@@ -349,7 +348,6 @@ int launch_kq_batch(const GemvOp& op, const LaunchCfg& cfg, bool dry, uint32_t* 
             const int rc = plan_kq(op, cfg, c * nbc * 256u, nbc * 256u, pc);
             if (rc) return rc;
             if (c > 0) pc.args.resid = op.y;
-            if (c + 1 < ks) pc.args.pub = Publish{};
             const int lrc = w0.fmt == WF_Q4_K ? launch_kq_fmt<KqK4<false>>(pc, cfg) : w0.fmt == WF_Q5_K ? launch_kq_fmt<KqK4<true>>(pc, cfg)
                                                                                                         : launch_kq_fmt<KqQ6K>(pc, cfg);
             if (lrc) return lrc;
@@ -401,7 +399,6 @@ int plan_stream_gemv(const GemvOp& op, const LaunchCfg& cfg, StreamPlan& pl) {
     a.npeers = std::min<uint32_t>(op.npeers, MAX_PEERS);
     for (uint32_t p = 0; p < a.npeers; p++) a.peer_y[p] = op.peer_y[p];
     a.wait_limit = op.wait_limit;
-    if (op.pub) a.pub = *op.pub;
     a.row_stride = a.row_bytes;   // contiguous staging unless the tensor-core planner says otherwise
     if ((w0.fmt == WF_Q1_0 || w0.fmt == WF_Q2_0 || w0.fmt == WF_TERNARY || w0.fmt == WF_SPARSE_TERNARY) && w0.cols % 4 == 0 &&
         ((uintptr_t)x & 15) == 0 && !op.norm_w && plan_mma_split(op, cfg, a, pl) == ALICE_OK)
@@ -530,7 +527,7 @@ int launch_single(const GemvOp& op, const LaunchCfg& cfg) {
                 const int rc = plan_mma(op, cfg, base, lo, n, pc);
                 if (rc) return rc;
                 if (c > 0) pc.args.resid = op.y;
-                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; pc.args.pub = Publish{}; }
+                if (c + 1 < pl.ksplit) { pc.args.argmax_key = nullptr; pc.args.npeers = 0; }
             }
             // the activation digit table of this (chunk of the) vector, prepared once ahead of the matvec
             const uint32_t ge = (w0.fmt == WF_Q2_0 || w0.fmt == WF_SPARSE_TERNARY) ? 64u : 128u;
@@ -574,8 +571,7 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         const int brc = launch_kq_batch(op, cfg, false, nullptr);
         if (brc != ALICE_E_SHAPE) return brc;
     }
-    // Formats without a batch kernel: one launch per input vector (the weights stream once per vector). A hand-over
-    // to the next op rides on the last launch (every earlier one has completed by then: same stream).
+    // Formats without a batch kernel: one launch per input vector (the weights stream once per vector).
     if (!op.w[0]) return ALICE_E_INVALID;
     uint32_t total_rows = 0;
     for (uint32_t i = 0; i < op.nw && i < 3; i++) if (op.w[i]) total_rows += op.w[i]->rows;
@@ -590,7 +586,6 @@ int launch_stream_gemv_op(const GemvOp& op, const LaunchCfg& cfg) {
         o.y = op.y + (size_t)k * ys;
         if (op.resid) o.resid = op.resid + (size_t)k * ys;
         for (uint32_t p = 0; p < op.npeers && p < MAX_PEERS; p++) o.peer_y[p] = op.peer_y[p] + (size_t)k * ys;
-        if (op.pub) o.pub = k + 1 == op.batch ? op.pub : nullptr;
         const int rc = launch_single(o, cfg);
         if (rc) return rc;
     }

@@ -56,7 +56,6 @@ struct GemvOp {
     const float* resid = nullptr;                          // y = resid + result (same layout as y)
     unsigned long long* argmax_key = nullptr;              // atomicMax of packed (value, ~index), see StreamArgs (batch 1 only)
     float* y = nullptr;
-    const Publish* pub = nullptr;                          // what to leave prepared for the next op
     uint32_t npeers = 0;                                   // tensor parallel: also store every row result on these GPUs
     float* peer_y[MAX_PEERS] = {};
     long long wait_limit = 0;                              // SM cycles a wait inside the kernel may take (0 = about a second)

@@ -589,7 +589,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, CTAS) stream_gemv_mma_kernel(c
     }
     pdl_wait();
     stream_consume_mma<M, SWIGLU, PEER>(a, cx);
-    if (a.pub.mode != PUB_NONE) stream_publish<PEER>(a, sm);
 }
 
 }  // namespace alice

@@ -10,8 +10,8 @@
 // inside the loop. A ninth warp is the copy producer.
 //
 // The input arrives already in the form the loop reads (Q8_K blocks for the K-quant formats, f32 otherwise): it was
-// prepared once by the kernel that produced it (csrc/publish.cuh) or by a small stand-alone kernel, never per CTA.
-// In turn this kernel can leave its own output prepared for the next op (StreamArgs::pub).
+// prepared once by a small stand-alone kernel launched between producer and consumer (csrc/q8k.cu, csrc/publish.cuh);
+// where no such kernel covers the case the CTAs prepare the raw vector themselves (pro_mode).
 //
 // Row result = fixed-order sum of the P warp partials (deterministic run to run).
 #pragma once
@@ -84,12 +84,10 @@ struct StreamArgs {
     uint32_t row_pad;    // bytes in front of the first wanted byte of a staged row (piece start rounded down to 16)
     uint32_t x_stride;   // elements between consecutive input vectors (the matrix's full column count)
     // Tensor parallel: every row result is also stored at the same index of the vector of each of npeers other GPUs
-    // (peer-mapped memory); the hand-over that tells the peers lives in `pub` (Publish::peer_flag).
+    // (peer-mapped memory); the hand-over that tells the peers is a kernel of its own behind this one (csrc/publish.cuh).
     uint32_t npeers;
     float* peer_y[MAX_PEERS];
     long long wait_limit;      // SM cycles a wait inside the kernel may take; 0 = WAIT_CYCLE_LIMIT
-    // What this kernel leaves prepared for the op that consumes its output.
-    Publish pub;
 };
 
 // Shared-memory header in front of the ring.
@@ -101,8 +99,6 @@ struct StreamSmem {
     float partial[MAX_STAGES][NCW][MAX_RPS][2];  // [stage][warp][row in set][gate|up]
     double norm_part[NCW];
     int abort_flag;
-    int pub_last;
-    uint32_t pub_mask;
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
@@ -173,8 +169,6 @@ __device__ __forceinline__ void stream_init_ring(StreamSmem* sm, uint32_t nstage
     else if (t == (2 + NCW) * nstages) {
         mbar_init(smem_u32(&sm->act_bar), 1);
         sm->abort_flag = 0;
-        sm->pub_last = 0;
-        sm->pub_mask = 0;
     }
     if (t <= (2 + NCW) * nstages) mbar_fence_init();
 }
@@ -321,32 +315,6 @@ __device__ __forceinline__ void stream_argmax(unsigned long long* argmax_key, un
         key = other > key ? other : key;
     }
     if (lane == 0) atomicMax(argmax_key, key);
-}
-
-// What the kernel leaves for the next op (csrc/publish.cuh), run by the NCW consumer warps after their last row.
-// Every consumer warp comes here, also after an abort (the barrier below must see all of them).
-template <bool PEER>
-static __device__ __noinline__ void stream_publish(const StreamArgs& a, StreamSmem* sm) {
-    const Publish& p = a.pub;
-    const uint32_t tid = threadIdx.x;
-    if (PEER && a.npeers) __threadfence_system(); else __threadfence();   // this thread's row stores come before the ticket
-    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-    if (sm->abort_flag) return;
-    {
-        if (tid == 0) {
-            const unsigned int t = atomicAdd(p.tickets, 1u);
-            int last = t == gridDim.x - 1 ? 1 : 0;
-            if (last) {
-                *p.tickets = 0;          // ready for the next launch
-                __threadfence();
-                if (PEER && !publish_peer_gate(p, a.status)) last = 0;
-            }
-            sm->pub_last = last;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        if (!sm->pub_last) return;
-        if (p.dst.qs != nullptr || p.dst.xn != nullptr) publish_vector<NCW, 1>(p, sm->norm_part, true);
-    }
 }
 
 // Per-CTA input preparation (pro_mode), run by the NCW consumer warps on the raw f32 vector in global memory.
@@ -605,7 +573,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, KL <= 2 ? 2 : 1) stream_gemv_k
     }
     pdl_wait();  // activations come from the previous kernel
     stream_consume<F, KL, SWIGLU, PEER, PLAIN>(a, cx);
-    if (!PLAIN && a.pub.mode == PUB_VECTOR) stream_publish<PEER>(a, sm);
 }
 
 }  // namespace alice

@@ -31,11 +31,10 @@ struct AttnArgs {
     float* attn_out;           // [batch][out_stride]; this GPU's heads start at attn_out (already offset by the caller)
     uint32_t out_stride;
     AttnQ8Out q8;
-    // tensor parallel: the output of this GPU's heads also goes to the same place of every peer's vector; the hand-over
-    // (and, where needed, the whole-vector Q8_K) is `pub`, run by the last CTA of the launch
+    // tensor parallel: the output of this GPU's heads also goes to the same place of every peer's vector (the hand-over
+    // is a kernel of its own behind this one)
     uint32_t npeers;
     float* peer_out[MAX_PEERS];
-    Publish pub;
     int* status;
 };
 

@@ -38,7 +38,7 @@ struct alice_model {
     float* hid_xn = nullptr;
     uint8_t* prep = nullptr;            // scratch of the bit-plane kernels: the activation digit table of the current input
     size_t prep_bytes = 0;
-    unsigned int *tk_vec = nullptr, *tk_attn = nullptr, *attn_tickets = nullptr;
+    unsigned int* attn_tickets = nullptr;
     unsigned long long* argmax_key = nullptr;
     uint32_t nsplit = 1;
     // tensor parallel (engine's group): every projection holds rows [r*R/n, (r+1)*R/n); l* are the local sizes
@@ -157,7 +157,7 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     auto vector_pub = [&](Publish& p, const float* src, uint32_t len, const float* norm_w, const Need& nd, uint8_t* q8_base, float* xn,
                           uint32_t flag_idx) {
         p = Publish{};
-        p.mode = PUB_VECTOR; p.n = len; p.batch = batch; p.src = src; p.tickets = m->tk_vec; p.norm_w = norm_w; p.eps = c.eps;
+        p.mode = PUB_VECTOR; p.n = len; p.batch = batch; p.src = src; p.norm_w = norm_w; p.eps = c.eps;
         fill_dst(p.dst, nd, q8_base, xn, len);
         p.wait_limit = m->e->wait_limit;
         if (peer) {
@@ -275,7 +275,6 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
         if (n > 1) {   // tensor parallel: the hand-over of the pushed rows
             Need none;
             vector_pub(attn_pub, m->attn_out, q_dim, nullptr, none, nullptr, nullptr, 4 * l + 0);
-            attn_pub.tickets = m->tk_attn;
         }
         if (peer) {
             aa.npeers = m->npeers;
@@ -452,8 +451,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
     if (!rc) rc = dev_alloc(m, &m->vcache, kv_elems);
     if (!rc) rc = dev_alloc(m, &m->attn_part, (size_t)B * m->nsplit * (c.num_heads / n) * (c.head_dim + 4));
     if (!rc) rc = dev_alloc(m, &m->attn_tickets, (size_t)B * (c.num_kv_heads / n));
-    if (!rc) rc = dev_alloc(m, &m->tk_vec, 1);
-    if (!rc) rc = dev_alloc(m, &m->tk_attn, 1);
     if (!rc) rc = dev_alloc(m, &m->rope_tab, (size_t)B * 128);
     if (!rc) rc = dev_alloc(m, &m->rope_freq, 64);
     if (!rc) rc = dev_alloc(m, &m->hid_q8, Q8KLayout::make((c.hidden_dim + 255) / 256, B).total);
@@ -476,8 +473,6 @@ int32_t alice_model_create(alice_engine* e, const alice_model_config* cfg, const
         if (err == cudaSuccess) err = cudaMemsetAsync(m->vcache, 0, kv_elems * 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_pos, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->attn_tickets, 0, (size_t)B * (c.num_kv_heads / n) * 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_vec, 0, 4, e->stream);
-        if (err == cudaSuccess) err = cudaMemsetAsync(m->tk_attn, 0, 4, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_token, 0, 4 * B, e->stream);
         if (err == cudaSuccess) err = cudaMemsetAsync(m->d_trace, 0, (size_t)c.max_seq_len * 4, e->stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);

@@ -2,9 +2,10 @@
 //
 // Every CTA of a matvec needs its whole input in the form its inner loop reads: Q8_K blocks for the K-quant
 // formats, the RMS-normalised f32 vector for the others. That form is the same in every CTA, so it is computed
-// once - by the last CTA of the PRODUCING kernel to finish (a ticket counter), or by a small stand-alone kernel
-// launched between producer and consumer (csrc/q8k.cu, publish_vector_kernel) - and left in global memory; the
-// consumer's CTAs fetch it straight into registers. Arithmetic: rms_norm (src/llama3.rs:5244-5256:
+// once - by a small stand-alone kernel launched between producer and consumer (publish_vector_kernel, one CTA; the
+// embedding kernel, itself one CTA, does it for its own output) - and left in global memory; the consumer's CTAs fetch
+// it straight into registers. With a tensor-parallel group the same kernel first runs the hand-over of the rows the
+// peers have pushed (publish_peer_gate). Arithmetic: rms_norm (src/llama3.rs:5244-5256:
 // f64 sum of squares, f32 mean / sqrt / divide, (x * scale) * w) and quantize_row_q8_k (src/gguf.rs:1323-1374).
 #pragma once
 #include "common.cuh"
@@ -32,7 +33,6 @@ struct Publish {
     uint32_t n;              // elements per vector
     uint32_t batch;          // vectors, src[k * n + i]
     const float* src;        // the f32 vector(s) this matvec writes rows of
-    unsigned int* tickets;   // one counter, zero between launches
     const float* norm_w;     // PUB_VECTOR: rms_norm weights, or null
     float eps;
     PublishDst dst;

@@ -232,9 +232,9 @@ int32_t alice_model_read_logits(alice_model* m, float* logits);
 /* Tensor parallel without collective calls: after every rank has created its model, each exports a handle to its
  * exchange region (ALICE_TP_HANDLE_BYTES; CUDA IPC, same node), the host gathers the handles of all ranks in rank
  * order and every rank connects. From then on the kernel that produces a sharded vector stores its rows straight
- * into every peer's copy over NVLink; its last CTA raises one counter per vector on every peer (release) and waits,
- * bounded (ALICE_E_KERNEL on expiry), until all peers have raised the same counter here, then prepares the complete
- * vector for the next op. The consuming kernels read local memory only. The connect result must be the same on every
+ * into every peer's copy over NVLink; a one-CTA kernel behind it raises one counter per vector on every peer (release)
+ * and waits, bounded (ALICE_E_KERNEL on expiry), until all peers have raised the same counter here, then prepares the
+ * complete vector for the next op. The consuming kernels read local memory only. The connect result must be the same on every
  * rank (all-reduce the status on the host and rebuild the models if any rank failed: a rank left on NCCL would block
  * in its next all-gather), and the ranks must meet in a host barrier before alice_model_destroy (a peer may still be
  * storing into the region). No reference counterpart (the reference is single device). */
