@@ -151,9 +151,8 @@ int enqueue_step(alice_model* m, uint32_t batch, bool greedy_feed) {
     int rc;
 
     // A whole-vector hand-over: what `consumers` need of vector `src` (length len), after rms_norm with norm_w (or none).
-    // Peer mode: the producing kernel's own Publish (its last CTA gates on the peers' rows, then prepares the vector).
-    // Single GPU and NCCL mode: the producing kernel publishes nothing; a one-CTA kernel prepares the vector after it
-    // (after the all-gather).
+    // A one-CTA kernel behind the producing kernel runs it: on one GPU it prepares the vector; in NCCL mode it follows
+    // the all-gather; in peer mode it first hands the pushed rows over (flags), then prepares the vector.
     auto vector_pub = [&](Publish& p, const float* src, uint32_t len, const float* norm_w, const Need& nd, uint8_t* q8_base, float* xn,
                           uint32_t flag_idx) {
         p = Publish{};

@@ -14,7 +14,7 @@
 namespace alice {
 
 constexpr uint32_t PUB_NONE = 0;
-constexpr uint32_t PUB_VECTOR = 2;   // whole vector, by the last CTA of the grid: optional rms_norm, then Q8_K and / or f32
+constexpr uint32_t PUB_VECTOR = 2;   // whole vector: optional rms_norm, then Q8_K and / or f32
 
 constexpr uint32_t MAX_PEERS = 7;
 constexpr int MAX_BATCH = 8;      // input vectors one pass over the weights can serve
@@ -36,9 +36,9 @@ struct Publish {
     const float* norm_w;     // PUB_VECTOR: rms_norm weights, or null
     float eps;
     PublishDst dst;
-    // Tensor parallel (PUB_VECTOR): other GPUs store rows of src straight into this GPU's copy. The last CTA tells every
+    // Tensor parallel (PUB_VECTOR): other GPUs store rows of src straight into this GPU's copy. One thread tells every
     // peer that this GPU's rows have landed there (peer_flag[p] += 1, release) and waits, bounded, until all peers have
-    // said the same here (*wait_flag >= (*epoch + 1) * npeers) before it reads the vector.
+    // said the same here (*wait_flag >= (*epoch + 1) * npeers) before the vector is read.
     // key_src (optional): a 64-bit value of this GPU (the packed maximum of its logits rows) that goes to peer_key[p]
     // on every peer before the flag, so the same hand-over covers it.
     uint32_t npeers;

@@ -189,9 +189,10 @@ int32_t alice_engine_tp_info(const alice_engine* e, uint32_t* rank, uint32_t* wo
  * of Llama3Model::forward_with_layer_hook (src/llama3.rs:13632-13687, 14167-14613): per layer
  * rms_norm -> q/k/v matvec -> RoPE -> KV append -> GQA attention -> o matvec + residual ->
  * rms_norm -> fused SwiGLU gate/up -> down matvec + residual; then output norm and head.
- * One decode step is 5 kernels per layer replayed from a CUDA graph; position and token live on
- * the device. K-quant projections use the CPU model's semantics (Q8_K-quantized activations). Every kernel leaves
- * its output in the form the next one reads (normalised, Q8_K-quantized), prepared once by its last CTA.
+ * One decode step is five large kernels per layer (q/k/v, attention, o, gate/up, down) with a small kernel in front of
+ * each matvec that prepares its input once (rms_norm, Q8_K blocks or the f32 vector and its digit table), replayed from a
+ * CUDA graph; position and token live on the device. K-quant projections use the CPU model's semantics (Q8_K-quantized
+ * activations).
  * On an engine that is rank r of a tensor-parallel group of n, the config stays the whole model's and the
  * weight handles are row shards: rows [r*R/n, (r+1)*R/n) of q, k, v, o, gate, up, down and the output
  * head (R = that matrix's row count; contiguous byte ranges of the raw blocks); the embedding table is
