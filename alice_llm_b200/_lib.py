@@ -48,6 +48,8 @@ SIGNATURES = {
     "alice_q8k_upload": (C.c_int32, [_vp, _vp, _vp, _vp, C.c_uint32, C.c_uint32, _pp]),
     "alice_q8k_free": (C.c_int32, [_vp]),
     "alice_debug_expire_wait": (C.c_int32, [_vp]),
+    "alice_buf_write_f32_async": (C.c_int32, [_vp, _vp, _vp, C.c_size_t]),
+    "alice_buf_read_f32_async": (C.c_int32, [_vp, _vp, _vp, C.c_size_t]),
     "alice_ternarize": (C.c_int32, [_vp, _vp, C.c_uint32, C.c_uint32, C.c_float, _pp]),
     "alice_sparsify": (C.c_int32, [_vp, _vp, _vp, C.c_uint32, _pp]),
     "alice_weights_download": (C.c_int32, [_vp, _vp, _vp, C.c_size_t, _vp]),

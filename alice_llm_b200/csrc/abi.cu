@@ -150,8 +150,10 @@ int32_t alice_engine_create(int32_t device, alice_engine** out) {
     e->own_stream = true;
     err = cudaMalloc(&e->status, sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(e->status, 0, sizeof(int));
+    if (err == cudaSuccess) err = cudaMallocHost(reinterpret_cast<void**>(&e->status_host), sizeof(int));
     if (err != cudaSuccess) {
         if (e->status) cudaFree(e->status);
+        if (e->status_host) cudaFreeHost(e->status_host);
         cudaStreamDestroy(e->stream); delete e;
         return cuda_fail(err, "status word");
     }
@@ -167,8 +169,9 @@ int32_t alice_engine_destroy(alice_engine* e) {
     if (e->scratch) cudaFree(e->scratch);
     if (e->prep) cudaFree(e->prep);
     if (e->status) cudaFree(e->status);
+    if (e->status_host) cudaFreeHost(e->status_host);
     if (e->own_stream) cudaStreamDestroy(e->stream);
-    e->scratch = e->prep = nullptr; e->status = nullptr; e->stream = nullptr;
+    e->scratch = e->prep = nullptr; e->status = nullptr; e->status_host = nullptr; e->stream = nullptr;
     e->dead = true;               // handles created on this engine may outlive it: they only free their own memory
     alice_engine_release(e);
     return ALICE_OK;
@@ -202,9 +205,11 @@ int32_t alice_engine_set_wait_limit(alice_engine* e, uint64_t sm_cycles) {
 
 int32_t alice_sync(alice_engine* e) {
     if (!e) return fail(ALICE_E_INVALID, "alice_sync: null engine");
+    CU(cudaSetDevice(e->device));
+    // the status word rides the same wait: its copy to pinned host memory is queued behind the work
+    CU(cudaMemcpyAsync(e->status_host, e->status, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     CU(cudaStreamSynchronize(e->stream));
-    int st = 0;
-    CU(cudaMemcpy(&st, e->status, sizeof(int), cudaMemcpyDeviceToHost));
+    const int st = *e->status_host;
     if (st != 0) {
         cudaMemset(e->status, 0, sizeof(int));
         static const char* const what[] = {"?", "unspecified wait", "weights did not land in shared memory", "partial sums of a row", "stage release",
@@ -381,6 +386,20 @@ int32_t alice_buf_write_f32(alice_engine* e, alice_buf* b, const float* data, si
     if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_write_f32: %zu floats into a buffer of %zu", len, b->len);
     CU(cudaMemcpyAsync(b->p, data, len * sizeof(float), cudaMemcpyHostToDevice, e->stream));
     CU(cudaStreamSynchronize(e->stream));  // the host slice is only borrowed for the call
+    return ALICE_OK;
+}
+
+int32_t alice_buf_write_f32_async(alice_engine* e, alice_buf* b, const float* data, size_t len) {
+    if (!e || !b || (!data && len)) return fail(ALICE_E_INVALID, "alice_buf_write_f32_async: null argument");
+    if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_write_f32_async: %zu floats into a buffer of %zu", len, b->len);
+    CU(cudaMemcpyAsync(b->p, data, len * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    return ALICE_OK;
+}
+
+int32_t alice_buf_read_f32_async(alice_engine* e, const alice_buf* b, float* out, size_t len) {
+    if (!e || !b || (!out && len)) return fail(ALICE_E_INVALID, "alice_buf_read_f32_async: null argument");
+    if (len > b->len) return fail(ALICE_E_SHAPE, "alice_buf_read_f32_async: %zu floats from a buffer of %zu", len, b->len);
+    CU(cudaMemcpyAsync(out, b->p, len * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
     return ALICE_OK;
 }
 

@@ -15,6 +15,7 @@ struct alice_engine {
     bool pdl = true;
     int force_rps = 0, force_stages = 0;
     int* status = nullptr;        // device status word
+    int* status_host = nullptr;   // pinned host word alice_sync copies it into
     void* scratch = nullptr;      // engine-owned scratch: Q8_K of the current input, or its f32 form
     size_t scratch_bytes = 0;
     void* prep = nullptr;         // engine-owned scratch of the bit-plane kernels: the activation digit table of the current input

@@ -269,6 +269,15 @@ class GpuEngine:
         check(self._lib.alice_buf_read_f32(self._h, buf._h, _ptr(out), n))
         return out
 
+    def write_f32_async(self, buf: GpuBuffer, host_ptr: int, length: int):
+        """Queues the copy of `length` floats at the (pinned) host address into `buf`; the memory must stay valid until the
+        next sync(). GpuEngine::write_f32 (queue.write_buffer) does not block either."""
+        check(self._lib.alice_buf_write_f32_async(self._h, buf._h, C.c_void_p(host_ptr), length))
+
+    def read_f32_async(self, buf: GpuBuffer, host_ptr: int, length: int):
+        """Queues the copy of `buf` to the (pinned) host address; the values are there after the next sync()."""
+        check(self._lib.alice_buf_read_f32_async(self._h, buf._h, C.c_void_p(host_ptr), length))
+
     def buf_from_device(self, device_ptr: int, length: int) -> GpuBuffer:
         h = C.c_void_p()
         check(self._lib.alice_buf_from_device(self._h, C.c_void_p(device_ptr), length, C.byref(h)))

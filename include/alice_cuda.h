@@ -110,7 +110,13 @@ int32_t alice_weights_free(alice_weights* w);
 int32_t alice_buf_alloc_f32(alice_engine* e, size_t len, alice_buf** out);
 int32_t alice_buf_upload_f32(alice_engine* e, const float* data, size_t len, alice_buf** out);
 int32_t alice_buf_write_f32(alice_engine* e, alice_buf* b, const float* data, size_t len);
-int32_t alice_buf_read_f32(alice_engine* e, const alice_buf* b, float* out, size_t len); /* blocks */
+int32_t alice_buf_read_f32(alice_engine* e, const alice_buf* b, float* out, size_t len);
+/* The same two copies queued on the engine's stream without waiting (GpuEngine::write_f32 is queue.write_buffer in the
+ * reference, src/gpu.rs:801, which does not block either): `data` / `out` must stay valid - and should be pinned host
+ * memory - until the next alice_sync (or any blocking call) has returned; `out` holds the values only then. With them a
+ * host-buffer step costs one synchronisation instead of two. */
+int32_t alice_buf_write_f32_async(alice_engine* e, alice_buf* b, const float* data, size_t len);
+int32_t alice_buf_read_f32_async(alice_engine* e, const alice_buf* b, float* out, size_t len); /* blocks */
 /* Wrap `len` floats of caller-owned device memory (not copied, not owned). */
 int32_t alice_buf_from_device(alice_engine* e, void* device_ptr, size_t len, alice_buf** out);
 int32_t alice_buf_free(alice_buf* b);
