@@ -222,6 +222,7 @@ def build_model(engine, name, seed=0, extra_positions=160, force_world=None):
     q_dim, kv_dim = c["num_heads"] * c["head_dim"], c["num_kv_heads"] * c["head_dim"]
     shapes = {"q": (q_dim, H), "k": (kv_dim, H), "v": (kv_dim, H), "o": (H, q_dim), "gate": (F, H), "up": (F, H), "down": (H, F)}
     keep, total_bytes, counter = [], 0, [0]
+    probe = {}      # layer 0's q projection (this rank's rows), kept for the parity check of the decode entry
 
     def tensor(role, rows, cols, shard=True):
         nonlocal total_bytes
@@ -235,7 +236,10 @@ def build_model(engine, name, seed=0, extra_positions=160, force_world=None):
             planes, scales = planes[lo:lo + n].contiguous().reshape(-1), scales[lo:lo + n].contiguous()
             keep.extend([planes, scales])
             total_bytes += rows * ((cols + 7) // 8 * 2 + 4)
-            return engine.ternary_from_device(planes.data_ptr(), scales.data_ptr(), n, cols)
+            h = engine.ternary_from_device(planes.data_ptr(), scales.data_ptr(), n, cols)
+            if role == "q" and not probe:
+                probe.update(handle=h, qtype=qt, rows=n, cols=cols, planes=planes.reshape(n, -1), scales=scales)
+            return h
         rb = synth.row_bytes(qt, cols)
         t = dev_ggml_tensor(gen, dev, qt, rows, cols)
         if n != rows:
@@ -243,7 +247,10 @@ def build_model(engine, name, seed=0, extra_positions=160, force_world=None):
         keep.append(t)
         if role != "embedding":
             total_bytes += rb * rows
-        return engine.weights_from_device(t.data_ptr(), t.numel(), n, cols, GpuQuantType(qt))
+        h = engine.weights_from_device(t.data_ptr(), t.numel(), n, cols, GpuQuantType(qt))
+        if role == "q" and not probe:
+            probe.update(handle=h, qtype=qt, rows=n, cols=cols, blocks=t)
+        return h
 
     def norm():
         return (1.0 + 0.02 * np.random.default_rng(seed).standard_normal(H)).astype(np.float32)
@@ -264,8 +271,26 @@ def build_model(engine, name, seed=0, extra_positions=160, force_world=None):
         gm.kv_write(l, 0, k, v)
     gm.set_position(c["context"])
     info = dict(name=name, weight_bytes_per_token=total_bytes + (H // 32) * 34, context=c["context"],
-                kv_bytes_per_token=2 * c["context"] * kv_dim * 4 * c["num_layers"])
+                kv_bytes_per_token=2 * c["context"] * kv_dim * 4 * c["num_layers"], probe=probe)
     return gm, info
+
+
+def projection_check(eng, probe):
+    """Layer 0's q projection of a device-drawn model (the rows this rank holds): the tensor is copied back to the host and
+    the matvec of a seeded N(0,1) vector compared with the CPU oracle. Returns max |err| / max(|ref|, 1)."""
+    from oracle import oracle as orc
+    orc.build()
+    rows, cols, qt = probe["rows"], probe["cols"], probe["qtype"]
+    x = np.random.default_rng(99).standard_normal(cols).astype(np.float32)
+    got = eng.matvec(probe["handle"], x).astype(np.float64)
+    if "planes" in probe:
+        planes = probe["planes"].cpu().numpy()
+        pb, nb = planes.shape[1] // 2, (cols + 7) // 8
+        ref = orc.ternary_matvec(np.ascontiguousarray(planes[:, :nb]), np.ascontiguousarray(planes[:, pb:pb + nb]),
+                                 probe["scales"].cpu().numpy(), rows, cols, x)
+    else:
+        ref = orc.matvec(qt, x, probe["blocks"].cpu().numpy(), rows, cols)
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)).max())
 
 
 def timed_decode(gm, ctx, tokens, stream, world, dist, dev):
@@ -295,6 +320,12 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak, n1):
     gm, info = build_model(eng, name)
     ctx = info["context"]
     nccl_ms = None
+    check = None
+    if world == 1 or dist.get_rank() == 0:
+        try:
+            check = projection_check(eng, info["probe"])
+        except Exception as exc:
+            check = f"{type(exc).__name__}: {exc}"[:200]
     if world > 1:
         # first with NCCL all-gathers (the baseline), then with the kernels pushing their rows into the peers' memory
         nccl_ms, nccl_toks = timed_decode(gm, ctx, tokens, stream, world, dist, dev)
@@ -312,7 +343,8 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak, n1):
     bound_ms = wb / world / (peak * 1e9) * 1e3
     entry = {"config": name, "tokens": tokens, "context": ctx, "weight_bytes_per_token": wb,
              "kv_bytes_per_token_at_context": info["kv_bytes_per_token"], "stream_bound_ms_per_token": bound_ms,
-             "first_tokens": [int(t) for t in toks[:8]]}
+             "first_tokens": [int(t) for t in toks[:8]],
+             "layer0_q_projection_max_rel_err_vs_oracle": check}
     if world == 1:
         entry["parallelism"] = "single GPU"
     else:
