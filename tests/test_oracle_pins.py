@@ -279,3 +279,15 @@ def test_sparse_and_dense_ternary_agree_on_synthetic(oracle):
     yd = oracle.ternary_matvec(pos, neg, sc, rows, cols, x)
     ys = oracle.sparse_ternary_matvec(active, sign, sc, rows, cols, x)
     assert np.allclose(yd, ys, rtol=1e-4, atol=1e-5)
+
+
+def test_synthetic_sparse_packing_equals_oracle_packer(oracle):
+    """synth.pack_2bit (what GpuModel.load uploads for sparse-ternary tensors) against the oracle's restatement of
+    SparseTernaryMatrix's packer (src/gguf.rs:5432-5450), ragged column counts included."""
+    import numpy as np
+    from alice_llm_b200 import synth
+    rng = np.random.default_rng(8)
+    for rows, cols in [(5, 70), (3, 16), (9, 1000), (2, 8192)]:
+        pos, neg, _ = synth.make_ternary(rng, rows, cols)
+        active, sign = synth.ternary_to_sparse(pos, neg, cols)
+        assert np.array_equal(synth.pack_2bit(pos, neg, cols).reshape(-1), oracle.sparse_pack_2bit(active, sign, rows, cols))
