@@ -334,6 +334,26 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak, n1):
         gm.tp_connect(handles)
         gm.set_position(ctx)
     ms, toks = timed_decode(gm, ctx, tokens, stream, world, dist, dev)
+    verify = None
+    if world == 1:
+        # speculative verify: 8 consecutive tokens per step (GpuModel::forward_batch), logits of all of them kept on the device
+        try:
+            batch_tokens = [int(t) for t in toks[:8]]
+            gm.set_position(ctx)
+            gm.forward_batch(batch_tokens)          # warm-up
+            eng.sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            nsteps = 8
+            gm.set_position(ctx)
+            e0.record(stream)
+            for _ in range(nsteps):
+                gm.forward_batch(batch_tokens)
+            e1.record(stream)
+            eng.sync()
+            vms = e0.elapsed_time(e1) / nsteps
+            verify = {"tokens_per_step": 8, "ms_per_step": vms, "ms_per_token": vms / 8, "tok_s": 8 / (vms * 1e-3)}
+        except Exception as exc:
+            verify = {"error": f"{type(exc).__name__}: {exc}"[:200]}
     if world > 1:
         dist.barrier()              # no rank frees memory its peers may still be writing into
     gm.free()
@@ -344,7 +364,7 @@ def run_decode(eng, name, tokens, stream, world, dist, dev, peak, n1):
     entry = {"config": name, "tokens": tokens, "context": ctx, "weight_bytes_per_token": wb,
              "kv_bytes_per_token_at_context": info["kv_bytes_per_token"], "stream_bound_ms_per_token": bound_ms,
              "first_tokens": [int(t) for t in toks[:8]],
-             "layer0_q_projection_max_rel_err_vs_oracle": check}
+             "layer0_q_projection_max_rel_err_vs_oracle": check, "verify_batch8": verify}
     if world == 1:
         entry["parallelism"] = "single GPU"
     else:
