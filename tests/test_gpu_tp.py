@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("mix", ["kquant", "q1_0", "ternary"])
+@pytest.mark.parametrize("mix", ["kquant", "q1_0", "q8_0", "ternary"])
 @pytest.mark.parametrize("world", [2])
 def test_tp_decode_matches_oracle(world, mix):
     import torch

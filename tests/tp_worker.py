@@ -3,7 +3,7 @@
 Every rank builds the same seeded synthetic model, uploads its row shards, joins the group and decodes
 greedily; rank 0 compares logits and token ids with the CPU oracle's forward of the whole model, and all
 ranks must agree on the tokens. The group id travels through a gloo process group (host side only).
-usage: tp_worker.py RANK WORLD PORT [MIX]   (MIX: kquant (default) | q1_0 | ternary - the weight formats of the model)"""
+usage: tp_worker.py RANK WORLD PORT [MIX]   (MIX: kquant (default) | q1_0 | q8_0 | ternary - the weight formats of the model)"""
 import json
 import os
 import sys
@@ -30,6 +30,8 @@ def main():
     if mix_name == "q1_0":       # the binary-weight configuration: Q1_0 projections, Q8_0 head, 5 query heads per KV head
         cfg.update(num_heads=10, num_kv_heads=2)
         mix = {**{n: synth.Q1_0 for n in roles}, "output": synth.Q8_0}
+    elif mix_name == "q8_0":     # f32-activation per-lane kernels on every exchanged vector (o and down read pushed rows)
+        mix = {n: synth.Q8_0 for n in roles + ("output",)}
     elif mix_name == "ternary":  # every projection and the head as ternary bit planes
         mix = {n: synth.TERNARY for n in roles + ("output",)}
     else:
