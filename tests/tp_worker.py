@@ -30,8 +30,9 @@ def main():
     if mix_name == "q1_0":       # the binary-weight configuration: Q1_0 projections, Q8_0 head, 5 query heads per KV head
         cfg.update(num_heads=10, num_kv_heads=2)
         mix = {**{n: synth.Q1_0 for n in roles}, "output": synth.Q8_0}
-    elif mix_name == "q8_0":     # f32-activation per-lane kernels on every exchanged vector (o and down read pushed rows)
-        mix = {n: synth.Q8_0 for n in roles + ("output",)}
+    elif mix_name == "q8_0":     # f32-activation per-lane kernels on the exchanged vectors: o reads the gathered attention
+        mix = {"o": synth.Q8_0, "down": synth.Q8_0, "output": synth.Q8_0}   # output, down the gathered SwiGLU output (the
+        # other projections stay K-quant: the reference reaches them through matvec_preq, which has no Q8_0 form)
     elif mix_name == "ternary":  # every projection and the head as ternary bit planes
         mix = {n: synth.TERNARY for n in roles + ("output",)}
     else:
